@@ -1,0 +1,209 @@
+/*
+ * es_b200.h -- C ABI of the B200-native kernel layer for einsummable's
+ * memgraph apply nodes (einsummable_t / touch_t kernels, fills, move_t copies).
+ *
+ * Plain pointers and sizes only; no C++ or torch types.  Every function returns
+ * an es_status_t (0 = ok); es_b200_last_error() gives the text of the last
+ * failure on the calling thread.  Nothing here traps or asserts on the device.
+ *
+ * All launches are asynchronous on the given stream; the caller observes
+ * completion through the stream, exactly as the reference's exec nodes do
+ * (src/engine/gpu/exec_graph.cc:318-332).  All device memory is owned by the
+ * caller (src/engine/gpu/exec_graph.cc:295-312).
+ *
+ * Each declaration cites the reference interface it stands in for
+ * (paths relative to the reference project).
+ */
+#ifndef ES_B200_H
+#define ES_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ES_MAX_RANK 12
+#define ES_MAX_INNS 8
+
+typedef enum {
+    ES_OK = 0,
+    ES_NOT_SUPPORTED = 1,       /* kernel_manager_t::build returning nullopt */
+    ES_BAD_DESCRIPTOR = 2,      /* malformed einsummable / touch / fill */
+    ES_WORKSPACE_TOO_SMALL = 3, /* src/engine/gpu/gpu_kernel_manager.cc:1585-1587 */
+    ES_CUDA_ERROR = 4,          /* src/engine/gpu/utility.cc:114-143 */
+    ES_NOT_BUILT = 5,           /* src/engine/gpu/gpu_kernel_manager.cc:1257-1261 */
+    ES_BAD_ARGUMENT = 6,
+    ES_COMPILE_ERROR = 7
+} es_status_t;
+
+/* dtype_t order of src/einsummable/scalarop.h:10 */
+typedef enum { ES_F16 = 0, ES_F32 = 1, ES_F64 = 2, ES_C64 = 3 } es_dtype_t;
+
+/* castable_t order of src/einsummable/scalarop.h:4; -1 = no castable */
+typedef enum {
+    ES_CASTABLE_NONE = -1,
+    ES_CASTABLE_ADD = 0,
+    ES_CASTABLE_MUL = 1,
+    ES_CASTABLE_MIN = 2,
+    ES_CASTABLE_MAX = 3
+} es_castable_t;
+
+/* Policy for f32 contractions on the tensor cores. */
+typedef enum {
+    ES_F32_3XTF32 = 0, /* default: hi/lo split, 3 MMAs, ~fp32 accuracy */
+    ES_F32_TF32 = 1    /* single TF32 MMA, ~1e-3 relative accuracy */
+} es_f32_policy_t;
+
+/*
+ * einsummable_t (src/einsummable/einsummable.h:8-31) as a POD.
+ * All tensors are dense row-major; input k has shape join_shape[inn_modes[k][*]];
+ * the output is join modes 0..out_rank-1.  `join` is the scalarop in the
+ * reference's text form (operator<<, src/einsummable/scalarop.cc:2878-3011),
+ * e.g. "*[hole|f32@0,hole|f32@1]".
+ */
+typedef struct {
+    int32_t     join_rank;
+    uint64_t    join_shape[ES_MAX_RANK];
+    int32_t     n_inn;
+    int32_t     inn_rank[ES_MAX_INNS];
+    int32_t     inn_modes[ES_MAX_INNS][ES_MAX_RANK];
+    int32_t     out_rank;
+    int32_t     castable; /* es_castable_t */
+    const char* join;
+} es_einsummable_desc_t;
+
+/* touchdim_t (src/einsummable/touch.h:8-14) */
+typedef struct {
+    uint64_t d_inn, d_out, offset_inn, offset_out, size;
+} es_touchdim_t;
+
+/* One touch of a batched launch (see es_b200_launch_touch_batch). */
+typedef struct {
+    es_touchdim_t dims[4];
+    int32_t       rank;
+    int32_t       castable; /* es_castable_t */
+    void*         out;
+    const void*   inn;
+} es_touch_item_t;
+
+typedef struct es_b200 es_b200_t;
+
+/* kernel_manager_t::kernel_manager_t(int device) / ~kernel_manager_t
+ * (src/engine/gpu/gpu_kernel_manager.h:274-277, gpu_kernel_manager.cc:29-57). */
+int es_b200_create(int device, es_b200_t** out);
+int es_b200_destroy(es_b200_t* h);
+
+/* Options on the handle; the reference has only compile-time switches here. */
+int es_b200_set_f32_policy(es_b200_t* h, int policy /* es_f32_policy_t */);
+
+/* kernel_manager_t::build(einsummable_t const&) -> optional<workspace_info_t>
+ * (src/engine/gpu/gpu_kernel_manager.h:300, gpu_kernel_manager.cc:590-958).
+ * Idempotent, keyed on the merged (merge_adjacent_dims) einsummable.
+ * ES_NOT_SUPPORTED plays the role of nullopt. */
+int es_b200_build_einsummable(es_b200_t*                   h,
+                              const es_einsummable_desc_t* desc,
+                              uint64_t*                    workspace_bytes,
+                              uint64_t*                    kernel_id);
+
+/* kernel_manager_t::workspace_size (src/engine/gpu/gpu_kernel_manager.h:302). */
+int es_b200_workspace_size(es_b200_t* h, uint64_t kernel_id, uint64_t* workspace_bytes);
+
+/* kernel_manager_t::operator()(einsummable_t const&, cudaStream_t, void* out,
+ * vector<void const*> inns, optional<tuple<void*,uint64_t>> workspace)
+ * (src/engine/gpu/gpu_kernel_manager.h:304-309, gpu_kernel_manager.cc:1000-1252).
+ * stream is a cudaStream_t. */
+int es_b200_launch_einsummable(es_b200_t*         h,
+                               uint64_t           kernel_id,
+                               void*              stream,
+                               void*              out,
+                               const void* const* inns,
+                               int                n_inn,
+                               void*              workspace,
+                               uint64_t           workspace_bytes);
+
+/* kernel_manager_t::operator()(touch_t const&, cudaStream_t, void* out, void const* inn)
+ * (src/engine/gpu/gpu_kernel_manager.h:311, gpu_kernel_manager.cc:980-998;
+ *  kernels: src/engine/gpu/cuda_kernels.cu:99-515).  Any rank >= 1 is accepted
+ * (the touch is simplified first, src/einsummable/touch.cc:3-28; at most 4
+ * dims may remain). */
+int es_b200_launch_touch(es_b200_t*           h,
+                         const es_touchdim_t* dims,
+                         int                  rank,
+                         int                  castable,
+                         int                  dtype,
+                         void*                stream,
+                         void*                out,
+                         const void*          inn);
+
+/* Many touches of one dtype in a single launch.  Stands in for a run of
+ * gpu_touch_t::launch calls (src/engine/gpu/exec_graph.cc:354-404) whose
+ * destinations do not overlap; items are staged through a caller-provided
+ * device buffer `items_dev` of n * sizeof(es_touch_item_t) bytes. */
+int es_b200_launch_touch_batch(es_b200_t*             h,
+                               const es_touch_item_t* items,
+                               int                    n,
+                               int                    dtype,
+                               void*                  stream,
+                               void*                  items_dev);
+
+/* kernel_manager_t::constant_fill (src/engine/gpu/gpu_kernel_manager.h:319,
+ * gpu_kernel_manager.cc:1064-1089).  value8 = the scalar's 8 raw bytes. */
+int es_b200_fill_constant(es_b200_t*  h,
+                          int         dtype,
+                          const void* value8,
+                          uint64_t    nelem,
+                          void*       stream,
+                          void*       out);
+
+/* kernel_manager_t::lowerTri_fill (src/engine/gpu/gpu_kernel_manager.h:315,
+ * gpu_kernel_manager.cc:1037-1062): out[i,j] = (i - start >= j) ? lower : upper,
+ * start signed (src/einsummable/fill.h:17-26). */
+int es_b200_fill_lowertri(es_b200_t*  h,
+                          int         dtype,
+                          const void* lower8,
+                          const void* upper8,
+                          uint64_t    nrow,
+                          uint64_t    ncol,
+                          int64_t     start,
+                          void*       stream,
+                          void*       out);
+
+/* gpu_copy_t::launch (src/engine/gpu/exec_graph.cc:406-467): copy `bytes` from
+ * src on src_device to dst on dst_device.  The handle must belong to
+ * dst_device; the stream is a stream of dst_device. */
+int es_b200_move(es_b200_t*  h,
+                 int         src_device,
+                 const void* src,
+                 int         dst_device,
+                 void*       dst,
+                 uint64_t    bytes,
+                 void*       stream);
+
+/* Introspection: "kind|merged str|vector width|..." of a built kernel. */
+int es_b200_kernel_info(es_b200_t* h, uint64_t kernel_id, char* buf, int buf_len);
+
+/* Host-only helpers (no GPU needed): what build() would generate.  `what`:
+ * 0 = merged form "str|join_shape|out_rank|inns", 1 = kernel kind,
+ * 2 = generated CUDA source (empty for precompiled kinds),
+ * 3 = compile the generated source for sm_100a and return the log. */
+int es_b200_describe(const es_einsummable_desc_t* desc, int what, char* buf, int buf_len);
+
+/* Simplify a touch (src/einsummable/touch.cc:3-28); returns the new rank in
+ * *out_rank, dims_out must hold `rank` entries. */
+int es_b200_touch_simplify(const es_touchdim_t* dims,
+                           int                  rank,
+                           es_touchdim_t*       dims_out,
+                           int*                 out_rank);
+
+/* Launch / byte counters since creation: launches[class], class order =
+ * einsummable, touch, fill, move. */
+int es_b200_query_counters(es_b200_t* h, uint64_t launches[4]);
+
+const char* es_b200_last_error(void);
+const char* es_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

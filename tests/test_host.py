@@ -1,0 +1,152 @@
+"""Host-side logic of the library, without a GPU: the C ABI loads and exports
+every declared symbol, descriptors are validated, merge_adjacent_dims / touch
+simplify match the reference fixtures, and every generated kernel compiles for
+sm_100a."""
+import ctypes
+import os
+import re
+
+import pytest
+
+import einsummable_b200 as es
+from einsummable_b200 import _lib, einsummable_t, scalarop_t, touch_t
+from conftest import ROOT, golden
+
+G = golden()
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "es_b200.h")).read()
+    declared = set(re.findall(r"\b(es_b200_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found"
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    for name in sorted(declared):
+        assert hasattr(lib, name), "missing symbol " + name
+    assert declared == set(_lib.SYMBOLS), declared ^ set(_lib.SYMBOLS)
+    assert b"sm_100a" in _lib.load().es_b200_version()
+
+
+def test_no_gpu_means_loud_failure_not_fallback():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("GPU present")
+    with pytest.raises(es.es_error) as ei:
+        es.kernel_manager_t(0)
+    assert ei.value.status == _lib.ES_CUDA_ERROR
+
+
+@pytest.mark.parametrize("case", G.meta["merge"] + G.meta["einsummable"],
+                         ids=lambda c: c.get("name", str(c["join_shape"])))
+def test_native_merge_matches_reference(case):
+    e = einsummable_t(case["join_shape"], case["inns"], case["out_rank"], case["join"], case["castable"])
+    s, shape, orank, inns = case["merged"].split("|")[:4]
+    m = e.merge_adjacent_dims()
+    assert m.str() == s
+    assert ",".join(map(str, m.join_shape)) == shape
+    assert str(m.out_rank) == orank
+    assert ";".join(",".join(map(str, t)) for t in m.inns) == inns
+    assert e.str() == case["merged"].split("|")[4]
+
+
+@pytest.mark.parametrize("case", G.meta["touch"], ids=lambda c: c["name"])
+def test_native_touch_simplify_matches_reference(case):
+    t = touch_t(case["selection"], case["castable"], case["dtype"]).simplify()
+    assert [list(s.astuple()) for s in t.selection] == case["simplified"]
+
+
+@pytest.mark.parametrize("case", G.meta["einsummable"], ids=lambda c: c["name"])
+def test_generated_kernel_compiles(case):
+    e = einsummable_t(case["join_shape"], case["inns"], case["out_rank"], case["join"], case["castable"])
+    kind = e.kernel_kind()
+    assert kind
+    log = e.compile_check()  # raises es_error(ES_COMPILE_ERROR) with the NVRTC log on failure
+    assert "error" not in log.lower()
+    assert "spill stores" not in log or " 0 bytes spill stores" in log
+
+
+def test_python_builders_match_reference_strings():
+    S = scalarop_t
+    gold = G.meta["scalarops"]
+    for dt in ("f16", "f32", "f64"):
+        assert S.make_identity(dt).text == gold["identity/" + dt]
+        assert S.make_add(dt).text == gold["add/" + dt]
+        assert S.make_mul(dt).text == gold["mul/" + dt]
+        assert S.make_sub(dt).text == gold["sub/" + dt]
+        assert S.make_div(dt).text == gold["div/" + dt]
+        assert S.make_neg(dt).text == gold["neg/" + dt]
+        assert S.make_max(dt).text == gold["max/" + dt]
+        assert S.make_min(dt).text == gold["min/" + dt]
+        assert S.make_exp(dt).text == gold["exp/" + dt]
+        assert S.make_log(dt).text == gold["log/" + dt]
+        assert S.make_silu(dt).text == gold["silu/" + dt]
+        assert S.make_sigmoid(dt).text == gold["sigmoid/" + dt]
+        assert S.make_relu(dt).text == gold["relu/" + dt]
+        assert S.make_square(dt).text == gold["square/" + dt]
+        assert S.make_sqrt(dt).text == gold["sqrt/" + dt]
+        assert S.make_inverse_sqrt(dt).text == gold["inverse_sqrt/" + dt]
+        assert S.make_is_equal(dt).text == gold["is_equal/" + dt]
+        assert S.make_scale(0.25, dt).text == gold["scale:0.25/" + dt]
+        assert S.combine(S.make_mul(dt), [S.make_silu(dt), S.make_identity(dt)]).text == gold["silu_mul/" + dt]
+        assert S.combine(S.make_exp(dt), [S.make_sub(dt)]).text == gold["exp_sub/" + dt]
+    assert S.make_convert_dtype("f16", "f32").text == gold["convert:f32/f16"]
+    assert S.make_conjugate().text == gold["conjugate/c64"]
+    assert S.make_silu("f16").out_dtype() == "f16"
+    assert S.make_convert_dtype("f16", "f32").out_dtype() == "f32"
+
+
+def _describe_status(e):
+    buf = ctypes.create_string_buffer(1 << 16)
+    return _lib.load().es_b200_describe(ctypes.byref(e.to_desc()), 1, buf, 1 << 16)
+
+
+def test_bad_descriptors_are_rejected_with_codes():
+    lib = _lib.load()
+    mul = scalarop_t.make_mul("f32")
+    good = einsummable_t([4, 5, 6], [[0, 2], [2, 1]], 2, mul, "add")
+    assert _describe_status(good) == _lib.ES_OK
+
+    d = good.to_desc(); d.join_shape[1] = 0   # zero extent (src/einsummable/einsummable.cc:79-83)
+    buf = ctypes.create_string_buffer(256)
+    assert lib.es_b200_describe(ctypes.byref(d), 1, buf, 256) == _lib.ES_BAD_DESCRIPTOR
+    assert b"zero" in lib.es_b200_last_error()
+
+    d = good.to_desc(); d.castable = -1       # aggregation without castable (:39-41)
+    assert lib.es_b200_describe(ctypes.byref(d), 1, buf, 256) == _lib.ES_BAD_DESCRIPTOR
+
+    d = good.to_desc(); d.inn_modes[0][1] = 7  # mode out of range
+    assert lib.es_b200_describe(ctypes.byref(d), 1, buf, 256) == _lib.ES_BAD_DESCRIPTOR
+
+    d = good.to_desc(); d.n_inn = 1            # join has 2 holes, 1 input (:43-49)
+    assert lib.es_b200_describe(ctypes.byref(d), 1, buf, 256) == _lib.ES_BAD_DESCRIPTOR
+
+    d = good.to_desc(); d.join = b"*[hole|f32@0,hole|f16@1]"   # type failure
+    assert lib.es_b200_describe(ctypes.byref(d), 1, buf, 256) == _lib.ES_BAD_DESCRIPTOR
+
+    d = good.to_desc(); d.join = b"*[hole|f32@0,variable{lr|f32}]"  # unresolved variable
+    assert lib.es_b200_describe(ctypes.byref(d), 1, buf, 256) == _lib.ES_BAD_DESCRIPTOR
+
+    d = good.to_desc(); d.join = b"bogus[hole|f32@0]"
+    assert lib.es_b200_describe(ctypes.byref(d), 1, buf, 256) == _lib.ES_BAD_DESCRIPTOR
+
+    assert lib.es_b200_describe(None, 1, buf, 256) == _lib.ES_BAD_ARGUMENT
+    # null handle on a launch entry point: error code, no crash
+    assert lib.es_b200_launch_touch(None, None, 1, -1, 0, None, None, None) == _lib.ES_BAD_ARGUMENT
+    assert lib.es_b200_fill_constant(None, 0, None, 4, None, None) == _lib.ES_BAD_ARGUMENT
+
+
+def test_kernel_kinds_of_the_llama_layer():
+    S = scalarop_t
+    kinds = {
+        "ew_vec": einsummable_t([8388608], [[0], [0]], 1, S.make_add("f16")),
+        "red_row": einsummable_t([65536, 512], [[0, 1]], 1, S.make_identity("f32"), "max"),
+        "ew_transpose": einsummable_t([64, 64], [[1, 0]], 2, S.make_identity("f32")),
+        "red_col": einsummable_t([4096, 2048], [[1, 0]], 1, S.make_identity("f32"), "add"),
+        "red_split": einsummable_t([4, 1 << 22], [[0, 1]], 1, S.make_identity("f32"), "add"),
+    }
+    for kind, e in kinds.items():
+        assert e.kernel_kind().startswith(kind), (kind, e.kernel_kind())
+    # ab,a->ab and ab,b->ab and the rope pattern all vectorise
+    assert einsummable_t([2048, 4096], [[0, 1], [0]], 2, S.make_mul("f32")).kernel_kind() == "ew_vec"
+    assert einsummable_t([2048, 4096], [[0, 1], [1]], 2, S.make_mul("f16")).kernel_kind() == "ew_vec"
+    assert einsummable_t([4, 512, 32, 64], [[0, 1, 2, 3], [1, 3]], 4, S.make_mul("c64")).kernel_kind() == "ew_vec"
+    assert einsummable_t([32, 512, 32, 128], [[0, 2, 1, 3]], 4, S.make_identity("f16")).kernel_kind() == "ew_vec"
