@@ -1,0 +1,425 @@
+#!/usr/bin/env python3
+"""Benchmark of the memgraph apply-node kernels on B200.
+
+Workload (N=1): BASELINE config 2 -- f16 tensors x, y of shape [8192, 11008]
+~ N(0,1); one step = one pass of the four einsummables over them, launched
+through the C ABI on one stream:
+    (i)   a,a->a    silu(x) * y
+    (ii)  ab->a     castable max            (row max of x)
+    (iii) ab,a->ab  exp(x - rowmax)
+    (iv)  ab->a     castable add            (row sum of (iii))
+Metric: algorithmic GB/s (inputs + outputs of every op, broadcast inputs at
+their own size) over the whole step.  Under torchrun every rank runs the same
+workload on its own GPU (the path shards by blocks with no data-path
+collective), value = bytes of all ranks / max-over-ranks device time.
+
+Prints ONE JSON line on rank 0.  `--impl reference` times the CPU restatement of
+the reference's CPU kernels (oracle/es_oracle.c) on the host cores instead.
+"""
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+ROWS, COLS = 8192, 11008
+N = ROWS * COLS
+# algorithmic bytes of one step (f16 = 2 bytes)
+BYTES_SILU_MUL = 3 * N * 2
+BYTES_ROWMAX = N * 2 + ROWS * 2
+BYTES_EXP_SUB = 2 * N * 2 + ROWS * 2
+BYTES_ROWSUM = N * 2 + ROWS * 2
+BYTES_STEP = BYTES_SILU_MUL + BYTES_ROWMAX + BYTES_EXP_SUB + BYTES_ROWSUM
+WORKLOAD = "C2 f16 [8192,11008]: silu(x)*y; rowmax; exp(x-rowmax); rowsum"
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the silu*y kernel,
+# from the ncu capture summarised in profiles/ (None until captured).
+SILU_MUL_DRAM_TRAFFIC = None
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# --------------------------------------------------------------------------
+# CPU baseline: the C restatement of the reference CPU engine's kernels
+# --------------------------------------------------------------------------
+def load_cpu_oracle():
+    lib = ctypes.CDLL(os.path.join(ROOT, "oracle", "libes_oracle.so"))
+    lib.oracle_num_threads.restype = ctypes.c_int
+    return lib
+
+
+def cpu_pass(lib, rows, x, y, out, m, ex, s):
+    p = lambda a: ctypes.c_void_p(a.ctypes.data)
+    n = rows * COLS
+    lib.oracle_silu_mul_f16(ctypes.c_uint64(n), p(out), p(x), p(y))
+    lib.oracle_reduce_ab_a_f16(3, ctypes.c_uint64(rows), ctypes.c_uint64(COLS), p(m), p(x))
+    lib.oracle_exp_sub_ab_a_f16(ctypes.c_uint64(rows), ctypes.c_uint64(COLS), p(ex), p(x), p(m))
+    lib.oracle_reduce_ab_a_f16(0, ctypes.c_uint64(rows), ctypes.c_uint64(COLS), p(s), p(ex))
+
+
+def cpu_bytes(rows):
+    n = rows * COLS
+    return 3 * n * 2 + (n * 2 + rows * 2) + (2 * n * 2 + rows * 2) + (n * 2 + rows * 2)
+
+
+def cpu_buffers(rows, seed=0):
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal(rows * COLS).astype(np.float16)
+    y = rng.standard_normal(rows * COLS).astype(np.float16)
+    return (x, y, np.empty_like(x), np.empty(rows, np.float16), np.empty_like(x), np.empty(rows, np.float16))
+
+
+def cpu_baseline(budget_s=10.0, rows=1024):
+    lib = load_cpu_oracle()
+    bufs = cpu_buffers(rows)
+    cpu_pass(lib, rows, *bufs)  # warm
+    t0 = time.perf_counter()
+    passes = 0
+    while True:
+        cpu_pass(lib, rows, *bufs)
+        passes += 1
+        dt = time.perf_counter() - t0
+        if dt >= budget_s or passes >= 200:
+            break
+    return {
+        "value": cpu_bytes(rows) * passes / dt / 1e9, "unit": "GB/s", "cores": lib.oracle_num_threads(),
+        "kind": "port",
+        "sample": "%d passes over the first %d of %d rows (same 4 ops, OpenMP over row blocks), %.1f s"
+                  % (passes, rows, ROWS, dt),
+    }
+
+
+def run_reference_arm(args):
+    """The reference's CPU implementation of the path on the host cores.  The
+    reference's MKL executor cannot be built here (no MKL; merge-conflict markers
+    in src/engine/cpu/kernel_executor.cc:1323-1445), so this is the C port of its
+    loops; each step is one pass over a bounded sample of the workload."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    rows = 1024
+    lib = load_cpu_oracle()
+    bufs = cpu_buffers(rows)
+    for _ in range(args.warmup):
+        cpu_pass(lib, rows, *bufs)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_pass(lib, rows, *bufs)
+    dt = time.perf_counter() - t0
+    value = cpu_bytes(rows) * args.steps / dt / 1e9
+    cores = lib.oracle_num_threads()
+    sample = "each step = one pass over the first %d of %d rows (same 4 ops)" % (rows, ROWS)
+    print(json.dumps({
+        "impl": "reference", "metric": "elementwise+reduction algorithmic GB/s", "value": value, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# --------------------------------------------------------------------------
+# clocks during the timed region
+# --------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.samples = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.FIELDS,
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append((time.perf_counter(), line.strip()))
+
+    def stop(self, t_begin, t_end):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()  # the exact process started above
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        rows = [l for (t, l) in self.samples if t_begin <= t <= t_end] or [l for (_, l) in self.samples]
+        sm, mx, reasons = [], [], set()
+        for l in rows:
+            f = [x.strip() for x in l.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------
+def run_gpu(args):
+    import torch
+    import einsummable_b200 as es
+    from einsummable_b200 import einsummable_t, scalarop_t as S, touch_t
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    km = es.kernel_manager_t(local)  # raises if the CUDA library or device is missing
+
+    f16 = "f16"
+    e_silu = einsummable_t([ROWS, COLS], [[0, 1], [0, 1]], 2,
+                           S.combine(S.make_mul(f16), [S.make_silu(f16), S.make_identity(f16)]))
+    e_max = einsummable_t([ROWS, COLS], [[0, 1]], 1, S.make_identity(f16), "max")
+    e_exp = einsummable_t([ROWS, COLS], [[0, 1], [0]], 2, S.combine(S.make_exp(f16), [S.make_sub(f16)]))
+    e_sum = einsummable_t([ROWS, COLS], [[0, 1]], 1, S.make_identity(f16), "add")
+    ops = [e_silu, e_max, e_exp, e_sum]
+    ws_bytes = max(km.build(e) for e in ops)
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
+    wsarg = (ws, ws_bytes) if ws_bytes else None
+
+    g = torch.Generator(device=dev)
+    g.manual_seed(1234 + rank)
+    x = torch.randn(N, dtype=torch.float16, device=dev, generator=g)
+    y = torch.randn(N, dtype=torch.float16, device=dev, generator=g)
+    o_silu = torch.empty(N, dtype=torch.float16, device=dev)
+    o_max = torch.empty(ROWS, dtype=torch.float16, device=dev)
+    o_exp = torch.empty(N, dtype=torch.float16, device=dev)
+    o_sum = torch.empty(ROWS, dtype=torch.float16, device=dev)
+    stream = torch.cuda.current_stream(dev)
+
+    def step(events=None):
+        if events is not None:
+            events[0].record(stream)
+        km(e_silu, stream, o_silu, [x, y], wsarg)
+        if events is not None:
+            events[1].record(stream)
+        km(e_max, stream, o_max, [x], wsarg)
+        if events is not None:
+            events[2].record(stream)
+        km(e_exp, stream, o_exp, [x, o_max], wsarg)
+        if events is not None:
+            events[3].record(stream)
+        km(e_sum, stream, o_sum, [o_exp], wsarg)
+        if events is not None:
+            events[4].record(stream)
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(args.steps)]
+    c0 = km.counters()
+    barrier()
+    t_begin = time.perf_counter()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record(stream)
+    for k in range(args.steps):
+        step(ev[k])
+    end.record(stream)
+    barrier()
+    t_end = time.perf_counter()
+    c1 = km.counters()
+    clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
+    ms = start.elapsed_time(end)
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    per_kernel_ms = [float(np.mean([ev[k][i].elapsed_time(ev[k][i + 1]) for k in range(args.steps)]))
+                     for i in range(4)]
+    launches = sum(c1[k] - c0[k] for k in c0)
+
+    # ---- end to end: host buffers in, results back on the host, every step ----
+    hx = torch.randn(N, dtype=torch.float16).pin_memory()
+    hy = torch.randn(N, dtype=torch.float16).pin_memory()
+    h_silu = torch.empty(N, dtype=torch.float16).pin_memory()
+    h_max = torch.empty(ROWS, dtype=torch.float16).pin_memory()
+    h_sum = torch.empty(ROWS, dtype=torch.float16).pin_memory()
+
+    def e2e_step():
+        x.copy_(hx, non_blocking=True)
+        y.copy_(hy, non_blocking=True)
+        step()
+        h_silu.copy_(o_silu, non_blocking=True)
+        h_max.copy_(o_max, non_blocking=True)
+        h_sum.copy_(o_sum, non_blocking=True)
+    e2e_steps = max(2, min(args.steps, 5))
+    e2e_step()
+    barrier()
+    s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s2.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    e2.record(stream)
+    barrier()
+    e2e_ms = s2.elapsed_time(e2)
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+
+    if rank != 0:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+        return
+
+    # ---- other kernel classes of the metric (outside the timed region above) ----
+    classes = {}
+    try:
+        classes = other_classes(km, dev, stream)
+    except Exception as exc:  # reported, never hidden
+        classes = {"error": repr(exc)}
+
+    peak, peak_kind = measured_peaks()
+    achieved = BYTES_SILU_MUL / (per_kernel_ms[0] * 1e-3) / 1e9
+    line = {
+        "metric": "elementwise+reduction algorithmic GB/s", "value": BYTES_STEP * world * args.steps / (ms * 1e-3) / 1e9,
+        "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "l2": "inputs larger than L2 (3 x 180 MB per op); no flush",
+                   "algorithmic_bytes_per_step": BYTES_STEP,
+                   "kernels": dict(zip(["silu_mul", "rowmax", "exp_sub", "rowsum"],
+                                       [km.kernel_info(e).split("|")[0] for e in ops]))},
+        "clocks": clocks,
+        "e2e": {"value": BYTES_STEP * world * e2e_steps / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
+                "h2d_bytes_per_step": 2 * N * 2, "d2h_bytes_per_step": N * 2 + 2 * ROWS * 2,
+                "ms_per_step": e2e_ms / e2e_steps},
+        "gpu_launches": int(launches),
+        "roofline": {"bound": "hbm", "kernel": "silu(x)*y a,a->a f16 (generated ew_vec)", "achieved": achieved,
+                     "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
+                     "traffic": SILU_MUL_DRAM_TRAFFIC, "algorithmic_bytes_per_launch": BYTES_SILU_MUL},
+        "per_kernel": {name: {"ms": t, "GB/s": b / (t * 1e-3) / 1e9, "frac_of_" + peak_kind: b / (t * 1e-3) / 1e9 / peak}
+                       for name, t, b in zip(["silu_mul", "rowmax", "exp_sub", "rowsum"], per_kernel_ms,
+                                             [BYTES_SILU_MUL, BYTES_ROWMAX, BYTES_EXP_SUB, BYTES_ROWSUM])},
+        "classes": classes,
+        "cpu_baseline": cpu_baseline() if world == 1 else None,
+    }
+    print(json.dumps(line))
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+def time_launches(fn, stream, iters=20, warm=3):
+    import torch
+    for _ in range(warm):
+        fn()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    s.record(stream)
+    for _ in range(iters):
+        fn()
+    e.record(stream)
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) / iters
+
+
+def other_classes(km, dev, stream):
+    """Short measurements of the other kernel classes named by the metric:
+    contraction TFLOP/s and touch / permutation GB/s (CUDA events, 20 launches)."""
+    import torch
+    from einsummable_b200 import einsummable_t, scalarop_t as S, touch_t
+    out = {}
+    # LLaMA FFN w1: ij,kj->ik f16 2048 x 11008 x 4096
+    for name, (i, j, k) in {"ffn_w1 ij,kj->ik f16 2048x4096x11008": (2048, 4096, 11008),
+                            "qkv ij,kj->ik f16 2048x4096x4096": (2048, 4096, 4096)}.items():
+        e = einsummable_t.from_matmul_st(i, j, k, "f16")
+        ws = km.build(e)
+        if "contraction_tc" not in km.kernel_info(e):
+            out[name] = {"kind": km.kernel_info(e).split("|")[0], "note": "SIMT fallback; not timed"}
+            continue
+        a = torch.randn(i * j, dtype=torch.float16, device=dev)
+        b = torch.randn(k * j, dtype=torch.float16, device=dev)
+        c = torch.empty(i * k, dtype=torch.float16, device=dev)
+        w = torch.empty(max(ws, 16), dtype=torch.uint8, device=dev)
+        ms = time_launches(lambda: km(e, stream, c, [a, b], (w, ws) if ws else None), stream)
+        out[name] = {"ms": ms, "TFLOP/s": 2.0 * i * j * k / (ms * 1e-3) / 1e12, "kind": km.kernel_info(e).split("|")[0]}
+    # C3: one source block of [32,512,32,128] split 2 per dim, copy and accumulate, f16
+    full = (32, 512, 32, 128)
+    sel = [(16, 32, 0, 16, 16), (256, 512, 0, 256, 256), (16, 32, 0, 16, 16), (64, 128, 0, 64, 64)]
+    src = torch.randn(16 * 256 * 16 * 64, dtype=torch.float16, device=dev)
+    dst = torch.zeros(int(np.prod(full)), dtype=torch.float16, device=dev)
+    nbytes = src.numel() * 2
+    for castable, mult in ((None, 2), ("add", 3)):
+        t = touch_t(sel, castable, "f16")
+        ms = time_launches(lambda: km(t, stream, dst, src), stream)
+        out["touch C3 p=2 f16 %s" % (castable or "copy")] = {"ms": ms, "GB/s": mult * nbytes / (ms * 1e-3) / 1e9}
+    e = einsummable_t([32, 32, 512, 128], [[0, 2, 1, 3]], 4, S.make_identity("f16"))
+    km.build(e)
+    big = torch.randn(int(np.prod(full)), dtype=torch.float16, device=dev)
+    ms = time_launches(lambda: km(e, stream, dst, [big]), stream)
+    out["permute bshd->bhsd f16 [32,512,32,128]"] = {"ms": ms, "GB/s": 2 * big.numel() * 2 / (ms * 1e-3) / 1e9}
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()
