@@ -45,6 +45,19 @@ WORKLOAD = "C2 f16 [8192,11008]: silu(x)*y; rowmax; exp(x-rowmax); rowsum"
 SILU_MUL_DRAM_TRAFFIC = None
 
 
+def set_rows(rows):
+    global ROWS, N, BYTES_SILU_MUL, BYTES_ROWMAX, BYTES_EXP_SUB, BYTES_ROWSUM, BYTES_STEP, WORKLOAD
+    if rows == ROWS:
+        return
+    ROWS, N = rows, rows * COLS
+    BYTES_SILU_MUL = 3 * N * 2
+    BYTES_ROWMAX = N * 2 + ROWS * 2
+    BYTES_EXP_SUB = 2 * N * 2 + ROWS * 2
+    BYTES_ROWSUM = N * 2 + ROWS * 2
+    BYTES_STEP = BYTES_SILU_MUL + BYTES_ROWMAX + BYTES_EXP_SUB + BYTES_ROWSUM
+    WORKLOAD = "REDUCED (profiling only) f16 [%d,11008]: silu(x)*y; rowmax; exp(x-rowmax); rowsum" % rows
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -282,6 +295,17 @@ def run_gpu(args):
                      for i in range(4)]
     launches = sum(c1[k] - c0[k] for k in c0)
 
+    if args.kernels_only:
+        if rank == 0:
+            print(json.dumps({"metric": "elementwise+reduction algorithmic GB/s (kernels only)",
+                              "value": BYTES_STEP * world * args.steps / (ms * 1e-3) / 1e9, "unit": "GB/s",
+                              "config": {"workload": WORKLOAD}, "ms_per_step": ms / args.steps,
+                              "per_kernel_ms": per_kernel_ms, "gpu_launches": int(launches)}))
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+        return
+
     # ---- end to end: host buffers in, results back on the host, every step ----
     hx = torch.randn(N, dtype=torch.float16).pin_memory()
     hy = torch.randn(N, dtype=torch.float16).pin_memory()
@@ -414,7 +438,13 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--rows", type=int, default=ROWS,
+                    help="rows of the [rows, 11008] tensors (default: the full C2 workload); "
+                         "smaller values are for profiler captures only")
+    ap.add_argument("--kernels-only", action="store_true",
+                    help="skip the end-to-end, other-class and CPU-baseline legs (profiler captures)")
     args = ap.parse_args()
+    set_rows(args.rows)
     if args.impl == "reference":
         run_reference_arm(args)
     else:
