@@ -189,6 +189,11 @@ int es_b200_build_einsummable(es_b200_t*                   h,
             if (plan_contraction(e, h->f32_policy, *cp)) {
                 k->kind = cp->kind;
                 k->workspace_bytes = cp->workspace_bytes;
+                for (auto const& pp : cp->pre_plans) {
+                    cp->pre_modules.emplace_back();
+                    cp->pre_functions.emplace_back();
+                    load_functions(pp, cp->pre_modules.back(), cp->pre_functions.back());
+                }
                 k->contraction = std::move(cp);
             }
         }
@@ -249,11 +254,20 @@ int es_b200_launch_einsummable(es_b200_t*         h,
                 fail(ES_BAD_ARGUMENT, "einsummable launch: workspace must be 16-byte aligned");
         }
         set_device(h);
-        if (k->contraction) {
+        if (k->contraction && contraction_pointers_ok(inns[0], inns[1])) {
             launch_contraction(*k->contraction, (cudaStream_t)stream, out, inns[0], inns[1],
                                workspace);
             h->counters[0] += k->contraction->n_launches;
             return;
+        }
+        if (k->contraction && k->functions.empty()) {
+            // operands not 16-byte aligned: TMA cannot address them; use the
+            // generated SIMT kernel, built on first need
+            std::lock_guard<std::mutex> lock(h->build_mutex);
+            if (k->functions.empty()) {
+                k->plan = plan_pointwise(k->e, false);
+                load_functions(k->plan, k->module, k->functions);
+            }
         }
         plan_t const*             plan = &k->plan;
         std::vector<void*> const* fns = &k->functions;
@@ -458,6 +472,17 @@ int es_b200_touch_simplify(const es_touchdim_t* dims, int rank, es_touchdim_t* d
         int           r = simplify_touch(dims, rank, tmp);
         std::memcpy(dims_out, tmp, sizeof(es_touchdim_t) * r);
         *out_rank = r;
+    });
+}
+
+int es_b200_device_status(es_b200_t* h, unsigned int* error_word)
+{
+    return guarded([&] {
+        check_handle(h);
+        if (!error_word) fail(ES_BAD_ARGUMENT, "null pointer");
+        set_device(h);
+        ES_CUDA_CHECK(cudaDeviceSynchronize());
+        *error_word = read_and_clear_tc_error();
     });
 }
 

@@ -1,15 +1,852 @@
+// Contraction einsummables on the 5th-generation tensor cores (sm_100a).
+//
+//   C[outer, m, n] = sum_k A[..] * B[..]       (join = x0*x1, castable add)
+//
+// replaces the reference's cublas{H,S}gemm / cutensorContract calls
+// (src/engine/gpu/gpu_kernel_manager.cc:1454-1609).  Neither operand is ever
+// permuted in memory: each keeps its own row-major layout and is described to
+// the TMA unit by a <=5-D tensor map built from its own mode order; whether its
+// innermost mode is a contracted mode ("K-major") or an output mode
+// ("MN-major") selects the major-ness bits of the tcgen05 shared-memory and
+// instruction descriptors, so ij,jk / ij,kj / ji,jk / ji,kj and the attention
+// contractions (acbe,adbe->abcd; abce,aebd->abcd; adbe,cde->abc) all run
+// without a transpose pass.
+//
+// One persistent CTA per SM, 6 warps:
+//   warp 0   : TMA producer  (cp.async.bulk.tensor -> 128B-swizzled smem ring, mbarrier tx)
+//   warp 1   : MMA issuer    (one lane issues tcgen05.mma, accumulators in TMEM, 2 stages)
+//   warps 2-5: epilogue      (tcgen05.ld -> convert -> global stores), overlapped with the
+//                            next tile's main loop through the second TMEM stage
+// f16 inputs accumulate in f32.  f32 inputs run as TF32: by default split into
+// hi + lo parts by a pre-pass into the workspace and multiplied with three MMAs
+// (hi*hi + hi*lo + lo*hi, ~fp32 accuracy); a single TF32 MMA is an opt-in policy.
+//
+// Every wait on an mbarrier is bounded by a clock limit; on expiry the kernel
+// records an error word, lets in-flight copies land, frees its TMEM and returns.
 #include "contraction.h"
+
+#include <cuda.h>
+
+#include <algorithm>
+#include <cstring>
+
+#include "jit.h"
 
 namespace es {
 
-bool plan_contraction(einsum_t const&, int, contraction_plan_t&)
+namespace {
+
+constexpr int      BM = 128;
+constexpr int      NUM_THREADS = 192;
+constexpr int      MAX_STAGES = 8;
+constexpr int      MAX_LOOP_MODES = 6;
+constexpr uint64_t WAIT_LIMIT_CYCLES = 4000000000ull; // ~2 s at 2 GHz
+
+enum src_kind_t : int8_t { SRC_ZERO = 0, SRC_MN_TILE = 1, SRC_K_BLOCK = 2, SRC_OUTER0 = 8, SRC_KOUTER0 = 24 };
+
+struct operand_t {
+    uint32_t n_boxes;       // TMA copies per stage (per term)
+    uint32_t box_bytes;     // bytes landed by one copy
+    uint32_t box_step;      // coordinate step along `box_dim` between copies
+    int32_t  box_dim;       // TMA dim the step applies to
+    uint32_t tile_bytes;    // smem bytes of one term's tile
+    uint32_t k_step_bytes;  // start-address advance per MMA k-step
+    uint32_t desc_hi;       // upper 32 bits of the smem descriptor (SBO, version, swizzle)
+    uint32_t desc_lbo;      // LBO field (bytes >> 4), goes to bits 16..29
+    int32_t  nd;            // tensor-map rank
+    int8_t   src[5];        // where each coordinate comes from
+    int8_t   pad[3];
+};
+
+struct alignas(64) tc_params_t {
+    CUtensorMap tm_a[2];    // [0] = hi (or the only) term, [1] = lo term
+    CUtensorMap tm_b[2];
+    operand_t   a, b;
+    uint32_t    n_outer;
+    uint32_t    outer_extent[MAX_LOOP_MODES];
+    int64_t     outer_out_stride[MAX_LOOP_MODES];
+    uint32_t    n_kouter;
+    uint32_t    kouter_extent[4];
+    uint32_t    m_tiles, n_tiles, k_blocks, kouter_total;
+    uint32_t    m_extent, n_extent;
+    int64_t     out_stride_m, out_stride_n;
+    uint32_t    total_tiles;
+    uint32_t    bn, bk_elems, stages, tmem_cols;
+    uint32_t    idesc;
+    uint32_t    stage_bytes;
+    uint32_t    out_is_f32;
+    uint32_t    n_terms;
+    uint32_t    k_chunk;    // k-iterations accumulated in TMEM before the epilogue takes the partial sum
+};
+
+__device__ unsigned int g_tc_error; // nonzero = a bounded wait expired (code, see below)
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(void const* p)
 {
-    return false;
+    return (uint32_t)__cvta_generic_to_shared(p);
 }
 
-void launch_contraction(contraction_plan_t const&, cudaStream_t, void*, void const*, void const*, void*)
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
 {
-    fail(ES_NOT_SUPPORTED, "tensor-core contraction not built");
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait.  Returns false (and raises the CTA-wide abort flag) when the
+// limit expires or another role already aborted.
+__device__ __forceinline__ bool
+mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t code)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    long long t0 = clock64();
+    uint32_t  spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 0x3ff) == 0) {
+            if (*abort_flag) return false;
+            if ((uint64_t)(clock64() - t0) > WAIT_LIMIT_CYCLES) {
+                *abort_flag = code;
+                atomicCAS(&g_tc_error, 0u, code);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+__device__ __forceinline__ void tma_load(uint32_t dst, CUtensorMap const* tm, uint32_t bar, int nd, int const* c)
+{
+    uint64_t desc = reinterpret_cast<uint64_t>(tm);
+    switch (nd) {
+        case 2:
+            asm volatile(
+                "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                ::"r"(dst), "l"(desc), "r"(bar), "r"(c[0]), "r"(c[1]) : "memory");
+            break;
+        case 3:
+            asm volatile(
+                "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                ::"r"(dst), "l"(desc), "r"(bar), "r"(c[0]), "r"(c[1]), "r"(c[2]) : "memory");
+            break;
+        case 4:
+            asm volatile(
+                "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+                ::"r"(dst), "l"(desc), "r"(bar), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]) : "memory");
+            break;
+        default:
+            asm volatile(
+                "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+                ::"r"(dst), "l"(desc), "r"(bar), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]), "r"(c[4]) : "memory");
+            break;
+    }
+}
+
+__device__ __forceinline__ void tc_fence_before()
+{
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after()
+{
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+template <int KIND> // 0 = f16, 1 = tf32
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate)
+{
+    if constexpr (KIND == 0) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+    }
+}
+
+__device__ __forceinline__ void umma_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r)
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi)
+{
+    uint32_t w;
+    asm("cvt.rn.f16x2.f32 %0, %2, %1;" : "=r"(w) : "f"(lo), "f"(hi));
+    return w;
+}
+
+__device__ __forceinline__ uint16_t f2h(float f)
+{
+    uint16_t h;
+    asm("cvt.rn.f16.f32 %0, %1;" : "=h"(h) : "f"(f));
+    return h;
+}
+
+// smem control block placed after the stage ring
+struct ctrl_t {
+    uint64_t full[MAX_STAGES];
+    uint64_t empty[MAX_STAGES];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+};
+
+__device__ __forceinline__ void
+decode_tile(tc_params_t const& p, uint32_t tile, uint32_t& m_tile, uint32_t& n_tile, uint32_t* outer)
+{
+    m_tile = tile % p.m_tiles;
+    uint32_t t = tile / p.m_tiles;
+    n_tile = t % p.n_tiles;
+    t /= p.n_tiles;
+    for (int j = (int)p.n_outer - 1; j >= 0; --j) {
+        outer[j] = t % p.outer_extent[j];
+        t /= p.outer_extent[j];
+    }
+}
+
+__device__ __forceinline__ void fill_coords(operand_t const& o,
+                                            uint32_t         mn_tile_elems,
+                                            uint32_t         k_elems,
+                                            uint32_t const*  outer,
+                                            uint32_t const*  kouter,
+                                            int*             c)
+{
+#pragma unroll
+    for (int d = 0; d < 5; ++d) {
+        int8_t s = o.src[d];
+        int    v = 0;
+        if (s == SRC_MN_TILE) v = (int)mn_tile_elems;
+        else if (s == SRC_K_BLOCK) v = (int)k_elems;
+        else if (s >= SRC_KOUTER0) v = (int)kouter[s - SRC_KOUTER0];
+        else if (s >= SRC_OUTER0) v = (int)outer[s - SRC_OUTER0];
+        c[d] = v;
+    }
+}
+
+template <int KIND, bool PROMOTE>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ out_)
+{
+    extern __shared__ uint8_t smem_raw[];
+    // 1024-byte alignment for the 128B swizzle atoms
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    ctrl_t*  ctrl = reinterpret_cast<ctrl_t*>(smem + (size_t)p.stages * p.stage_bytes);
+    volatile uint32_t* abort_flag = &ctrl->abort_flag;
+
+    int const warp = threadIdx.x >> 5;
+    int const lane = threadIdx.x & 31;
+    uint32_t const smem_base = smem_u32(smem);
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < p.stages; ++s) {
+            mbar_init(smem_u32(&ctrl->full[s]), 1);
+            mbar_init(smem_u32(&ctrl->empty[s]), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(smem_u32(&ctrl->tmem_full[a]), 1);
+            mbar_init(smem_u32(&ctrl->tmem_empty[a]), 4);
+        }
+        ctrl->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&ctrl->tmem_base)), "r"(p.tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    uint32_t const tmem_base = ctrl->tmem_base;
+
+    uint32_t const k_iters = p.k_blocks * p.kouter_total;
+    uint32_t const term_a_bytes = p.a.tile_bytes, term_b_bytes = p.b.tile_bytes;
+    uint32_t const a_region = term_a_bytes * p.n_terms; // A tiles first, then B tiles
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool     ok = true;
+            for (uint32_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+                uint32_t m_tile, n_tile, outer[MAX_LOOP_MODES];
+                decode_tile(p, tile, m_tile, n_tile, outer);
+                for (uint32_t ki = 0; ki < k_iters; ++ki, ++it) {
+                    uint32_t s = it % p.stages, ph = (it / p.stages) & 1;
+                    if (!mbar_wait(smem_u32(&ctrl->empty[s]), ph ^ 1, abort_flag, 1)) { ok = false; break; }
+                    uint32_t kb = ki % p.k_blocks, ko = ki / p.k_blocks;
+                    uint32_t kouter[4] = {0, 0, 0, 0};
+                    for (int j = (int)p.n_kouter - 1; j >= 0; --j) {
+                        kouter[j] = ko % p.kouter_extent[j];
+                        ko /= p.kouter_extent[j];
+                    }
+                    uint32_t bar = smem_u32(&ctrl->full[s]);
+                    mbar_arrive_expect_tx(bar, p.stage_bytes);
+                    uint32_t stage_base = smem_base + s * p.stage_bytes;
+                    int      c[5];
+                    fill_coords(p.a, m_tile * BM, kb * p.bk_elems, outer, kouter, c);
+                    for (uint32_t t = 0; t < p.n_terms; ++t) {
+                        int c0 = c[p.a.box_dim];
+                        for (uint32_t bx = 0; bx < p.a.n_boxes; ++bx) {
+                            c[p.a.box_dim] = c0 + (int)(bx * p.a.box_step);
+                            tma_load(stage_base + t * term_a_bytes + bx * p.a.box_bytes, &p.tm_a[t], bar, p.a.nd, c);
+                        }
+                        c[p.a.box_dim] = c0;
+                    }
+                    fill_coords(p.b, n_tile * p.bn, kb * p.bk_elems, outer, kouter, c);
+                    for (uint32_t t = 0; t < p.n_terms; ++t) {
+                        int c0 = c[p.b.box_dim];
+                        for (uint32_t bx = 0; bx < p.b.n_boxes; ++bx) {
+                            c[p.b.box_dim] = c0 + (int)(bx * p.b.box_step);
+                            tma_load(stage_base + a_region + t * term_b_bytes + bx * p.b.box_bytes, &p.tm_b[t], bar,
+                                     p.b.nd, c);
+                        }
+                        c[p.b.box_dim] = c0;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            uint32_t it = 0, q = 0; // q counts accumulator uses (one per k-chunk)
+            bool     ok = true;
+            uint64_t const a_hi = ((uint64_t)p.a.desc_hi << 32) | ((uint64_t)p.a.desc_lbo << 16);
+            uint64_t const b_hi = ((uint64_t)p.b.desc_hi << 32) | ((uint64_t)p.b.desc_lbo << 16);
+            uint32_t const k_steps = 4; // a 128-byte swizzle row holds four MMA k-steps
+            for (uint32_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+                for (uint32_t ki0 = 0; ki0 < k_iters && ok; ki0 += p.k_chunk, ++q) {
+                    uint32_t acc = q & 1, acc_ph = (q >> 1) & 1;
+                    if (!mbar_wait(smem_u32(&ctrl->tmem_empty[acc]), acc_ph ^ 1, abort_flag, 2)) { ok = false; break; }
+                    tc_fence_after();
+                    uint32_t tmem_d = tmem_base + acc * p.bn;
+                    uint32_t first = 1;
+                    uint32_t ki1 = min(ki0 + p.k_chunk, k_iters);
+                    for (uint32_t ki = ki0; ki < ki1; ++ki, ++it) {
+                        uint32_t s = it % p.stages, ph = (it / p.stages) & 1;
+                        if (!mbar_wait(smem_u32(&ctrl->full[s]), ph, abort_flag, 3)) { ok = false; break; }
+                        tc_fence_after();
+                        uint32_t a_base = smem_base + s * p.stage_bytes;
+                        uint32_t b_base = a_base + a_region;
+                        for (uint32_t ks = 0; ks < k_steps; ++ks) {
+                            // with hi/lo operand copies: lo*hi, hi*lo, then hi*hi
+                            for (uint32_t t = 0; t < (p.n_terms == 1 ? 1u : 3u); ++t) {
+                                uint32_t ta = (p.n_terms == 1) ? 0 : (t == 0 ? 1 : 0);
+                                uint32_t tb = (p.n_terms == 1) ? 0 : (t == 1 ? 1 : 0);
+                                uint32_t aa = a_base + ta * term_a_bytes + ks * p.a.k_step_bytes;
+                                uint32_t bb = b_base + tb * term_b_bytes + ks * p.b.k_step_bytes;
+                                uint64_t da = a_hi | (uint64_t)((aa >> 4) & 0x3fff);
+                                uint64_t db = b_hi | (uint64_t)((bb >> 4) & 0x3fff);
+                                umma<KIND>(tmem_d, da, db, p.idesc, first ? 0u : 1u);
+                                first = 0;
+                            }
+                        }
+                        umma_commit(smem_u32(&ctrl->empty[s])); // frees the smem stage when these MMAs retire
+                    }
+                    if (ok) umma_commit(smem_u32(&ctrl->tmem_full[acc]));
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..5)
+        uint32_t const quarter = warp & 3; // TMEM lanes 32*quarter .. +31 belong to this warp
+        uint32_t q = 0;
+        bool     ok = true;
+        // PROMOTE: partial sums of each k-chunk are added in registers with
+        // round-to-nearest f32 adds.  The tensor core's own accumulation truncates,
+        // which over hundreds of MMAs biases a long f32 sum beyond 1e-5.
+        float accr[PROMOTE ? 4 : 1][32];
+        for (uint32_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+            uint32_t m_tile, n_tile, outer[MAX_LOOP_MODES];
+            decode_tile(p, tile, m_tile, n_tile, outer);
+            int64_t base = 0;
+            for (uint32_t j = 0; j < p.n_outer; ++j) base += (int64_t)outer[j] * p.outer_out_stride[j];
+            uint32_t m = m_tile * BM + quarter * 32 + lane;
+            uint32_t n0 = n_tile * p.bn;
+            for (uint32_t ki0 = 0; ki0 < k_iters && ok; ki0 += p.k_chunk, ++q) {
+                uint32_t acc = q & 1, acc_ph = (q >> 1) & 1;
+                bool const first_chunk = ki0 == 0, last_chunk = ki0 + p.k_chunk >= k_iters;
+                if (!mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_ph, abort_flag, 4)) { ok = false; break; }
+                tc_fence_after();
+#pragma unroll
+                for (uint32_t ch = 0; ch < (PROMOTE ? 4u : 8u); ++ch) {
+                    if (ch * 32 >= p.bn) break;
+                    uint32_t r[32];
+                    tmem_ld32(tmem_base + ((quarter * 32u) << 16) + acc * p.bn + ch * 32, r);
+                    if constexpr (PROMOTE) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            float v = __uint_as_float(r[j]);
+                            accr[ch][j] = first_chunk ? v : __fadd_rn(accr[ch][j], v);
+                            r[j] = __float_as_uint(accr[ch][j]);
+                        }
+                    }
+                    if (!last_chunk) continue;
+                    uint32_t n = n0 + ch * 32;
+                    if (m < p.m_extent && n < p.n_extent) {
+                        int64_t off = base + (int64_t)m * p.out_stride_m + (int64_t)n * p.out_stride_n;
+                        bool    full = n + 32 <= p.n_extent;
+                        if (p.out_is_f32) {
+                            float* o = static_cast<float*>(out_) + off;
+                            if (p.out_stride_n == 1 && full && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+#pragma unroll
+                                for (int j = 0; j < 32; j += 4)
+                                    *reinterpret_cast<uint4*>(o + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+                            } else {
+                                for (int j = 0; j < 32 && n + j < p.n_extent; ++j)
+                                    o[(int64_t)j * p.out_stride_n] = __uint_as_float(r[j]);
+                            }
+                        } else {
+                            uint16_t* o = static_cast<uint16_t*>(out_) + off;
+                            if (p.out_stride_n == 1 && full && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+#pragma unroll
+                                for (int j = 0; j < 32; j += 8) {
+                                    uint4 w;
+                                    w.x = pack_h2(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+                                    w.y = pack_h2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                                    w.z = pack_h2(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+                                    w.w = pack_h2(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+                                    *reinterpret_cast<uint4*>(o + j) = w;
+                                }
+                            } else {
+                                for (int j = 0; j < 32 && n + j < p.n_extent; ++j)
+                                    o[(int64_t)j * p.out_stride_n] = f2h(__uint_as_float(r[j]));
+                            }
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&ctrl->tmem_empty[acc]));
+            }
+        }
+    }
+
+    // ------------------------------------------------------------------ teardown
+    tc_fence_before();
+    __syncthreads();
+    if (ctrl->abort_flag) {
+        // a bounded wait expired: give copies already issued time to land before the
+        // shared memory is released (bounded: ~1 ms)
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_cols) : "memory");
+    }
+}
+
+// f32 -> (hi, lo) with hi = tf32(x) (round to nearest), lo = x - hi (exact in f32)
+__global__ void __launch_bounds__(256) split_tf32_kernel(float const* x, float* hi, float* __restrict__ lo,
+                                                         uint64_t n4) // hi may alias x (in-place split)
+{
+    uint64_t nth = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += nth) {
+        float4 v = reinterpret_cast<float4 const*>(x)[i];
+        float4 h, l;
+        uint32_t t;
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(t) : "f"(v.x)); h.x = __uint_as_float(t); l.x = v.x - h.x;
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(t) : "f"(v.y)); h.y = __uint_as_float(t); l.y = v.y - h.y;
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(t) : "f"(v.z)); h.z = __uint_as_float(t); l.z = v.z - h.z;
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(t) : "f"(v.w)); h.w = __uint_as_float(t); l.w = v.w - h.w;
+        reinterpret_cast<float4*>(hi)[i] = h;
+        reinterpret_cast<float4*>(lo)[i] = l;
+    }
+}
+
+// ------------------------------------------------------------------ host side
+struct tc_plan_t {
+    tc_params_t p;
+    int         kind;          // 0 f16, 1 tf32
+    uint32_t    smem_bytes;
+    uint32_t    grid;
+    // tensor-map recipes (the base pointer is only known at launch)
+    struct map_recipe_t {
+        uint32_t nd;
+        uint64_t dims[5];
+        uint64_t strides_bytes[4];
+        uint32_t box[5];
+        int      dtype; // CUtensorMapDataType
+    } ra, rb;
+    uint64_t a_elems, b_elems; // for the split pre-pass
+    int      swap;             // the second input plays the A (128-row) role
+    int      promote;          // chunked accumulation with register promotion (3xTF32)
+    int      a_perm, b_perm;   // operand is first copied K-major into the workspace
+    uint64_t ws_b_offset;      // float offset of B's workspace region
+};
+
+using encode_fn_t = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, cuuint64_t const*,
+                                 cuuint64_t const*, cuuint32_t const*, cuuint32_t const*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+void encode_map(CUtensorMap* tm, tc_plan_t::map_recipe_t const& r, void const* base)
+{
+    static encode_fn_t fn = (encode_fn_t)driver_entry("cuTensorMapEncodeTiled");
+    cuuint32_t         elem_strides[5] = {1, 1, 1, 1, 1};
+    cuuint64_t         dims[5];
+    cuuint64_t         strides[4];
+    cuuint32_t         box[5];
+    for (uint32_t i = 0; i < r.nd; ++i) {
+        dims[i] = r.dims[i];
+        box[i] = r.box[i];
+        if (i + 1 < r.nd) strides[i] = r.strides_bytes[i];
+    }
+    CUresult rc = fn(tm, (CUtensorMapDataType)r.dtype, r.nd, const_cast<void*>(base), dims, strides, box,
+                     elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) fail(ES_CUDA_ERROR, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)rc));
+}
+
+enum mode_class_t { MC_BATCH, MC_M, MC_N, MC_K, MC_BAD };
+
+} // namespace
+
+bool plan_contraction(einsum_t const& e, int f32_policy, contraction_plan_t& plan)
+{
+    if (!e.is_contraction()) return false;
+    int dt = e.out_dtype();
+    if (dt != ES_F16 && dt != ES_F32) return false;
+    if (e.inn_dtype(0) != dt || e.inn_dtype(1) != dt) return false;
+    int const      r = e.join_rank();
+    int const      esize = dtype_size(dt);
+    // The product is symmetric in its operands.  When the first input has very
+    // few rows along its innermost output mode (e.g. the last-token vocabulary
+    // projection, 4 x 32000 x 4096) the roles are swapped so that the long mode
+    // fills the 128-row side of the MMA tile.
+    bool swap = false;
+    {
+        auto extent_of_innermost_out_mode = [&](int k) {
+            auto const& t = e.inns[k];
+            auto const  other = e.inn_strides(1 - k);
+            for (int i = (int)t.size() - 1; i >= 0; --i)
+                if (t[i] < e.out_rank && other[t[i]] == 0) return e.join_shape[t[i]];
+            return (uint64_t)0;
+        };
+        uint64_t m0 = extent_of_innermost_out_mode(0), n0 = extent_of_innermost_out_mode(1);
+        swap = m0 > 0 && n0 > 0 && m0 <= 64 && n0 > m0;
+    }
+    int const      ia = swap ? 1 : 0, ib = swap ? 0 : 1;
+    auto const     sa_orig = e.inn_strides(ia), sb_orig = e.inn_strides(ib), so = e.out_strides();
+    auto const&    A_orig = e.inns[ia];
+    auto const&    B_orig = e.inns[ib];
+    if (A_orig.size() > 5 || B_orig.size() > 5 || A_orig.size() < 2 || B_orig.size() < 2) return false;
+
+    std::vector<mode_class_t> cls(r);
+    for (int m = 0; m != r; ++m) {
+        bool ia = sa_orig[m] != 0, ib = sb_orig[m] != 0, io = m < e.out_rank;
+        if (ia && ib && io) cls[m] = MC_BATCH;
+        else if (ia && !ib && io) cls[m] = MC_M;
+        else if (!ia && ib && io) cls[m] = MC_N;
+        else if (ia && ib && !io) cls[m] = MC_K;
+        else return false;
+        if (e.join_shape[m] > 0x7fffffffull) return false;
+    }
+    // innermost (smallest stride) M mode of A, N mode of B, K mode of each
+    auto innermost = [&](std::vector<int> const& modes, mode_class_t c) {
+        for (int i = (int)modes.size() - 1; i >= 0; --i)
+            if (cls[modes[i]] == c) return modes[i];
+        return -1;
+    };
+    int m_in = innermost(A_orig, MC_M), n_in = innermost(B_orig, MC_N);
+    int k_in = innermost(A_orig, MC_K);
+    if (m_in < 0 || n_in < 0 || k_in < 0 || innermost(B_orig, MC_K) != k_in) return false;
+    bool a_mn = A_orig.back() == m_in, b_mn = B_orig.back() == n_in;
+    if (!a_mn && A_orig.back() != k_in) return false;
+    if (!b_mn && B_orig.back() != k_in) return false;
+
+    // f32 operands run as TF32 with K-major tiles only: an operand whose innermost
+    // mode is an output mode is copied (pre-pass, generated permutation kernel)
+    // into the workspace with the contracted mode moved innermost.
+    std::vector<int>      A = A_orig, B = B_orig;
+    std::vector<uint64_t> sa = sa_orig, sb = sb_orig;
+    bool const            a_perm = dt == ES_F32 && a_mn, b_perm = dt == ES_F32 && b_mn;
+    auto k_last = [&](std::vector<int>& modes, std::vector<uint64_t>& st) {
+        modes.erase(std::find(modes.begin(), modes.end(), k_in));
+        modes.push_back(k_in);
+        std::fill(st.begin(), st.end(), 0);
+        uint64_t s = 1;
+        for (int i = (int)modes.size() - 1; i >= 0; --i) {
+            st[modes[i]] = s;
+            s *= e.join_shape[modes[i]];
+        }
+    };
+    if (a_perm) { k_last(A, sa); a_mn = false; }
+    if (b_perm) { k_last(B, sb); b_mn = false; }
+    auto perm_plan = [&](std::vector<int> const& orig, std::vector<int> const& eff) {
+        einsum_t pe;
+        pe.out_rank = (int)eff.size();
+        pe.castable = ES_CASTABLE_NONE;
+        pe.join = scalarop_t::parse("hole|f32@0");
+        std::vector<int> in_modes;
+        for (int m : eff) pe.join_shape.push_back(e.join_shape[m]);
+        for (int m : orig) in_modes.push_back((int)(std::find(eff.begin(), eff.end(), m) - eff.begin()));
+        pe.inns.push_back(in_modes);
+        return plan_pointwise(pe.merge_adjacent_dims(), false);
+    };
+
+    // TMA: every non-innermost stride must be a multiple of 16 bytes
+    for (int m : A)
+        if (m != A.back() && (sa[m] * esize) % 16) return false;
+    for (int m : B)
+        if (m != B.back() && (sb[m] * esize) % 16) return false;
+
+    tc_plan_t tp;
+    std::memset(&tp, 0, sizeof tp);
+    tc_params_t& p = tp.p;
+    tp.kind = dt == ES_F16 ? 0 : 1;
+    p.n_terms = (dt == ES_F32 && f32_policy == ES_F32_3XTF32) ? 2 : 1; // number of operand copies (hi, lo)
+    uint32_t const row_elems = 128 / esize;   // elements in one 128-byte swizzle row
+    p.bk_elems = row_elems;
+    uint64_t const M = e.join_shape[m_in], Nn = e.join_shape[n_in], K = e.join_shape[k_in];
+    uint32_t bn;
+    if (p.n_terms == 2) bn = Nn > 64 ? 128 : 64;
+    else bn = Nn > 128 ? 256 : (Nn > 64 ? 128 : 64);
+    p.bn = bn;
+    p.m_extent = (uint32_t)M;
+    p.n_extent = (uint32_t)Nn;
+    p.m_tiles = (uint32_t)((M + BM - 1) / BM);
+    p.n_tiles = (uint32_t)((Nn + bn - 1) / bn);
+    p.k_blocks = (uint32_t)((K + row_elems - 1) / row_elems);
+    p.out_stride_m = (int64_t)so[m_in];
+    p.out_stride_n = (int64_t)so[n_in];
+    p.out_is_f32 = dt == ES_F32;
+
+    // loop modes
+    std::vector<int> outer_idx(r, -1), kouter_idx(r, -1);
+    uint64_t         total = (uint64_t)p.m_tiles * p.n_tiles;
+    p.kouter_total = 1;
+    for (int m = 0; m != r; ++m) {
+        if (m == m_in || m == n_in || m == k_in) continue;
+        if (cls[m] == MC_K) {
+            if (p.n_kouter >= 4) return false;
+            kouter_idx[m] = (int)p.n_kouter;
+            p.kouter_extent[p.n_kouter++] = (uint32_t)e.join_shape[m];
+            if ((uint64_t)p.kouter_total * e.join_shape[m] > 0x7fffffffull) return false;
+            p.kouter_total *= (uint32_t)e.join_shape[m];
+        } else {
+            if (p.n_outer >= MAX_LOOP_MODES) return false;
+            outer_idx[m] = (int)p.n_outer;
+            p.outer_extent[p.n_outer] = (uint32_t)e.join_shape[m];
+            p.outer_out_stride[p.n_outer] = (int64_t)so[m];
+            ++p.n_outer;
+            total *= e.join_shape[m];
+        }
+    }
+    if (total > 0x7fffffffull) return false;
+    p.total_tiles = (uint32_t)total;
+
+    // operands
+    auto setup = [&](std::vector<int> const& modes, std::vector<uint64_t> const& st, bool mn_major, int mn_mode,
+                     uint32_t tile_mn, operand_t& o, tc_plan_t::map_recipe_t& rc) {
+        int nd = (int)modes.size();
+        o.nd = nd;
+        rc.nd = nd;
+        rc.dtype = dt == ES_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+        for (int d = 0; d < 5; ++d) o.src[d] = SRC_ZERO;
+        for (int d = 0; d != nd; ++d) {
+            int m = modes[nd - 1 - d]; // TMA dim 0 = innermost
+            rc.dims[d] = e.join_shape[m];
+            if (d > 0) rc.strides_bytes[d - 1] = st[m] * esize;
+            rc.box[d] = 1;
+            if (m == mn_mode) o.src[d] = SRC_MN_TILE;
+            else if (m == k_in) o.src[d] = SRC_K_BLOCK;
+            else if (kouter_idx[m] >= 0) o.src[d] = (int8_t)(SRC_KOUTER0 + kouter_idx[m]);
+            else o.src[d] = (int8_t)(SRC_OUTER0 + outer_idx[m]);
+            if (m == mn_mode) o.box_dim = d;
+        }
+        int k_dim = -1, mn_dim = o.box_dim;
+        for (int d = 0; d != nd; ++d)
+            if (modes[nd - 1 - d] == k_in) k_dim = d;
+        uint32_t const version = 1u << 14; // descriptor version field (bit 46 of the 64-bit word)
+        uint32_t const sw128 = 2u << 29;   // layout type SWIZZLE_128B (bits 61..63)
+        uint32_t const sbo = (1024u >> 4); // 8 rows x 128 bytes between core-matrix groups
+        o.tile_bytes = tile_mn * 128;
+        if (!mn_major) {
+            // K-major: rows of the tile are MN indices, 128 bytes of K each
+            rc.box[k_dim] = row_elems;
+            rc.box[mn_dim] = tile_mn; // <= 256
+            o.n_boxes = 1;
+            o.box_bytes = tile_mn * 128;
+            o.box_step = 0;
+            o.k_step_bytes = 32;
+            o.desc_lbo = 0;
+            o.desc_hi = sbo | version | sw128;
+        } else {
+            // MN-major: rows are K indices, 128 bytes of MN each; one copy per 128-byte column block
+            rc.box[mn_dim] = row_elems;
+            rc.box[k_dim] = row_elems; // BK rows (BK = elements per 128 bytes of K in the other operand)
+            o.n_boxes = tile_mn / row_elems;
+            o.box_bytes = row_elems * 128;
+            o.box_step = row_elems;
+            o.k_step_bytes = (32 / esize) * 128; // UMMA_K rows
+            o.desc_lbo = (o.box_bytes >> 4);     // byte distance between column blocks
+            o.desc_hi = sbo | version | sw128;
+        }
+        return true;
+    };
+    setup(A, sa, a_mn, m_in, BM, p.a, tp.ra);
+    setup(B, sb, b_mn, n_in, bn, p.b, tp.rb);
+    // the K extent of one block must be the same for both operands: row_elems elements
+    p.stage_bytes = (p.a.tile_bytes + p.b.tile_bytes) * p.n_terms;
+    uint32_t const smem_budget = 227 * 1024 - 1024 /*alignment*/ - (uint32_t)sizeof(ctrl_t) - 256;
+    p.stages = std::min<uint32_t>(MAX_STAGES, smem_budget / p.stage_bytes);
+    if (p.stages < 2) return false;
+    p.tmem_cols = 2 * bn < 32 ? 32 : 2 * bn; // 128, 256 or 512: powers of two
+    // 3xTF32: promote the partial sum to registers every 8 k-blocks (256 contracted elements)
+    tp.promote = p.n_terms == 2 ? 1 : 0;
+    p.k_chunk = tp.promote ? 8u : (p.k_blocks * p.kouter_total);
+    // instruction descriptor: D=f32, A/B format, majors, N>>3, M>>4
+    uint32_t fmt = dt == ES_F16 ? 0u : 2u;
+    p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
+              ((bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+    tp.smem_bytes = p.stages * p.stage_bytes + (uint32_t)sizeof(ctrl_t) + 1024;
+    tp.grid = std::min<uint32_t>(p.total_tiles, 148);
+    tp.a_elems = e.inn_nelem(ia);
+    tp.b_elems = e.inn_nelem(ib);
+    tp.swap = swap ? 1 : 0;
+
+    plan.kind = dt == ES_F16 ? "contraction_tc_f16" : (p.n_terms == 2 ? "contraction_tc_3xtf32" : "contraction_tc_tf32");
+    plan.n_launches = 1;
+    plan.pre_plans.clear();
+    tp.a_perm = a_perm;
+    tp.b_perm = b_perm;
+    if (a_perm) plan.pre_plans.push_back(perm_plan(A_orig, A));
+    if (b_perm) plan.pre_plans.push_back(perm_plan(B_orig, B));
+    plan.n_launches += (int)plan.pre_plans.size();
+    // workspace (floats): [A copy / A hi][A lo][B copy / B hi][B lo], parts present as needed
+    uint64_t a_ws = 0, b_ws = 0;
+    if (p.n_terms == 2) {
+        if ((tp.a_elems % 4) || (tp.b_elems % 4)) return false;
+        a_ws = 2 * tp.a_elems;
+        b_ws = 2 * tp.b_elems;
+        plan.n_launches += 2;
+    } else {
+        a_ws = a_perm ? tp.a_elems : 0;
+        b_ws = b_perm ? tp.b_elems : 0;
+    }
+    a_ws = (a_ws + 3) & ~3ull; // keep the B region 16-byte aligned
+    tp.ws_b_offset = a_ws;
+    plan.workspace_bytes = (a_ws + b_ws) * 4;
+    plan.info = "bm=128,bn=" + std::to_string(bn) + ",bk=" + std::to_string(row_elems) + ",stages=" +
+                std::to_string(p.stages) + ",tiles=" + std::to_string(p.total_tiles) + ",a=" +
+                (a_mn ? "mn" : "k") + "-major,b=" + (b_mn ? "mn" : "k") + "-major" + (swap ? ",swapped" : "") +
+                (a_perm ? ",a-prepermuted" : "") + (b_perm ? ",b-prepermuted" : "");
+    plan.blob.resize(sizeof tp);
+    std::memcpy(plan.blob.data(), &tp, sizeof tp);
+    return true;
+}
+
+void launch_contraction(contraction_plan_t const& plan,
+                        cudaStream_t              stream,
+                        void*                     out,
+                        void const*               lhs,
+                        void const*               rhs,
+                        void*                     workspace)
+{
+    tc_plan_t tp;
+    std::memcpy(&tp, plan.blob.data(), sizeof tp);
+    tc_params_t& p = tp.p;
+    if (tp.swap) std::swap(lhs, rhs);
+    if ((reinterpret_cast<uintptr_t>(lhs) | reinterpret_cast<uintptr_t>(rhs)) & 15)
+        fail(ES_BAD_ARGUMENT, "tensor-core contraction needs 16-byte aligned operands");
+    {
+        float* w = static_cast<float*>(workspace);
+        auto   blocks = [](uint64_t n4) { return (unsigned)std::min<uint64_t>((n4 + 255) / 256, 148ull * 8); };
+        size_t pre = 0;
+        auto   stage = [&](void const* src, int perm, uint64_t elems, float* region, CUtensorMap* tm,
+                         tc_plan_t::map_recipe_t const& rc) {
+            float const* cur = static_cast<float const*>(src);
+            if (perm) {
+                // generated permutation kernel: (out, x0, workspace)
+                plan_t const& pp = plan.pre_plans[pre];
+                void*         o = region;
+                void*         x = const_cast<void*>(src);
+                void*         none = nullptr;
+                void*         args[3] = {&o, &x, &none};
+                for (size_t i = 0; i != pp.launches.size(); ++i)
+                    launch_function(plan.pre_functions[pre][i], pp.launches[i].grid, pp.launches[i].block,
+                                    pp.launches[i].smem, stream, args);
+                cur = region;
+                ++pre;
+            }
+            if (p.n_terms == 2) {
+                float* hi = region;
+                float* lo = region + elems;
+                split_tf32_kernel<<<blocks(elems / 4), 256, 0, stream>>>(cur, hi, lo, elems / 4);
+                encode_map(&tm[0], rc, hi);
+                encode_map(&tm[1], rc, lo);
+            } else {
+                encode_map(&tm[0], rc, cur);
+                tm[1] = tm[0];
+            }
+        };
+        stage(lhs, tp.a_perm, tp.a_elems, w, p.tm_a, tp.ra);
+        stage(rhs, tp.b_perm, tp.b_elems, w + tp.ws_b_offset, p.tm_b, tp.rb);
+    }
+    auto launch = [&](auto kernel, int slot) {
+        static bool attr_set[3][64] = {};
+        int         dev = 0;
+        cudaGetDevice(&dev);
+        if (!attr_set[slot][dev & 63]) {
+            ES_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+            attr_set[slot][dev & 63] = true;
+        }
+        kernel<<<tp.grid, NUM_THREADS, tp.smem_bytes, stream>>>(p, out);
+    };
+    if (tp.kind == 0) launch(tc_contraction_kernel<0, false>, 0);
+    else if (tp.promote) launch(tc_contraction_kernel<1, true>, 1);
+    else launch(tc_contraction_kernel<1, false>, 2);
+    ES_CUDA_CHECK(cudaGetLastError());
+}
+
+unsigned int read_and_clear_tc_error()
+{
+    unsigned int v = 0, zero = 0;
+    ES_CUDA_CHECK(cudaMemcpyFromSymbol(&v, g_tc_error, sizeof v));
+    if (v) ES_CUDA_CHECK(cudaMemcpyToSymbol(g_tc_error, &zero, sizeof zero));
+    return v;
 }
 
 } // namespace es

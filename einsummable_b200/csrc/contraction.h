@@ -5,7 +5,9 @@
 #include <string>
 #include <vector>
 
+#include "codegen.h"
 #include "einsum.h"
+#include "jit.h"
 
 namespace es {
 
@@ -15,6 +17,12 @@ struct contraction_plan_t {
     uint64_t          workspace_bytes = 0;
     int               n_launches = 1;
     std::vector<char> blob;            // kernel parameters prepared at build time
+    // Pre-pass permutation kernels (generated): an f32 operand whose innermost
+    // mode is an output mode is first copied into the workspace with its
+    // contracted mode innermost, so that the TF32 MMAs only ever see K-major tiles.
+    std::vector<plan_t>                    pre_plans;   // one per permuted operand, in A, B order
+    std::vector<std::shared_ptr<module_t>> pre_modules; // loaded by the owner of the plan at build
+    std::vector<std::vector<void*>>        pre_functions;
 };
 
 // Returns false when the einsummable cannot be mapped onto the tensor-core
@@ -28,5 +36,15 @@ void launch_contraction(contraction_plan_t const& plan,
                         void const*               lhs,
                         void const*               rhs,
                         void*                     workspace);
+
+// True when both operand pointers satisfy the TMA base alignment (16 bytes).
+inline bool contraction_pointers_ok(void const* lhs, void const* rhs)
+{
+    return ((reinterpret_cast<uintptr_t>(lhs) | reinterpret_cast<uintptr_t>(rhs)) & 15) == 0;
+}
+
+// Reads and clears the device-side error word of the tensor-core kernels
+// (nonzero = a bounded wait inside a kernel expired).  Synchronises the device.
+unsigned int read_and_clear_tc_error();
 
 } // namespace es

@@ -162,6 +162,12 @@ class kernel_manager_t:
         _lib.check(self._lib.es_b200_move(
             self._h, src_device, _ptr(src), self.device, _ptr(dst), int(nbytes), _stream(stream)))
 
+    def device_status(self):
+        """Synchronises and returns the tensor-core kernels' error word (0 = fine)."""
+        w = ctypes.c_uint(0)
+        _lib.check(self._lib.es_b200_device_status(self._h, ctypes.byref(w)))
+        return w.value
+
     def counters(self):
         arr = (ctypes.c_uint64 * 4)()
         _lib.check(self._lib.es_b200_query_counters(self._h, arr))

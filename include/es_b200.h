@@ -196,6 +196,12 @@ int es_b200_touch_simplify(const es_touchdim_t* dims,
                            es_touchdim_t*       dims_out,
                            int*                 out_rank);
 
+/* Synchronises the device and returns (and clears) the error word of the
+ * tensor-core kernels: 0 = fine; nonzero = a bounded wait inside a kernel gave
+ * up (1 producer, 2/3 MMA issuer, 4 epilogue) and that launch's output is not
+ * valid.  The reference has no counterpart: its library kernels cannot report. */
+int es_b200_device_status(es_b200_t* h, unsigned int* error_word);
+
 /* Launch / byte counters since creation: launches[class], class order =
  * einsummable, touch, fill, move. */
 int es_b200_query_counters(es_b200_t* h, uint64_t launches[4]);
