@@ -14,6 +14,7 @@
 #include "contraction.h"
 #include "einsum.h"
 #include "jit.h"
+#include "handle.h"
 #include "kernels.h"
 
 namespace es {
@@ -25,32 +26,7 @@ void set_last_error(std::string const& msg)
     g_last_error = msg;
 }
 
-struct built_kernel_t {
-    einsum_t                     e; // merged form
-    std::string                  kind;
-    // generated (JIT) kernels
-    plan_t                       plan;
-    std::shared_ptr<module_t>    module;
-    std::vector<void*>           functions;
-    // scalar twin for pointers that are not 16-byte aligned, built on first use
-    std::unique_ptr<plan_t>      scalar_plan;
-    std::shared_ptr<module_t>    scalar_module;
-    std::vector<void*>           scalar_functions;
-    // tensor-core contraction
-    std::unique_ptr<contraction_plan_t> contraction;
-    uint64_t                     workspace_bytes = 0;
-};
-
 } // namespace es
-
-struct es_b200 {
-    int                                              device = 0;
-    int                                              f32_policy = ES_F32_3XTF32;
-    std::mutex                                       build_mutex;
-    std::map<std::string, uint64_t>                  by_key;
-    std::vector<std::unique_ptr<es::built_kernel_t>> kernels;
-    std::atomic<uint64_t>                            counters[4];
-};
 
 namespace {
 
