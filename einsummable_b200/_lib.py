@@ -62,6 +62,7 @@ SYMBOLS = {
     "es_b200_kernel_info": (_i, [_vp, _u64, _cp, _i]),
     "es_b200_describe": (_i, [_desc_p, _i, _cp, _i]),
     "es_b200_touch_simplify": (_i, [_td_p, _i, _td_p, ctypes.POINTER(_i)]),
+    "es_b200_rowsum_f32_noalloc": (_i, [_vp, _vp, _vp, _u64, _u64, _vp]),
     "es_b200_device_status": (_i, [_vp, ctypes.POINTER(ctypes.c_uint)]),
     "es_b200_query_counters": (_i, [_vp, ctypes.POINTER(_u64)]),
     "es_b200_last_error": (_cp, []),

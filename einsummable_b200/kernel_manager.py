@@ -162,6 +162,17 @@ class kernel_manager_t:
         _lib.check(self._lib.es_b200_move(
             self._h, src_device, _ptr(src), self.device, _ptr(dst), int(nbytes), _stream(stream)))
 
+    def rowsum_f32_noalloc(self, stream, out, inn, rows, cols):
+        """out[a] = sum_b inn[a,b] for f32 without any device allocation: the
+        scratch of the two-pass reduction is a fixed array inside the library
+        (rows <= 65536).  Meant for callers that cannot call cudaMalloc -- all
+        device memory already belongs to the memgraph buffer, or the event loop
+        cannot take cudaMalloc's device synchronisation.  Calls on one device
+        share that array, so launches that may overlap on the GPU race; make the
+        first call on a device before starting a stream capture."""
+        _lib.check(self._lib.es_b200_rowsum_f32_noalloc(
+            self._h, _ptr(inn), _ptr(out), int(rows), int(cols), _stream(stream)))
+
     def device_status(self):
         """Synchronises and returns the tensor-core kernels' error word (0 = fine)."""
         w = ctypes.c_uint(0)

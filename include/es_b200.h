@@ -196,6 +196,28 @@ int es_b200_touch_simplify(const es_touchdim_t* dims,
                            es_touchdim_t*       dims_out,
                            int*                 out_rank);
 
+/* Row sum of a dense f32 matrix, out[a] = sum_b in[a,b] (the "ab->a" castable-add
+ * einsummable), for callers that cannot allocate device memory: engines that
+ * have already given all of the GPU's memory to one memgraph buffer (a later
+ * cudaMalloc has nothing to return), and event loops that must not take
+ * cudaMalloc's device-wide synchronisation.  It has no counterpart in the
+ * reference, whose workspace manager allocates on demand.
+ * The partial sums of the two-pass reduction live in a fixed array inside the
+ * library (65536 floats = 256 KiB per GPU, held from load to exit), so:
+ *   - rows must be <= 65536, otherwise ES_NOT_SUPPORTED (use
+ *     es_b200_launch_einsummable with a workspace instead);
+ *   - the first call on a device looks up the array's address; issue it before
+ *     any stream capture begins;
+ *   - all calls on one device share the array: calls whose kernels can overlap
+ *     on that GPU race.  Nothing needs clearing between calls.
+ * Never calls cudaMalloc/cudaFree or any allocating routine. */
+int es_b200_rowsum_f32_noalloc(es_b200_t*   h,
+                               const float* in,
+                               float*       out,
+                               uint64_t     rows,
+                               uint64_t     cols,
+                               void*        stream);
+
 /* Synchronises the device and returns (and clears) the error word of the
  * tensor-core kernels: 0 = fine; nonzero = a bounded wait inside a kernel gave
  * up (1 producer, 2/3 MMA issuer, 4 epilogue) and that launch's output is not
