@@ -432,6 +432,56 @@ def other_classes(km, dev, stream):
     return out
 
 
+def run_only(args):
+    """One kernel class alone, `steps` launches after `warmup`, CUDA events."""
+    import torch
+    import einsummable_b200 as es
+    from einsummable_b200 import einsummable_t, scalarop_t as S, touch_t
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    km = es.kernel_manager_t(0)
+    stream = torch.cuda.current_stream(dev)
+    mul16 = S.make_mul("f16")
+    if args.only.startswith("gemm") or args.only.startswith("attn"):
+        if args.only == "gemm_qkv":
+            e = einsummable_t.from_matmul_st(2048, 4096, 4096, "f16")
+        elif args.only == "gemm_ffn":
+            e = einsummable_t.from_matmul_st(2048, 4096, 11008, "f16")
+        elif args.only == "gemm_f32":
+            e = einsummable_t.from_matmul(2048, 2048, 2048, "f32")
+        elif args.only == "attn_scores":
+            e = einsummable_t.from_str("acbe,adbe->abcd", dict(a=4, b=32, c=512, d=512, e=128), mul16, "add")
+        else:
+            e = einsummable_t.from_str("abce,aebd->abcd", dict(a=4, b=32, c=512, d=128, e=512), mul16, "add")
+        dt = torch.float16 if e.out_dtype() == "f16" else torch.float32
+        ws = km.build(e)
+        ins = [torch.randn(int(np.prod(e.inn_shape(k))), dtype=dt, device=dev) for k in range(2)]
+        out = torch.empty(e.out_nelem(), dtype=dt, device=dev)
+        w = torch.empty(max(ws, 16), dtype=torch.uint8, device=dev)
+        fn = lambda: km(e, stream, out, ins, (w, ws) if ws else None)
+        work, unit = 2.0 * float(np.prod(e.join_shape)), "TFLOP/s"
+        nbytes = sum(t.numel() * t.element_size() for t in ins + [out])
+        info = km.kernel_info(e)
+    elif args.only == "touch":
+        sel = [(16, 32, 0, 16, 16), (256, 512, 0, 256, 256), (16, 32, 0, 16, 16), (64, 128, 0, 64, 64)]
+        src = torch.randn(16 * 256 * 16 * 64, dtype=torch.float16, device=dev)
+        dst = torch.zeros(32 * 512 * 32 * 128, dtype=torch.float16, device=dev)
+        t = touch_t(sel, "add", "f16")
+        fn = lambda: km(t, stream, dst, src)
+        work, unit, nbytes, info = 3.0 * src.numel() * 2, "GB/s", 3 * src.numel() * 2, "touch add f16 C3 p=2"
+    else:
+        e = einsummable_t([32, 32, 512, 128], [[0, 2, 1, 3]], 4, S.make_identity("f16"))
+        km.build(e)
+        src = torch.randn(32 * 512 * 32 * 128, dtype=torch.float16, device=dev)
+        dst = torch.empty_like(src)
+        fn = lambda: km(e, stream, dst, [src])
+        work, unit, nbytes, info = 2.0 * src.numel() * 2, "GB/s", 2 * src.numel() * 2, km.kernel_info(e)
+    ms = time_launches(fn, stream, iters=args.steps, warm=args.warmup)
+    scale = 1e12 if unit == "TFLOP/s" else 1e9
+    print(json.dumps({"only": args.only, "ms": ms, "value": work / (ms * 1e-3) / scale, "unit": unit,
+                      "bytes": nbytes, "device_status": km.device_status(), "info": info}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -441,12 +491,17 @@ def main():
     ap.add_argument("--rows", type=int, default=ROWS,
                     help="rows of the [rows, 11008] tensors (default: the full C2 workload); "
                          "smaller values are for profiler captures only")
+    ap.add_argument("--only", default=None,
+                    choices=["gemm_qkv", "gemm_ffn", "gemm_f32", "attn_scores", "attn_pv", "touch", "permute"],
+                    help="time one other kernel class alone (profiler captures); prints its own small JSON line")
     ap.add_argument("--kernels-only", action="store_true",
                     help="skip the end-to-end, other-class and CPU-baseline legs (profiler captures)")
     args = ap.parse_args()
     set_rows(args.rows)
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.only:
+        run_only(args)
     else:
         run_gpu(args)
 

@@ -289,7 +289,7 @@ plan_t gen_ew_vec(ctx_t const& c, bool force_scalar)
 
     src_t s;
     s.raw(k_preamble);
-    c.signature(s, "es_k0", B);
+    c.signature(s, "es_ew_vec_k0", B);
     s.add("  const %s NV = %s;", c.idx(), c.lit(NV).c_str());
     s.add("  const %s v0 = (%s)blockIdx.x * %du + threadIdx.x;", c.idx(), c.idx(), B * U);
     for (int k = 0; k != c.n; ++k) {
@@ -339,7 +339,7 @@ plan_t gen_ew_vec(ctx_t const& c, bool force_scalar)
     p.vec = V;
     p.align = V > 1 ? 16 : 1;
     launch_t l;
-    l.entry = "es_k0";
+    l.entry = "es_ew_vec_k0";
     l.block = B;
     uint64_t grid = (NV + uint64_t(B) * U - 1) / (uint64_t(B) * U);
     if (grid > 0x7fffffffull) fail(ES_NOT_SUPPORTED, "elementwise grid too large");
@@ -358,7 +358,7 @@ plan_t gen_ew_gather(ctx_t const& c)
     int const       B = 256;
     src_t           s;
     s.raw(k_preamble);
-    c.signature(s, "es_k0", B);
+    c.signature(s, "es_ew_gather_k0", B);
     s.add("  const %s ee = (%s)blockIdx.x * %du + threadIdx.x;", c.idx(), c.idx(), B);
     s.add("  if (ee >= %s) return;", c.lit(N).c_str());
     c.decompose(s, "ee", 0, c.r, "  ");
@@ -375,7 +375,7 @@ plan_t gen_ew_gather(ctx_t const& c)
     p.kind = "ew_gather";
     p.source = s.s;
     launch_t l;
-    l.entry = "es_k0";
+    l.entry = "es_ew_gather_k0";
     l.block = B;
     uint64_t grid = (N + B - 1) / B;
     if (grid > 0x7fffffffull) fail(ES_NOT_SUPPORTED, "elementwise grid too large");
@@ -401,7 +401,7 @@ plan_t gen_ew_transpose(ctx_t const& c, int P)
     uint64_t        outer = e.out_nelem() / (JL * JP);
     src_t           s;
     s.raw(k_preamble);
-    c.signature(s, "es_k0", 256);
+    c.signature(s, "es_ew_transpose_k0", 256);
     for (int k = 0; k != c.n; ++k) {
         if (c.st[k][P] == 1)
             s.add("  __shared__ %s tile%d[32][33];", compute_type(e.inn_dtype(k)), k);
@@ -465,7 +465,7 @@ plan_t gen_ew_transpose(ctx_t const& c, int P)
     p.kind = "ew_transpose";
     p.source = s.s;
     launch_t l;
-    l.entry = "es_k0";
+    l.entry = "es_ew_transpose_k0";
     l.block = 256;
     uint64_t grid = tl * tp * outer;
     if (grid > 0x7fffffffull) fail(ES_NOT_SUPPORTED, "transpose grid too large");
@@ -524,7 +524,7 @@ plan_t gen_red_row(ctx_t const& c, bool force_scalar)
 
     src_t s;
     s.raw(k_preamble);
-    c.signature(s, "es_k0", 256);
+    c.signature(s, "es_red_row_k0", 256);
     if (G == 32) {
         s.add("  const int lane = threadIdx.x & 31;");
         s.add("  const %s row = (%s)blockIdx.x * %du + (threadIdx.x >> 5);", c.idx(), c.idx(),
@@ -602,7 +602,7 @@ plan_t gen_red_row(ctx_t const& c, bool force_scalar)
     p.vec = V;
     p.align = V > 1 ? 16 : 1;
     launch_t l;
-    l.entry = "es_k0";
+    l.entry = "es_red_row_k0";
     l.block = 256;
     uint64_t grid = G == 32 ? (NO + rows_per_cta - 1) / rows_per_cta : NO * S;
     if (grid > 0x7fffffffull) fail(ES_NOT_SUPPORTED, "reduction grid too large");
@@ -611,7 +611,7 @@ plan_t gen_red_row(ctx_t const& c, bool force_scalar)
 
     if (S > 1) {
         // second pass: one thread per output combines the S partials
-        c.signature(s, "es_k1", 256);
+        c.signature(s, "es_red_row_k1", 256);
         s.add("  const %s row = (%s)blockIdx.x * 256u + threadIdx.x;", c.idx(), c.idx());
         s.add("  if (row >= %s) return;", c.lit(NO).c_str());
         s.add("  const %s* part = (const %s*)ws_ + row * %s;", ct, ct, c.lit(S).c_str());
@@ -621,7 +621,7 @@ plan_t gen_red_row(ctx_t const& c, bool force_scalar)
         s.add("  st_%s<1>(out + row, &r);", dt_suffix(od));
         s.add("}");
         launch_t l2;
-        l2.entry = "es_k1";
+        l2.entry = "es_red_row_k1";
         l2.block = 256;
         l2.grid = (uint32_t)((NO + 255) / 256);
         p.launches.push_back(l2);
@@ -656,7 +656,7 @@ plan_t gen_red_col(ctx_t const& c)
 
     src_t s;
     s.raw(k_preamble);
-    c.signature(s, "es_k0", 256);
+    c.signature(s, "es_red_col_k0", 256);
     s.add("  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;");
     s.add("  const %s cb = blockIdx.x %% %s;", c.idx(), c.lit(col_blocks).c_str());
     s.add("  const %s chunk = blockIdx.x / %s;", c.idx(), c.lit(col_blocks).c_str());
@@ -706,14 +706,14 @@ plan_t gen_red_col(ctx_t const& c)
     plan_t p;
     p.kind = S == 1 ? "red_col" : "red_col_split";
     launch_t l;
-    l.entry = "es_k0";
+    l.entry = "es_red_col_k0";
     l.block = 256;
     uint64_t grid = col_blocks * S;
     if (grid > 0x7fffffffull) fail(ES_NOT_SUPPORTED, "reduction grid too large");
     l.grid = (uint32_t)grid;
     p.launches.push_back(l);
     if (S > 1) {
-        c.signature(s, "es_k1", 256);
+        c.signature(s, "es_red_col_k1", 256);
         s.add("  const %s row = (%s)blockIdx.x * 256u + threadIdx.x;", c.idx(), c.idx());
         s.add("  if (row >= %s) return;", c.lit(NO).c_str());
         s.add("  const %s* part = (const %s*)ws_ + row * %s;", ct, ct, c.lit(S).c_str());
@@ -723,7 +723,7 @@ plan_t gen_red_col(ctx_t const& c)
         s.add("  st_%s<1>(out + row, &r);", dt_suffix(od));
         s.add("}");
         launch_t l2;
-        l2.entry = "es_k1";
+        l2.entry = "es_red_col_k1";
         l2.block = 256;
         l2.grid = (uint32_t)((NO + 255) / 256);
         p.launches.push_back(l2);

@@ -40,9 +40,10 @@ constexpr int      BM = 128;
 constexpr int      NUM_THREADS = 192;
 constexpr int      MAX_STAGES = 8;
 constexpr int      MAX_LOOP_MODES = 6;
+constexpr uint32_t STAGING_BYTES = 4 * 2 * 4096;
 constexpr uint64_t WAIT_LIMIT_CYCLES = 4000000000ull; // ~2 s at 2 GHz
 
-enum src_kind_t : int8_t { SRC_ZERO = 0, SRC_MN_TILE = 1, SRC_K_BLOCK = 2, SRC_OUTER0 = 8, SRC_KOUTER0 = 24 };
+enum src_kind_t : int8_t { SRC_ZERO = 0, SRC_MN_TILE = 1, SRC_K_BLOCK = 2, SRC_N_TILE = 3, SRC_OUTER0 = 8, SRC_KOUTER0 = 24 };
 
 struct operand_t {
     uint32_t n_boxes;       // TMA copies per stage (per term)
@@ -77,6 +78,12 @@ struct alignas(64) tc_params_t {
     uint32_t    out_is_f32;
     uint32_t    n_terms;
     uint32_t    k_chunk;    // k-iterations accumulated in TMEM before the epilogue takes the partial sum
+    // epilogue through TMA stores (output's innermost mode is the N mode and its layout is TMA-describable)
+    CUtensorMap tm_out;
+    uint32_t    out_tma;
+    int32_t     out_nd;
+    int8_t      out_src[8]; // SRC_MN_TILE (row), SRC_N_TILE (column) or SRC_OUTER0+j per TMA dim
+    uint32_t    staging_offset; // byte offset of the epilogue staging buffers inside dynamic smem
 };
 
 __device__ unsigned int g_tc_error; // nonzero = a bounded wait expired (code, see below)
@@ -163,6 +170,30 @@ __device__ __forceinline__ void tma_load(uint32_t dst, CUtensorMap const* tm, ui
     }
 }
 
+__device__ __forceinline__ void tma_store(CUtensorMap const* tm, uint32_t src, int nd, int const* c)
+{
+    uint64_t desc = reinterpret_cast<uint64_t>(tm);
+    switch (nd) {
+        case 2:
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                         ::"l"(desc), "r"(src), "r"(c[0]), "r"(c[1]) : "memory");
+            break;
+        case 3:
+            asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                         ::"l"(desc), "r"(src), "r"(c[0]), "r"(c[1]), "r"(c[2]) : "memory");
+            break;
+        case 4:
+            asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                         ::"l"(desc), "r"(src), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]) : "memory");
+            break;
+        default:
+            asm volatile("cp.async.bulk.tensor.5d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5, %6}], [%1];"
+                         ::"l"(desc), "r"(src), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]), "r"(c[4]) : "memory");
+            break;
+    }
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
 __device__ __forceinline__ void tc_fence_before()
 {
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -232,35 +263,94 @@ struct ctrl_t {
     uint32_t abort_flag;
 };
 
+// All index arrays below are only ever indexed by compile-time constants inside
+// fully unrolled loops, so they live in registers: a version with run-time
+// indexing put them in local memory and the dependent local-memory round trips
+// (~2300 cycles per k-block) made the producer, not the tensor pipe, the bottleneck.
 __device__ __forceinline__ void
-decode_tile(tc_params_t const& p, uint32_t tile, uint32_t& m_tile, uint32_t& n_tile, uint32_t* outer)
+decode_tile(tc_params_t const& p, uint32_t tile, uint32_t& m_tile, uint32_t& n_tile, uint32_t (&outer)[MAX_LOOP_MODES])
 {
     m_tile = tile % p.m_tiles;
     uint32_t t = tile / p.m_tiles;
     n_tile = t % p.n_tiles;
     t /= p.n_tiles;
-    for (int j = (int)p.n_outer - 1; j >= 0; --j) {
-        outer[j] = t % p.outer_extent[j];
-        t /= p.outer_extent[j];
+#pragma unroll
+    for (int j = MAX_LOOP_MODES - 1; j >= 0; --j) {
+        if (j < (int)p.n_outer) {
+            outer[j] = t % p.outer_extent[j];
+            t /= p.outer_extent[j];
+        } else {
+            outer[j] = 0;
+        }
     }
 }
 
-__device__ __forceinline__ void fill_coords(operand_t const& o,
-                                            uint32_t         mn_tile_elems,
-                                            uint32_t         k_elems,
-                                            uint32_t const*  outer,
-                                            uint32_t const*  kouter,
-                                            int*             c)
+__device__ __forceinline__ uint32_t pick6(uint32_t const (&v)[MAX_LOOP_MODES], int i)
+{
+    uint32_t r = v[0];
+#pragma unroll
+    for (int j = 1; j < MAX_LOOP_MODES; ++j) r = (i == j) ? v[j] : r;
+    return r;
+}
+
+__device__ __forceinline__ uint32_t pick4(uint32_t const (&v)[4], int i)
+{
+    uint32_t r = v[0];
+#pragma unroll
+    for (int j = 1; j < 4; ++j) r = (i == j) ? v[j] : r;
+    return r;
+}
+
+// Per-tile part of an operand's TMA coordinates (tile origin and outer modes).
+__device__ __forceinline__ void
+tile_coords(operand_t const& o, uint32_t mn_elems, uint32_t const (&outer)[MAX_LOOP_MODES], int (&base)[5])
 {
 #pragma unroll
     for (int d = 0; d < 5; ++d) {
-        int8_t s = o.src[d];
-        int    v = 0;
-        if (s == SRC_MN_TILE) v = (int)mn_tile_elems;
-        else if (s == SRC_K_BLOCK) v = (int)k_elems;
-        else if (s >= SRC_KOUTER0) v = (int)kouter[s - SRC_KOUTER0];
-        else if (s >= SRC_OUTER0) v = (int)outer[s - SRC_OUTER0];
+        int s = o.src[d];
+        int v = 0;
+        if (s == SRC_MN_TILE) v = (int)mn_elems;
+        else if (s >= SRC_OUTER0 && s < SRC_KOUTER0) v = (int)pick6(outer, s - SRC_OUTER0);
+        base[d] = v;
+    }
+}
+
+// Full coordinates of an operand for (tile, k block, outer-K indices).
+__device__ __forceinline__ void full_coords(operand_t const& o,
+                                            int const (&base)[5],
+                                            uint32_t k_elems,
+                                            uint32_t const (&kouter)[4],
+                                            int (&c)[5])
+{
+#pragma unroll
+    for (int d = 0; d < 5; ++d) {
+        int s = o.src[d];
+        int v = base[d];
+        if (s == SRC_K_BLOCK) v = (int)k_elems;
+        else if (s >= SRC_KOUTER0) v = (int)pick4(kouter, s - SRC_KOUTER0);
         c[d] = v;
+    }
+}
+
+// Issues the copies of one operand for one k-iteration from ready coordinates.
+__device__ __forceinline__ void issue_operand(operand_t const&   o,
+                                              CUtensorMap const* tm,
+                                              uint32_t           n_terms,
+                                              int const (&c)[5],
+                                              uint32_t dst,
+                                              uint32_t bar)
+{
+    if (n_terms == 1 && o.n_boxes == 1) {
+        tma_load(dst, tm, bar, o.nd, c);
+        return;
+    }
+    for (uint32_t t = 0; t < n_terms; ++t) {
+        for (uint32_t bx = 0; bx < o.n_boxes; ++bx) {
+            int cc[5];
+#pragma unroll
+            for (int d = 0; d < 5; ++d) cc[d] = c[d] + (d == o.box_dim ? (int)(bx * o.box_step) : 0);
+            tma_load(dst + t * o.tile_bytes + bx * o.box_bytes, &tm[t], bar, o.nd, cc);
+        }
     }
 }
 
@@ -271,7 +361,8 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment for the 128B swizzle atoms
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    ctrl_t*  ctrl = reinterpret_cast<ctrl_t*>(smem + (size_t)p.stages * p.stage_bytes);
+    // layout: [stage ring][epilogue staging, 4 warps x 2 x 4 KiB][control block]
+    ctrl_t*  ctrl = reinterpret_cast<ctrl_t*>(smem + (size_t)p.stages * p.stage_bytes + STAGING_BYTES);
     volatile uint32_t* abort_flag = &ctrl->abort_flag;
 
     int const warp = threadIdx.x >> 5;
@@ -307,42 +398,45 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            uint32_t it = 0;
+            uint32_t stage = 0, phase = 0;
             bool     ok = true;
             for (uint32_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
                 uint32_t m_tile, n_tile, outer[MAX_LOOP_MODES];
                 decode_tile(p, tile, m_tile, n_tile, outer);
-                for (uint32_t ki = 0; ki < k_iters; ++ki, ++it) {
-                    uint32_t s = it % p.stages, ph = (it / p.stages) & 1;
-                    if (!mbar_wait(smem_u32(&ctrl->empty[s]), ph ^ 1, abort_flag, 1)) { ok = false; break; }
-                    uint32_t kb = ki % p.k_blocks, ko = ki / p.k_blocks;
-                    uint32_t kouter[4] = {0, 0, 0, 0};
-                    for (int j = (int)p.n_kouter - 1; j >= 0; --j) {
-                        kouter[j] = ko % p.kouter_extent[j];
-                        ko /= p.kouter_extent[j];
-                    }
-                    uint32_t bar = smem_u32(&ctrl->full[s]);
+                int base_a[5], base_b[5];
+                tile_coords(p.a, m_tile * BM, outer, base_a);
+                tile_coords(p.b, n_tile * p.bn, outer, base_b);
+                // odometer over (outer K modes ..., k block): the last entry runs fastest
+                uint32_t kb = 0, kouter[4] = {0, 0, 0, 0};
+                int      ca[5], cb[5];
+                full_coords(p.a, base_a, 0, kouter, ca);
+                full_coords(p.b, base_b, 0, kouter, cb);
+                for (uint32_t ki = 0; ki < k_iters; ++ki) {
+                    if (!mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, 1)) { ok = false; break; }
+                    uint32_t bar = smem_u32(&ctrl->full[stage]);
                     mbar_arrive_expect_tx(bar, p.stage_bytes);
-                    uint32_t stage_base = smem_base + s * p.stage_bytes;
-                    int      c[5];
-                    fill_coords(p.a, m_tile * BM, kb * p.bk_elems, outer, kouter, c);
-                    for (uint32_t t = 0; t < p.n_terms; ++t) {
-                        int c0 = c[p.a.box_dim];
-                        for (uint32_t bx = 0; bx < p.a.n_boxes; ++bx) {
-                            c[p.a.box_dim] = c0 + (int)(bx * p.a.box_step);
-                            tma_load(stage_base + t * term_a_bytes + bx * p.a.box_bytes, &p.tm_a[t], bar, p.a.nd, c);
+                    uint32_t stage_base = smem_base + stage * p.stage_bytes;
+                    issue_operand(p.a, p.tm_a, p.n_terms, ca, stage_base, bar);
+                    issue_operand(p.b, p.tm_b, p.n_terms, cb, stage_base + a_region, bar);
+                    if (++stage == p.stages) { stage = 0; phase ^= 1; }
+                    if (++kb == p.k_blocks) {
+                        kb = 0;
+                        bool carry = true;
+#pragma unroll
+                        for (int j = 3; j >= 0; --j) {
+                            if (carry && j < (int)p.n_kouter) {
+                                if (++kouter[j] == p.kouter_extent[j]) kouter[j] = 0;
+                                else carry = false;
+                            }
                         }
-                        c[p.a.box_dim] = c0;
-                    }
-                    fill_coords(p.b, n_tile * p.bn, kb * p.bk_elems, outer, kouter, c);
-                    for (uint32_t t = 0; t < p.n_terms; ++t) {
-                        int c0 = c[p.b.box_dim];
-                        for (uint32_t bx = 0; bx < p.b.n_boxes; ++bx) {
-                            c[p.b.box_dim] = c0 + (int)(bx * p.b.box_step);
-                            tma_load(stage_base + a_region + t * term_b_bytes + bx * p.b.box_bytes, &p.tm_b[t], bar,
-                                     p.b.nd, c);
+                        full_coords(p.a, base_a, 0, kouter, ca);
+                        full_coords(p.b, base_b, 0, kouter, cb);
+                    } else {
+#pragma unroll
+                        for (int d = 0; d < 5; ++d) {
+                            ca[d] += (p.a.src[d] == SRC_K_BLOCK) ? (int)p.bk_elems : 0;
+                            cb[d] += (p.b.src[d] == SRC_K_BLOCK) ? (int)p.bk_elems : 0;
                         }
-                        c[p.b.box_dim] = c0;
                     }
                 }
             }
@@ -350,36 +444,40 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            uint32_t it = 0, q = 0; // q counts accumulator uses (one per k-chunk)
+            uint32_t stage = 0, phase = 0, q = 0; // q counts accumulator uses (one per k-chunk)
             bool     ok = true;
+            constexpr uint32_t NT = PROMOTE ? 3u : 1u; // MMAs per k-step: (lo*hi, hi*lo, hi*hi) or one
             uint64_t const a_hi = ((uint64_t)p.a.desc_hi << 32) | ((uint64_t)p.a.desc_lbo << 16);
             uint64_t const b_hi = ((uint64_t)p.b.desc_hi << 32) | ((uint64_t)p.b.desc_lbo << 16);
-            uint32_t const k_steps = 4; // a 128-byte swizzle row holds four MMA k-steps
+            // descriptor start-address fields are in 16-byte units; shared addresses stay below 2^18
+            uint32_t const a_kstep = p.a.k_step_bytes >> 4, b_kstep = p.b.k_step_bytes >> 4;
+            uint32_t const a_term = term_a_bytes >> 4, b_term = term_b_bytes >> 4;
+            uint32_t const idesc = p.idesc, stages = p.stages, stage_units = p.stage_bytes >> 4;
+            uint32_t const a_region_units = a_region >> 4, base_units = smem_base >> 4;
             for (uint32_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
                 for (uint32_t ki0 = 0; ki0 < k_iters && ok; ki0 += p.k_chunk, ++q) {
                     uint32_t acc = q & 1, acc_ph = (q >> 1) & 1;
                     if (!mbar_wait(smem_u32(&ctrl->tmem_empty[acc]), acc_ph ^ 1, abort_flag, 2)) { ok = false; break; }
                     tc_fence_after();
-                    uint32_t tmem_d = tmem_base + acc * p.bn;
-                    uint32_t first = 1;
-                    uint32_t ki1 = min(ki0 + p.k_chunk, k_iters);
-                    for (uint32_t ki = ki0; ki < ki1; ++ki, ++it) {
-                        uint32_t s = it % p.stages, ph = (it / p.stages) & 1;
-                        if (!mbar_wait(smem_u32(&ctrl->full[s]), ph, abort_flag, 3)) { ok = false; break; }
+                    uint32_t const tmem_d = tmem_base + acc * p.bn;
+                    uint32_t const ki1 = min(ki0 + p.k_chunk, k_iters);
+                    for (uint32_t ki = ki0; ki < ki1; ++ki) {
+                        uint32_t const s = stage;
+                        if (!mbar_wait(smem_u32(&ctrl->full[s]), phase, abort_flag, 3)) { ok = false; break; }
+                        if (++stage == stages) { stage = 0; phase ^= 1; }
                         tc_fence_after();
-                        uint32_t a_base = smem_base + s * p.stage_bytes;
-                        uint32_t b_base = a_base + a_region;
-                        for (uint32_t ks = 0; ks < k_steps; ++ks) {
-                            // with hi/lo operand copies: lo*hi, hi*lo, then hi*hi
-                            for (uint32_t t = 0; t < (p.n_terms == 1 ? 1u : 3u); ++t) {
-                                uint32_t ta = (p.n_terms == 1) ? 0 : (t == 0 ? 1 : 0);
-                                uint32_t tb = (p.n_terms == 1) ? 0 : (t == 1 ? 1 : 0);
-                                uint32_t aa = a_base + ta * term_a_bytes + ks * p.a.k_step_bytes;
-                                uint32_t bb = b_base + tb * term_b_bytes + ks * p.b.k_step_bytes;
-                                uint64_t da = a_hi | (uint64_t)((aa >> 4) & 0x3fff);
-                                uint64_t db = b_hi | (uint64_t)((bb >> 4) & 0x3fff);
-                                umma<KIND>(tmem_d, da, db, p.idesc, first ? 0u : 1u);
-                                first = 0;
+                        uint32_t const a0 = base_units + s * stage_units;
+                        uint32_t const b0 = a0 + a_region_units;
+                        uint32_t const keep = ki != ki0; // the first MMA of a chunk overwrites the accumulator
+#pragma unroll
+                        for (uint32_t ks = 0; ks < 4; ++ks) { // a 128-byte swizzle row holds four MMA k-steps
+#pragma unroll
+                            for (uint32_t t = 0; t < NT; ++t) {
+                                uint32_t const ta = (NT == 1) ? 0 : (t == 0 ? 1 : 0);
+                                uint32_t const tb = (NT == 1) ? 0 : (t == 1 ? 1 : 0);
+                                uint64_t const da = a_hi | (uint64_t)(a0 + ta * a_term + ks * a_kstep);
+                                uint64_t const db = b_hi | (uint64_t)(b0 + tb * b_term + ks * b_kstep);
+                                umma<KIND>(tmem_d, da, db, idesc, (ks == 0 && t == 0) ? keep : 1u);
                             }
                         }
                         umma_commit(smem_u32(&ctrl->empty[s])); // frees the smem stage when these MMAs retire
@@ -391,67 +489,132 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
     } else {
         // ------------------------------------------------------------ epilogue (warps 2..5)
         uint32_t const quarter = warp & 3; // TMEM lanes 32*quarter .. +31 belong to this warp
-        uint32_t q = 0;
+        uint32_t q = 0, store_seq = 0;
         bool     ok = true;
         // PROMOTE: partial sums of each k-chunk are added in registers with
         // round-to-nearest f32 adds.  The tensor core's own accumulation truncates,
         // which over hundreds of MMAs biases a long f32 sum beyond 1e-5.
         float accr[PROMOTE ? 4 : 1][32];
+        // A "piece" is 128 bytes of one output row: 64 f16 or 32 f32 columns.
+        uint32_t const piece_cols = p.out_is_f32 ? 32u : 64u;
+        uint32_t const pieces = p.bn / piece_cols;
+        // per-warp staging for TMA stores: 2 buffers of 32 rows x 128 bytes, 128B-swizzled
+        uint32_t const stage_buf = smem_base + p.staging_offset + (uint32_t)(warp - 2) * 8192u;
         for (uint32_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
             uint32_t m_tile, n_tile, outer[MAX_LOOP_MODES];
             decode_tile(p, tile, m_tile, n_tile, outer);
             int64_t base = 0;
-            for (uint32_t j = 0; j < p.n_outer; ++j) base += (int64_t)outer[j] * p.outer_out_stride[j];
-            uint32_t m = m_tile * BM + quarter * 32 + lane;
-            uint32_t n0 = n_tile * p.bn;
+#pragma unroll
+            for (int j = 0; j < MAX_LOOP_MODES; ++j)
+                if (j < (int)p.n_outer) base += (int64_t)outer[j] * p.outer_out_stride[j];
+            uint32_t const m_warp = m_tile * BM + quarter * 32;
+            uint32_t const m = m_warp + lane;
+            uint32_t const n0 = n_tile * p.bn;
+            int oc[5]; // TMA store coordinates; the column entry is filled per piece
+#pragma unroll
+            for (int d = 0; d < 5; ++d) {
+                int sk = p.out_src[d];
+                oc[d] = sk == SRC_MN_TILE ? (int)m_warp
+                        : (sk >= SRC_OUTER0 ? (int)pick6(outer, sk - SRC_OUTER0) : 0);
+            }
             for (uint32_t ki0 = 0; ki0 < k_iters && ok; ki0 += p.k_chunk, ++q) {
                 uint32_t acc = q & 1, acc_ph = (q >> 1) & 1;
                 bool const first_chunk = ki0 == 0, last_chunk = ki0 + p.k_chunk >= k_iters;
                 if (!mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_ph, abort_flag, 4)) { ok = false; break; }
                 tc_fence_after();
+                uint32_t const trow = tmem_base + ((quarter * 32u) << 16) + acc * p.bn;
+                for (uint32_t pc = 0; pc < pieces; ++pc) {
+                    uint4 w[8]; // this lane's 128 bytes of the piece, in the output dtype
+                    if (p.out_is_f32) {
+                        uint32_t r[32];
+                        tmem_ld32(trow + pc * 32, r);
+                        if constexpr (PROMOTE) {
 #pragma unroll
-                for (uint32_t ch = 0; ch < (PROMOTE ? 4u : 8u); ++ch) {
-                    if (ch * 32 >= p.bn) break;
-                    uint32_t r[32];
-                    tmem_ld32(tmem_base + ((quarter * 32u) << 16) + acc * p.bn + ch * 32, r);
-                    if constexpr (PROMOTE) {
+                            for (int j = 0; j < 32; ++j) {
+                                float v = __uint_as_float(r[j]);
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            float v = __uint_as_float(r[j]);
-                            accr[ch][j] = first_chunk ? v : __fadd_rn(accr[ch][j], v);
-                            r[j] = __float_as_uint(accr[ch][j]);
+                                for (int c4 = 0; c4 < 4; ++c4) {
+                                    if ((int)pc == c4) {
+                                        accr[c4][j] = first_chunk ? v : __fadd_rn(accr[c4][j], v);
+                                        r[j] = __float_as_uint(accr[c4][j]);
+                                    }
+                                }
+                            }
+                        }
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) w[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+                    } else {
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            uint32_t r[32];
+                            tmem_ld32(trow + pc * 64 + h * 32, r);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                w[h * 4 + j].x = pack_h2(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1]));
+                                w[h * 4 + j].y = pack_h2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+                                w[h * 4 + j].z = pack_h2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+                                w[h * 4 + j].w = pack_h2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+                            }
                         }
                     }
                     if (!last_chunk) continue;
-                    uint32_t n = n0 + ch * 32;
-                    if (m < p.m_extent && n < p.n_extent) {
+                    uint32_t const n = n0 + pc * piece_cols;
+                    if (p.out_tma) {
+                        // 32 rows x 128 bytes -> swizzled staging -> one TMA store per warp and piece
+                        // (rows / columns beyond the tensor are clipped by the TMA unit)
+                        uint32_t const buf = stage_buf + (store_seq & 1) * 4096u;
+                        if (store_seq >= 2) {
+                            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                            __syncwarp();
+                        }
+                        ++store_seq;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            uint32_t dst = buf + lane * 128u + ((uint32_t)(j ^ (lane & 7)) << 4);
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                                         ::"r"(dst), "r"(w[j].x), "r"(w[j].y), "r"(w[j].z), "r"(w[j].w) : "memory");
+                        }
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0 && n < p.n_extent && m_warp < p.m_extent) {
+                            int cc[5];
+#pragma unroll
+                            for (int d = 0; d < 5; ++d) cc[d] = (p.out_src[d] == SRC_N_TILE) ? (int)n : oc[d];
+                            tma_store(&p.tm_out, buf, p.out_nd, cc);
+                        }
+                    } else if (m < p.m_extent && n < p.n_extent) {
                         int64_t off = base + (int64_t)m * p.out_stride_m + (int64_t)n * p.out_stride_n;
-                        bool    full = n + 32 <= p.n_extent;
+                        bool    full = n + piece_cols <= p.n_extent;
                         if (p.out_is_f32) {
                             float* o = static_cast<float*>(out_) + off;
                             if (p.out_stride_n == 1 && full && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
 #pragma unroll
-                                for (int j = 0; j < 32; j += 4)
-                                    *reinterpret_cast<uint4*>(o + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+                                for (int j = 0; j < 8; ++j) *reinterpret_cast<uint4*>(o + 4 * j) = w[j];
                             } else {
-                                for (int j = 0; j < 32 && n + j < p.n_extent; ++j)
-                                    o[(int64_t)j * p.out_stride_n] = __uint_as_float(r[j]);
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) {
+                                    uint32_t const e4[4] = {w[j].x, w[j].y, w[j].z, w[j].w};
+#pragma unroll
+                                    for (int i = 0; i < 4; ++i)
+                                        if (n + 4 * j + i < p.n_extent)
+                                            o[(int64_t)(4 * j + i) * p.out_stride_n] = __uint_as_float(e4[i]);
+                                }
                             }
                         } else {
                             uint16_t* o = static_cast<uint16_t*>(out_) + off;
                             if (p.out_stride_n == 1 && full && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
 #pragma unroll
-                                for (int j = 0; j < 32; j += 8) {
-                                    uint4 w;
-                                    w.x = pack_h2(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
-                                    w.y = pack_h2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                                    w.z = pack_h2(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
-                                    w.w = pack_h2(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
-                                    *reinterpret_cast<uint4*>(o + j) = w;
-                                }
+                                for (int j = 0; j < 8; ++j) *reinterpret_cast<uint4*>(o + 8 * j) = w[j];
                             } else {
-                                for (int j = 0; j < 32 && n + j < p.n_extent; ++j)
-                                    o[(int64_t)j * p.out_stride_n] = f2h(__uint_as_float(r[j]));
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) {
+                                    uint32_t const e4[4] = {w[j].x, w[j].y, w[j].z, w[j].w};
+#pragma unroll
+                                    for (int i = 0; i < 8; ++i)
+                                        if (n + 8 * j + i < p.n_extent)
+                                            o[(int64_t)(8 * j + i) * p.out_stride_n] =
+                                                (uint16_t)((i & 1) ? (e4[i >> 1] >> 16) : (e4[i >> 1] & 0xffffu));
+                                }
                             }
                         }
                     }
@@ -461,6 +624,9 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
                 if (lane == 0) mbar_arrive(smem_u32(&ctrl->tmem_empty[acc]));
             }
         }
+        // all of this warp's stores must have read their staging buffers before smem goes away
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        __syncwarp();
     }
 
     // ------------------------------------------------------------------ teardown
@@ -509,7 +675,8 @@ struct tc_plan_t {
         uint64_t strides_bytes[4];
         uint32_t box[5];
         int      dtype; // CUtensorMapDataType
-    } ra, rb;
+    } ra, rb, rout;
+    int      out_tma;
     uint64_t a_elems, b_elems; // for the split pre-pass
     int      swap;             // the second input plays the A (128-row) role
     int      promote;          // chunked accumulation with register promotion (3xTF32)
@@ -730,7 +897,7 @@ bool plan_contraction(einsum_t const& e, int f32_policy, contraction_plan_t& pla
     setup(B, sb, b_mn, n_in, bn, p.b, tp.rb);
     // the K extent of one block must be the same for both operands: row_elems elements
     p.stage_bytes = (p.a.tile_bytes + p.b.tile_bytes) * p.n_terms;
-    uint32_t const smem_budget = 227 * 1024 - 1024 /*alignment*/ - (uint32_t)sizeof(ctrl_t) - 256;
+    uint32_t const smem_budget = 227 * 1024 - 1024 /*alignment*/ - STAGING_BYTES - (uint32_t)sizeof(ctrl_t) - 64;
     p.stages = std::min<uint32_t>(MAX_STAGES, smem_budget / p.stage_bytes);
     if (p.stages < 2) return false;
     p.tmem_cols = 2 * bn < 32 ? 32 : 2 * bn; // 128, 256 or 512: powers of two
@@ -741,7 +908,38 @@ bool plan_contraction(einsum_t const& e, int f32_policy, contraction_plan_t& pla
     uint32_t fmt = dt == ES_F16 ? 0u : 2u;
     p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
               ((bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-    tp.smem_bytes = p.stages * p.stage_bytes + (uint32_t)sizeof(ctrl_t) + 1024;
+    p.staging_offset = p.stages * p.stage_bytes;
+    tp.smem_bytes = p.stages * p.stage_bytes + STAGING_BYTES + (uint32_t)sizeof(ctrl_t) + 1024;
+    // epilogue through TMA stores when the output's innermost mode is the N mode and every other
+    // output stride is a multiple of 16 bytes
+    {
+        bool ok_tma = so[n_in] == 1 && e.out_rank <= 5 && e.out_rank >= 2;
+        for (int m = 0; m != e.out_rank; ++m)
+            if (m != n_in && (so[m] * esize) % 16) ok_tma = false;
+        tp.out_tma = ok_tma ? 1 : 0;
+        if (ok_tma) {
+            auto& rc = tp.rout;
+            rc.nd = e.out_rank;
+            p.out_nd = e.out_rank;
+            rc.dtype = dt == ES_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+            // output modes sorted by stride: the output is row-major over modes 0..out_rank-1
+            for (int d = 0; d != e.out_rank; ++d) {
+                int m = e.out_rank - 1 - d;
+                rc.dims[d] = e.join_shape[m];
+                if (d > 0) rc.strides_bytes[d - 1] = so[m] * esize;
+                rc.box[d] = 1;
+                if (m == n_in) {
+                    rc.box[d] = row_elems;
+                    p.out_src[d] = SRC_N_TILE;
+                } else if (m == m_in) {
+                    rc.box[d] = 32;
+                    p.out_src[d] = SRC_MN_TILE;
+                } else {
+                    p.out_src[d] = (int8_t)(SRC_OUTER0 + outer_idx[m]);
+                }
+            }
+        }
+    }
     tp.grid = std::min<uint32_t>(p.total_tiles, 148);
     tp.a_elems = e.inn_nelem(ia);
     tp.b_elems = e.inn_nelem(ib);
@@ -824,6 +1022,11 @@ void launch_contraction(contraction_plan_t const& plan,
         };
         stage(lhs, tp.a_perm, tp.a_elems, w, p.tm_a, tp.ra);
         stage(rhs, tp.b_perm, tp.b_elems, w + tp.ws_b_offset, p.tm_b, tp.rb);
+    }
+    p.out_tma = 0;
+    if (tp.out_tma && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+        encode_map(&p.tm_out, tp.rout, out);
+        p.out_tma = 1;
     }
     auto launch = [&](auto kernel, int slot) {
         static bool attr_set[3][64] = {};
