@@ -401,19 +401,31 @@ def other_classes(km, dev, stream):
     from einsummable_b200 import einsummable_t, scalarop_t as S, touch_t
     out = {}
     # LLaMA FFN w1: ij,kj->ik f16 2048 x 11008 x 4096
-    for name, (i, j, k) in {"ffn_w1 ij,kj->ik f16 2048x4096x11008": (2048, 4096, 11008),
-                            "qkv ij,kj->ik f16 2048x4096x4096": (2048, 4096, 4096)}.items():
-        e = einsummable_t.from_matmul_st(i, j, k, "f16")
+    mul16 = S.make_mul("f16")
+    specs = {
+        "ffn_w1 ij,kj->ik f16 2048x4096x11008": einsummable_t.from_matmul_st(2048, 4096, 11008, "f16"),
+        "qkv ij,kj->ik f16 2048x4096x4096": einsummable_t.from_matmul_st(2048, 4096, 4096, "f16"),
+        "C1 block ij,jk->ik f32 2048^3 (3xTF32)": einsummable_t.from_matmul(2048, 2048, 2048, "f32"),
+        "attn scores acbe,adbe->abcd f16 [4,32,512,512,128]": einsummable_t.from_str(
+            "acbe,adbe->abcd", dict(a=4, b=32, c=512, d=512, e=128), mul16, "add"),
+        "attn PV abce,aebd->abcd f16 [4,32,512,128,512]": einsummable_t.from_str(
+            "abce,aebd->abcd", dict(a=4, b=32, c=512, d=128, e=512), mul16, "add"),
+    }
+    for name, e in specs.items():
+        i, k, j = 0, 0, 0
         ws = km.build(e)
         if "contraction_tc" not in km.kernel_info(e):
             out[name] = {"kind": km.kernel_info(e).split("|")[0], "note": "SIMT fallback; not timed"}
             continue
-        a = torch.randn(i * j, dtype=torch.float16, device=dev)
-        b = torch.randn(k * j, dtype=torch.float16, device=dev)
-        c = torch.empty(i * k, dtype=torch.float16, device=dev)
+        tdt = torch.float16 if e.out_dtype() == "f16" else torch.float32
+        a = torch.randn(int(np.prod(e.inn_shape(0))), dtype=tdt, device=dev)
+        b = torch.randn(int(np.prod(e.inn_shape(1))), dtype=tdt, device=dev)
+        c = torch.empty(e.out_nelem(), dtype=tdt, device=dev)
         w = torch.empty(max(ws, 16), dtype=torch.uint8, device=dev)
         ms = time_launches(lambda: km(e, stream, c, [a, b], (w, ws) if ws else None), stream)
-        out[name] = {"ms": ms, "TFLOP/s": 2.0 * i * j * k / (ms * 1e-3) / 1e12, "kind": km.kernel_info(e).split("|")[0]}
+        nbytes = (a.numel() + b.numel() + c.numel()) * a.element_size()
+        out[name] = {"ms": ms, "TFLOP/s": 2.0 * float(np.prod(e.join_shape)) / (ms * 1e-3) / 1e12,
+                     "GB/s": nbytes / (ms * 1e-3) / 1e9, "kind": km.kernel_info(e).split("|")[0]}
     # C3: one source block of [32,512,32,128] split 2 per dim, copy and accumulate, f16
     full = (32, 512, 32, 128)
     sel = [(16, 32, 0, 16, 16), (256, 512, 0, 256, 256), (16, 32, 0, 16, 16), (64, 128, 0, 64, 64)]
@@ -424,6 +436,26 @@ def other_classes(km, dev, stream):
         t = touch_t(sel, castable, "f16")
         ms = time_launches(lambda: km(t, stream, dst, src), stream)
         out["touch C3 p=2 f16 %s" % (castable or "copy")] = {"ms": ms, "GB/s": mult * nbytes / (ms * 1e-3) / 1e9}
+    # the whole C3 sweep at p blocks per dim as ONE batched launch: every source block of the
+    # [32,512,32,128] tensor is copied (or accumulated) into its place in the destination
+    for pdim in (2, 4, 8):
+        bs = [f // pdim for f in full]
+        blk = int(np.prod(bs))
+        nblk = pdim ** 4
+        srcs = torch.randn(nblk * blk, dtype=torch.float16, device=dev)
+        items = torch.empty(nblk * 256, dtype=torch.uint8, device=dev)
+        for castable, mult in ((None, 2), ("add", 3)):
+            touches, outs, inns = [], [], []
+            for b in range(nblk):
+                idx = np.unravel_index(b, (pdim,) * 4)
+                sel_b = [(bs[d], full[d], 0, int(idx[d]) * bs[d], bs[d]) for d in range(4)]
+                touches.append(touch_t(sel_b, castable, "f16"))
+                outs.append(dst)
+                inns.append(srcs[b * blk:(b + 1) * blk])
+            ms = time_launches(lambda: km.touch_batch(touches, stream, outs, inns, items), stream, iters=5, warm=2)
+            out["touch C3 sweep p=%d f16 %s (1 batched launch, %d touches)" % (pdim, castable or "copy", nblk)] = {
+                "ms": ms, "GB/s": mult * nblk * blk * 2 / (ms * 1e-3) / 1e9}
+        del srcs
     e = einsummable_t([32, 32, 512, 128], [[0, 2, 1, 3]], 4, S.make_identity("f16"))
     km.build(e)
     big = torch.randn(int(np.prod(full)), dtype=torch.float16, device=dev)

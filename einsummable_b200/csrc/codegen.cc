@@ -76,6 +76,65 @@ template <int V> __device__ __forceinline__ void ld_c64(const cf* p, cf* o) {
         if constexpr (V > 2) ld_c64<V - 2>(p + 2, o + 2);
     }
 }
+// ---- raw (packed) loads: data stays packed in registers until it is used ----
+template <int BYTES> struct raw_t { uint4 q[BYTES / 16]; };
+template <> struct raw_t<8> { uint2 q[1]; };
+template <> struct raw_t<4> { u32 q[1]; };
+template <> struct raw_t<2> { u16 q[1]; };
+template <int BYTES> __device__ __forceinline__ void ld_raw(const void* p, raw_t<BYTES>& r) {
+    if constexpr (BYTES >= 16) {
+#pragma unroll
+        for (int i = 0; i < BYTES / 16; ++i) r.q[i] = ((const uint4*)p)[i];
+    } else if constexpr (BYTES == 8) { r.q[0] = *(const uint2*)p; }
+    else if constexpr (BYTES == 4) { r.q[0] = *(const u32*)p; }
+    else { r.q[0] = *(const u16*)p; }
+}
+template <int V> __device__ __forceinline__ void cv_f16(const raw_t<2 * V>& r, float* o) {
+    if constexpr (V == 1) { o[0] = es_h2f(r.q[0]); }
+    else if constexpr (V == 2) { es_unpack2(r.q[0], o[0], o[1]); }
+    else if constexpr (V == 4) { es_unpack2(r.q[0].x, o[0], o[1]); es_unpack2(r.q[0].y, o[2], o[3]); }
+    else {
+#pragma unroll
+        for (int i = 0; i < V / 8; ++i) {
+            es_unpack2(r.q[i].x, o[8 * i + 0], o[8 * i + 1]); es_unpack2(r.q[i].y, o[8 * i + 2], o[8 * i + 3]);
+            es_unpack2(r.q[i].z, o[8 * i + 4], o[8 * i + 5]); es_unpack2(r.q[i].w, o[8 * i + 6], o[8 * i + 7]);
+        }
+    }
+}
+template <int V> __device__ __forceinline__ void cv_f32(const raw_t<4 * V>& r, float* o) {
+    if constexpr (V == 1) { o[0] = __uint_as_float(r.q[0]); }
+    else if constexpr (V == 2) { o[0] = __uint_as_float(r.q[0].x); o[1] = __uint_as_float(r.q[0].y); }
+    else {
+#pragma unroll
+        for (int i = 0; i < V / 4; ++i) {
+            o[4 * i + 0] = __uint_as_float(r.q[i].x); o[4 * i + 1] = __uint_as_float(r.q[i].y);
+            o[4 * i + 2] = __uint_as_float(r.q[i].z); o[4 * i + 3] = __uint_as_float(r.q[i].w);
+        }
+    }
+}
+template <int V> __device__ __forceinline__ void cv_f64(const raw_t<8 * V>& r, double* o) {
+    if constexpr (V == 1) { o[0] = __hiloint2double((int)r.q[0].y, (int)r.q[0].x); }
+    else {
+#pragma unroll
+        for (int i = 0; i < V / 2; ++i) {
+            o[2 * i + 0] = __hiloint2double((int)r.q[i].y, (int)r.q[i].x);
+            o[2 * i + 1] = __hiloint2double((int)r.q[i].w, (int)r.q[i].z);
+        }
+    }
+}
+template <int V> __device__ __forceinline__ void cv_c64(const raw_t<8 * V>& r, cf* o) {
+    if constexpr (V == 1) { o[0] = cf_make(__uint_as_float(r.q[0].x), __uint_as_float(r.q[0].y)); }
+    else {
+#pragma unroll
+        for (int i = 0; i < V / 2; ++i) {
+            o[2 * i + 0] = cf_make(__uint_as_float(r.q[i].x), __uint_as_float(r.q[i].y));
+            o[2 * i + 1] = cf_make(__uint_as_float(r.q[i].z), __uint_as_float(r.q[i].w));
+        }
+    }
+}
+__device__ __forceinline__ float es_rcp_approx(float x) {
+    float r; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x)); return r;
+}
 // ---- stores ----
 template <int V> __device__ __forceinline__ void st_f16(u16* p, const float* o) {
     if constexpr (V == 1) { *p = es_f2h(o[0]); }
@@ -294,7 +353,7 @@ plan_t gen_ew_vec(ctx_t const& c, bool force_scalar)
     s.add("  const %s v0 = (%s)blockIdx.x * %du + threadIdx.x;", c.idx(), c.idx(), B * U);
     for (int k = 0; k != c.n; ++k) {
         bool vec = c.has_mode(k, L);
-        if (vec) s.add("  %s a%d[%d][%d];", compute_type(e.inn_dtype(k)), k, U, V);
+        if (vec) s.add("  raw_t<%d> q%d[%d];", V * dtype_size(e.inn_dtype(k)), k, U);
         else s.add("  %s b%d[%d];", compute_type(e.inn_dtype(k)), k, U);
     }
     s.add("  #pragma unroll");
@@ -306,8 +365,7 @@ plan_t gen_ew_vec(ctx_t const& c, bool force_scalar)
     for (int k = 0; k != c.n; ++k) {
         std::string off = straight[k] ? std::string("ee") : c.offset_expr(c.st[k], 0, c.r);
         if (c.has_mode(k, L))
-            s.add("      ld_%s<%d>(x%d + (%s), a%d[u]);", dt_suffix(e.inn_dtype(k)), V, k,
-                  off.c_str(), k);
+            s.add("      ld_raw<%d>(x%d + (%s), q%d[u]);", V * dtype_size(e.inn_dtype(k)), k, off.c_str(), k);
         else
             s.add("      ld_%s<1>(x%d + (%s), &b%d[u]);", dt_suffix(e.inn_dtype(k)), k, off.c_str(),
                   k);
@@ -318,12 +376,17 @@ plan_t gen_ew_vec(ctx_t const& c, bool force_scalar)
     s.add("  for (int u = 0; u < %d; ++u) {", U);
     s.add("    const %s v = v0 + (%s)u * %du;", c.idx(), c.idx(), B);
     s.add("    if (v < NV) {");
+    for (int k = 0; k != c.n; ++k) {
+        if (c.has_mode(k, L))
+            s.add("      %s a%d[%d]; cv_%s<%d>(q%d[u], a%d);", compute_type(e.inn_dtype(k)), k, V,
+                  dt_suffix(e.inn_dtype(k)), V, k, k);
+    }
     s.add("      %s r[%d];", compute_type(e.out_dtype()), V);
     s.add("      #pragma unroll");
     s.add("      for (int i = 0; i < %d; ++i) {", V);
     std::vector<std::string> names;
     for (int k = 0; k != c.n; ++k) {
-        names.push_back(c.has_mode(k, L) ? "a" + std::to_string(k) + "[u][i]"
+        names.push_back(c.has_mode(k, L) ? "a" + std::to_string(k) + "[i]"
                                          : "b" + std::to_string(k) + "[u]");
     }
     s.add("        r[i] = %s;", e.join.emit(names).c_str());
@@ -563,26 +626,62 @@ plan_t gen_red_row(ctx_t const& c, bool force_scalar)
     s.add("  #pragma unroll");
     s.add("  for (int i = 0; i < %d; ++i) acc[i] = %s;", V,
           identity_literal(e.castable, od).c_str());
-    s.add("  #pragma unroll 4");
-    s.add("  for (%s p = p_begin + lane; p < p_end; p += %du) {", c.idx(), G);
-    s.add("    const %s ea = p * %du;", c.idx(), V);
-    c.decompose(s, "ea", orank, c.r, "    ");
+    // Loads are issued in batches of NB before any of them is consumed, so that
+    // each thread keeps NB 16-byte requests in flight.  Short rows (few trips per
+    // thread, known here) are unrolled completely.
+    uint64_t const max_trips = ((S == 1 ? AV : CH) + G - 1) / G;
+    int const      NB = (int)std::min<uint64_t>(max_trips, 4);
+    bool const     whole = S == 1 && max_trips <= 8; // every trip of a thread in one batch
+    int const      batch = whole ? (int)max_trips : NB;
+    for (int k = 0; k != c.n; ++k) {
+        if (c.any_mode_in(k, orank, c.r) && c.has_mode(k, L))
+            s.add("  raw_t<%d> q%d[%d];", V * dtype_size(e.inn_dtype(k)), k, batch);
+    }
+    if (whole) s.add("  {");
+    else s.add("  for (%s p0 = p_begin + lane; p0 < p_end; p0 += %du) {", c.idx(), G * batch);
+    if (whole) s.add("    const %s p0 = p_begin + lane;", c.idx());
+    // load phase
+    s.add("    #pragma unroll");
+    s.add("    for (int t = 0; t < %d; ++t) {", batch);
+    s.add("      const %s p = p0 + (%s)t * %du;", c.idx(), c.idx(), G);
+    s.add("      if (p < p_end) {");
+    s.add("        const %s ea = p * %du;", c.idx(), V);
+    c.decompose(s, "ea", orank, c.r, "        ");
+    for (int k = 0; k != c.n; ++k) {
+        if (!c.any_mode_in(k, orank, c.r) || !c.has_mode(k, L)) continue;
+        s.add("        ld_raw<%d>(x%d + base%d + (%s), q%d[t]);", V * dtype_size(e.inn_dtype(k)), k, k,
+              c.offset_expr(c.st[k], orank, c.r).c_str(), k);
+    }
+    s.add("      }");
+    s.add("    }");
+    // compute phase
+    s.add("    #pragma unroll");
+    s.add("    for (int t = 0; t < %d; ++t) {", batch);
+    s.add("      const %s p = p0 + (%s)t * %du;", c.idx(), c.idx(), G);
+    s.add("      if (p < p_end) {");
+    bool need_scalar = false;
+    for (int k = 0; k != c.n; ++k)
+        if (c.any_mode_in(k, orank, c.r) && !c.has_mode(k, L)) need_scalar = true;
+    if (need_scalar) {
+        s.add("        const %s ea = p * %du;", c.idx(), V);
+        c.decompose(s, "ea", orank, c.r, "        ");
+    }
     for (int k = 0; k != c.n; ++k) {
         if (!c.any_mode_in(k, orank, c.r)) continue;
-        std::string off = c.offset_expr(c.st[k], orank, c.r);
         if (c.has_mode(k, L)) {
-            s.add("    %s a%d[%d]; ld_%s<%d>(x%d + base%d + (%s), a%d);",
-                  compute_type(e.inn_dtype(k)), k, V, dt_suffix(e.inn_dtype(k)), V, k, k,
-                  off.c_str(), k);
+            s.add("        %s a%d[%d]; cv_%s<%d>(q%d[t], a%d);", compute_type(e.inn_dtype(k)), k, V,
+                  dt_suffix(e.inn_dtype(k)), V, k, k);
         } else {
-            s.add("    %s s%d; ld_%s<1>(x%d + base%d + (%s), &s%d);", compute_type(e.inn_dtype(k)),
-                  k, dt_suffix(e.inn_dtype(k)), k, k, off.c_str(), k);
+            s.add("        %s s%d; ld_%s<1>(x%d + base%d + (%s), &s%d);", compute_type(e.inn_dtype(k)),
+                  k, dt_suffix(e.inn_dtype(k)), k, k, c.offset_expr(c.st[k], orank, c.r).c_str(), k);
         }
     }
-    s.add("    #pragma unroll");
-    s.add("    for (int i = 0; i < %d; ++i) {", V);
-    s.add("      const %s val = %s;", ct, e.join.emit(names).c_str());
-    s.add("      acc[i] = %s;", combine_expr(e.castable, od, "acc[i]", "val").c_str());
+    s.add("        #pragma unroll");
+    s.add("        for (int i = 0; i < %d; ++i) {", V);
+    s.add("          const %s val = %s;", ct, e.join.emit(names).c_str());
+    s.add("          acc[i] = %s;", combine_expr(e.castable, od, "acc[i]", "val").c_str());
+    s.add("        }");
+    s.add("      }");
     s.add("    }");
     s.add("  }");
     s.add("  %s r = acc[0];", ct);

@@ -348,7 +348,7 @@ std::string emit_node(node_t const& n, std::vector<std::string> const& names)
             if (p == 2.0) return "es_sq(" + x + ")";
             if (p == 3.0) return "es_cube(" + x + ")";
             if (p == -1.0) {
-                if (half) return "__frcp_rn(" + x + ")";
+                if (half) return "es_rcp_approx(" + x + ")";
                 return "(" + one + "/" + x + ")";
             }
             if (p == -2.0) return "(" + one + "/es_sq(" + x + "))";
