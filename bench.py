@@ -436,6 +436,14 @@ def other_classes(km, dev, stream):
         t = touch_t(sel, castable, "f16")
         ms = time_launches(lambda: km(t, stream, dst, src), stream)
         out["touch C3 p=2 f16 %s" % (castable or "copy")] = {"ms": ms, "GB/s": mult * nbytes / (ms * 1e-3) / 1e9}
+    # C1: one partial-sum block, rank-1 after simplify, 4194304 f32 (copy then accumulate)
+    n1 = 2048 * 2048
+    p0 = torch.randn(n1, dtype=torch.float32, device=dev)
+    acc = torch.zeros(n1, dtype=torch.float32, device=dev)
+    for castable, mult in ((None, 2), ("add", 3)):
+        t = touch_t([(n1, n1, 0, 0, n1)], castable, "f32")
+        ms = time_launches(lambda: km(t, stream, acc, p0), stream)
+        out["touch C1 block f32 4194304 %s" % (castable or "copy")] = {"ms": ms, "GB/s": mult * n1 * 4 / (ms * 1e-3) / 1e9}
     # the whole C3 sweep at p blocks per dim as ONE batched launch: every source block of the
     # [32,512,32,128] tensor is copied (or accumulated) into its place in the destination
     for pdim in (2, 4, 8):
@@ -452,8 +460,9 @@ def other_classes(km, dev, stream):
                 touches.append(touch_t(sel_b, castable, "f16"))
                 outs.append(dst)
                 inns.append(srcs[b * blk:(b + 1) * blk])
-            ms = time_launches(lambda: km.touch_batch(touches, stream, outs, inns, items), stream, iters=5, warm=2)
-            out["touch C3 sweep p=%d f16 %s (1 batched launch, %d touches)" % (pdim, castable or "copy", nblk)] = {
+            prepared = km.prepare_touch_batch(touches, stream, outs, inns, items)
+            ms = time_launches(lambda: km.launch_prepared_touch_batch(prepared, stream), stream, iters=10, warm=2)
+            out["touch C3 sweep p=%d f16 %s (1 prepared batched launch, %d touches)" % (pdim, castable or "copy", nblk)] = {
                 "ms": ms, "GB/s": mult * nblk * blk * 2 / (ms * 1e-3) / 1e9}
         del srcs
     e = einsummable_t([32, 32, 512, 128], [[0, 2, 1, 3]], 4, S.make_identity("f16"))

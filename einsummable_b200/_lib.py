@@ -41,6 +41,11 @@ class es_touch_item_t(ctypes.Structure):
     ]
 
 
+class es_touch_batch_t(ctypes.Structure):
+    _fields_ = [("n", ctypes.c_int32), ("dtype", ctypes.c_int32), ("width", ctypes.c_int32),
+                ("pad", ctypes.c_int32), ("max_slots", ctypes.c_uint64), ("items_dev", ctypes.c_void_p)]
+
+
 LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libes_b200.so")
 
 # every symbol include/es_b200.h declares: name -> (restype, argtypes)
@@ -56,6 +61,9 @@ SYMBOLS = {
     "es_b200_launch_einsummable": (_i, [_vp, _u64, _vp, _vp, ctypes.POINTER(_vp), _i, _vp, _u64]),
     "es_b200_launch_touch": (_i, [_vp, _td_p, _i, _i, _i, _vp, _vp, _vp]),
     "es_b200_launch_touch_batch": (_i, [_vp, ctypes.POINTER(es_touch_item_t), _i, _i, _vp, _vp]),
+    "es_b200_prepare_touch_batch": (_i, [_vp, ctypes.POINTER(es_touch_item_t), _i, _i, _vp, _vp,
+                                         ctypes.POINTER(es_touch_batch_t)]),
+    "es_b200_launch_prepared_touch_batch": (_i, [_vp, ctypes.POINTER(es_touch_batch_t), _vp]),
     "es_b200_fill_constant": (_i, [_vp, _i, _vp, _u64, _vp, _vp]),
     "es_b200_fill_lowertri": (_i, [_vp, _i, _vp, _vp, _u64, _u64, ctypes.c_int64, _vp, _vp]),
     "es_b200_move": (_i, [_vp, _i, _vp, _i, _vp, _u64, _vp]),

@@ -296,15 +296,18 @@ int es_b200_launch_touch(es_b200_t*           h,
     });
 }
 
-int es_b200_launch_touch_batch(es_b200_t*             h,
-                               const es_touch_item_t* items,
-                               int                    n,
-                               int                    dtype,
-                               void*                  stream,
-                               void*                  items_dev)
+int es_b200_prepare_touch_batch(es_b200_t*             h,
+                                const es_touch_item_t* items,
+                                int                    n,
+                                int                    dtype,
+                                void*                  stream,
+                                void*                  items_dev,
+                                es_touch_batch_t*      prepared)
 {
     return guarded([&] {
         check_handle(h);
+        if (!prepared) fail(ES_BAD_ARGUMENT, "touch batch: null pointer");
+        std::memset(prepared, 0, sizeof *prepared);
         if (n <= 0) return;
         if (!items || !items_dev) fail(ES_BAD_ARGUMENT, "touch batch: null pointer");
         static_assert(sizeof(touch_args_t) <= sizeof(es_touch_item_t),
@@ -327,10 +330,40 @@ int es_b200_launch_touch_batch(es_b200_t*             h,
         // the host copy is consumed before cudaMemcpyAsync returns (pageable source)
         ES_CUDA_CHECK(cudaMemcpyAsync(items_dev, args.data(), sizeof(touch_args_t) * n,
                                       cudaMemcpyHostToDevice, (cudaStream_t)stream));
-        launch_touch_batch(static_cast<touch_args_t const*>(items_dev), n, max_slots, w, dtype,
-                           (cudaStream_t)stream);
+        prepared->n = n;
+        prepared->dtype = dtype;
+        prepared->width = w;
+        prepared->max_slots = max_slots;
+        prepared->items_dev = items_dev;
+    });
+}
+
+int es_b200_launch_prepared_touch_batch(es_b200_t* h, const es_touch_batch_t* prepared, void* stream)
+{
+    return guarded([&] {
+        check_handle(h);
+        if (!prepared) fail(ES_BAD_ARGUMENT, "touch batch: null pointer");
+        if (prepared->n <= 0) return;
+        dtype_size(prepared->dtype);
+        if (!prepared->items_dev) fail(ES_BAD_ARGUMENT, "touch batch: not prepared");
+        set_device(h);
+        launch_touch_batch(static_cast<touch_args_t const*>(prepared->items_dev), prepared->n,
+                           prepared->max_slots, prepared->width, prepared->dtype, (cudaStream_t)stream);
         h->counters[1] += 1;
     });
+}
+
+int es_b200_launch_touch_batch(es_b200_t*             h,
+                               const es_touch_item_t* items,
+                               int                    n,
+                               int                    dtype,
+                               void*                  stream,
+                               void*                  items_dev)
+{
+    es_touch_batch_t prepared;
+    int              st = es_b200_prepare_touch_batch(h, items, n, dtype, stream, items_dev, &prepared);
+    if (st != ES_OK) return st;
+    return es_b200_launch_prepared_touch_batch(h, &prepared, stream);
 }
 
 int es_b200_fill_constant(

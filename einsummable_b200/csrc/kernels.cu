@@ -22,14 +22,22 @@ __host__ fastdiv_t make_fastdiv(uint32_t d)
 {
     fastdiv_t f;
     f.d = d;
-    // m = floor(2^64 / d) + 1 ; exact for every 32-bit numerator.  d == 1 -> special-cased on device
-    f.m = d <= 1 ? 0 : (~0ull / d) + 1;
+    f.pad = 0;
+    f.m = 0;
+    f.s = 0;
+    if (d > 1) {
+        // with e = m*d - 2^(31+l) in [0, d) and n < 2^31: n*e < 2^(31+l), so the quotient is exact
+        uint32_t l = 0;
+        while ((1ull << l) < d) ++l;
+        f.m = (uint32_t)(((1ull << (31 + l)) + d - 1) / d);
+        f.s = l - 1;
+    }
     return f;
 }
 
 __device__ __forceinline__ uint32_t fdiv(uint32_t n, fastdiv_t const& f)
 {
-    return f.d <= 1 ? n : (uint32_t)__umul64hi((uint64_t)n, f.m);
+    return f.d <= 1 ? n : (__umulhi(n, f.m) >> f.s);
 }
 
 template <int W> struct word_t;
@@ -143,11 +151,11 @@ constexpr int TOUCH_BLOCK = 256;
 
 template <int W>
 __device__ __forceinline__ bool
-touch_locate(touch_args_t const& a, uint64_t slot, char const*& pin, char*& pout)
+touch_locate(touch_args_t const& a, uint32_t slot, char const*& pin, char*& pout)
 {
-    if (slot >= a.total_slots) return false;
-    uint32_t seg = (uint32_t)(slot >> a.seg_shift);
-    uint32_t lane = (uint32_t)(slot & ((1u << a.seg_shift) - 1u));
+    if (slot >= (uint32_t)a.total_slots) return false;
+    uint32_t seg = slot >> a.seg_shift;
+    uint32_t lane = slot & ((1u << a.seg_shift) - 1u);
     uint32_t row = fdiv(seg, a.div_segs);
     uint32_t col = ((seg - row * a.segs_per_row) << a.seg_shift) + lane;
     if (col >= a.row_vecs) return false;
@@ -162,7 +170,7 @@ touch_locate(touch_args_t const& a, uint64_t slot, char const*& pin, char*& pout
 }
 
 template <int W, int DT, int CAST>
-__device__ __forceinline__ void touch_body(touch_args_t const& a, uint64_t slot0, uint64_t stride)
+__device__ __forceinline__ void touch_body(touch_args_t const& a, uint32_t slot0, uint32_t stride)
 {
     using V = typename word_t<W>::type;
     V     vi[TOUCH_UNROLL], vo[TOUCH_UNROLL];
@@ -187,7 +195,7 @@ __device__ __forceinline__ void touch_body(touch_args_t const& a, uint64_t slot0
 }
 
 template <int W, int DT>
-__device__ __forceinline__ void touch_dispatch(touch_args_t const& a, uint64_t slot0, uint64_t stride)
+__device__ __forceinline__ void touch_dispatch(touch_args_t const& a, uint32_t slot0, uint32_t stride)
 {
     switch (a.castable) {
         case ES_CASTABLE_NONE: touch_body<W, DT, ES_CASTABLE_NONE>(a, slot0, stride); break;
@@ -206,7 +214,7 @@ __device__ __forceinline__ void touch_dispatch(touch_args_t const& a, uint64_t s
 template <int W, int DT>
 __global__ void __launch_bounds__(TOUCH_BLOCK) touch_kernel(const __grid_constant__ touch_args_t a)
 {
-    uint64_t slot0 = (uint64_t)blockIdx.x * (TOUCH_BLOCK * TOUCH_UNROLL) + threadIdx.x;
+    uint32_t slot0 = blockIdx.x * (TOUCH_BLOCK * TOUCH_UNROLL) + threadIdx.x;
     touch_dispatch<W, DT>(a, slot0, TOUCH_BLOCK);
 }
 
@@ -221,7 +229,7 @@ __global__ void __launch_bounds__(TOUCH_BLOCK) touch_batch_kernel(touch_args_t c
         for (int i = threadIdx.x; i < (int)(sizeof(touch_args_t) / 4); i += TOUCH_BLOCK) dst[i] = src[i];
     }
     __syncthreads();
-    uint64_t slot0 = (uint64_t)blockIdx.x * (TOUCH_BLOCK * TOUCH_UNROLL) + threadIdx.x;
+    uint32_t slot0 = blockIdx.x * (TOUCH_BLOCK * TOUCH_UNROLL) + threadIdx.x;
     if ((uint64_t)blockIdx.x * (TOUCH_BLOCK * TOUCH_UNROLL) >= a.total_slots) return;
     touch_dispatch<W, DT>(a, slot0, TOUCH_BLOCK);
 }
@@ -297,8 +305,8 @@ void finish_args(touch_args_t& a, uint32_t n0, uint32_t n1, uint32_t n2, uint64_
     a.seg_shift = ceil_log2(seg);
     a.segs_per_row = (uint32_t)((row_vecs + seg - 1) / seg);
     uint64_t rows = (uint64_t)n0 * n1 * n2;
-    if (rows > 0xffffffffull || rows * a.segs_per_row > 0xffffffffull)
-        fail(ES_NOT_SUPPORTED, "touch has too many rows");
+    if (rows > 0x7fffffffull || ((rows * a.segs_per_row) << a.seg_shift) >= 0x7fffffffull)
+        fail(ES_NOT_SUPPORTED, "touch region too large for one launch (2^31 vectors)");
     a.n_rows = (uint32_t)rows;
     a.div_n1 = make_fastdiv(n1);
     a.div_n2 = make_fastdiv(n2);

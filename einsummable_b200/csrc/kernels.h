@@ -6,10 +6,13 @@
 
 namespace es {
 
-// Exact division of 32-bit numerators by a fixed divisor: q = hi64(n * m).
+// Exact division of numerators below 2^31 by a fixed divisor d:
+// q = umulhi(n, m) >> s with l = ceil(log2 d), m = ceil(2^(31+l) / d), s = l - 1.
 struct fastdiv_t {
-    uint64_t m;
+    uint32_t m;
+    uint32_t s;
     uint32_t d;
+    uint32_t pad;
 };
 
 // A simplified touch prepared for the device: byte pointers already advanced to
@@ -25,7 +28,7 @@ struct touch_args_t {
     uint32_t    row_vecs;                 // vectors per innermost row
     uint32_t    seg_shift;                // log2(vectors per segment)
     uint32_t    segs_per_row;
-    uint64_t    total_slots;              // n_rows * segs_per_row << seg_shift
+    uint64_t    total_slots;              // n_rows * segs_per_row << seg_shift  (< 2^31)
     int32_t     castable;
     int32_t     pad;
 };

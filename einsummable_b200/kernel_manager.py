@@ -127,9 +127,7 @@ class kernel_manager_t:
             self._h, t.c_dims(), len(t.selection), CASTABLE_CODE[t.castable], DTYPE_CODE[t.dtype],
             _stream(stream), _ptr(out), _ptr(inn)))
 
-    def touch_batch(self, touches, stream, outs, inns, items_dev):
-        """Launches many touches of one dtype at once; items_dev is a device
-        buffer of at least len(touches) * sizeof(es_touch_item_t) bytes."""
+    def _touch_items(self, touches, outs, inns):
         n = len(touches)
         items = (_lib.es_touch_item_t * n)()
         for i, t in enumerate(touches):
@@ -141,8 +139,27 @@ class kernel_manager_t:
             items[i].castable = CASTABLE_CODE[t.castable]
             items[i].out = _ptr(outs[i])
             items[i].inn = _ptr(inns[i])
+        return items
+
+    def touch_batch(self, touches, stream, outs, inns, items_dev):
+        """Launches many touches of one dtype at once; items_dev is a device
+        buffer of at least len(touches) * sizeof(es_touch_item_t) bytes."""
+        items = self._touch_items(touches, outs, inns)
         _lib.check(self._lib.es_b200_launch_touch_batch(
-            self._h, items, n, DTYPE_CODE[touches[0].dtype], _stream(stream), _ptr(items_dev)))
+            self._h, items, len(touches), DTYPE_CODE[touches[0].dtype], _stream(stream), _ptr(items_dev)))
+
+    def prepare_touch_batch(self, touches, stream, outs, inns, items_dev):
+        """Validates and lowers the touches once and stages them in items_dev;
+        the result can be launched repeatedly with launch_prepared_touch_batch."""
+        items = self._touch_items(touches, outs, inns)
+        prepared = _lib.es_touch_batch_t()
+        _lib.check(self._lib.es_b200_prepare_touch_batch(
+            self._h, items, len(touches), DTYPE_CODE[touches[0].dtype], _stream(stream), _ptr(items_dev),
+            ctypes.byref(prepared)))
+        return prepared
+
+    def launch_prepared_touch_batch(self, prepared, stream):
+        _lib.check(self._lib.es_b200_launch_prepared_touch_batch(self._h, ctypes.byref(prepared), _stream(stream)))
 
     def constant_fill(self, c, stream, out):
         n = 1

@@ -147,6 +147,23 @@ int es_b200_launch_touch_batch(es_b200_t*             h,
                                void*                  stream,
                                void*                  items_dev);
 
+/* The same in two steps, for exec graphs whose touches are fixed: prepare once
+ * (validates, lowers and copies the descriptors to items_dev on `stream`), then
+ * launch any number of times with no per-touch host work. */
+typedef struct {
+    int32_t  n, dtype, width, pad;
+    uint64_t max_slots;
+    void*    items_dev;
+} es_touch_batch_t;
+int es_b200_prepare_touch_batch(es_b200_t*             h,
+                                const es_touch_item_t* items,
+                                int                    n,
+                                int                    dtype,
+                                void*                  stream,
+                                void*                  items_dev,
+                                es_touch_batch_t*      prepared);
+int es_b200_launch_prepared_touch_batch(es_b200_t* h, const es_touch_batch_t* prepared, void* stream);
+
 /* kernel_manager_t::constant_fill (src/engine/gpu/gpu_kernel_manager.h:319,
  * gpu_kernel_manager.cc:1064-1089).  value8 = the scalar's 8 raw bytes. */
 int es_b200_fill_constant(es_b200_t*  h,

@@ -79,6 +79,15 @@ def test_touch_batch_bit_exact(km):
     torch.cuda.synchronize()
     for o, w, c in zip(outs, wants, cases):
         assert to_host(o).tobytes() == w.tobytes(), c["name"]
+    # prepared form: copy touches are idempotent, so a second launch must leave the same bits
+    copies = [i for i, c in enumerate(cases) if c["castable"] is None]
+    outs2 = [to_dev(G.arrays["touch/%s/out0" % cases[i]["name"]]) for i in copies]
+    prepared = km.prepare_touch_batch([touches[i] for i in copies], None, outs2, [inns[i] for i in copies], items)
+    km.launch_prepared_touch_batch(prepared, None)
+    km.launch_prepared_touch_batch(prepared, None)
+    torch.cuda.synchronize()
+    for o, i in zip(outs2, copies):
+        assert to_host(o).tobytes() == wants[i].tobytes(), cases[i]["name"]
 
 
 @pytest.mark.parametrize("i", range(len(G.meta["fill"])))
