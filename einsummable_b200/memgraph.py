@@ -1,0 +1,226 @@
+"""Runs a memgraph (the reference's per-device program of apply / touch / fill /
+move nodes) on the B200 kernel layer.
+
+This is the caller side of the boundary, kept deliberately thin: it does what
+the reference's GPU exec nodes do around the kernel manager
+(src/engine/gpu/exec_graph.cc:277-467) -- pointer arithmetic on one big buffer
+per location, build-once / launch-many of every einsummable, the
+first-touch-of-a-group-is-a-copy rule (src/engine/gpu/exec_graph.cc:167-172,
+368-378), fills and moves -- in the memgraph's own node order (a valid
+topological order, src/einsummable/memgraph.h:167-173), on one stream per
+process.  The memgraph itself comes from the reference's compilers as a JSON
+document (oracle/ref_graphs.cc writes it); nothing here plans or partitions.
+
+Two placements of the locations:
+  * single process: every location is a buffer on a device this process can see
+    (several locations may share one GPU);
+  * one process per GPU (torchrun): rank r owns location r; a move between
+    locations is an NCCL send/recv pair issued in node order on both sides.
+"""
+import gzip
+import json
+
+import numpy as np
+import torch
+
+from .einsummable import einsummable_t, fill_t, touch_t
+from .kernel_manager import kernel_manager_t
+from .scalarop import DTYPE_SIZE
+
+NP_DTYPE = {"f16": np.float16, "f32": np.float32, "f64": np.float64, "c64": np.complex64}
+
+
+def load_memgraph(path):
+    opener = gzip.open if str(path).endswith(".gz") else open
+    with opener(path, "rt") as f:
+        return json.load(f)
+
+
+def _scalar_from_raw(raw, dtype):
+    b = bytes(raw[:DTYPE_SIZE[dtype]])
+    return np.frombuffer(b, dtype=NP_DTYPE[dtype])[0]
+
+
+def _blocks_of(shape, partdims):
+    """Yields (slices) of every block in row-major block order (vtensor_t order)."""
+    starts = [np.concatenate([[0], np.cumsum(p)]) for p in partdims]
+    grid = [len(p) for p in partdims]
+    for flat in range(int(np.prod(grid))):
+        idx = np.unravel_index(flat, grid)
+        yield tuple(slice(int(starts[d][i]), int(starts[d][i + 1])) for d, i in enumerate(idx))
+
+
+class memgraph_runner_t:
+    def __init__(self, mg, devices=None, rank=None, world=None):
+        self.mg = mg
+        self.num_locs = mg["num_locs"]
+        self.distributed = rank is not None
+        if self.distributed:
+            if world != self.num_locs:
+                raise ValueError("one process per location: world size %d != %d locations" % (world, self.num_locs))
+            self.rank = rank
+            dev = torch.cuda.current_device()
+            self.devices = {rank: dev}
+        else:
+            devices = devices or [0] * self.num_locs
+            self.devices = {loc: devices[loc] for loc in range(self.num_locs)}
+        self.kms = {}
+        for loc, dev in self.devices.items():
+            if dev not in self.kms:
+                self.kms[dev] = kernel_manager_t(dev)
+        self.buffers = {}
+        for loc, dev in self.devices.items():
+            size = int(mg["mem_sizes"][loc]) + 256
+            self.buffers[loc] = torch.zeros(size, dtype=torch.uint8, device="cuda:%d" % dev)
+        self._prepare()
+
+    def owns(self, loc):
+        return loc in self.devices
+
+    def km(self, loc):
+        return self.kms[self.devices[loc]]
+
+    def ptr(self, loc, offset):
+        return self.buffers[loc].data_ptr() + int(offset)
+
+    # ------------------------------------------------------------------ build
+    def _prepare(self):
+        self.program = []
+        ws_need = {loc: 0 for loc in self.devices}
+        self.stats = {"einsummable": 0, "touch": 0, "move": 0, "fill": 0, "move_bytes": 0}
+        for node in self.mg["nodes"]:
+            kind = node["kind"]
+            if kind == "apply":
+                loc = node["loc"]
+                if not self.owns(loc):
+                    continue
+                if "einsummable" in node:
+                    d = node["einsummable"]
+                    e = einsummable_t(d["join_shape"], d["inns"], d["out_rank"], d["join"], d["castable"])
+                    ws = self.km(loc).build(e)
+                    if ws is None:
+                        raise RuntimeError("build returned nullopt for %r" % (e,))
+                    ws_need[loc] = max(ws_need[loc], ws)
+                    self.program.append(("einsummable", loc, e, [m[0] for m in node["mems"]], ws))
+                    self.stats["einsummable"] += 1
+                else:
+                    d = node["touch"]
+                    t = touch_t(d["selection"], d["castable"], d["dtype"])
+                    t_copy = touch_t(d["selection"], None, d["dtype"])
+                    self.program.append(("touch", loc, t, t_copy, node["group"], [m[0] for m in node["mems"]]))
+                    self.stats["touch"] += 1
+            elif kind == "constant":
+                if not self.owns(node["loc"]):
+                    continue
+                f = node["fill"]
+                if f["type"] == "constant":
+                    dt = f["value"]["dtype"]
+                    fill = fill_t.constant_t(_scalar_from_raw(f["value"]["raw"], dt), [f["nelem"]], dt)
+                    self.program.append(("constant_fill", node["loc"], fill, node["offset"]))
+                else:
+                    dt = f["lower"]["dtype"]
+                    fill = fill_t.lowertri_t(_scalar_from_raw(f["lower"]["raw"], dt),
+                                             _scalar_from_raw(f["upper"]["raw"], dt), f["nrow"], f["ncol"],
+                                             f["start"], dt)
+                    self.program.append(("lowertri_fill", node["loc"], fill, node["offset"]))
+                self.stats["fill"] += 1
+            elif kind == "move":
+                s, d = node["src_loc"], node["dst_loc"]
+                if self.owns(s) or self.owns(d):
+                    self.program.append(("move", s, node["src_offset"], d, node["dst_offset"], node["size"]))
+                    self.stats["move"] += 1
+                    self.stats["move_bytes"] += node["size"]
+            elif kind == "copy":
+                if self.owns(node["loc"]):
+                    self.program.append(("move", node["loc"], node["src_offset"], node["loc"], node["dst_offset"],
+                                         node["size"]))
+            # inputmem, alloc, del, partialize: bookkeeping nodes, nothing to launch
+        self.workspace = {}
+        for loc, need in ws_need.items():
+            dev = self.devices[loc]
+            self.workspace[loc] = (torch.empty(max(need, 16), dtype=torch.uint8, device="cuda:%d" % dev), need)
+
+    # ------------------------------------------------------------------ data
+    def _tensor_desc(self, which, key):
+        for t in self.mg[which]:
+            if t["gid"] == key or t["name"] == key:
+                return t
+        raise KeyError(key)
+
+    def set_input(self, key, array):
+        t = self._tensor_desc("inputs", key)
+        a = np.ascontiguousarray(array, dtype=NP_DTYPE[t["dtype"]]).reshape(t["shape"])
+        for blk, sl in zip(t["blocks"], _blocks_of(t["shape"], t["partdims"])):
+            if not self.owns(blk["loc"]):
+                continue
+            raw = np.ascontiguousarray(a[sl]).view(np.uint8).reshape(-1)
+            assert raw.size == blk["size"], (raw.size, blk)
+            self.buffers[blk["loc"]][blk["offset"]:blk["offset"] + blk["size"]].copy_(torch.from_numpy(raw))
+
+    def get_output(self, key):
+        """The saved tensor assembled from its blocks (blocks on other ranks are left zero)."""
+        t = self._tensor_desc("outputs", key)
+        out = np.zeros(t["shape"], dtype=NP_DTYPE[t["dtype"]])
+        for blk, sl in zip(t["blocks"], _blocks_of(t["shape"], t["partdims"])):
+            if not self.owns(blk["loc"]):
+                continue
+            raw = self.buffers[blk["loc"]][blk["offset"]:blk["offset"] + blk["size"]].cpu().numpy()
+            out[sl] = raw.view(NP_DTYPE[t["dtype"]]).reshape(out[sl].shape)
+        return out
+
+    # ------------------------------------------------------------------ run
+    def run(self, stream=None):
+        """Launches the whole program; asynchronous on `stream` (single process) or
+        on the current stream (one process per GPU)."""
+        groups_touched = set()
+        for op in self.program:
+            kind = op[0]
+            if kind == "einsummable":
+                _, loc, e, offs, ws = op
+                w = self.workspace[loc]
+                self.km(loc)(e, self._stream(loc, stream), self.ptr(loc, offs[0]),
+                             [self.ptr(loc, o) for o in offs[1:]], (w[0], w[1]) if ws else None)
+            elif kind == "touch":
+                _, loc, t, t_copy, group, offs = op
+                first = group < 0 or (loc, group) not in groups_touched
+                if group >= 0:
+                    groups_touched.add((loc, group))
+                self.km(loc)(t_copy if first else t, self._stream(loc, stream), self.ptr(loc, offs[0]),
+                             self.ptr(loc, offs[1]))
+            elif kind == "constant_fill":
+                _, loc, fill, off = op
+                self.km(loc).constant_fill(fill, self._stream(loc, stream), self.ptr(loc, off))
+            elif kind == "lowertri_fill":
+                _, loc, fill, off = op
+                self.km(loc).lowerTri_fill(fill, self._stream(loc, stream), self.ptr(loc, off))
+            elif kind == "move":
+                self._move(op, stream)
+
+    def _stream(self, loc, stream):
+        return stream
+
+    def _move(self, op, stream):
+        _, s, s_off, d, d_off, size = op
+        if not self.distributed:
+            if self.devices[s] != self.devices[d]:
+                # single process, two GPUs, one stream per device would need events; the
+                # single-process mode is for locations that share a device or for tests
+                torch.cuda.synchronize(self.devices[s])
+            self.km(d).move(self.devices[s], self.ptr(s, s_off), self.ptr(d, d_off), size, stream)
+            if self.devices[s] != self.devices[d]:
+                torch.cuda.synchronize(self.devices[d])
+            return
+        import torch.distributed as dist
+        if s == d:
+            self.km(d).move(self.devices[s], self.ptr(s, s_off), self.ptr(d, d_off), size, stream)
+        elif self.rank == s:
+            dist.send(self.buffers[s][s_off:s_off + size], dst=d)
+        elif self.rank == d:
+            dist.recv(self.buffers[d][d_off:d_off + size], src=s)
+
+    def device_status(self):
+        return max(km.device_status() for km in self.kms.values())
+
+    def close(self):
+        for km in self.kms.values():
+            km.close()

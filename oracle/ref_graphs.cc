@@ -1,1 +1,405 @@
-// placeholder
+// Test infrastructure, not product code.
+//
+// Produces the reference's own partitioned graphs for the graph-level configs and
+// runs the reference's own memgraph interpreter on them:
+//   * config 1: build_matmul_even_splits (exps/GPU_correctness.cc:207-223) +
+//     alocate01 (src/autoplace/alocate.h:20-23)
+//   * configs 4: builder_t::make_first_token (llama/builder.cc:3-77) +
+//     autoplace01(make_default01) (src/autoplace/autoplace.h:40-66)
+//   then taskgraph_t::make (src/einsummable/taskgraph.h:15-19) and
+//   memgraph_t::make_without_evict with gpu_alignment_settings
+//   (src/einsummable/memgraph.h:117-147).
+// ref_graph_write_json dumps the memgraph (every node with its dependencies,
+// offsets, einsummable / touch / fill payload and group) plus where each block of
+// every input and saved tensor lives; ref_graph_run interprets the memgraph on
+// caller buffers with the reference's own per-op functions (see there).  The JSON
+// files are the fixtures the product's memgraph runner is tested and benchmarked on.
+#include "src/einsummable/reference.h"
+#include "src/einsummable/memgraph.h"
+#include "src/einsummable/taskgraph.h"
+#include "src/autoplace/autoplace.h"
+#include "src/autoplace/alocate.h"
+#include "llama/builder.h"
+
+#include <fstream>
+
+namespace {
+
+struct built_graph_t {
+    graph_t                  graph;
+    vector<placement_t>      placements;
+    map<int, vtensor_t<int>> inn_tids, save_tids;
+    taskgraph_t              taskgraph;
+    map<int, mem_t>          inn_mem, save_mem;
+    memgraph_t               memgraph;
+    map<int, string>         names; // graph id -> name (weights etc.)
+};
+
+vector<built_graph_t*> g_graphs;
+thread_local string    g_gerr;
+
+int finish(built_graph_t* b)
+{
+    auto [inn_tids, save_tids, tg] = taskgraph_t::make(b->graph, b->placements);
+    b->inn_tids = inn_tids;
+    b->save_tids = save_tids;
+    b->taskgraph = tg;
+    auto [inn_mem, save_mem, mg] =
+        memgraph_t::make_without_evict(b->taskgraph, {}, allocator_settings_t::gpu_alignment_settings());
+    b->inn_mem = inn_mem;
+    b->save_mem = save_mem;
+    b->memgraph = mg;
+    g_graphs.push_back(b);
+    return int(g_graphs.size()) - 1;
+}
+
+string jstr(string const& s)
+{
+    string o = "\"";
+    for (char c : s) {
+        if (c == '"' || c == '\\') {
+            o.push_back('\\');
+        }
+        o.push_back(c);
+    }
+    return o + "\"";
+}
+
+template <typename T> string jvec(vector<T> const& v)
+{
+    std::stringstream ss;
+    ss << "[";
+    for (size_t i = 0; i != v.size(); ++i) {
+        ss << (i ? "," : "") << v[i];
+    }
+    ss << "]";
+    return ss.str();
+}
+
+string castable_json(optional<castable_t> const& c)
+{
+    if (!c) {
+        return "null";
+    }
+    switch (c.value()) {
+        case castable_t::add: return "\"add\"";
+        case castable_t::mul: return "\"mul\"";
+        case castable_t::min: return "\"min\"";
+        case castable_t::max: return "\"max\"";
+    }
+    return "null";
+}
+
+string scalar_json(scalar_t const& s)
+{
+    // the 8 raw payload bytes as an integer list (exact for every dtype, incl. -inf)
+    vector<int> b(8, 0);
+    for (int i = 0; i != int(dtype_size(s.dtype)); ++i) {
+        b[i] = s.data[i]; // bytes past the dtype's size are not part of the value
+    }
+    return "{\"dtype\":" + jstr(write_with_ss(s.dtype)) + ",\"raw\":" + jvec(b) + "}";
+}
+
+void tensor_json(std::ostream& out, built_graph_t const& b, int gid, vtensor_t<int> const& tids,
+                 map<int, mem_t> const& mems)
+{
+    auto const& node = b.graph.nodes[gid];
+    auto const& part = b.placements[gid].partition;
+    out << "{\"gid\":" << gid << ",\"dtype\":" << jstr(write_with_ss(node.op.out_dtype()))
+        << ",\"shape\":" << jvec(node.op.out_shape()) << ",\"name\":"
+        << jstr(b.names.count(gid) ? b.names.at(gid) : string("")) << ",\"partdims\":[";
+    for (size_t d = 0; d != part.partdims.size(); ++d) {
+        out << (d ? "," : "") << jvec(part.partdims[d].sizes());
+    }
+    out << "],\"blocks\":[";
+    auto const& vec = tids.get();
+    for (size_t i = 0; i != vec.size(); ++i) {
+        int          tid = vec[i];
+        mem_t const& m = mems.at(tid);
+        out << (i ? "," : "") << "{\"loc\":" << b.taskgraph.out_loc(tid) << ",\"offset\":" << m.offset
+            << ",\"size\":" << m.size << "}";
+    }
+    out << "]}";
+}
+
+} // namespace
+
+extern "C" {
+
+char const* ref_graph_last_error()
+{
+    return g_gerr.c_str();
+}
+
+#define G_BEGIN try {
+#define G_END                                                                                      \
+    }                                                                                              \
+    catch (std::exception const& e)                                                                \
+    {                                                                                              \
+        g_gerr = e.what();                                                                         \
+        return -1;                                                                                 \
+    }
+
+// config 1: ij,jk->ik, n x n, every dim split n_split ways, blocks placed on nlocs locations
+int ref_graph_build_c1(uint64_t n, int n_split, int nlocs, int dtype_code)
+{
+    G_BEGIN
+    dtype_t     dtype = dtype_code == 0 ? dtype_t::f16 : dtype_t::f32;
+    partdim_t   pd = partdim_t::split(n, n_split);
+    partition_t part2({pd, pd});
+    partition_t part3({pd, pd, pd});
+    graph_constructor_t g;
+    int lhs = g.insert_input(part2, dtype);
+    int rhs = g.insert_input(part2, dtype);
+    int join = g.insert_einsummable(part3, einsummable_t::from_matmul(n, n, n, dtype), {lhs, rhs});
+    int out = g.insert_formation(part2, join, true);
+    auto* b = new built_graph_t();
+    b->graph = g.graph;
+    vector<partition_t> parts = vector_from_each_member(g.get_placements(), partition_t, partition);
+    b->placements = alocate01(b->graph, parts, nlocs, 100);
+    b->names[lhs] = "lhs";
+    b->names[rhs] = "rhs";
+    b->names[out] = "out";
+    return finish(b);
+    G_END
+}
+
+// config 4: one (or more) LLaMA transformer layers, first-token graph
+int ref_graph_build_llama(uint64_t dim,
+                          uint64_t n_heads,
+                          uint64_t multiple_of,
+                          uint64_t vocab_size,
+                          int      n_layers,
+                          uint64_t batch,
+                          uint64_t seqlen,
+                          int      nlocs,
+                          int      dtype_code)
+{
+    G_BEGIN
+    set_default_dtype(dtype_code == 0 ? dtype_t::f16 : dtype_t::f32);
+    model_args_t args = model_args_t::llama_7B(batch);
+    args.dim = dim;
+    args.n_heads = n_heads;
+    args.multiple_of = multiple_of;
+    args.vocab_size = vocab_size;
+    args.n_layers = n_layers;
+    args.max_seq_len = seqlen; // unused freqs_cis blocks would make memgraph_t::make_ throw
+    builder_t builder = builder_t::make_first_token(args, seqlen);
+    auto*     b = new built_graph_t();
+    b->graph = builder.graph;
+    b->placements = autoplace01(b->graph, autoplace_config_t::make_default01(nlocs, 1));
+    for (auto const& [name, gid] : builder.weights) {
+        b->names[gid] = name;
+    }
+    b->names[builder.freqs_cis] = "freqs_cis";
+    b->names[builder.embeddings] = "embeddings";
+    if (builder.mask) {
+        b->names[builder.mask.value()] = "mask";
+    }
+    b->names[builder.scores] = "scores";
+    return finish(b);
+    G_END
+}
+
+int ref_graph_num_locs(int h)
+{
+    return g_graphs.at(h)->memgraph.num_compute_locs;
+}
+
+int ref_graph_mem_sizes(int h, uint64_t* out)
+{
+    G_BEGIN
+    auto sizes = g_graphs.at(h)->memgraph.mem_sizes();
+    for (size_t i = 0; i != sizes.size(); ++i) {
+        out[i] = sizes[i];
+    }
+    return int(sizes.size());
+    G_END
+}
+
+int ref_graph_write_json(int h, char const* path)
+{
+    G_BEGIN
+    built_graph_t const& b = *g_graphs.at(h);
+    memgraph_t const&    mg = b.memgraph;
+    std::ofstream        out(path);
+    out << "{\"num_locs\":" << mg.num_compute_locs << ",\"mem_sizes\":" << jvec(mg.mem_sizes());
+    // statistics of the taskgraph
+    {
+        int      n_apply = 0, n_move = 0, n_partialize = 0;
+        uint64_t move_bytes = 0;
+        double   flops = 0;
+        for (auto const& node : b.taskgraph.nodes) {
+            if (node.op.is_apply()) {
+                n_apply++;
+                auto const& e = node.op.get_apply().einsummable;
+                if (e.is_contraction()) {
+                    flops += 2.0 * double(product(e.join_shape));
+                }
+            } else if (node.op.is_move()) {
+                n_move++;
+                move_bytes += node.op.get_move().size;
+            } else if (node.op.is_partialize()) {
+                n_partialize++;
+            }
+        }
+        out << ",\"taskgraph\":{\"nodes\":" << b.taskgraph.nodes.size() << ",\"apply\":" << n_apply
+            << ",\"move\":" << n_move << ",\"move_bytes\":" << move_bytes
+            << ",\"partialize\":" << n_partialize << ",\"contraction_flops\":" << flops << "}";
+    }
+    out << ",\"inputs\":[";
+    {
+        bool first = true;
+        for (auto const& [gid, tids] : b.inn_tids) {
+            out << (first ? "" : ",");
+            first = false;
+            tensor_json(out, b, gid, tids, b.inn_mem);
+        }
+    }
+    out << "],\"outputs\":[";
+    {
+        bool first = true;
+        for (auto const& [gid, tids] : b.save_tids) {
+            out << (first ? "" : ",");
+            first = false;
+            tensor_json(out, b, gid, tids, b.save_mem);
+        }
+    }
+    out << "],\"nodes\":[";
+    for (int id = 0; id != int(mg.nodes.size()); ++id) {
+        auto const& node = mg.nodes[id];
+        auto const& op = node.op;
+        out << (id ? "," : "") << "\n{\"id\":" << id << ",\"inns\":"
+            << jvec(vector<int>(node.inns.begin(), node.inns.end()));
+        if (op.is_inputmem()) {
+            auto const& x = op.get_inputmem();
+            out << ",\"kind\":\"inputmem\",\"loc\":" << x.loc << ",\"offset\":" << x.offset
+                << ",\"size\":" << x.size;
+        } else if (op.is_constant()) {
+            auto const& x = op.get_constant();
+            out << ",\"kind\":\"constant\",\"loc\":" << x.loc << ",\"offset\":" << x.offset;
+            if (x.fill.is_constant()) {
+                auto const& c = x.fill.get_constant();
+                out << ",\"fill\":{\"type\":\"constant\",\"value\":" << scalar_json(c.value)
+                    << ",\"nelem\":" << product(c.shape) << "}";
+            } else {
+                auto const& l = x.fill.get_lowertri();
+                out << ",\"fill\":{\"type\":\"lowertri\",\"lower\":" << scalar_json(l.lower)
+                    << ",\"upper\":" << scalar_json(l.upper) << ",\"nrow\":" << l.nrow
+                    << ",\"ncol\":" << l.ncol << ",\"start\":" << l.start << "}";
+            }
+        } else if (op.is_apply()) {
+            auto const& a = op.get_apply();
+            out << ",\"kind\":\"apply\",\"loc\":" << a.loc << ",\"group\":" << a.group << ",\"mems\":[";
+            for (size_t i = 0; i != a.mems.size(); ++i) {
+                out << (i ? "," : "") << "[" << a.mems[i].offset << "," << a.mems[i].size << "]";
+            }
+            out << "]";
+            if (a.is_einsummable()) {
+                auto const& e = a.get_einsummable();
+                out << ",\"einsummable\":{\"join_shape\":" << jvec(e.join_shape) << ",\"inns\":[";
+                for (size_t i = 0; i != e.inns.size(); ++i) {
+                    out << (i ? "," : "") << jvec(e.inns[i]);
+                }
+                out << "],\"out_rank\":" << e.out_rank << ",\"join\":" << jstr(write_with_ss(e.join))
+                    << ",\"castable\":" << castable_json(e.castable) << "}";
+            } else {
+                auto const& t = a.get_touch();
+                out << ",\"touch\":{\"dtype\":" << jstr(write_with_ss(t.dtype))
+                    << ",\"castable\":" << castable_json(t.castable) << ",\"selection\":[";
+                for (size_t i = 0; i != t.selection.size(); ++i) {
+                    auto const& s = t.selection[i];
+                    out << (i ? "," : "") << "[" << s.d_inn << "," << s.d_out << "," << s.offset_inn
+                        << "," << s.offset_out << "," << s.size << "]";
+                }
+                out << "]}";
+            }
+        } else if (op.is_move()) {
+            auto const& m = op.get_move();
+            out << ",\"kind\":\"move\",\"src_loc\":" << std::get<0>(m.src)
+                << ",\"src_offset\":" << std::get<1>(m.src) << ",\"dst_loc\":" << std::get<0>(m.dst)
+                << ",\"dst_offset\":" << std::get<1>(m.dst) << ",\"size\":" << m.size;
+        } else if (op.is_copy()) {
+            auto const& c = op.get_copy();
+            out << ",\"kind\":\"copy\",\"loc\":" << c.loc << ",\"size\":" << c.size
+                << ",\"src_offset\":" << c.src_offset << ",\"dst_offset\":" << c.dst_offset;
+        } else if (op.is_partialize()) {
+            auto const& x = op.get_partialize();
+            out << ",\"kind\":\"partialize\",\"loc\":" << x.loc;
+        } else if (op.is_alloc()) {
+            auto const& x = op.get_alloc();
+            out << ",\"kind\":\"alloc\",\"loc\":" << x.loc;
+        } else if (op.is_del()) {
+            auto const& x = op.get_del();
+            out << ",\"kind\":\"del\",\"loc\":" << x.loc;
+        } else {
+            throw std::runtime_error("memgraph node kind not expected without storage");
+        }
+        out << "}";
+    }
+    out << "\n]}\n";
+    return 0;
+    G_END
+}
+
+// The memgraph executed op by op with the reference's own per-op interpreter
+// functions, in get_order() order, with the first-touch-of-a-group-is-a-copy rule
+// -- the loop of reference_compute_memgraph (src/einsummable/reference.cc:191-307)
+// extended by the one case it lacks: constant (fill) nodes, which a LLaMA
+// memgraph contains (the causal mask) and which reference_compute_memgraph
+// rejects ("should not happen").  Fills use the reference's reference_fill.
+int ref_graph_run(int h, void** loc_buffers)
+{
+    G_BEGIN
+    built_graph_t const& b = *g_graphs.at(h);
+    memgraph_t const&    mg = b.memgraph;
+    auto                 at = [&](int loc, uint64_t offset) {
+        return reinterpret_cast<uint8_t*>(loc_buffers[loc]) + offset;
+    };
+    set<int> groups_touched;
+    for (int const& id : mg.get_order()) {
+        auto const& op = mg.nodes[id].op;
+        if (op.is_constant()) {
+            auto const& c = op.get_constant();
+            dbuffer_t   v = reference_fill(c.fill);
+            std::copy((uint8_t*)v.raw(), (uint8_t*)v.raw() + v.size(), at(c.loc, c.offset));
+        } else if (op.is_apply()) {
+            auto const& apply = op.get_apply();
+            auto        buf = [&](int i, dtype_t d) {
+                return dbuffer_t(d, make_buffer_reference(at(apply.loc, apply.mems[i].offset), apply.mems[i].size));
+            };
+            if (apply.is_einsummable()) {
+                auto const&       e = apply.get_einsummable();
+                vector<dbuffer_t> inns;
+                for (int i = 1; i != apply.mems.size(); ++i) {
+                    inns.push_back(buf(i, e.inn_dtype(i - 1)));
+                }
+                reference_einsummable_inplace(e, buf(0, e.out_dtype()), inns);
+            } else {
+                touch_t touch = apply.get_touch();
+                if (apply.group < 0) {
+                    touch.castable.reset();
+                } else if (groups_touched.count(apply.group) == 0) {
+                    touch.castable.reset();
+                    groups_touched.insert(apply.group);
+                }
+                reference_touch(touch, buf(0, touch.dtype), buf(1, touch.dtype));
+            }
+        } else if (op.is_move()) {
+            auto const& m = op.get_move();
+            uint8_t*    src = at(std::get<0>(m.src), std::get<1>(m.src));
+            std::copy(src, src + m.size, at(std::get<0>(m.dst), std::get<1>(m.dst)));
+        } else if (op.is_copy()) {
+            auto const& c = op.get_copy();
+            std::copy(at(c.loc, c.src_offset), at(c.loc, c.src_offset) + c.size, at(c.loc, c.dst_offset));
+        } else if (op.is_inputmem() || op.is_partialize() || op.is_alloc() || op.is_del()) {
+            // nothing to do
+        } else {
+            throw std::runtime_error("ref_graph_run: storage nodes are not expected here");
+        }
+    }
+    return 0;
+    G_END
+}
+
+} // extern "C"

@@ -1,0 +1,137 @@
+#!/usr/bin/env python3
+"""Generates the graph-level fixtures under tests/golden/graphs/ from the
+reference's own compilers and interpreter (oracle/_ref/libes_ref.so, built from
+the reference sources by oracle/Makefile; see oracle/ref_graphs.cc).
+
+For every case: the memgraph as JSON (what the reference's graph -> taskgraph ->
+memgraph pipeline emits for that graph and placement).  For the small cases also
+seeded inputs and the outputs of the reference's reference_compute_memgraph on
+them (graphs.npz).  Runs only where the reference tree exists.
+
+usage: python tests/golden/make_graphs.py
+"""
+import ctypes
+import gzip
+import json
+import os
+import shutil
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+OUT = os.path.join(HERE, "graphs")
+NP = {"f16": np.float16, "f32": np.float32, "f64": np.float64, "c64": np.complex64}
+
+L = ctypes.CDLL(os.path.join(ROOT, "oracle", "_ref", "libes_ref.so"))
+L.ref_graph_last_error.restype = ctypes.c_char_p
+u64 = ctypes.c_uint64
+
+
+def ok(h):
+    if h < 0:
+        raise RuntimeError(L.ref_graph_last_error().decode())
+    return h
+
+
+def blocks_of(shape, partdims):
+    starts = [np.concatenate([[0], np.cumsum(p)]) for p in partdims]
+    grid = [len(p) for p in partdims]
+    for flat in range(int(np.prod(grid))):
+        idx = np.unravel_index(flat, grid)
+        yield tuple(slice(int(starts[d][i]), int(starts[d][i + 1])) for d, i in enumerate(idx))
+
+
+def write_json(h, name, compress):
+    tmp = os.path.join(OUT, name + ".json")
+    ok(L.ref_graph_write_json(h, tmp.encode()))
+    with open(tmp) as f:
+        mg = json.load(f)
+    if compress:
+        with open(tmp, "rb") as f, gzip.GzipFile(tmp + ".gz", "wb", mtime=0) as g:
+            shutil.copyfileobj(f, g)
+        os.remove(tmp)
+    return mg
+
+
+def run_reference(h, mg, inputs):
+    bufs = [np.zeros(int(s) + 256, dtype=np.uint8) for s in mg["mem_sizes"]]
+    for t in mg["inputs"]:
+        a = inputs[t["name"]].reshape(t["shape"])
+        for blk, sl in zip(t["blocks"], blocks_of(t["shape"], t["partdims"])):
+            raw = np.ascontiguousarray(a[sl]).view(np.uint8).reshape(-1)
+            assert raw.size == blk["size"]
+            bufs[blk["loc"]][blk["offset"]:blk["offset"] + blk["size"]] = raw
+    ptrs = (ctypes.c_void_p * len(bufs))(*[b.ctypes.data for b in bufs])
+    ok(L.ref_graph_run(h, ptrs))
+    outs = {}
+    for t in mg["outputs"]:
+        out = np.zeros(t["shape"], dtype=NP[t["dtype"]])
+        for blk, sl in zip(t["blocks"], blocks_of(t["shape"], t["partdims"])):
+            raw = bufs[blk["loc"]][blk["offset"]:blk["offset"] + blk["size"]]
+            out[sl] = raw.view(NP[t["dtype"]]).reshape(out[sl].shape)
+        outs[t["name"]] = out
+    return outs
+
+
+def llama_inputs(mg, rng, weight_std):
+    ins = {}
+    for t in mg["inputs"]:
+        shape, name = t["shape"], t["name"]
+        if name == "freqs_cis":
+            seq, half = shape
+            theta = 1.0 / (10000.0 ** (np.arange(half) / half))
+            ang = np.outer(np.arange(seq), theta)
+            ins[name] = (np.cos(ang) + 1j * np.sin(ang)).astype(np.complex64)
+        elif name.endswith("norm.weight"):
+            ins[name] = rng.uniform(0.5, 1.5, shape).astype(NP[t["dtype"]])
+        elif name == "embeddings":
+            ins[name] = rng.standard_normal(shape).astype(NP[t["dtype"]])
+        else:
+            ins[name] = (rng.standard_normal(shape) * weight_std).astype(NP[t["dtype"]])
+    return ins
+
+
+def main():
+    os.makedirs(OUT, exist_ok=True)
+    arrays = {}
+
+    # config 1, small (with the reference's result) and full size (graph only)
+    for nlocs in (1, 2):
+        h = ok(L.ref_graph_build_c1(u64(64), 2, nlocs, 1))
+        mg = write_json(h, "c1_n64_locs%d" % nlocs, False)
+        rng = np.random.default_rng(5)
+        ins = {"lhs": rng.uniform(-1, 1, (64, 64)).astype(np.float32),
+               "rhs": rng.uniform(-1, 1, (64, 64)).astype(np.float32)}
+        outs = run_reference(h, mg, ins)
+        for k, v in ins.items():
+            arrays["c1_n64_locs%d/in/%s" % (nlocs, k)] = v
+        for k, v in outs.items():
+            arrays["c1_n64_locs%d/out/%s" % (nlocs, k)] = v
+    for nlocs in (1, 2, 8):
+        h = ok(L.ref_graph_build_c1(u64(4096), 2, nlocs, 1))
+        write_json(h, "c1_n4096_locs%d" % nlocs, True)
+
+    # config 4, tiny model through the reference's memgraph interpreter
+    for nlocs in (1, 2, 4):
+        h = ok(L.ref_graph_build_llama(u64(64), u64(2), u64(32), u64(128), 1, u64(2), u64(16), nlocs, 0))
+        mg = write_json(h, "llama_tiny_locs%d" % nlocs, False)
+        ins = llama_inputs(mg, np.random.default_rng(11), 0.3)
+        outs = run_reference(h, mg, ins)
+        for k, v in ins.items():
+            arrays["llama_tiny_locs%d/in/%s" % (nlocs, k)] = v
+        for k, v in outs.items():
+            arrays["llama_tiny_locs%d/out/%s" % (nlocs, k)] = v
+        print("llama tiny", nlocs, "locs:", {k: float(np.abs(v.astype(np.float64)).max()) for k, v in outs.items()})
+
+    # config 4, LLaMA-7B-shape layer (graph only): dim 4096, 32 heads, FFN 11008, vocab 32000, B=4, S=512
+    for nlocs in (1, 2, 4, 8):
+        h = ok(L.ref_graph_build_llama(u64(4096), u64(32), u64(256), u64(32000), 1, u64(4), u64(512), nlocs, 0))
+        mg = write_json(h, "llama7b_layer_locs%d" % nlocs, True)
+        print("llama 7B layer", nlocs, "locs:", mg["taskgraph"], "nodes", len(mg["nodes"]))
+
+    np.savez_compressed(os.path.join(OUT, "graphs.npz"), **arrays)
+
+
+if __name__ == "__main__":
+    main()

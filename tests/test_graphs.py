@@ -1,0 +1,71 @@
+"""Graph level on CPU: the oracle's memgraph interpreter against the results the
+reference's own interpreter produced for the same memgraphs (tests/golden/graphs)."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+import es_oracle as O
+from conftest import GOLDEN_DIR
+
+GRAPHS = os.path.join(GOLDEN_DIR, "graphs")
+ARR = np.load(os.path.join(GRAPHS, "graphs.npz"))
+SMALL = ["c1_n64_locs1", "c1_n64_locs2", "llama_tiny_locs1", "llama_tiny_locs2", "llama_tiny_locs4"]
+
+
+def load(name):
+    with open(os.path.join(GRAPHS, name + ".json")) as f:
+        return json.load(f)
+
+
+def inputs_of(name):
+    pre = name + "/in/"
+    return {k[len(pre):]: ARR[k] for k in ARR.files if k.startswith(pre)}
+
+
+def outputs_of(name):
+    pre = name + "/out/"
+    return {k[len(pre):]: ARR[k] for k in ARR.files if k.startswith(pre)}
+
+
+@pytest.mark.parametrize("name", SMALL)
+def test_oracle_memgraph_interp_matches_reference(name):
+    mg = load(name)
+    bufs = O.memgraph_place_inputs(mg, inputs_of(name))
+    O.run_memgraph(mg, bufs, "interp")
+    got = O.memgraph_collect_outputs(mg, bufs)
+    for k, want in outputs_of(name).items():
+        g = got[k]
+        assert g.shape == want.shape and g.dtype == want.dtype
+        scale = np.abs(want.astype(np.float64)).max()
+        err = np.abs(g.astype(np.float64) - want.astype(np.float64)).max()
+        # f16 trees with exp / pow differ from half.hpp in the last place here and there
+        tol = 4e-3 if want.dtype == np.float16 else 1e-6
+        assert err <= tol * scale, (name, k, err, scale)
+
+
+@pytest.mark.parametrize("name", SMALL)
+def test_oracle_memgraph_executor_mode_close(name):
+    mg = load(name)
+    bufs = O.memgraph_place_inputs(mg, inputs_of(name))
+    O.run_memgraph(mg, bufs, "executor")
+    got = O.memgraph_collect_outputs(mg, bufs)
+    for k, want in outputs_of(name).items():
+        scale = np.abs(want.astype(np.float64)).max()
+        err = np.abs(got[k].astype(np.float64) - want.astype(np.float64)).max()
+        # a whole layer chains ~15 f16 ops; the interpreter additionally accumulates every
+        # contraction in f16, so the two conventions drift apart by about 1e-2 of the output scale
+        tol = 2e-2 if want.dtype == np.float16 else 1e-5
+        assert err <= tol * scale, (name, k, err, scale)
+
+
+def test_llama7b_layer_statistics_match_the_survey():
+    import gzip
+    want = {1: (0, 0), 2: (29, 189059072), 4: (145, 541472768), 8: (429, 675930112)}
+    for n, (moves, nbytes) in want.items():
+        with gzip.open(os.path.join(GRAPHS, "llama7b_layer_locs%d.json.gz" % n), "rt") as f:
+            mg = json.load(f)
+        assert mg["num_locs"] == n
+        assert mg["taskgraph"]["move"] == moves and mg["taskgraph"]["move_bytes"] == nbytes
+        assert abs(mg["taskgraph"]["contraction_flops"] - 847.157e9) < 1e7
