@@ -336,6 +336,13 @@ def run_gpu(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
 
+    # ---- config 4: LLaMA-7B-shape layer forward, the reference's own memgraph for `world` GPUs ----
+    llama = None
+    try:
+        llama = llama_layer_leg(rank, world, dev)
+    except Exception as exc:  # reported, never hidden
+        llama = {"error": repr(exc)[:300]}
+
     if rank != 0:
         if world > 1:
             import torch.distributed as dist
@@ -372,12 +379,77 @@ def run_gpu(args):
                        for name, t, b in zip(["silu_mul", "rowmax", "exp_sub", "rowsum"], per_kernel_ms,
                                              [BYTES_SILU_MUL, BYTES_ROWMAX, BYTES_EXP_SUB, BYTES_ROWSUM])},
         "classes": classes,
+        "llama7b_layer": llama,
         "cpu_baseline": cpu_baseline() if world == 1 else None,
     }
     print(json.dumps(line))
     if world > 1:
         import torch.distributed as dist
         dist.destroy_process_group()
+
+
+def llama_layer_leg(rank, world, dev, runs=10):
+    """tokens/s of one LLaMA-7B-shape transformer layer forward (dim 4096, 32 heads, FFN 11008,
+    B=4, S=512, f16, plus final norm and last-token vocabulary projection), executed from the
+    memgraph the reference's compilers produce for `world` locations; one process per GPU, moves
+    over NCCL send/recv.  Synthetic N(0, 0.02) weights."""
+    import torch
+    from einsummable_b200.memgraph import load_memgraph, memgraph_runner_t
+    path = os.path.join(ROOT, "tests", "golden", "graphs", "llama7b_layer_locs%d.json.gz" % world)
+    if not os.path.exists(path):
+        return {"skipped": "no memgraph fixture for %d locations" % world}
+    mg = load_memgraph(path)
+    r = memgraph_runner_t(mg, rank=rank, world=world) if world > 1 else memgraph_runner_t(mg, devices=[dev.index])
+    rng = np.random.default_rng(7)
+    for t in mg["inputs"]:
+        shape, name = t["shape"], t["name"]
+        if name == "freqs_cis":
+            seq, half = shape
+            ang = np.outer(np.arange(seq), 1.0 / (10000.0 ** (np.arange(half) / half)))
+            v = (np.cos(ang) + 1j * np.sin(ang)).astype(np.complex64)
+        elif name.endswith("norm.weight"):
+            v = np.ones(shape, dtype=np.float16)
+        else:
+            v = (rng.standard_normal(shape).astype(np.float32) * 0.02).astype(np.float16)
+        r.set_input(name, v)
+    stream = torch.cuda.current_stream(dev)
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def timed(fn):
+        fn()
+        barrier()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record(stream)
+        for _ in range(runs):
+            fn()
+        e.record(stream)
+        barrier()
+        ms = s.elapsed_time(e) / runs
+        if world > 1:
+            import torch.distributed as dist
+            t = torch.tensor([ms], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    out = {"tokens": 2048, "gpus": world, "nodes_this_rank": dict(r.stats),
+           "taskgraph": mg["taskgraph"], "contraction_gflop": mg["taskgraph"]["contraction_flops"] / 1e9}
+    ms_eager = timed(lambda: r.run(stream))
+    out["eager"] = {"ms": ms_eager, "tokens/s": 2048 / (ms_eager * 1e-3)}
+    try:
+        r.capture()
+        ms_graph = timed(r.replay)
+        out["cuda_graph"] = {"ms": ms_graph, "tokens/s": 2048 / (ms_graph * 1e-3),
+                             "TFLOP/s": mg["taskgraph"]["contraction_flops"] / (ms_graph * 1e-3) / 1e12}
+    except Exception as exc:
+        out["cuda_graph"] = {"error": repr(exc)[:200]}
+    out["device_status"] = r.device_status()
+    return out
 
 
 def time_launches(fn, stream, iters=20, warm=3):

@@ -88,8 +88,15 @@ class memgraph_runner_t:
         self.program = []
         ws_need = {loc: 0 for loc in self.devices}
         self.stats = {"einsummable": 0, "touch": 0, "move": 0, "fill": 0, "move_bytes": 0}
+        self._last_global_kind = None
+        prev_kind = None
         for node in self.mg["nodes"]:
             kind = node["kind"]
+            # bookkeeping nodes do not break a run of moves
+            if kind in ("alloc", "del", "inputmem", "partialize"):
+                continue
+            self._last_global_kind = prev_kind
+            prev_kind = kind
             if kind == "apply":
                 loc = node["loc"]
                 if not self.owns(loc):
@@ -127,7 +134,16 @@ class memgraph_runner_t:
             elif kind == "move":
                 s, d = node["src_loc"], node["dst_loc"]
                 if self.owns(s) or self.owns(d):
-                    self.program.append(("move", s, node["src_offset"], d, node["dst_offset"], node["size"]))
+                    mv = ("move", s, node["src_offset"], d, node["dst_offset"], node["size"])
+                    # A run of move nodes that are adjacent in the memgraph's global order is the same
+                    # run on every rank, so its cross-rank members can be posted as one NCCL group.
+                    if (self.distributed and s != d and self.program and self.program[-1][0] == "move_batch"
+                            and self._last_global_kind == "move"):
+                        self.program[-1][1].append(mv)
+                    elif self.distributed and s != d:
+                        self.program.append(("move_batch", [mv]))
+                    else:
+                        self.program.append(mv)
                     self.stats["move"] += 1
                     self.stats["move_bytes"] += node["size"]
             elif kind == "copy":
@@ -170,8 +186,10 @@ class memgraph_runner_t:
 
     # ------------------------------------------------------------------ run
     def run(self, stream=None):
-        """Launches the whole program; asynchronous on `stream` (single process) or
-        on the current stream (one process per GPU)."""
+        """Launches the whole program; asynchronous on `stream` (default: torch's
+        current stream of the first device)."""
+        if stream is None:
+            stream = torch.cuda.current_stream(next(iter(self.devices.values())))
         groups_touched = set()
         for op in self.program:
             kind = op[0]
@@ -195,6 +213,8 @@ class memgraph_runner_t:
                 self.km(loc).lowerTri_fill(fill, self._stream(loc, stream), self.ptr(loc, off))
             elif kind == "move":
                 self._move(op, stream)
+            elif kind == "move_batch":
+                self._move_batch(op[1])
 
     def _stream(self, loc, stream):
         return stream
@@ -217,6 +237,35 @@ class memgraph_runner_t:
             dist.send(self.buffers[s][s_off:s_off + size], dst=d)
         elif self.rank == d:
             dist.recv(self.buffers[d][d_off:d_off + size], src=s)
+
+    def _move_batch(self, moves):
+        import torch.distributed as dist
+        ops = []
+        for (_, s, s_off, d, d_off, size) in moves:
+            if self.rank == s:
+                ops.append(dist.P2POp(dist.isend, self.buffers[s][s_off:s_off + size], d))
+            else:
+                ops.append(dist.P2POp(dist.irecv, self.buffers[d][d_off:d_off + size], s))
+        for w in dist.batch_isend_irecv(ops):
+            w.wait()  # stream-ordered for NCCL: does not block the host
+
+    def capture(self):
+        """Captures one run of the program into a CUDA graph (after two eager warm-up
+        runs): a layer is a few hundred sub-millisecond launches, so replaying a graph
+        removes the per-node host round trip the reference pays through
+        cudaStreamAddCallback (src/engine/gpu/exec_graph.cc:318-332)."""
+        self.run()
+        self.run()
+        for dev in set(self.devices.values()):
+            torch.cuda.synchronize(dev)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.run(torch.cuda.current_stream())
+        self.graph = g
+        return g
+
+    def replay(self):
+        self.graph.replay()
 
     def device_status(self):
         return max(km.device_status() for km in self.kms.values())
