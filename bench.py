@@ -40,9 +40,11 @@ BYTES_ROWSUM = N * 2 + ROWS * 2
 BYTES_STEP = BYTES_SILU_MUL + BYTES_ROWMAX + BYTES_EXP_SUB + BYTES_ROWSUM
 WORKLOAD = "C2 f16 [8192,11008]: silu(x)*y; rowmax; exp(x-rowmax); rowsum"
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the silu*y kernel,
-# from the ncu capture summarised in profiles/ (None until captured).
-SILU_MUL_DRAM_TRAFFIC = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the silu*y kernel: ncu capture of
+# the [4096,11008] case (180.37 MB read + 47.75 MB written, profiles/c2_kernels_f16_4096x11008.md)
+# scaled x2 to the full launch.  Below the algorithmic 541 MB because part of the output is still
+# dirty in the 126 MB L2 when the kernel ends.
+SILU_MUL_DRAM_TRAFFIC = 2 * (180374528 + 47752960) * (8192 * 11008) // (8192 * 11008)
 
 
 def set_rows(rows):
@@ -374,7 +376,7 @@ def run_gpu(args):
         "gpu_launches": int(launches),
         "roofline": {"bound": "hbm", "kernel": "silu(x)*y a,a->a f16 (generated ew_vec)", "achieved": achieved,
                      "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
-                     "traffic": SILU_MUL_DRAM_TRAFFIC, "algorithmic_bytes_per_launch": BYTES_SILU_MUL},
+                     "traffic": SILU_MUL_DRAM_TRAFFIC if ROWS == 8192 else None, "algorithmic_bytes_per_launch": BYTES_SILU_MUL},
         "per_kernel": {name: {"ms": t, "GB/s": b / (t * 1e-3) / 1e9, "frac_of_" + peak_kind: b / (t * 1e-3) / 1e9 / peak}
                        for name, t, b in zip(["silu_mul", "rowmax", "exp_sub", "rowsum"], per_kernel_ms,
                                              [BYTES_SILU_MUL, BYTES_ROWMAX, BYTES_EXP_SUB, BYTES_ROWSUM])},
@@ -555,6 +557,23 @@ def run_only(args):
     km = es.kernel_manager_t(0)
     stream = torch.cuda.current_stream(dev)
     mul16 = S.make_mul("f16")
+    if args.only == "move":
+        # move_t between two GPUs driven by one process (the reference's server model):
+        # source buffer on cuda:1, destination on cuda:0, through es_b200_move
+        if torch.cuda.device_count() < 2:
+            print(json.dumps({"only": "move", "skipped": "needs 2 visible GPUs"}))
+            return
+        res = {}
+        for nbytes in (64 << 10, 1 << 20, 4 << 20, 16 << 20, 90 << 20, 512 << 20):
+            src = torch.randint(0, 255, (nbytes,), dtype=torch.uint8, device="cuda:1")
+            dst = torch.zeros(nbytes, dtype=torch.uint8, device="cuda:0")
+            torch.cuda.synchronize(1)
+            ms = time_launches(lambda: km.move(1, src, dst, nbytes, stream), stream, iters=args.steps, warm=args.warmup)
+            ok = bool((dst == src.to("cuda:0")).all().item())
+            res["%d KiB" % (nbytes >> 10)] = {"ms": ms, "GB/s": nbytes / (ms * 1e-3) / 1e9, "bit_exact": ok}
+        print(json.dumps({"only": "move", "path": "<=4 MiB: SM pull kernel over NVLink; larger: copy engine",
+                          "reference_peer_copy_GB/s": 770, "sizes": res}))
+        return
     if args.only.startswith("gemm") or args.only.startswith("attn"):
         if args.only == "gemm_qkv":
             e = einsummable_t.from_matmul_st(2048, 4096, 4096, "f16")
@@ -598,14 +617,14 @@ def run_only(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=ROWS,
                     help="rows of the [rows, 11008] tensors (default: the full C2 workload); "
                          "smaller values are for profiler captures only")
     ap.add_argument("--only", default=None,
-                    choices=["gemm_qkv", "gemm_ffn", "gemm_f32", "attn_scores", "attn_pv", "touch", "permute"],
+                    choices=["gemm_qkv", "gemm_ffn", "gemm_f32", "attn_scores", "attn_pv", "touch", "permute", "move"],
                     help="time one other kernel class alone (profiler captures); prints its own small JSON line")
     ap.add_argument("--kernels-only", action="store_true",
                     help="skip the end-to-end, other-class and CPU-baseline legs (profiler captures)")

@@ -412,6 +412,24 @@ int es_b200_move(es_b200_t*  h,
         if (bytes == 0) return;
         if (!src || !dst) fail(ES_BAD_ARGUMENT, "move: null pointer");
         set_device(h);
+        if (src_device != dst_device) {
+            // peer mapping of the source GPU's memory into this device's address space, once per
+            // pair (the reference's server enables all pairs at start-up, src/server/gpu/server.cc:54-80)
+            static std::mutex           peer_mutex;
+            static bool                 enabled[64][64] = {};
+            std::lock_guard<std::mutex> lock(peer_mutex);
+            if (src_device < 0 || src_device >= 64 || dst_device >= 64)
+                fail(ES_BAD_ARGUMENT, "move: device ordinal out of range");
+            if (!enabled[dst_device][src_device]) {
+                int can = 0;
+                ES_CUDA_CHECK(cudaDeviceCanAccessPeer(&can, dst_device, src_device));
+                if (!can) fail(ES_NOT_SUPPORTED, "move: no peer access between the two GPUs");
+                cudaError_t e = cudaDeviceEnablePeerAccess(src_device, 0);
+                if (e == cudaErrorPeerAccessAlreadyEnabled) cudaGetLastError();
+                else if (e != cudaSuccess) fail(ES_CUDA_ERROR, std::string("cudaDeviceEnablePeerAccess: ") + cudaGetErrorString(e));
+                enabled[dst_device][src_device] = true;
+            }
+        }
         // Small or latency-critical blobs: SM pull kernel on the destination GPU
         // reading the peer-mapped source with 128-bit loads.  Large blobs: the
         // copy engine, which leaves the SMs to the compute kernels.

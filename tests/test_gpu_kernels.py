@@ -288,3 +288,17 @@ def test_build_is_idempotent(km):
     e2 = einsummable_t([8, 8, 64], [[0, 1, 2], [2]], 3, S.make_add("f32"))
     km.build(e2)
     assert km._ids[km._key(e2)][0] == first[0]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_move_between_two_gpus_bit_exact(km):
+    """move_t across GPUs (one process, peer access), small (pull kernel) and large (copy engine)."""
+    for nbytes in (4096, (3 << 20) + 16, (9 << 20)):
+        src = torch.randint(0, 255, (nbytes,), dtype=torch.uint8, device="cuda:1")
+        dst = torch.zeros(nbytes + 32, dtype=torch.uint8, device="cuda:0")
+        torch.cuda.synchronize(1)
+        km.move(1, src, dst[16:], nbytes, None)
+        torch.cuda.synchronize(0)
+        d = to_host(dst)
+        assert d[16:16 + nbytes].tobytes() == to_host(src).tobytes()
+        assert not d[:16].any() and not d[16 + nbytes:].any()
