@@ -67,6 +67,9 @@ SYMBOLS = {
     "es_b200_fill_constant": (_i, [_vp, _i, _vp, _u64, _vp, _vp]),
     "es_b200_fill_lowertri": (_i, [_vp, _i, _vp, _vp, _u64, _u64, ctypes.c_int64, _vp, _vp]),
     "es_b200_move": (_i, [_vp, _i, _vp, _i, _vp, _u64, _vp]),
+    "es_b200_flag_signal": (_i, [_vp, _vp, ctypes.c_uint32, _vp]),
+    "es_b200_flag_wait": (_i, [_vp, _vp, ctypes.c_uint32, _vp]),
+    "es_b200_pull": (_i, [_vp, _vp, _vp, _u64, _vp]),
     "es_b200_kernel_info": (_i, [_vp, _u64, _cp, _i]),
     "es_b200_describe": (_i, [_desc_p, _i, _cp, _i]),
     "es_b200_touch_simplify": (_i, [_td_p, _i, _td_p, ctypes.POINTER(_i)]),

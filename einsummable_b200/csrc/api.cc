@@ -509,7 +509,41 @@ int es_b200_device_status(es_b200_t* h, unsigned int* error_word)
         if (!error_word) fail(ES_BAD_ARGUMENT, "null pointer");
         set_device(h);
         ES_CUDA_CHECK(cudaDeviceSynchronize());
-        *error_word = read_and_clear_tc_error();
+        unsigned int tc = read_and_clear_tc_error();
+        unsigned int fl = read_and_clear_flag_error();
+        *error_word = tc | (fl << 8);
+    });
+}
+
+int es_b200_flag_signal(es_b200_t* h, void* flag, uint32_t limit_ms, void* stream)
+{
+    return guarded([&] {
+        check_handle(h);
+        set_device(h);
+        launch_flag_signal(static_cast<uint32_t*>(flag), limit_ms, (cudaStream_t)stream);
+        h->counters[3] += 1;
+    });
+}
+
+int es_b200_flag_wait(es_b200_t* h, void* flag, uint32_t limit_ms, void* stream)
+{
+    return guarded([&] {
+        check_handle(h);
+        set_device(h);
+        launch_flag_wait(static_cast<uint32_t*>(flag), limit_ms, (cudaStream_t)stream);
+        h->counters[3] += 1;
+    });
+}
+
+int es_b200_pull(es_b200_t* h, const void* src, void* dst, uint64_t bytes, void* stream)
+{
+    return guarded([&] {
+        check_handle(h);
+        if (bytes == 0) return;
+        if (!src || !dst) fail(ES_BAD_ARGUMENT, "pull: null pointer");
+        set_device(h);
+        launch_pull_copy(src, dst, bytes, (cudaStream_t)stream);
+        h->counters[3] += 1;
     });
 }
 

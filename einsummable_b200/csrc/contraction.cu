@@ -12,10 +12,11 @@
 // contractions (acbe,adbe->abcd; abce,aebd->abcd; adbe,cde->abc) all run
 // without a transpose pass.
 //
-// One persistent CTA per SM, 6 warps:
+// One persistent CTA per SM, 10 warps:
 //   warp 0   : TMA producer  (cp.async.bulk.tensor -> 128B-swizzled smem ring, mbarrier tx)
 //   warp 1   : MMA issuer    (one lane issues tcgen05.mma, accumulators in TMEM, 2 stages)
-//   warps 2-5: epilogue      (tcgen05.ld -> convert -> global stores), overlapped with the
+//   warps 2-9: epilogue      (tcgen05.ld -> convert -> swizzled smem staging -> TMA store; plain
+//                            stores when the output is not TMA-describable), overlapped with the
 //                            next tile's main loop through the second TMEM stage
 // f16 inputs accumulate in f32.  f32 inputs run as TF32: by default split into
 // hi + lo parts by a pre-pass into the workspace and multiplied with three MMAs
@@ -37,10 +38,10 @@ namespace es {
 namespace {
 
 constexpr int      BM = 128;
-constexpr int      NUM_THREADS = 192;
+constexpr int      NUM_THREADS = 320; // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue (two per TMEM quarter)
 constexpr int      MAX_STAGES = 8;
 constexpr int      MAX_LOOP_MODES = 6;
-constexpr uint32_t STAGING_BYTES = 4 * 2 * 4096;
+constexpr uint32_t STAGING_BYTES = 8 * 4096; // one 32-row x 128-byte staging tile per epilogue warp
 constexpr uint64_t WAIT_LIMIT_CYCLES = 4000000000ull; // ~2 s at 2 GHz
 
 enum src_kind_t : int8_t { SRC_ZERO = 0, SRC_MN_TILE = 1, SRC_K_BLOCK = 2, SRC_N_TILE = 3, SRC_OUTER0 = 8, SRC_KOUTER0 = 24 };
@@ -376,7 +377,7 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(smem_u32(&ctrl->tmem_full[a]), 1);
-            mbar_init(smem_u32(&ctrl->tmem_empty[a]), 4);
+            mbar_init(smem_u32(&ctrl->tmem_empty[a]), 8);
         }
         ctrl->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -487,19 +488,22 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
             }
         }
     } else {
-        // ------------------------------------------------------------ epilogue (warps 2..5)
+        // ------------------------------------------------------------ epilogue (warps 2..9)
+        // Two warps share each TMEM lane quarter and take alternate 128-byte pieces of the tile's
+        // columns, so that short-K contractions (attention) are not bound by one warp's epilogue.
         uint32_t const quarter = warp & 3; // TMEM lanes 32*quarter .. +31 belong to this warp
+        uint32_t const half = (uint32_t)(warp - 2) >> 2;
         uint32_t q = 0, store_seq = 0;
         bool     ok = true;
         // PROMOTE: partial sums of each k-chunk are added in registers with
         // round-to-nearest f32 adds.  The tensor core's own accumulation truncates,
         // which over hundreds of MMAs biases a long f32 sum beyond 1e-5.
-        float accr[PROMOTE ? 4 : 1][32];
+        float accr[PROMOTE ? 2 : 1][32];
         // A "piece" is 128 bytes of one output row: 64 f16 or 32 f32 columns.
         uint32_t const piece_cols = p.out_is_f32 ? 32u : 64u;
         uint32_t const pieces = p.bn / piece_cols;
-        // per-warp staging for TMA stores: 2 buffers of 32 rows x 128 bytes, 128B-swizzled
-        uint32_t const stage_buf = smem_base + p.staging_offset + (uint32_t)(warp - 2) * 8192u;
+        // per-warp staging for TMA stores: 32 rows x 128 bytes, 128B-swizzled
+        uint32_t const stage_buf = smem_base + p.staging_offset + (uint32_t)(warp - 2) * 4096u;
         for (uint32_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
             uint32_t m_tile, n_tile, outer[MAX_LOOP_MODES];
             decode_tile(p, tile, m_tile, n_tile, outer);
@@ -523,7 +527,7 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
                 if (!mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_ph, abort_flag, 4)) { ok = false; break; }
                 tc_fence_after();
                 uint32_t const trow = tmem_base + ((quarter * 32u) << 16) + acc * p.bn;
-                for (uint32_t pc = 0; pc < pieces; ++pc) {
+                for (uint32_t pc = half; pc < pieces; pc += 2) {
                     uint4 w[8]; // this lane's 128 bytes of the piece, in the output dtype
                     if (p.out_is_f32) {
                         uint32_t r[32];
@@ -533,10 +537,10 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
                             for (int j = 0; j < 32; ++j) {
                                 float v = __uint_as_float(r[j]);
 #pragma unroll
-                                for (int c4 = 0; c4 < 4; ++c4) {
-                                    if ((int)pc == c4) {
-                                        accr[c4][j] = first_chunk ? v : __fadd_rn(accr[c4][j], v);
-                                        r[j] = __float_as_uint(accr[c4][j]);
+                                for (int c2 = 0; c2 < 2; ++c2) {
+                                    if ((int)(pc >> 1) == c2) { // bn <= 128: at most 4 pieces, 2 per warp
+                                        accr[c2][j] = first_chunk ? v : __fadd_rn(accr[c2][j], v);
+                                        r[j] = __float_as_uint(accr[c2][j]);
                                     }
                                 }
                             }
@@ -562,9 +566,9 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
                     if (p.out_tma) {
                         // 32 rows x 128 bytes -> swizzled staging -> one TMA store per warp and piece
                         // (rows / columns beyond the tensor are clipped by the TMA unit)
-                        uint32_t const buf = stage_buf + (store_seq & 1) * 4096u;
-                        if (store_seq >= 2) {
-                            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                        uint32_t const buf = stage_buf;
+                        if (store_seq >= 1) { // the previous store of this warp must have read the tile
+                            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
                             __syncwarp();
                         }
                         ++store_seq;

@@ -290,6 +290,37 @@ __global__ void __launch_bounds__(256) pull_copy_kernel(uint4 const* __restrict_
     if (tid < ntail) dst_tail[tid] = src_tail[tid];
 }
 
+__device__ unsigned int g_flag_error; // 1 = a signal gave up, 2 = a wait gave up
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(uint32_t const* p)
+{
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v)
+{
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// expected: the value the flag must have before it is flipped to `next`
+__global__ void flag_kernel(uint32_t* flag, uint32_t expected, uint32_t next, unsigned long long limit_cycles,
+                            unsigned int code)
+{
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    long long t0 = clock64();
+    while (ld_acquire_sys(flag) != expected) {
+        if ((unsigned long long)(clock64() - t0) > limit_cycles) {
+            atomicCAS(&g_flag_error, 0u, code);
+            return; // give up: the flag is left alone, the stream goes on, the host sees the error word
+        }
+        __nanosleep(64);
+    }
+    __threadfence_system();
+    st_release_sys(flag, next);
+}
+
 uint32_t ceil_log2(uint32_t v)
 {
     uint32_t s = 0;
@@ -531,6 +562,34 @@ void launch_fill_lowertri(int          dtype,
         default: fail(ES_BAD_DESCRIPTOR, "fill: bad dtype");
     }
     ES_CUDA_CHECK(cudaGetLastError());
+}
+
+static unsigned long long limit_cycles(uint32_t limit_ms)
+{
+    // clock64 ticks at the SM clock (<= ~2 GHz here); the limit is an upper bound, not a timer
+    return (unsigned long long)(limit_ms ? limit_ms : 2000) * 2000000ull;
+}
+
+void launch_flag_signal(uint32_t* flag, uint32_t limit_ms, cudaStream_t s)
+{
+    if (!flag || (reinterpret_cast<uintptr_t>(flag) & 3)) fail(ES_BAD_ARGUMENT, "flag: null or unaligned pointer");
+    flag_kernel<<<1, 32, 0, s>>>(flag, 0u, 1u, limit_cycles(limit_ms), 1u);
+    ES_CUDA_CHECK(cudaGetLastError());
+}
+
+void launch_flag_wait(uint32_t* flag, uint32_t limit_ms, cudaStream_t s)
+{
+    if (!flag || (reinterpret_cast<uintptr_t>(flag) & 3)) fail(ES_BAD_ARGUMENT, "flag: null or unaligned pointer");
+    flag_kernel<<<1, 32, 0, s>>>(flag, 1u, 0u, limit_cycles(limit_ms), 2u);
+    ES_CUDA_CHECK(cudaGetLastError());
+}
+
+unsigned int read_and_clear_flag_error()
+{
+    unsigned int v = 0, zero = 0;
+    ES_CUDA_CHECK(cudaMemcpyFromSymbol(&v, g_flag_error, sizeof v));
+    if (v) ES_CUDA_CHECK(cudaMemcpyToSymbol(g_flag_error, &zero, sizeof zero));
+    return v;
 }
 
 void launch_pull_copy(void const* src, void* dst, uint64_t bytes, cudaStream_t s)

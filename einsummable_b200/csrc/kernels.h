@@ -67,6 +67,15 @@ void launch_fill_lowertri(int          dtype,
                           cudaStream_t s,
                           void*        out);
 
+// Cross-GPU flags for move hand-shakes between processes that each drive one GPU.
+// A flag is a 32-bit word in memory both GPUs can address (peer-mapped).
+//   signal: wait (bounded) until *flag == 0, then store 1 (system-scope release)
+//   wait  : wait (bounded) until *flag == 1, then store 0 (the flag is local)
+// A wait that exceeds `limit_ms` records an error word and returns; nothing traps.
+void launch_flag_signal(uint32_t* flag, uint32_t limit_ms, cudaStream_t s);
+void launch_flag_wait(uint32_t* flag, uint32_t limit_ms, cudaStream_t s);
+unsigned int read_and_clear_flag_error();
+
 // SM pull-copy: 128-bit loads from `src` (possibly peer-mapped) into local `dst`.
 void launch_pull_copy(void const* src, void* dst, uint64_t bytes, cudaStream_t s);
 

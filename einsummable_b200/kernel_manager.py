@@ -179,6 +179,18 @@ class kernel_manager_t:
         _lib.check(self._lib.es_b200_move(
             self._h, src_device, _ptr(src), self.device, _ptr(dst), int(nbytes), _stream(stream)))
 
+    def flag_signal(self, flag, stream, limit_ms=0):
+        """Stream-ordered: wait until the (peer-visible) flag is 0, then set it to 1."""
+        _lib.check(self._lib.es_b200_flag_signal(self._h, _ptr(flag), int(limit_ms), _stream(stream)))
+
+    def flag_wait(self, flag, stream, limit_ms=0):
+        """Stream-ordered: wait until the local flag is 1, then reset it to 0."""
+        _lib.check(self._lib.es_b200_flag_wait(self._h, _ptr(flag), int(limit_ms), _stream(stream)))
+
+    def pull(self, src, dst, nbytes, stream):
+        """SM copy from a peer-mapped source into local memory."""
+        _lib.check(self._lib.es_b200_pull(self._h, _ptr(src), _ptr(dst), int(nbytes), _stream(stream)))
+
     def rowsum_f32_noalloc(self, stream, out, inn, rows, cols):
         """out[a] = sum_b inn[a,b] for f32 without any device allocation: the
         scratch of the two-pass reduction is a fixed array inside the library

@@ -51,10 +51,16 @@ def _blocks_of(shape, partdims):
 
 
 class memgraph_runner_t:
-    def __init__(self, mg, devices=None, rank=None, world=None):
+    def __init__(self, mg, devices=None, rank=None, world=None, transport="nccl", wait_limit_ms=0):
+        """transport (one process per GPU only): "nccl" = send/recv pairs; "p2p" = every
+        location buffer lives in symmetric memory, the destination rank pulls the bytes over
+        NVLink with an SM copy kernel, and the two ranks hand-shake through bounded flag
+        kernels (data ready / copy finished)."""
         self.mg = mg
         self.num_locs = mg["num_locs"]
         self.distributed = rank is not None
+        self.transport = transport if self.distributed else "local"
+        self.wait_limit_ms = wait_limit_ms
         if self.distributed:
             if world != self.num_locs:
                 raise ValueError("one process per location: world size %d != %d locations" % (world, self.num_locs))
@@ -69,10 +75,35 @@ class memgraph_runner_t:
             if dev not in self.kms:
                 self.kms[dev] = kernel_manager_t(dev)
         self.buffers = {}
-        for loc, dev in self.devices.items():
-            size = int(mg["mem_sizes"][loc]) + 256
-            self.buffers[loc] = torch.zeros(size, dtype=torch.uint8, device="cuda:%d" % dev)
+        if self.transport == "p2p":
+            self._alloc_symmetric()
+        else:
+            for loc, dev in self.devices.items():
+                size = int(mg["mem_sizes"][loc]) + 256
+                self.buffers[loc] = torch.zeros(size, dtype=torch.uint8, device="cuda:%d" % dev)
         self._prepare()
+
+    def _alloc_symmetric(self):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        self.cross_moves = [n["id"] for n in self.mg["nodes"] if n["kind"] == "move" and n["src_loc"] != n["dst_loc"]]
+        self.move_index = {nid: k for k, nid in enumerate(self.cross_moves)}
+        nm = len(self.cross_moves)
+        self.flag_off = (int(max(self.mg["mem_sizes"])) + 256 + 255) // 256 * 256
+        total = self.flag_off + 8 * nm + 256
+        dev = self.devices[self.rank]
+        buf = symm_mem.empty(total, dtype=torch.uint8, device="cuda:%d" % dev)
+        buf.zero_()
+        torch.cuda.synchronize(dev)
+        hdl = symm_mem.rendezvous(buf, dist.group.WORLD)
+        self.peer_base = [int(p) for p in hdl.buffer_ptrs]
+        self._symm_handle = hdl
+        self.buffers[self.rank] = buf
+        dist.barrier()
+
+    def _flag_ptr(self, owner_rank, kind, k):
+        """kind 0: ready flag (in the destination's buffer), 1: done flag (in the source's buffer)."""
+        return self.peer_base[owner_rank] + self.flag_off + 4 * (kind * len(self.cross_moves) + k)
 
     def owns(self, loc):
         return loc in self.devices
@@ -90,11 +121,35 @@ class memgraph_runner_t:
         self.stats = {"einsummable": 0, "touch": 0, "move": 0, "fill": 0, "move_bytes": 0}
         self._last_global_kind = None
         prev_kind = None
+        # p2p transport: a source rank must not touch memory a peer is still reading.  For every
+        # node, the set of this rank's outgoing moves it depends on through chains of bookkeeping
+        # nodes (del -> alloc -> ...); before such a node runs the move's "done" flag is awaited.
+        self._pending_done = set()
+        waits_for = {}
+        if self.transport == "p2p":
+            bookkeeping = ("alloc", "del", "inputmem", "partialize")
+            for node in self.mg["nodes"]:
+                acc = set()
+                for i in node["inns"]:
+                    dep = self.mg["nodes"][i]
+                    if dep["kind"] == "move" and dep["src_loc"] != dep["dst_loc"] and dep["src_loc"] == self.rank:
+                        acc.add(i)
+                    elif dep["kind"] in bookkeeping:
+                        acc |= waits_for.get(i, set())
+                waits_for[node["id"]] = acc
         for node in self.mg["nodes"]:
             kind = node["kind"]
             # bookkeeping nodes do not break a run of moves
             if kind in ("alloc", "del", "inputmem", "partialize"):
                 continue
+            if self.transport == "p2p":
+                node_loc = node.get("loc", node.get("dst_loc"))
+                mine = node_loc == self.rank or (kind == "move" and node["src_loc"] == self.rank)
+                if mine:
+                    for mid in sorted(waits_for.get(node["id"], ())):
+                        if mid in self._pending_done:
+                            self.program.append(("wait", self._flag_ptr(self.rank, 1, self.move_index[mid])))
+                            self._pending_done.discard(mid)
             self._last_global_kind = prev_kind
             prev_kind = kind
             if kind == "apply":
@@ -135,9 +190,19 @@ class memgraph_runner_t:
                 s, d = node["src_loc"], node["dst_loc"]
                 if self.owns(s) or self.owns(d):
                     mv = ("move", s, node["src_offset"], d, node["dst_offset"], node["size"])
+                    if self.transport == "p2p" and s != d:
+                        k = self.move_index[node["id"]]
+                        if self.rank == s:
+                            self.program.append(("signal", self._flag_ptr(d, 0, k)))
+                            self._pending_done.add(node["id"])
+                        else:
+                            self.program.append(("wait", self._flag_ptr(d, 0, k)))
+                            self.program.append(("pull", self.peer_base[s] + node["src_offset"], d, node["dst_offset"],
+                                                 node["size"]))
+                            self.program.append(("signal", self._flag_ptr(s, 1, k)))
                     # A run of move nodes that are adjacent in the memgraph's global order is the same
                     # run on every rank, so its cross-rank members can be posted as one NCCL group.
-                    if (self.distributed and s != d and self.program and self.program[-1][0] == "move_batch"
+                    elif (self.distributed and s != d and self.program and self.program[-1][0] == "move_batch"
                             and self._last_global_kind == "move"):
                         self.program[-1][1].append(mv)
                     elif self.distributed and s != d:
@@ -151,6 +216,11 @@ class memgraph_runner_t:
                     self.program.append(("move", node["loc"], node["src_offset"], node["loc"], node["dst_offset"],
                                          node["size"]))
             # inputmem, alloc, del, partialize: bookkeeping nodes, nothing to launch
+        # outgoing moves nobody on this rank depended on: their sources may be overwritten by the next
+        # run, so the run ends by collecting their "done" flags (which also leaves every flag at zero)
+        for mid in sorted(self._pending_done):
+            self.program.append(("wait", self._flag_ptr(self.rank, 1, self.move_index[mid])))
+        self._pending_done = set()
         self.workspace = {}
         for loc, need in ws_need.items():
             dev = self.devices[loc]
@@ -215,6 +285,13 @@ class memgraph_runner_t:
                 self._move(op, stream)
             elif kind == "move_batch":
                 self._move_batch(op[1])
+            elif kind == "signal":
+                self.km(self.rank).flag_signal(op[1], stream, self.wait_limit_ms)
+            elif kind == "wait":
+                self.km(self.rank).flag_wait(op[1], stream, self.wait_limit_ms)
+            elif kind == "pull":
+                _, src_ptr, d, d_off, size = op
+                self.km(d).pull(src_ptr, self.ptr(d, d_off), size, stream)
 
     def _stream(self, loc, stream):
         return stream

@@ -197,6 +197,21 @@ int es_b200_move(es_b200_t*  h,
                  uint64_t    bytes,
                  void*       stream);
 
+/* move_t between two processes that each drive one GPU (the reference drives all
+ * GPUs of a box from one process and needs no hand-shake: src/engine/gpu/exec_graph.cc:406-467;
+ * these three calls have no counterpart there).  `flag` is a zero-initialised 32-bit word
+ * in memory both GPUs can address (e.g. symmetric / IPC-mapped memory):
+ *   es_b200_flag_signal : stream-ordered; waits until *flag == 0, then stores 1.  Used on the
+ *                         peer's flag ("my data is ready" / "I have finished reading").
+ *   es_b200_flag_wait   : stream-ordered; waits until *flag == 1, then stores 0.
+ *   es_b200_pull        : SM copy of `bytes` from a peer-mapped `src` into local `dst`
+ *                         (128-bit loads over NVLink), any size.
+ * Waits are bounded by limit_ms (0 = 2000 ms): on expiry the kernel records an error word
+ * (bits 8..15 of es_b200_device_status: 1 = signal, 2 = wait) and returns; nothing traps. */
+int es_b200_flag_signal(es_b200_t* h, void* flag, uint32_t limit_ms, void* stream);
+int es_b200_flag_wait(es_b200_t* h, void* flag, uint32_t limit_ms, void* stream);
+int es_b200_pull(es_b200_t* h, const void* src, void* dst, uint64_t bytes, void* stream);
+
 /* Introspection: "kind|merged str|vector width|..." of a built kernel. */
 int es_b200_kernel_info(es_b200_t* h, uint64_t kernel_id, char* buf, int buf_len);
 
