@@ -375,12 +375,16 @@ def run_gpu(args):
     torch.cuda.synchronize(dev)
     e2e_ok = bool(torch.equal(o_silu.cpu(), h_silu) and torch.equal(o_sum.cpu(), h_sum))
 
-    # ---- config 4: LLaMA-7B-shape layer forward, the reference's own memgraph for `world` GPUs ----
-    llama = None
+    # ---- configs 4 and 5: LLaMA-7B-shape graphs, the reference's own memgraphs for `world` GPUs ----
+    llama, llama_train = None, None
     try:
         llama = llama_layer_leg(rank, world, dev)
     except Exception as exc:  # reported, never hidden
         llama = {"error": repr(exc)[:300]}
+    try:
+        llama_train = llama_layer_leg(rank, world, dev, fixture="llama7b_train_l4", runs=5)
+    except Exception as exc:  # reported, never hidden
+        llama_train = {"error": repr(exc)[:300]}
 
     if rank != 0:
         if world > 1:
@@ -420,6 +424,7 @@ def run_gpu(args):
                                              [BYTES_SILU_MUL, BYTES_ROWMAX, BYTES_EXP_SUB, BYTES_ROWSUM])},
         "classes": classes,
         "llama7b_layer": llama,
+        "llama7b_train_4layers": llama_train,
         "cpu_baseline": cpu_baseline() if world == 1 else None,
     }
     print(json.dumps(line))
@@ -428,14 +433,15 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
-def llama_layer_leg(rank, world, dev, runs=10):
-    """tokens/s of one LLaMA-7B-shape transformer layer forward (dim 4096, 32 heads, FFN 11008,
-    B=4, S=512, f16, plus final norm and last-token vocabulary projection), executed from the
-    memgraph the reference's compilers produce for `world` locations; one process per GPU, moves
-    over NCCL send/recv.  Synthetic N(0, 0.02) weights."""
+def llama_layer_leg(rank, world, dev, fixture="llama7b_layer", runs=10):
+    """tokens/s of a LLaMA-7B-shape graph (dim 4096, 32 heads, FFN 11008, B=4, S=512, f16) executed
+    from the memgraph the reference's compilers produce for `world` locations, one process per GPU,
+    moves over peer memory (or NCCL send/recv).  `llama7b_layer`: one transformer layer forward plus
+    final norm and last-token vocabulary projection.  `llama7b_train_l4`: four layers forward, the
+    log-softmax loss, backward and the vanilla weight update.  Synthetic N(0, 0.02) weights."""
     import torch
     from einsummable_b200.memgraph import load_memgraph, memgraph_runner_t
-    path = os.path.join(ROOT, "tests", "golden", "graphs", "llama7b_layer_locs%d.json.gz" % world)
+    path = os.path.join(ROOT, "tests", "golden", "graphs", "%s_locs%d.json.gz" % (fixture, world))
     if not os.path.exists(path):
         return {"skipped": "no memgraph fixture for %d locations" % world}
     mg = load_memgraph(path)
@@ -460,6 +466,9 @@ def llama_layer_leg(rank, world, dev, runs=10):
             v = (np.cos(ang) + 1j * np.sin(ang)).astype(np.complex64)
         elif name.endswith("norm.weight"):
             v = np.ones(shape, dtype=np.float16)
+        elif name == "labels":
+            v = np.zeros(shape, dtype=np.float16)
+            v[np.arange(shape[0]), rng.integers(0, shape[1], shape[0])] = 1.0
         else:
             v = (rng.standard_normal(shape).astype(np.float32) * 0.02).astype(np.float16)
         r.set_input(name, v)
@@ -503,6 +512,10 @@ def llama_layer_leg(rank, world, dev, runs=10):
     except Exception as exc:
         out["cuda_graph"] = {"error": repr(exc)[:200]}
     out["device_status"] = r.device_status()
+    r.graph = None
+    r.close()
+    del r
+    torch.cuda.empty_cache()
     return out
 
 

@@ -85,6 +85,13 @@ struct alignas(64) tc_params_t {
     int32_t     out_nd;
     int8_t      out_src[8]; // SRC_MN_TILE (row), SRC_N_TILE (column) or SRC_OUTER0+j per TMA dim
     uint32_t    staging_offset; // byte offset of the epilogue staging buffers inside dynamic smem
+    // 256-row work items ("big": two 128-row halves that share one B tile in shared memory, each
+    // with its own accumulator slot) followed by 128-row items for the tail of the schedule
+    uint32_t    mh;          // 2 when big items exist (the A region of a stage then holds two tiles)
+    uint32_t    m_pairs;     // m_tiles / 2
+    uint32_t    n_big;       // big items come first in the item order
+    uint32_t    pair_small;  // 128-row items cut from the row pairs that are not big items
+    uint32_t    total_items;
 };
 
 __device__ unsigned int g_tc_error; // nonzero = a bounded wait expired (code, see below)
@@ -286,6 +293,44 @@ decode_tile(tc_params_t const& p, uint32_t tile, uint32_t& m_tile, uint32_t& n_t
     }
 }
 
+// Work item -> (first 128-row tile, halves, column tile, outer indices).  Without big items this is
+// decode_tile.  With them: items [0, n_big) are row pairs (2j, 2j+1) of one column tile; the next
+// pair_small items are the single rows of the remaining pairs; the rest is the unpaired last row.
+template <bool BIG>
+__device__ __forceinline__ void decode_item(tc_params_t const& p, uint32_t it, uint32_t& m_tile, uint32_t& halves,
+                                            uint32_t& n_tile, uint32_t (&outer)[MAX_LOOP_MODES])
+{
+    halves = 1;
+    if constexpr (!BIG) {
+        decode_tile(p, it, m_tile, n_tile, outer);
+        return;
+    }
+    uint32_t rest;
+    if (it < p.n_big) {
+        halves = 2;
+        m_tile = 2 * (it % p.m_pairs);
+        rest = it / p.m_pairs;
+    } else if (it - p.n_big < p.pair_small) {
+        uint32_t const s = it - p.n_big, b = p.n_big + (s >> 1);
+        m_tile = 2 * (b % p.m_pairs) + (s & 1);
+        rest = b / p.m_pairs;
+    } else {
+        m_tile = p.m_tiles - 1;
+        rest = it - p.n_big - p.pair_small;
+    }
+    n_tile = rest % p.n_tiles;
+    uint32_t t = rest / p.n_tiles;
+#pragma unroll
+    for (int j = MAX_LOOP_MODES - 1; j >= 0; --j) {
+        if (j < (int)p.n_outer) {
+            outer[j] = t % p.outer_extent[j];
+            t /= p.outer_extent[j];
+        } else {
+            outer[j] = 0;
+        }
+    }
+}
+
 __device__ __forceinline__ uint32_t pick6(uint32_t const (&v)[MAX_LOOP_MODES], int i)
 {
     uint32_t r = v[0];
@@ -339,9 +384,10 @@ __device__ __forceinline__ void issue_operand(operand_t const&   o,
                                               uint32_t           n_terms,
                                               int const (&c)[5],
                                               uint32_t dst,
-                                              uint32_t bar)
+                                              uint32_t bar,
+                                              uint32_t mn_offset = 0)
 {
-    if (n_terms == 1 && o.n_boxes == 1) {
+    if (n_terms == 1 && o.n_boxes == 1 && mn_offset == 0) {
         tma_load(dst, tm, bar, o.nd, c);
         return;
     }
@@ -349,13 +395,13 @@ __device__ __forceinline__ void issue_operand(operand_t const&   o,
         for (uint32_t bx = 0; bx < o.n_boxes; ++bx) {
             int cc[5];
 #pragma unroll
-            for (int d = 0; d < 5; ++d) cc[d] = c[d] + (d == o.box_dim ? (int)(bx * o.box_step) : 0);
+            for (int d = 0; d < 5; ++d) cc[d] = c[d] + (d == o.box_dim ? (int)(mn_offset + bx * o.box_step) : 0);
             tma_load(dst + t * o.tile_bytes + bx * o.box_bytes, &tm[t], bar, o.nd, cc);
         }
     }
 }
 
-template <int KIND, bool PROMOTE>
+template <int KIND, bool PROMOTE, bool BIG> // BIG: the schedule holds 256-row items (p.mh == 2)
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ out_)
 {
@@ -394,16 +440,17 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
 
     uint32_t const k_iters = p.k_blocks * p.kouter_total;
     uint32_t const term_a_bytes = p.a.tile_bytes, term_b_bytes = p.b.tile_bytes;
-    uint32_t const a_region = term_a_bytes * p.n_terms; // A tiles first, then B tiles
+    uint32_t const a_region = term_a_bytes * p.n_terms * (BIG ? 2u : 1u); // A tiles first, then B tiles
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool     ok = true;
-            for (uint32_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
-                uint32_t m_tile, n_tile, outer[MAX_LOOP_MODES];
-                decode_tile(p, tile, m_tile, n_tile, outer);
+            for (uint32_t tile = blockIdx.x; tile < p.total_items && ok; tile += gridDim.x) {
+                uint32_t m_tile, halves, n_tile, outer[MAX_LOOP_MODES];
+                decode_item<BIG>(p, tile, m_tile, halves, n_tile, outer);
+                uint32_t const tx_bytes = p.stage_bytes - ((BIG ? 2u : 1u) - halves) * term_a_bytes;
                 int base_a[5], base_b[5];
                 tile_coords(p.a, m_tile * BM, outer, base_a);
                 tile_coords(p.b, n_tile * p.bn, outer, base_b);
@@ -415,9 +462,10 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
                 for (uint32_t ki = 0; ki < k_iters; ++ki) {
                     if (!mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, 1)) { ok = false; break; }
                     uint32_t bar = smem_u32(&ctrl->full[stage]);
-                    mbar_arrive_expect_tx(bar, p.stage_bytes);
+                    mbar_arrive_expect_tx(bar, tx_bytes);
                     uint32_t stage_base = smem_base + stage * p.stage_bytes;
                     issue_operand(p.a, p.tm_a, p.n_terms, ca, stage_base, bar);
+                    if (BIG && halves == 2) issue_operand(p.a, p.tm_a, 1, ca, stage_base + term_a_bytes, bar, BM);
                     issue_operand(p.b, p.tm_b, p.n_terms, cb, stage_base + a_region, bar);
                     if (++stage == p.stages) { stage = 0; phase ^= 1; }
                     if (++kb == p.k_blocks) {
@@ -445,7 +493,7 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            uint32_t stage = 0, phase = 0, q = 0; // q counts accumulator uses (one per k-chunk)
+            uint32_t stage = 0, phase = 0, use0 = 0, use1 = 0; // uses of each accumulator slot so far
             bool     ok = true;
             constexpr uint32_t NT = PROMOTE ? 3u : 1u; // MMAs per k-step: (lo*hi, hi*lo, hi*hi) or one
             uint64_t const a_hi = ((uint64_t)p.a.desc_hi << 32) | ((uint64_t)p.a.desc_lbo << 16);
@@ -455,12 +503,19 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
             uint32_t const a_term = term_a_bytes >> 4, b_term = term_b_bytes >> 4;
             uint32_t const idesc = p.idesc, stages = p.stages, stage_units = p.stage_bytes >> 4;
             uint32_t const a_region_units = a_region >> 4, base_units = smem_base >> 4;
-            for (uint32_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
-                for (uint32_t ki0 = 0; ki0 < k_iters && ok; ki0 += p.k_chunk, ++q) {
-                    uint32_t acc = q & 1, acc_ph = (q >> 1) & 1;
-                    if (!mbar_wait(smem_u32(&ctrl->tmem_empty[acc]), acc_ph ^ 1, abort_flag, 2)) { ok = false; break; }
+            for (uint32_t tile = blockIdx.x; tile < p.total_items && ok; tile += gridDim.x) {
+                uint32_t m_tile, halves, n_tile, outer[MAX_LOOP_MODES];
+                decode_item<BIG>(p, tile, m_tile, halves, n_tile, outer);
+                for (uint32_t ki0 = 0; ki0 < k_iters && ok; ki0 += p.k_chunk) {
+                    // accumulator slots: a big item takes both (one per half); anything else the
+                    // slot used less often so far, which alternates 0, 1, 0, ... between big items
+                    uint32_t slot0, par0, par1 = 0;
+                    if (BIG && halves == 2) { slot0 = 0; par0 = use0++ & 1; par1 = use1++ & 1; }
+                    else if (use0 <= use1) { slot0 = 0; par0 = use0++ & 1; }
+                    else { slot0 = 1; par0 = use1++ & 1; }
+                    if (!mbar_wait(smem_u32(&ctrl->tmem_empty[slot0]), par0 ^ 1, abort_flag, 2)) { ok = false; break; }
                     tc_fence_after();
-                    uint32_t const tmem_d = tmem_base + acc * p.bn;
+                    uint32_t const tmem_d = tmem_base + slot0 * p.bn;
                     uint32_t const ki1 = min(ki0 + p.k_chunk, k_iters);
                     for (uint32_t ki = ki0; ki < ki1; ++ki) {
                         uint32_t const s = stage;
@@ -481,9 +536,25 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
                                 umma<KIND>(tmem_d, da, db, idesc, (ks == 0 && t == 0) ? keep : 1u);
                             }
                         }
+                        if (BIG && halves == 2) {
+                            // second 128 rows: its own A tile and accumulator slot, the same B tile
+                            if (ki == ki0) {
+                                if (!mbar_wait(smem_u32(&ctrl->tmem_empty[1]), par1 ^ 1, abort_flag, 2)) { ok = false; break; }
+                                tc_fence_after();
+                            }
+#pragma unroll
+                            for (uint32_t ks = 0; ks < 4; ++ks) {
+                                uint64_t const da = a_hi | (uint64_t)(a0 + a_term + ks * a_kstep);
+                                uint64_t const db = b_hi | (uint64_t)(b0 + ks * b_kstep);
+                                umma<KIND>(tmem_base + p.bn, da, db, idesc, ks == 0 ? keep : 1u);
+                            }
+                        }
                         umma_commit(smem_u32(&ctrl->empty[s])); // frees the smem stage when these MMAs retire
                     }
-                    if (ok) umma_commit(smem_u32(&ctrl->tmem_full[acc]));
+                    if (ok) {
+                        umma_commit(smem_u32(&ctrl->tmem_full[slot0]));
+                        if (BIG && halves == 2) umma_commit(smem_u32(&ctrl->tmem_full[1]));
+                    }
                 }
             }
         }
@@ -493,7 +564,7 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
         // columns, so that short-K contractions (attention) are not bound by one warp's epilogue.
         uint32_t const quarter = warp & 3; // TMEM lanes 32*quarter .. +31 belong to this warp
         uint32_t const half = (uint32_t)(warp - 2) >> 2;
-        uint32_t q = 0, store_seq = 0;
+        uint32_t use0 = 0, use1 = 0, store_seq = 0; // accumulator slot uses: the MMA issuer's rule
         bool     ok = true;
         // PROMOTE: partial sums of each k-chunk are added in registers with
         // round-to-nearest f32 adds.  The tensor core's own accumulation truncates,
@@ -504,13 +575,15 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
         uint32_t const pieces = p.bn / piece_cols;
         // per-warp staging for TMA stores: 32 rows x 128 bytes, 128B-swizzled
         uint32_t const stage_buf = smem_base + p.staging_offset + (uint32_t)(warp - 2) * 4096u;
-        for (uint32_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
-            uint32_t m_tile, n_tile, outer[MAX_LOOP_MODES];
-            decode_tile(p, tile, m_tile, n_tile, outer);
+        for (uint32_t tile = blockIdx.x; tile < p.total_items && ok; tile += gridDim.x) {
+            uint32_t m_first, halves, n_tile, outer[MAX_LOOP_MODES];
+            decode_item<BIG>(p, tile, m_first, halves, n_tile, outer);
             int64_t base = 0;
 #pragma unroll
             for (int j = 0; j < MAX_LOOP_MODES; ++j)
                 if (j < (int)p.n_outer) base += (int64_t)outer[j] * p.outer_out_stride[j];
+          for (uint32_t hf = 0; hf < halves && ok; ++hf) {
+            uint32_t const m_tile = m_first + hf;
             uint32_t const m_warp = m_tile * BM + quarter * 32;
             uint32_t const m = m_warp + lane;
             uint32_t const n0 = n_tile * p.bn;
@@ -521,8 +594,11 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
                 oc[d] = sk == SRC_MN_TILE ? (int)m_warp
                         : (sk >= SRC_OUTER0 ? (int)pick6(outer, sk - SRC_OUTER0) : 0);
             }
-            for (uint32_t ki0 = 0; ki0 < k_iters && ok; ki0 += p.k_chunk, ++q) {
-                uint32_t acc = q & 1, acc_ph = (q >> 1) & 1;
+            for (uint32_t ki0 = 0; ki0 < k_iters && ok; ki0 += p.k_chunk) {
+                uint32_t acc, acc_ph;
+                if (BIG && halves == 2) { acc = hf; acc_ph = (hf == 0 ? use0++ : use1++) & 1; }
+                else if (use0 <= use1) { acc = 0; acc_ph = use0++ & 1; }
+                else { acc = 1; acc_ph = use1++ & 1; }
                 bool const first_chunk = ki0 == 0, last_chunk = ki0 + p.k_chunk >= k_iters;
                 if (!mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_ph, abort_flag, 4)) { ok = false; break; }
                 tc_fence_after();
@@ -627,6 +703,7 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&ctrl->tmem_empty[acc]));
             }
+          }
         }
         // all of this warp's stores must have read their staging buffers before smem goes away
         if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
@@ -902,6 +979,55 @@ bool plan_contraction(einsum_t const& e, int f32_policy, contraction_plan_t& pla
     // the K extent of one block must be the same for both operands: row_elems elements
     p.stage_bytes = (p.a.tile_bytes + p.b.tile_bytes) * p.n_terms;
     uint32_t const smem_budget = 227 * 1024 - 1024 /*alignment*/ - STAGING_BYTES - (uint32_t)sizeof(ctrl_t) - 64;
+    // 256-row items.  A 128 x 256 tile streams 48 KiB per k-block for 512 cycles of MMA work; the
+    // copies were measured at 750 cycles per k-block (64 bytes per clock into the SM), so the tile
+    // is bound by its operand stream, not by the tensor pipe.  Two 128-row halves that share the
+    // B tile stream 64 KiB for 1024 cycles of MMA work.  They take both accumulator slots, so the
+    // epilogue of an item overlaps the next item only half by half; and items twice as large
+    // quantise worse over 148 SMs, so the tail of the schedule falls back to 128-row items.  The
+    // split is chosen by the estimated makespan of the round-robin schedule.
+    p.mh = 1;
+    p.total_items = p.total_tiles;
+    {
+        uint32_t const k_iters = p.k_blocks * p.kouter_total;
+        uint32_t const big_stage = 2 * p.a.tile_bytes + p.b.tile_bytes;
+        bool const     eligible = dt == ES_F16 && p.n_terms == 1 && bn == 256 && p.m_tiles >= 2 && k_iters >= 16 &&
+                              smem_budget / big_stage >= 3;
+        if (eligible) {
+            uint32_t const G = 148;
+            uint64_t const rest = total / p.m_tiles;              // column tiles x outer indices
+            uint32_t const m_pairs = p.m_tiles / 2;
+            uint64_t const pairs = (uint64_t)m_pairs * rest;      // candidate big items
+            uint64_t const odd_rows = (p.m_tiles & 1) ? rest : 0; // items of the unpaired last row
+            double const   cost_small = 750.0, cost_big = 1140.0; // cycles per k-block (incl. epilogue stall)
+            auto makespan = [&](uint64_t n_big) {
+                uint64_t const n_small = 2 * (pairs - n_big) + odd_rows;
+                double         worst = 0;
+                for (uint32_t c = 0; c < G; ++c) {
+                    uint64_t big_c = n_big / G + (c < n_big % G ? 1 : 0);
+                    // small item j runs on CTA (n_big + j) % G
+                    uint64_t first = (c + G - n_big % G) % G; // smallest j with (n_big + j) % G == c
+                    uint64_t small_c = n_small > first ? (n_small - first + G - 1) / G : 0;
+                    worst = std::max(worst, big_c * cost_big + small_c * cost_small);
+                }
+                return worst;
+            };
+            uint64_t best = 0;
+            double   best_t = makespan(0);
+            for (uint64_t cand : {pairs, pairs / G * G}) {
+                double t = makespan(cand);
+                if (t < best_t) { best_t = t; best = cand; }
+            }
+            if (best > 0) {
+                p.mh = 2;
+                p.m_pairs = m_pairs;
+                p.n_big = (uint32_t)best;
+                p.pair_small = (uint32_t)(2 * (pairs - best));
+                p.total_items = (uint32_t)(best + 2 * (pairs - best) + odd_rows);
+                p.stage_bytes = big_stage;
+            }
+        }
+    }
     p.stages = std::min<uint32_t>(MAX_STAGES, smem_budget / p.stage_bytes);
     if (p.stages < 2) return false;
     p.tmem_cols = 2 * bn < 32 ? 32 : 2 * bn; // 128, 256 or 512: powers of two
@@ -944,7 +1070,7 @@ bool plan_contraction(einsum_t const& e, int f32_policy, contraction_plan_t& pla
             }
         }
     }
-    tp.grid = std::min<uint32_t>(p.total_tiles, 148);
+    tp.grid = std::min<uint32_t>(p.total_items, 148);
     tp.a_elems = e.inn_nelem(ia);
     tp.b_elems = e.inn_nelem(ib);
     tp.swap = swap ? 1 : 0;
@@ -972,7 +1098,11 @@ bool plan_contraction(einsum_t const& e, int f32_policy, contraction_plan_t& pla
     tp.ws_b_offset = a_ws;
     plan.workspace_bytes = (a_ws + b_ws) * 4;
     plan.info = "bm=128,bn=" + std::to_string(bn) + ",bk=" + std::to_string(row_elems) + ",stages=" +
-                std::to_string(p.stages) + ",tiles=" + std::to_string(p.total_tiles) + ",a=" +
+                std::to_string(p.stages) + ",tiles=" + std::to_string(p.total_tiles) +
+                (p.mh == 2 ? ",items256=" + std::to_string(p.n_big) + ",items128=" +
+                                 std::to_string(p.total_items - p.n_big)
+                           : std::string()) +
+                ",a=" +
                 (a_mn ? "mn" : "k") + "-major,b=" + (b_mn ? "mn" : "k") + "-major" + (swap ? ",swapped" : "") +
                 (a_perm ? ",a-prepermuted" : "") + (b_perm ? ",b-prepermuted" : "");
     plan.blob.resize(sizeof tp);
@@ -1033,7 +1163,7 @@ void launch_contraction(contraction_plan_t const& plan,
         p.out_tma = 1;
     }
     auto launch = [&](auto kernel, int slot) {
-        static bool attr_set[3][64] = {};
+        static bool attr_set[4][64] = {};
         int         dev = 0;
         cudaGetDevice(&dev);
         if (!attr_set[slot][dev & 63]) {
@@ -1042,9 +1172,10 @@ void launch_contraction(contraction_plan_t const& plan,
         }
         kernel<<<tp.grid, NUM_THREADS, tp.smem_bytes, stream>>>(p, out);
     };
-    if (tp.kind == 0) launch(tc_contraction_kernel<0, false>, 0);
-    else if (tp.promote) launch(tc_contraction_kernel<1, true>, 1);
-    else launch(tc_contraction_kernel<1, false>, 2);
+    if (tp.kind == 0 && p.mh == 2) launch(tc_contraction_kernel<0, false, true>, 3);
+    else if (tp.kind == 0) launch(tc_contraction_kernel<0, false, false>, 0);
+    else if (tp.promote) launch(tc_contraction_kernel<1, true, false>, 1);
+    else launch(tc_contraction_kernel<1, false, false>, 2);
     ES_CUDA_CHECK(cudaGetLastError());
 }
 

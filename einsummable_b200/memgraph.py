@@ -50,6 +50,36 @@ def _blocks_of(shape, partdims):
         yield tuple(slice(int(starts[d][i]), int(starts[d][i + 1])) for d, i in enumerate(idx))
 
 
+def move_runs(mg):
+    """Run number of every move node.  A run is a stretch of move nodes that are adjacent in the
+    memgraph's global order (bookkeeping nodes aside) and do not depend on one another, so a rank
+    may post its members of a run as one NCCL group.  The numbering uses the whole graph only:
+    every rank cuts its groups at the same places.  (Groups that straddle a cut on one rank but
+    not on its peer can wait on each other for ever.)"""
+    bookkeeping = ("alloc", "del", "inputmem", "partialize")
+    moved_from = {}
+    runs = {}
+    run_id, members = 0, set()
+    for node in mg["nodes"]:
+        acc = set()
+        for i in node["inns"]:
+            dep = mg["nodes"][i]
+            if dep["kind"] == "move":
+                acc.add(i)
+            elif dep["kind"] in bookkeeping:
+                acc |= moved_from.get(i, set())
+        moved_from[node["id"]] = acc
+        if node["kind"] in bookkeeping:
+            continue
+        if node["kind"] != "move" or (acc & members):
+            run_id += 1
+            members = set()
+        if node["kind"] == "move":
+            members.add(node["id"])
+            runs[node["id"]] = run_id
+    return runs
+
+
 class memgraph_runner_t:
     def __init__(self, mg, devices=None, rank=None, world=None, transport="nccl", wait_limit_ms=0):
         """transport (one process per GPU only): "nccl" = send/recv pairs; "p2p" = every
@@ -119,8 +149,7 @@ class memgraph_runner_t:
         self.program = []
         ws_need = {loc: 0 for loc in self.devices}
         self.stats = {"einsummable": 0, "touch": 0, "move": 0, "fill": 0, "move_bytes": 0}
-        self._last_global_kind = None
-        prev_kind = None
+        move_run = move_runs(self.mg) if self.transport == "nccl" else {}
         # p2p transport: a source rank must not touch memory a peer is still reading.  For every
         # node, the set of this rank's outgoing moves it depends on through chains of bookkeeping
         # nodes (del -> alloc -> ...); before such a node runs the move's "done" flag is awaited.
@@ -150,8 +179,6 @@ class memgraph_runner_t:
                         if mid in self._pending_done:
                             self.program.append(("wait", self._flag_ptr(self.rank, 1, self.move_index[mid])))
                             self._pending_done.discard(mid)
-            self._last_global_kind = prev_kind
-            prev_kind = kind
             if kind == "apply":
                 loc = node["loc"]
                 if not self.owns(loc):
@@ -200,13 +227,17 @@ class memgraph_runner_t:
                             self.program.append(("pull", self.peer_base[s] + node["src_offset"], d, node["dst_offset"],
                                                  node["size"]))
                             self.program.append(("signal", self._flag_ptr(s, 1, k)))
-                    # A run of move nodes that are adjacent in the memgraph's global order is the same
-                    # run on every rank, so its cross-rank members can be posted as one NCCL group.
+                    # The cross-rank members of one run (move_runs) are posted as one NCCL group.
                     elif (self.distributed and s != d and self.program and self.program[-1][0] == "move_batch"
-                            and self._last_global_kind == "move"):
+                            and self.program[-1][2] == move_run[node["id"]]):
                         self.program[-1][1].append(mv)
                     elif self.distributed and s != d:
-                        self.program.append(("move_batch", [mv]))
+                        self.program.append(("move_batch", [mv], move_run[node["id"]]))
+                    elif (self.distributed and self.program and self.program[-1][0] == "move_batch"
+                            and self.program[-1][2] == move_run.get(node["id"])):
+                        # a local copy inside a run: members of a run are independent, so it goes in
+                        # front of the group instead of splitting it on this rank only
+                        self.program.insert(len(self.program) - 1, mv)
                     else:
                         self.program.append(mv)
                     self.stats["move"] += 1

@@ -6,6 +6,9 @@
 //     alocate01 (src/autoplace/alocate.h:20-23)
 //   * configs 4: builder_t::make_first_token (llama/builder.cc:3-77) +
 //     autoplace01(make_default01) (src/autoplace/autoplace.h:40-66)
+//   * config 5: transformer_t forward, the log-softmax loss and graph_writer_t::backprop as
+//     llama/gpu_train.cc:154-322 builds them (without LoRA), plus the vanilla update
+//     w - lr * g of src/misc/update.cc:13-30 with the learning rate as a constant
 //   then taskgraph_t::make (src/einsummable/taskgraph.h:15-19) and
 //   memgraph_t::make_without_evict with gpu_alignment_settings
 //   (src/einsummable/memgraph.h:117-147).
@@ -20,6 +23,7 @@
 #include "src/autoplace/autoplace.h"
 #include "src/autoplace/alocate.h"
 #include "llama/builder.h"
+#include "llama/modules.h"
 
 #include <fstream>
 
@@ -197,6 +201,87 @@ int ref_graph_build_llama(uint64_t dim,
         b->names[builder.mask.value()] = "mask";
     }
     b->names[builder.scores] = "scores";
+    return finish(b);
+    G_END
+}
+
+// config 5: forward + backward + vanilla weight update of n_layers LLaMA layers
+int ref_graph_build_llama_train(uint64_t dim,
+                                uint64_t n_heads,
+                                uint64_t multiple_of,
+                                uint64_t vocab_size,
+                                int      n_layers,
+                                uint64_t batch,
+                                uint64_t seqlen,
+                                int      nlocs,
+                                int      dtype_code,
+                                double   learning_rate,
+                                int      save_grads)
+{
+    G_BEGIN
+    dtype_t dtype = dtype_code == 0 ? dtype_t::f16 : dtype_t::f32;
+    set_default_dtype(dtype);
+    model_args_t args = model_args_t::llama_7B(batch);
+    args.dim = dim;
+    args.n_heads = n_heads;
+    args.multiple_of = multiple_of;
+    args.vocab_size = vocab_size;
+    args.n_layers = n_layers;
+    args.max_seq_len = seqlen;
+    auto* b = new built_graph_t();
+    {
+        graph_writer_t writer;
+        transformer_t  model(&writer, args, 0);
+        tensor_t       embeddings = writer.input(full_shape_t(
+            {full_dim_t::singleton(args.batch_size), full_dim_t::singleton(seqlen), args.full_dim()}));
+        tensor_t predictions = model.forward(embeddings);
+        tensor_t labels = writer.input(vector<uint64_t>{args.batch_size, args.vocab_size}, dtype);
+        tensor_t loss;
+        {
+            tensor_t v = predictions;
+            tensor_t c = writer.reduction("bv->b", castable_t::max, v);
+            v = writer.ew("bv,b->bv", scalarop_t::make_sub(dtype), v, c);
+            tensor_t ev = writer.ew(scalarop_t::make_exp(dtype), v);
+            tensor_t evsubset = writer.contraction("bv,bv->b", ev, labels);
+            tensor_t evsum = writer.reduction("bv->b", castable_t::add, ev);
+            tensor_t lll = writer.ew("b,b->b", scalarop_t::make_div(dtype), evsubset, evsum);
+            lll = writer.ew(scalarop_t::make_log(dtype), lll);
+            loss = lll.scale(scalar_t(dtype, write_with_ss(1.0 / double(args.batch_size))));
+        }
+        loss.save_inplace();
+        vector<tensor_t> ws;
+        vector<string>   wnames;
+        for (auto [name, tensor] : model.weight_map()) {
+            ws.push_back(tensor);
+            wnames.push_back(name);
+            b->names[tensor.get_id()] = name;
+        }
+        vector<tensor_t> grads = writer.backprop(loss, ws);
+        b->names[embeddings.get_id()] = "embeddings";
+        b->names[labels.get_id()] = "labels";
+        b->names[loss.get_id()] = "loss";
+        b->names[model.full_freqs_cis.get_id()] = "freqs_cis";
+        vector<int> weight_ids = vector_from_each_method(ws, int, get_id);
+        vector<int> grad_ids = vector_from_each_method(grads, int, get_id);
+        b->graph = writer.get_graph();
+        scalarop_t update = scalarop_t::combine(
+            scalarop_t::make_sub(dtype),
+            {scalarop_t::make_identity(dtype),
+             scalarop_t::make_scale(scalar_t(dtype, write_with_ss(learning_rate)))});
+        for (size_t i = 0; i != weight_ids.size(); ++i) {
+            vector<uint64_t> shape = b->graph.out_shape(weight_ids[i]);
+            int              rank = shape.size();
+            einsummable_t    e(shape, vector<vector<int>>(2, vector_iota<int>(rank)), rank, update);
+            int              id = b->graph.insert_einsummable(e, {weight_ids[i], grad_ids[i]});
+            b->graph.nodes[id].op.set_save(true);
+            b->names[id] = "new." + wnames[i];
+            if (save_grads) {
+                b->graph.nodes[grad_ids[i]].op.set_save(true);
+                b->names[grad_ids[i]] = "grad." + wnames[i];
+            }
+        }
+    }
+    b->placements = autoplace01(b->graph, autoplace_config_t::make_default01(nlocs, 1));
     return finish(b);
     G_END
 }

@@ -8,13 +8,18 @@ memgraph pipeline emits for that graph and placement).  For the small cases also
 seeded inputs and the outputs of the reference's reference_compute_memgraph on
 them (graphs.npz).  Runs only where the reference tree exists.
 
-usage: python tests/golden/make_graphs.py
+The full-size training graphs take the reference's autoplacer and memgraph
+compiler up to half an hour each (8 locations: 49003 memgraph nodes), so an
+existing file is kept unless --force is given.
+
+usage: python tests/golden/make_graphs.py [--force]
 """
 import ctypes
 import gzip
 import json
 import os
 import shutil
+import sys
 
 import numpy as np
 
@@ -129,6 +134,36 @@ def main():
         h = ok(L.ref_graph_build_llama(u64(4096), u64(32), u64(256), u64(32000), 1, u64(4), u64(512), nlocs, 0))
         mg = write_json(h, "llama7b_layer_locs%d" % nlocs, True)
         print("llama 7B layer", nlocs, "locs:", mg["taskgraph"], "nodes", len(mg["nodes"]))
+
+    # config 5, tiny: forward + backward + vanilla update in f32 through the reference's interpreter;
+    # the gradients themselves are saved so that the comparison is not swamped by the weights
+    for nlocs in (1, 2):
+        h = ok(L.ref_graph_build_llama_train(u64(64), u64(2), u64(32), u64(128), 1, u64(2), u64(16), nlocs, 1,
+                                             ctypes.c_double(0.01), 1))
+        name = "llama_train_tiny_locs%d" % nlocs
+        mg = write_json(h, name, True)
+        ins = llama_inputs(mg, np.random.default_rng(3), 0.3)
+        labels = np.zeros((2, 128), dtype=np.float32)
+        labels[0, 5] = labels[1, 77] = 1.0
+        ins["labels"] = labels
+        outs = run_reference(h, mg, ins)
+        for k, v in ins.items():
+            arrays["%s/in/%s" % (name, k)] = v
+        for k, v in outs.items():
+            arrays["%s/out/%s" % (name, k)] = v
+        print(name, mg["taskgraph"], "loss", outs["loss"])
+
+    # config 5, LLaMA-7B shape (graph only): 4 layers forward + backward + update, f16, B=4, S=512
+    force = "--force" in sys.argv[1:]
+    for n_layers, nlocs in ((1, 1), (4, 1), (4, 2), (4, 4), (4, 8)):
+        name = "llama7b_train_l%d_locs%d" % (n_layers, nlocs)
+        if os.path.exists(os.path.join(OUT, name + ".json.gz")) and not force:
+            print(name, "kept")
+            continue
+        h = ok(L.ref_graph_build_llama_train(u64(4096), u64(32), u64(256), u64(32000), n_layers, u64(4), u64(512),
+                                             nlocs, 0, ctypes.c_double(1e-3), 0))
+        mg = write_json(h, name, True)
+        print(name, mg["taskgraph"], "nodes", len(mg["nodes"]))
 
     np.savez_compressed(os.path.join(OUT, "graphs.npz"), **arrays)
 

@@ -66,6 +66,22 @@ def test_f16_contractions(km, spec, extents):
     check(km, spec, extents, "f16")
 
 
+@pytest.mark.parametrize("spec,extents,big,small", [
+    ("ij,kj->ik", dict(i=2048, j=1024, k=4096), 128, 0),     # every row pair is one 256-row item
+    ("ij,kj->ik", dict(i=2176, j=1024, k=2816), 88, 11),     # odd number of 128-row tiles: last row alone
+    ("ij,kj->ik", dict(i=2048, j=1024, k=5632), 148, 56),    # one wave of 256-row items, 128-row tail
+    ("ij,kj->ik", dict(i=2000, j=1032, k=4100), 136, 0),     # ragged M, N and K
+    ("ji,kj->ik", dict(i=2048, j=1024, k=4096), 128, 0),     # A MN-major: two copies per half
+    ("ij,jk->ik", dict(i=2048, j=1024, k=4096), 128, 0),     # B MN-major
+    ("bij,bkj->bik", dict(b=2, i=1024, j=1024, k=2560), 80, 0),   # batched
+])
+def test_f16_contractions_256_row_items(km, spec, extents, big, small):
+    """Large f16 contractions schedule 256-row items (two 128-row halves sharing one B tile in
+    shared memory) first and 128-row items for the tail; both kinds in one launch."""
+    info = check(km, spec, extents, "f16")
+    assert "items256=%d,items128=%d" % (big, small) in info, info
+
+
 @pytest.mark.parametrize("spec,extents", [
     ("ij,jk->ik", dict(i=256, j=256, k=256)),
     ("ij,kj->ik", dict(i=128, j=512, k=256)),

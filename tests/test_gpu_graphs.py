@@ -19,7 +19,13 @@ from einsummable_b200.memgraph import load_memgraph, memgraph_runner_t
 pytestmark = pytest.mark.gpu
 GRAPHS = os.path.join(GOLDEN_DIR, "graphs")
 ARR = np.load(os.path.join(GRAPHS, "graphs.npz"))
-SMALL = ["c1_n64_locs1", "c1_n64_locs2", "llama_tiny_locs1", "llama_tiny_locs2", "llama_tiny_locs4"]
+SMALL = ["c1_n64_locs1", "c1_n64_locs2", "llama_tiny_locs1", "llama_tiny_locs2", "llama_tiny_locs4",
+         "llama_train_tiny_locs1", "llama_train_tiny_locs2"]
+
+
+def graph_path(name):
+    path = os.path.join(GRAPHS, name + ".json")
+    return path if os.path.exists(path) else path + ".gz"
 
 
 def inputs_of(name):
@@ -34,7 +40,7 @@ def outputs_of(name):
 
 @pytest.mark.parametrize("name", SMALL)
 def test_small_memgraphs_match_oracle_and_reference(name):
-    mg = load_memgraph(os.path.join(GRAPHS, name + ".json"))
+    mg = load_memgraph(graph_path(name))
     ins = inputs_of(name)
     r = memgraph_runner_t(mg)
     for k, v in ins.items():
@@ -51,8 +57,11 @@ def test_small_memgraphs_match_oracle_and_reference(name):
         scale = np.abs(ref.astype(np.float64)).max()
         err_oracle = np.abs(got.astype(np.float64) - oracle[k].astype(np.float64)).max()
         err_ref = np.abs(got.astype(np.float64) - ref.astype(np.float64)).max()
-        assert err_oracle <= (1e-2 if f16 else 1e-5) * scale, (name, k, err_oracle, scale)
-        assert err_ref <= (2e-2 if f16 else 1e-5) * scale, (name, k, err_ref, scale)
+        # backward pass: gradients that are small differences of large sums move by 1e-5 of their
+        # own scale with the summation order alone, hence 1e-4 for the training graphs (f32)
+        tol32 = 1e-4 if name.startswith("llama_train") else 1e-5
+        assert err_oracle <= (1e-2 if f16 else tol32) * scale, (name, k, err_oracle, scale)
+        assert err_ref <= (2e-2 if f16 else tol32) * scale, (name, k, err_ref, scale)
     # a second run of the same program gives the same bits (groups reset per run)
     first = {k: r.get_output(k).copy() for k in outputs_of(name)}
     r.run()
