@@ -391,6 +391,15 @@ __device__ __forceinline__ void issue_operand(operand_t const&   o,
         tma_load(dst, tm, bar, o.nd, c);
         return;
     }
+    if (o.n_boxes == 1) {
+        // one copy per term: no loops, coordinates stay in registers
+        int cc[5];
+#pragma unroll
+        for (int d = 0; d < 5; ++d) cc[d] = c[d] + (d == o.box_dim ? (int)mn_offset : 0);
+        tma_load(dst, &tm[0], bar, o.nd, cc);
+        if (n_terms == 2) tma_load(dst + o.tile_bytes, &tm[1], bar, o.nd, cc);
+        return;
+    }
     for (uint32_t t = 0; t < n_terms; ++t) {
         for (uint32_t bx = 0; bx < o.n_boxes; ++bx) {
             int cc[5];
@@ -603,23 +612,33 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
                 if (!mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_ph, abort_flag, 4)) { ok = false; break; }
                 tc_fence_after();
                 uint32_t const trow = tmem_base + ((quarter * 32u) << 16) + acc * p.bn;
-                for (uint32_t pc = half; pc < pieces; pc += 2) {
+                if constexpr (PROMOTE) {
+                    // this chunk's partial sums join the running sums in registers; piece slots are
+                    // compile-time indices (bn <= 128: at most 4 pieces, 2 per warp)
+#pragma unroll
+                    for (int c2 = 0; c2 < 2; ++c2) {
+                        uint32_t const pc = half + 2u * (uint32_t)c2;
+                        if (pc < pieces) {
+                            uint32_t r[32];
+                            tmem_ld32(trow + pc * 32, r);
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                float const v = __uint_as_float(r[j]);
+                                accr[c2][j] = first_chunk ? v : __fadd_rn(accr[c2][j], v);
+                            }
+                        }
+                    }
+                }
+                for (uint32_t pc = half; pc < pieces && (last_chunk || !PROMOTE); pc += 2) {
                     uint4 w[8]; // this lane's 128 bytes of the piece, in the output dtype
                     if (p.out_is_f32) {
                         uint32_t r[32];
-                        tmem_ld32(trow + pc * 32, r);
                         if constexpr (PROMOTE) {
+                            bool const second = (pc >> 1) != 0;
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) {
-                                float v = __uint_as_float(r[j]);
-#pragma unroll
-                                for (int c2 = 0; c2 < 2; ++c2) {
-                                    if ((int)(pc >> 1) == c2) { // bn <= 128: at most 4 pieces, 2 per warp
-                                        accr[c2][j] = first_chunk ? v : __fadd_rn(accr[c2][j], v);
-                                        r[j] = __float_as_uint(accr[c2][j]);
-                                    }
-                                }
-                            }
+                            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(second ? accr[1][j] : accr[0][j]);
+                        } else {
+                            tmem_ld32(trow + pc * 32, r);
                         }
 #pragma unroll
                         for (int j = 0; j < 8; ++j) w[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
