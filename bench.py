@@ -646,6 +646,10 @@ def run_only(args):
             e = einsummable_t.from_matmul_st(2048, 4096, 11008, "f16")
         elif args.only == "gemm_f32":
             e = einsummable_t.from_matmul(2048, 2048, 2048, "f32")
+        elif args.only == "gemm_nn":    # ij,jk->ik: the second operand's innermost mode is an output mode
+            e = einsummable_t.from_str("ij,jk->ik", dict(i=2048, j=4096, k=4096), mul16, "add")
+        elif args.only == "gemm_tn":    # ji,jk->ik: both are (the weight-gradient shape of a backward pass)
+            e = einsummable_t.from_str("ji,jk->ik", dict(i=4096, j=2048, k=4096), mul16, "add")
         elif args.only == "attn_scores":
             e = einsummable_t.from_str("acbe,adbe->abcd", dict(a=4, b=32, c=512, d=512, e=128), mul16, "add")
         else:
@@ -689,7 +693,7 @@ def main():
                     help="rows of the [rows, 11008] tensors (default: the full C2 workload); "
                          "smaller values are for profiler captures only")
     ap.add_argument("--only", default=None,
-                    choices=["gemm_qkv", "gemm_ffn", "gemm_f32", "attn_scores", "attn_pv", "touch", "permute", "move"],
+                    choices=["gemm_qkv", "gemm_ffn", "gemm_f32", "gemm_nn", "gemm_tn", "attn_scores", "attn_pv", "touch", "permute", "move"],
                     help="time one other kernel class alone (profiler captures); prints its own small JSON line")
     ap.add_argument("--kernels-only", action="store_true",
                     help="skip the end-to-end, other-class and CPU-baseline legs (profiler captures)")

@@ -60,6 +60,12 @@ struct operand_t {
     int8_t   pad[3];
 };
 
+// Exact division of numerators below 2^31 by a fixed divisor: q = umulhi(n, m) >> s with
+// l = ceil(log2 d), m = ceil(2^(31+l) / d), s = l - 1 (d <= 1: q = n).
+struct fd_t {
+    uint32_t m, s, d;
+};
+
 struct alignas(64) tc_params_t {
     CUtensorMap tm_a[2];    // [0] = hi (or the only) term, [1] = lo term
     CUtensorMap tm_b[2];
@@ -70,6 +76,10 @@ struct alignas(64) tc_params_t {
     uint32_t    n_kouter;
     uint32_t    kouter_extent[4];
     uint32_t    m_tiles, n_tiles, k_blocks, kouter_total;
+    fd_t        fd_m_tiles, fd_n_tiles, fd_m_pairs, fd_outer[MAX_LOOP_MODES];
+    // digits of the grid size in the mixed radix (m_tiles, n_tiles, outer extents): a CTA steps from
+    // one of its tiles to the next by adding them with carries instead of decoding the tile index
+    uint32_t    step_m, step_n, step_outer[MAX_LOOP_MODES];
     uint32_t    m_extent, n_extent;
     int64_t     out_stride_m, out_stride_n;
     uint32_t    total_tiles;
@@ -151,31 +161,13 @@ mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t
     return true;
 }
 
-__device__ __forceinline__ void tma_load(uint32_t dst, CUtensorMap const* tm, uint32_t bar, int nd, int const* c)
+// Operand maps are always encoded with five dims (missing ones have extent 1), so the producer
+// needs no switch on the rank.
+__device__ __forceinline__ void tma_load5(uint32_t dst, uint64_t desc, uint32_t bar, int c0, int c1, int c2, int c3, int c4)
 {
-    uint64_t desc = reinterpret_cast<uint64_t>(tm);
-    switch (nd) {
-        case 2:
-            asm volatile(
-                "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                ::"r"(dst), "l"(desc), "r"(bar), "r"(c[0]), "r"(c[1]) : "memory");
-            break;
-        case 3:
-            asm volatile(
-                "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-                ::"r"(dst), "l"(desc), "r"(bar), "r"(c[0]), "r"(c[1]), "r"(c[2]) : "memory");
-            break;
-        case 4:
-            asm volatile(
-                "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-                ::"r"(dst), "l"(desc), "r"(bar), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]) : "memory");
-            break;
-        default:
-            asm volatile(
-                "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
-                ::"r"(dst), "l"(desc), "r"(bar), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]), "r"(c[4]) : "memory");
-            break;
-    }
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(dst), "l"(desc), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
 }
 
 __device__ __forceinline__ void tma_store(CUtensorMap const* tm, uint32_t src, int nd, int const* c)
@@ -275,20 +267,53 @@ struct ctrl_t {
 // fully unrolled loops, so they live in registers: a version with run-time
 // indexing put them in local memory and the dependent local-memory round trips
 // (~2300 cycles per k-block) made the producer, not the tensor pipe, the bottleneck.
+__device__ __forceinline__ uint32_t fd_div(uint32_t n, fd_t const& f)
+{
+    return f.d <= 1 ? n : (__umulhi(n, f.m) >> f.s);
+}
+
+// t -> (t / d, t % d)
+__device__ __forceinline__ uint32_t fd_divmod(uint32_t& t, fd_t const& f)
+{
+    uint32_t const q = fd_div(t, f), r = t - q * f.d;
+    t = q;
+    return r;
+}
+
+__device__ __forceinline__ void
+decode_rest(tc_params_t const& p, uint32_t t, uint32_t& n_tile, uint32_t (&outer)[MAX_LOOP_MODES])
+{
+    n_tile = fd_divmod(t, p.fd_n_tiles);
+#pragma unroll
+    for (int j = MAX_LOOP_MODES - 1; j >= 0; --j) outer[j] = j < (int)p.n_outer ? fd_divmod(t, p.fd_outer[j]) : 0u;
+}
+
 __device__ __forceinline__ void
 decode_tile(tc_params_t const& p, uint32_t tile, uint32_t& m_tile, uint32_t& n_tile, uint32_t (&outer)[MAX_LOOP_MODES])
 {
-    m_tile = tile % p.m_tiles;
-    uint32_t t = tile / p.m_tiles;
-    n_tile = t % p.n_tiles;
-    t /= p.n_tiles;
+    m_tile = fd_divmod(tile, p.fd_m_tiles);
+    decode_rest(p, tile, n_tile, outer);
+}
+
+// (m_tile, n_tile, outer) of tile t  ->  of tile t + gridDim.x  (schedules without 256-row items)
+template <bool BIG>
+__device__ __forceinline__ void
+step_tile(tc_params_t const& p, uint32_t& m_tile, uint32_t& n_tile, uint32_t (&outer)[MAX_LOOP_MODES])
+{
+    if constexpr (!BIG) {
+        uint32_t v = m_tile + p.step_m;
+        uint32_t c = v >= p.m_tiles ? 1u : 0u;
+        m_tile = c ? v - p.m_tiles : v;
+        v = n_tile + p.step_n + c;
+        c = v >= p.n_tiles ? 1u : 0u;
+        n_tile = c ? v - p.n_tiles : v;
 #pragma unroll
-    for (int j = MAX_LOOP_MODES - 1; j >= 0; --j) {
-        if (j < (int)p.n_outer) {
-            outer[j] = t % p.outer_extent[j];
-            t /= p.outer_extent[j];
-        } else {
-            outer[j] = 0;
+        for (int j = MAX_LOOP_MODES - 1; j >= 0; --j) {
+            if (j < (int)p.n_outer) {
+                v = outer[j] + p.step_outer[j] + c;
+                c = v >= p.outer_extent[j] ? 1u : 0u;
+                outer[j] = c ? v - p.outer_extent[j] : v;
+            }
         }
     }
 }
@@ -308,27 +333,17 @@ __device__ __forceinline__ void decode_item(tc_params_t const& p, uint32_t it, u
     uint32_t rest;
     if (it < p.n_big) {
         halves = 2;
-        m_tile = 2 * (it % p.m_pairs);
-        rest = it / p.m_pairs;
+        rest = it;
+        m_tile = 2 * fd_divmod(rest, p.fd_m_pairs);
     } else if (it - p.n_big < p.pair_small) {
-        uint32_t const s = it - p.n_big, b = p.n_big + (s >> 1);
-        m_tile = 2 * (b % p.m_pairs) + (s & 1);
-        rest = b / p.m_pairs;
+        uint32_t const s = it - p.n_big;
+        rest = p.n_big + (s >> 1);
+        m_tile = 2 * fd_divmod(rest, p.fd_m_pairs) + (s & 1);
     } else {
         m_tile = p.m_tiles - 1;
         rest = it - p.n_big - p.pair_small;
     }
-    n_tile = rest % p.n_tiles;
-    uint32_t t = rest / p.n_tiles;
-#pragma unroll
-    for (int j = MAX_LOOP_MODES - 1; j >= 0; --j) {
-        if (j < (int)p.n_outer) {
-            outer[j] = t % p.outer_extent[j];
-            t /= p.outer_extent[j];
-        } else {
-            outer[j] = 0;
-        }
-    }
+    decode_rest(p, rest, n_tile, outer);
 }
 
 __device__ __forceinline__ uint32_t pick6(uint32_t const (&v)[MAX_LOOP_MODES], int i)
@@ -347,67 +362,69 @@ __device__ __forceinline__ uint32_t pick4(uint32_t const (&v)[4], int i)
     return r;
 }
 
-// Per-tile part of an operand's TMA coordinates (tile origin and outer modes).
-__device__ __forceinline__ void
-tile_coords(operand_t const& o, uint32_t mn_elems, uint32_t const (&outer)[MAX_LOOP_MODES], int (&base)[5])
+// Everything the producer lane needs about one operand, read from the kernel parameters once and
+// kept in registers (arrays are only ever indexed by compile-time constants).  The loop itself then
+// touches no parameter memory: with parameter reads, selects and a switch on the rank inside the
+// loop one copy cost the single producer lane ~370 cycles, which - not the tensor pipe and not
+// the memory system - bounded every contraction.
+struct prod_operand_t {
+    uint64_t desc0, desc1;   // tensor maps of the (hi / only) and lo terms
+    uint32_t n_boxes, box_bytes, box_step, tile_bytes;
+    int      src[5];         // where each coordinate comes from
+    int      kinc[5];        // coordinate advance per k-block
+    int      hinc[5];        // coordinate offset of the second 128-row half
+};
+
+__device__ __forceinline__ prod_operand_t load_operand(operand_t const& o, CUtensorMap const* tm, uint32_t bk_elems)
 {
+    prod_operand_t r;
+    r.desc0 = reinterpret_cast<uint64_t>(&tm[0]);
+    r.desc1 = reinterpret_cast<uint64_t>(&tm[1]);
+    r.n_boxes = o.n_boxes;
+    r.box_bytes = o.box_bytes;
+    r.box_step = o.box_step;
+    r.tile_bytes = o.tile_bytes;
 #pragma unroll
     for (int d = 0; d < 5; ++d) {
-        int s = o.src[d];
-        int v = 0;
-        if (s == SRC_MN_TILE) v = (int)mn_elems;
-        else if (s >= SRC_OUTER0 && s < SRC_KOUTER0) v = (int)pick6(outer, s - SRC_OUTER0);
-        base[d] = v;
+        r.src[d] = o.src[d];
+        r.kinc[d] = o.src[d] == SRC_K_BLOCK ? (int)bk_elems : 0;
+        r.hinc[d] = d == o.box_dim ? BM : 0;
     }
+    return r;
 }
 
-// Full coordinates of an operand for (tile, k block, outer-K indices).
-__device__ __forceinline__ void full_coords(operand_t const& o,
-                                            int const (&base)[5],
-                                            uint32_t k_elems,
-                                            uint32_t const (&kouter)[4],
-                                            int (&c)[5])
+// Coordinates of an operand for (tile origin, outer indices, outer-K indices) at k block 0.
+__device__ __forceinline__ void operand_coords(prod_operand_t const& o,
+                                               uint32_t              mn_elems,
+                                               uint32_t const (&outer)[MAX_LOOP_MODES],
+                                               uint32_t const (&kouter)[4],
+                                               int (&c)[5])
 {
 #pragma unroll
     for (int d = 0; d < 5; ++d) {
-        int s = o.src[d];
-        int v = base[d];
-        if (s == SRC_K_BLOCK) v = (int)k_elems;
+        int const s = o.src[d];
+        int       v = 0;
+        if (s == SRC_MN_TILE) v = (int)mn_elems;
         else if (s >= SRC_KOUTER0) v = (int)pick4(kouter, s - SRC_KOUTER0);
+        else if (s >= SRC_OUTER0) v = (int)pick6(outer, s - SRC_OUTER0);
         c[d] = v;
     }
 }
 
-// Issues the copies of one operand for one k-iteration from ready coordinates.
-__device__ __forceinline__ void issue_operand(operand_t const&   o,
-                                              CUtensorMap const* tm,
-                                              uint32_t           n_terms,
-                                              int const (&c)[5],
-                                              uint32_t dst,
-                                              uint32_t bar,
-                                              uint32_t mn_offset = 0)
+// Issues the copies of one operand for one k-iteration.  Several copies per tile only occur for
+// MN-major f16 operands (column blocks of 64 along TMA dim 0, one term).
+__device__ __forceinline__ void
+issue_operand(prod_operand_t const& o, uint32_t n_terms, int const (&c)[5], uint32_t dst, uint32_t bar)
 {
-    if (n_terms == 1 && o.n_boxes == 1 && mn_offset == 0) {
-        tma_load(dst, tm, bar, o.nd, c);
-        return;
-    }
     if (o.n_boxes == 1) {
-        // one copy per term: no loops, coordinates stay in registers
-        int cc[5];
-#pragma unroll
-        for (int d = 0; d < 5; ++d) cc[d] = c[d] + (d == o.box_dim ? (int)mn_offset : 0);
-        tma_load(dst, &tm[0], bar, o.nd, cc);
-        if (n_terms == 2) tma_load(dst + o.tile_bytes, &tm[1], bar, o.nd, cc);
+        tma_load5(dst, o.desc0, bar, c[0], c[1], c[2], c[3], c[4]);
+        if (n_terms == 2) tma_load5(dst + o.tile_bytes, o.desc1, bar, c[0], c[1], c[2], c[3], c[4]);
         return;
     }
-    for (uint32_t t = 0; t < n_terms; ++t) {
-        for (uint32_t bx = 0; bx < o.n_boxes; ++bx) {
-            int cc[5];
 #pragma unroll
-            for (int d = 0; d < 5; ++d) cc[d] = c[d] + (d == o.box_dim ? (int)(mn_offset + bx * o.box_step) : 0);
-            tma_load(dst + t * o.tile_bytes + bx * o.box_bytes, &tm[t], bar, o.nd, cc);
-        }
-    }
+    for (uint32_t bx = 0; bx < 4; ++bx)
+        if (bx < o.n_boxes)
+            tma_load5(dst + bx * o.box_bytes, o.desc0, bar, c[0] + (int)(bx * o.box_step), c[1], c[2], c[3], c[4]);
 }
 
 template <int KIND, bool PROMOTE, bool BIG> // BIG: the schedule holds 256-row items (p.mh == 2)
@@ -456,44 +473,54 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool     ok = true;
-            for (uint32_t tile = blockIdx.x; tile < p.total_items && ok; tile += gridDim.x) {
-                uint32_t m_tile, halves, n_tile, outer[MAX_LOOP_MODES];
-                decode_item<BIG>(p, tile, m_tile, halves, n_tile, outer);
-                uint32_t const tx_bytes = p.stage_bytes - ((BIG ? 2u : 1u) - halves) * term_a_bytes;
-                int base_a[5], base_b[5];
-                tile_coords(p.a, m_tile * BM, outer, base_a);
-                tile_coords(p.b, n_tile * p.bn, outer, base_b);
+            prod_operand_t const oa = load_operand(p.a, p.tm_a, p.bk_elems);
+            prod_operand_t const ob = load_operand(p.b, p.tm_b, p.bk_elems);
+            uint32_t const n_terms = p.n_terms, stages = p.stages, stage_bytes = p.stage_bytes, bn = p.bn;
+            uint32_t const k_blocks = p.k_blocks, n_kouter = p.n_kouter;
+            uint32_t const kouter_extent[4] = {p.kouter_extent[0], p.kouter_extent[1], p.kouter_extent[2],
+                                               p.kouter_extent[3]};
+            uint32_t const full0 = smem_u32(&ctrl->full[0]), empty0 = smem_u32(&ctrl->empty[0]);
+            uint32_t m_tile = 0, halves = 1, n_tile = 0, outer[MAX_LOOP_MODES] = {0, 0, 0, 0, 0, 0};
+            if constexpr (!BIG) decode_tile(p, blockIdx.x, m_tile, n_tile, outer);
+            for (uint32_t tile = blockIdx.x; tile < p.total_items && ok;
+                 tile += gridDim.x, step_tile<BIG>(p, m_tile, n_tile, outer)) {
+                if constexpr (BIG) decode_item<true>(p, tile, m_tile, halves, n_tile, outer);
+                uint32_t const tx_bytes = stage_bytes - ((BIG ? 2u : 1u) - halves) * term_a_bytes;
                 // odometer over (outer K modes ..., k block): the last entry runs fastest
                 uint32_t kb = 0, kouter[4] = {0, 0, 0, 0};
                 int      ca[5], cb[5];
-                full_coords(p.a, base_a, 0, kouter, ca);
-                full_coords(p.b, base_b, 0, kouter, cb);
+                operand_coords(oa, m_tile * BM, outer, kouter, ca);
+                operand_coords(ob, n_tile * bn, outer, kouter, cb);
                 for (uint32_t ki = 0; ki < k_iters; ++ki) {
-                    if (!mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, 1)) { ok = false; break; }
-                    uint32_t bar = smem_u32(&ctrl->full[stage]);
+                    if (!mbar_wait(empty0 + stage * 8u, phase ^ 1, abort_flag, 1)) { ok = false; break; }
+                    uint32_t const bar = full0 + stage * 8u;
                     mbar_arrive_expect_tx(bar, tx_bytes);
-                    uint32_t stage_base = smem_base + stage * p.stage_bytes;
-                    issue_operand(p.a, p.tm_a, p.n_terms, ca, stage_base, bar);
-                    if (BIG && halves == 2) issue_operand(p.a, p.tm_a, 1, ca, stage_base + term_a_bytes, bar, BM);
-                    issue_operand(p.b, p.tm_b, p.n_terms, cb, stage_base + a_region, bar);
-                    if (++stage == p.stages) { stage = 0; phase ^= 1; }
-                    if (++kb == p.k_blocks) {
+                    uint32_t const stage_base = smem_base + stage * stage_bytes;
+                    issue_operand(oa, n_terms, ca, stage_base, bar);
+                    if (BIG && halves == 2) {
+                        int const ch[5] = {ca[0] + oa.hinc[0], ca[1] + oa.hinc[1], ca[2] + oa.hinc[2], ca[3] + oa.hinc[3],
+                                           ca[4] + oa.hinc[4]};
+                        issue_operand(oa, 1, ch, stage_base + term_a_bytes, bar);
+                    }
+                    issue_operand(ob, n_terms, cb, stage_base + a_region, bar);
+                    if (++stage == stages) { stage = 0; phase ^= 1; }
+                    if (++kb == k_blocks) {
                         kb = 0;
                         bool carry = true;
 #pragma unroll
                         for (int j = 3; j >= 0; --j) {
-                            if (carry && j < (int)p.n_kouter) {
-                                if (++kouter[j] == p.kouter_extent[j]) kouter[j] = 0;
+                            if (carry && j < (int)n_kouter) {
+                                if (++kouter[j] == kouter_extent[j]) kouter[j] = 0;
                                 else carry = false;
                             }
                         }
-                        full_coords(p.a, base_a, 0, kouter, ca);
-                        full_coords(p.b, base_b, 0, kouter, cb);
+                        operand_coords(oa, m_tile * BM, outer, kouter, ca);
+                        operand_coords(ob, n_tile * bn, outer, kouter, cb);
                     } else {
 #pragma unroll
                         for (int d = 0; d < 5; ++d) {
-                            ca[d] += (p.a.src[d] == SRC_K_BLOCK) ? (int)p.bk_elems : 0;
-                            cb[d] += (p.b.src[d] == SRC_K_BLOCK) ? (int)p.bk_elems : 0;
+                            ca[d] += oa.kinc[d];
+                            cb[d] += ob.kinc[d];
                         }
                     }
                 }
@@ -513,8 +540,11 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
             uint32_t const idesc = p.idesc, stages = p.stages, stage_units = p.stage_bytes >> 4;
             uint32_t const a_region_units = a_region >> 4, base_units = smem_base >> 4;
             for (uint32_t tile = blockIdx.x; tile < p.total_items && ok; tile += gridDim.x) {
-                uint32_t m_tile, halves, n_tile, outer[MAX_LOOP_MODES];
-                decode_item<BIG>(p, tile, m_tile, halves, n_tile, outer);
+                uint32_t halves = 1;
+                if constexpr (BIG) {
+                    uint32_t m_tile, n_tile, outer[MAX_LOOP_MODES];
+                    decode_item<true>(p, tile, m_tile, halves, n_tile, outer);
+                }
                 for (uint32_t ki0 = 0; ki0 < k_iters && ok; ki0 += p.k_chunk) {
                     // accumulator slots: a big item takes both (one per half); anything else the
                     // slot used less often so far, which alternates 0, 1, 0, ... between big items
@@ -584,9 +614,11 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
         uint32_t const pieces = p.bn / piece_cols;
         // per-warp staging for TMA stores: 32 rows x 128 bytes, 128B-swizzled
         uint32_t const stage_buf = smem_base + p.staging_offset + (uint32_t)(warp - 2) * 4096u;
-        for (uint32_t tile = blockIdx.x; tile < p.total_items && ok; tile += gridDim.x) {
-            uint32_t m_first, halves, n_tile, outer[MAX_LOOP_MODES];
-            decode_item<BIG>(p, tile, m_first, halves, n_tile, outer);
+        uint32_t m_first = 0, halves = 1, n_tile = 0, outer[MAX_LOOP_MODES] = {0, 0, 0, 0, 0, 0};
+        if constexpr (!BIG) decode_tile(p, blockIdx.x, m_first, n_tile, outer);
+        for (uint32_t tile = blockIdx.x; tile < p.total_items && ok;
+             tile += gridDim.x, step_tile<BIG>(p, m_first, n_tile, outer)) {
+            if constexpr (BIG) decode_item<true>(p, tile, m_first, halves, n_tile, outer);
             int64_t base = 0;
 #pragma unroll
             for (int j = 0; j < MAX_LOOP_MODES; ++j)
@@ -788,7 +820,9 @@ using encode_fn_t = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, 
                                  cuuint64_t const*, cuuint32_t const*, cuuint32_t const*, CUtensorMapInterleave,
                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-void encode_map(CUtensorMap* tm, tc_plan_t::map_recipe_t const& r, void const* base)
+// pad5: encode with five dims, the missing outer ones with extent 1 (operand maps: the producer
+// always issues the 5-D form of the copy)
+void encode_map(CUtensorMap* tm, tc_plan_t::map_recipe_t const& r, void const* base, bool pad5 = false)
 {
     static encode_fn_t fn = (encode_fn_t)driver_entry("cuTensorMapEncodeTiled");
     cuuint32_t         elem_strides[5] = {1, 1, 1, 1, 1};
@@ -800,13 +834,38 @@ void encode_map(CUtensorMap* tm, tc_plan_t::map_recipe_t const& r, void const* b
         box[i] = r.box[i];
         if (i + 1 < r.nd) strides[i] = r.strides_bytes[i];
     }
-    CUresult rc = fn(tm, (CUtensorMapDataType)r.dtype, r.nd, const_cast<void*>(base), dims, strides, box,
+    uint32_t nd = r.nd;
+    if (pad5) {
+        uint64_t const esize = r.dtype == CU_TENSOR_MAP_DATA_TYPE_FLOAT16 ? 2 : 4;
+        for (; nd < 5; ++nd) {
+            // stride of a new outermost dim of extent 1: the byte size of everything below it,
+            // rounded up to the 16 bytes a stride must be a multiple of
+            uint64_t below = nd == 1 ? dims[0] * esize : strides[nd - 2] * dims[nd - 1];
+            strides[nd - 1] = (below + 15) & ~uint64_t(15);
+            dims[nd] = 1;
+            box[nd] = 1;
+        }
+    }
+    CUresult rc = fn(tm, (CUtensorMapDataType)r.dtype, nd, const_cast<void*>(base), dims, strides, box,
                      elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (rc != CUDA_SUCCESS) fail(ES_CUDA_ERROR, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)rc));
 }
 
 enum mode_class_t { MC_BATCH, MC_M, MC_N, MC_K, MC_BAD };
+
+fd_t make_fd(uint32_t d)
+{
+    fd_t f{0, 0, d};
+    if (d > 1) {
+        // with e = m*d - 2^(31+l) in [0, d) and n < 2^31: n*e < 2^(31+l), so the quotient is exact
+        uint32_t l = 0;
+        while ((1ull << l) < d) ++l;
+        f.m = (uint32_t)(((1ull << (31 + l)) + d - 1) / d);
+        f.s = l - 1;
+    }
+    return f;
+}
 
 } // namespace
 
@@ -1049,6 +1108,10 @@ bool plan_contraction(einsum_t const& e, int f32_policy, contraction_plan_t& pla
     }
     p.stages = std::min<uint32_t>(MAX_STAGES, smem_budget / p.stage_bytes);
     if (p.stages < 2) return false;
+    p.fd_m_tiles = make_fd(p.m_tiles);
+    p.fd_n_tiles = make_fd(p.n_tiles);
+    p.fd_m_pairs = make_fd(p.m_pairs);
+    for (uint32_t j = 0; j < MAX_LOOP_MODES; ++j) p.fd_outer[j] = make_fd(j < p.n_outer ? p.outer_extent[j] : 1u);
     p.tmem_cols = 2 * bn < 32 ? 32 : 2 * bn; // 128, 256 or 512: powers of two
     // 3xTF32: promote the partial sum to registers every 8 k-blocks (256 contracted elements)
     tp.promote = p.n_terms == 2 ? 1 : 0;
@@ -1090,6 +1153,17 @@ bool plan_contraction(einsum_t const& e, int f32_policy, contraction_plan_t& pla
         }
     }
     tp.grid = std::min<uint32_t>(p.total_items, 148);
+    {
+        uint32_t g = tp.grid;
+        p.step_m = g % p.m_tiles;
+        g /= p.m_tiles;
+        p.step_n = g % p.n_tiles;
+        g /= p.n_tiles;
+        for (int j = (int)p.n_outer - 1; j >= 0; --j) {
+            p.step_outer[j] = g % p.outer_extent[j];
+            g /= p.outer_extent[j];
+        }
+    }
     tp.a_elems = e.inn_nelem(ia);
     tp.b_elems = e.inn_nelem(ib);
     tp.swap = swap ? 1 : 0;
@@ -1166,10 +1240,10 @@ void launch_contraction(contraction_plan_t const& plan,
                 float* hi = region;
                 float* lo = region + elems;
                 split_tf32_kernel<<<blocks(elems / 4), 256, 0, stream>>>(cur, hi, lo, elems / 4);
-                encode_map(&tm[0], rc, hi);
-                encode_map(&tm[1], rc, lo);
+                encode_map(&tm[0], rc, hi, true);
+                encode_map(&tm[1], rc, lo, true);
             } else {
-                encode_map(&tm[0], rc, cur);
+                encode_map(&tm[0], rc, cur, true);
                 tm[1] = tm[0];
             }
         };
