@@ -170,27 +170,11 @@ __device__ __forceinline__ void tma_load5(uint32_t dst, uint64_t desc, uint32_t 
         ::"r"(dst), "l"(desc), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
 }
 
-__device__ __forceinline__ void tma_store(CUtensorMap const* tm, uint32_t src, int nd, int const* c)
+// The output map is encoded with five dims like the operand maps.
+__device__ __forceinline__ void tma_store5(uint64_t desc, uint32_t src, int c0, int c1, int c2, int c3, int c4)
 {
-    uint64_t desc = reinterpret_cast<uint64_t>(tm);
-    switch (nd) {
-        case 2:
-            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-                         ::"l"(desc), "r"(src), "r"(c[0]), "r"(c[1]) : "memory");
-            break;
-        case 3:
-            asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
-                         ::"l"(desc), "r"(src), "r"(c[0]), "r"(c[1]), "r"(c[2]) : "memory");
-            break;
-        case 4:
-            asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
-                         ::"l"(desc), "r"(src), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]) : "memory");
-            break;
-        default:
-            asm volatile("cp.async.bulk.tensor.5d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5, %6}], [%1];"
-                         ::"l"(desc), "r"(src), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]), "r"(c[4]) : "memory");
-            break;
-    }
+    asm volatile("cp.async.bulk.tensor.5d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5, %6}], [%1];"
+                 ::"l"(desc), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
 
@@ -504,6 +488,7 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
                     }
                     issue_operand(ob, n_terms, cb, stage_base + a_region, bar);
                     if (++stage == stages) { stage = 0; phase ^= 1; }
+                    if (ki + 1 == k_iters) break; // the next tile computes its own coordinates
                     if (++kb == k_blocks) {
                         kb = 0;
                         bool carry = true;
@@ -614,24 +599,33 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
         uint32_t const pieces = p.bn / piece_cols;
         // per-warp staging for TMA stores: 32 rows x 128 bytes, 128B-swizzled
         uint32_t const stage_buf = smem_base + p.staging_offset + (uint32_t)(warp - 2) * 4096u;
+        // per-tile work below reads registers only (parameter reads per tile cost the epilogue
+        // warps ~1000 cycles, which shows when a tile is two k-blocks long)
+        uint32_t const out_tma = p.out_tma, bn = p.bn, m_extent = p.m_extent, n_extent = p.n_extent;
+        uint64_t const out_desc = reinterpret_cast<uint64_t>(&p.tm_out);
+        int osrc[5];
+#pragma unroll
+        for (int d = 0; d < 5; ++d) osrc[d] = p.out_src[d];
         uint32_t m_first = 0, halves = 1, n_tile = 0, outer[MAX_LOOP_MODES] = {0, 0, 0, 0, 0, 0};
         if constexpr (!BIG) decode_tile(p, blockIdx.x, m_first, n_tile, outer);
         for (uint32_t tile = blockIdx.x; tile < p.total_items && ok;
              tile += gridDim.x, step_tile<BIG>(p, m_first, n_tile, outer)) {
             if constexpr (BIG) decode_item<true>(p, tile, m_first, halves, n_tile, outer);
             int64_t base = 0;
+            if (!out_tma) {
 #pragma unroll
-            for (int j = 0; j < MAX_LOOP_MODES; ++j)
-                if (j < (int)p.n_outer) base += (int64_t)outer[j] * p.outer_out_stride[j];
+                for (int j = 0; j < MAX_LOOP_MODES; ++j)
+                    if (j < (int)p.n_outer) base += (int64_t)outer[j] * p.outer_out_stride[j];
+            }
           for (uint32_t hf = 0; hf < halves && ok; ++hf) {
             uint32_t const m_tile = m_first + hf;
             uint32_t const m_warp = m_tile * BM + quarter * 32;
             uint32_t const m = m_warp + lane;
-            uint32_t const n0 = n_tile * p.bn;
+            uint32_t const n0 = n_tile * bn;
             int oc[5]; // TMA store coordinates; the column entry is filled per piece
 #pragma unroll
             for (int d = 0; d < 5; ++d) {
-                int sk = p.out_src[d];
+                int const sk = osrc[d];
                 oc[d] = sk == SRC_MN_TILE ? (int)m_warp
                         : (sk >= SRC_OUTER0 ? (int)pick6(outer, sk - SRC_OUTER0) : 0);
             }
@@ -690,7 +684,7 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
                     }
                     if (!last_chunk) continue;
                     uint32_t const n = n0 + pc * piece_cols;
-                    if (p.out_tma) {
+                    if (out_tma) {
                         // 32 rows x 128 bytes -> swizzled staging -> one TMA store per warp and piece
                         // (rows / columns beyond the tensor are clipped by the TMA unit)
                         uint32_t const buf = stage_buf;
@@ -707,15 +701,15 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
                         }
                         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                         __syncwarp();
-                        if (lane == 0 && n < p.n_extent && m_warp < p.m_extent) {
+                        if (lane == 0 && n < n_extent && m_warp < m_extent) {
                             int cc[5];
 #pragma unroll
-                            for (int d = 0; d < 5; ++d) cc[d] = (p.out_src[d] == SRC_N_TILE) ? (int)n : oc[d];
-                            tma_store(&p.tm_out, buf, p.out_nd, cc);
+                            for (int d = 0; d < 5; ++d) cc[d] = (osrc[d] == SRC_N_TILE) ? (int)n : oc[d];
+                            tma_store5(out_desc, buf, cc[0], cc[1], cc[2], cc[3], cc[4]);
                         }
-                    } else if (m < p.m_extent && n < p.n_extent) {
+                    } else if (m < m_extent && n < n_extent) {
                         int64_t off = base + (int64_t)m * p.out_stride_m + (int64_t)n * p.out_stride_n;
-                        bool    full = n + piece_cols <= p.n_extent;
+                        bool    full = n + piece_cols <= n_extent;
                         if (p.out_is_f32) {
                             float* o = static_cast<float*>(out_) + off;
                             if (p.out_stride_n == 1 && full && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
@@ -727,7 +721,7 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
                                     uint32_t const e4[4] = {w[j].x, w[j].y, w[j].z, w[j].w};
 #pragma unroll
                                     for (int i = 0; i < 4; ++i)
-                                        if (n + 4 * j + i < p.n_extent)
+                                        if (n + 4 * j + i < n_extent)
                                             o[(int64_t)(4 * j + i) * p.out_stride_n] = __uint_as_float(e4[i]);
                                 }
                             }
@@ -742,7 +736,7 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
                                     uint32_t const e4[4] = {w[j].x, w[j].y, w[j].z, w[j].w};
 #pragma unroll
                                     for (int i = 0; i < 8; ++i)
-                                        if (n + 8 * j + i < p.n_extent)
+                                        if (n + 8 * j + i < n_extent)
                                             o[(int64_t)(8 * j + i) * p.out_stride_n] =
                                                 (uint16_t)((i & 1) ? (e4[i >> 1] >> 16) : (e4[i >> 1] & 0xffffu));
                                 }
@@ -1252,7 +1246,7 @@ void launch_contraction(contraction_plan_t const& plan,
     }
     p.out_tma = 0;
     if (tp.out_tma && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
-        encode_map(&p.tm_out, tp.rout, out);
+        encode_map(&p.tm_out, tp.rout, out, true);
         p.out_tma = 1;
     }
     auto launch = [&](auto kernel, int slot) {
