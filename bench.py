@@ -545,6 +545,10 @@ def other_classes(km, dev, stream):
         "ffn_w1 ij,kj->ik f16 2048x4096x11008": einsummable_t.from_matmul_st(2048, 4096, 11008, "f16"),
         "qkv ij,kj->ik f16 2048x4096x4096": einsummable_t.from_matmul_st(2048, 4096, 4096, "f16"),
         "C1 block ij,jk->ik f32 2048^3 (3xTF32)": einsummable_t.from_matmul(2048, 2048, 2048, "f32"),
+        "ij,jk->ik f16 2048x4096x4096 (B MN-major)": einsummable_t.from_str(
+            "ij,jk->ik", dict(i=2048, j=4096, k=4096), mul16, "add"),
+        "ji,jk->ik f16 4096x2048x4096 (both MN-major, weight-gradient shape)": einsummable_t.from_str(
+            "ji,jk->ik", dict(i=4096, j=2048, k=4096), mul16, "add"),
         "attn scores acbe,adbe->abcd f16 [4,32,512,512,128]": einsummable_t.from_str(
             "acbe,adbe->abcd", dict(a=4, b=32, c=512, d=512, e=128), mul16, "add"),
         "attn PV abce,aebd->abcd f16 [4,32,512,128,512]": einsummable_t.from_str(
