@@ -346,43 +346,63 @@ __device__ __forceinline__ uint32_t pick4(uint32_t const (&v)[4], int i)
     return r;
 }
 
-// Everything the producer lane needs about one operand, read from the kernel parameters once and
-// kept in registers (arrays are only ever indexed by compile-time constants).  The loop itself then
-// touches no parameter memory: with parameter reads, selects and a switch on the rank inside the
-// loop one copy cost the single producer lane ~370 cycles, which - not the tensor pipe and not
-// the memory system - bounded every contraction.
-struct prod_operand_t {
-    uint64_t desc0, desc1;   // tensor maps of the (hi / only) and lo terms
-    uint32_t n_boxes, box_bytes, box_step, tile_bytes;
-    int      src[5];         // where each coordinate comes from
-    int      kinc[5];        // coordinate advance per k-block
-    int      hinc[5];        // coordinate offset of the second 128-row half
+// The producer warp issues one k-block's copies as one SIMT instruction: lane l owns copy l (operand,
+// 128-row half, term, column block).  Everything a lane needs is read from the kernel parameters
+// once and kept in registers (arrays are only ever indexed by compile-time constants), so the loop
+// touches no parameter memory.  Issued one after the other by a single lane, with parameter reads,
+// selects and a switch on the rank in between, a copy cost ~370 cycles, which - not the tensor pipe
+// and not the memory system - bounded every contraction.
+struct prod_lane_t {
+    uint64_t desc;     // tensor map of this lane's term
+    uint32_t dst_off;  // byte offset of the copy's destination inside a stage
+    uint32_t half;     // 128-row half of a 256-row item (A copies only)
+    uint32_t is_a;
+    uint32_t active;
+    int      src[5];   // where each coordinate comes from
+    int      kinc[5];  // coordinate advance per k-block
+    int      off[5];   // constant coordinate offset of this copy (second half, column block)
 };
 
-__device__ __forceinline__ prod_operand_t load_operand(operand_t const& o, CUtensorMap const* tm, uint32_t bk_elems)
+template <bool BIG>
+__device__ __forceinline__ prod_lane_t make_prod_lane(tc_params_t const& p, uint32_t lane, uint32_t a_region)
 {
-    prod_operand_t r;
-    r.desc0 = reinterpret_cast<uint64_t>(&tm[0]);
-    r.desc1 = reinterpret_cast<uint64_t>(&tm[1]);
-    r.n_boxes = o.n_boxes;
-    r.box_bytes = o.box_bytes;
-    r.box_step = o.box_step;
-    r.tile_bytes = o.tile_bytes;
+    uint32_t const n_terms = p.n_terms;
+    uint32_t const nA1 = n_terms * p.a.n_boxes; // copies of one 128-row A tile
+    uint32_t const nA = nA1 * (BIG ? 2u : 1u);
+    uint32_t const nB = n_terms * p.b.n_boxes;
+    prod_lane_t r;
+    r.is_a = lane < nA ? 1u : 0u;
+    r.active = lane < nA + nB ? 1u : 0u;
+    uint32_t const idx = r.is_a ? lane : lane - nA;
+    r.half = r.is_a ? idx / nA1 : 0u;
+    uint32_t const idx1 = r.is_a ? idx - r.half * nA1 : idx;
+    uint32_t const n_boxes = r.is_a ? p.a.n_boxes : p.b.n_boxes;
+    uint32_t const term = idx1 / n_boxes, box = idx1 - term * n_boxes;
+    uint32_t const tile_bytes = r.is_a ? p.a.tile_bytes : p.b.tile_bytes;
+    uint32_t const box_bytes = r.is_a ? p.a.box_bytes : p.b.box_bytes;
+    uint32_t const box_step = r.is_a ? p.a.box_step : p.b.box_step;
+    int const      box_dim = r.is_a ? p.a.box_dim : p.b.box_dim;
+    CUtensorMap const* tm = r.is_a ? p.tm_a : p.tm_b;
+    r.desc = reinterpret_cast<uint64_t>(term ? &tm[1] : &tm[0]);
+    // stage layout: A tiles (half 0 / term 0, then half 1 or term 1), then B tiles
+    r.dst_off = (r.is_a ? 0u : a_region) + (r.half + term) * tile_bytes + box * box_bytes;
 #pragma unroll
     for (int d = 0; d < 5; ++d) {
-        r.src[d] = o.src[d];
-        r.kinc[d] = o.src[d] == SRC_K_BLOCK ? (int)bk_elems : 0;
-        r.hinc[d] = d == o.box_dim ? BM : 0;
+        int const sa = p.a.src[d], sb = p.b.src[d];
+        r.src[d] = r.is_a ? sa : sb;
+        r.kinc[d] = r.src[d] == SRC_K_BLOCK ? (int)p.bk_elems : 0;
+        // column blocks step along TMA dim 0 (an operand with several copies is MN-major)
+        r.off[d] = (d == box_dim ? (int)(r.half * BM) : 0) + (d == 0 ? (int)(box * box_step) : 0);
     }
     return r;
 }
 
-// Coordinates of an operand for (tile origin, outer indices, outer-K indices) at k block 0.
-__device__ __forceinline__ void operand_coords(prod_operand_t const& o,
-                                               uint32_t              mn_elems,
-                                               uint32_t const (&outer)[MAX_LOOP_MODES],
-                                               uint32_t const (&kouter)[4],
-                                               int (&c)[5])
+// Coordinates of a lane's copy for (tile origin, outer indices, outer-K indices) at k block 0.
+__device__ __forceinline__ void lane_coords(prod_lane_t const& o,
+                                            uint32_t           mn_elems,
+                                            uint32_t const (&outer)[MAX_LOOP_MODES],
+                                            uint32_t const (&kouter)[4],
+                                            int (&c)[5])
 {
 #pragma unroll
     for (int d = 0; d < 5; ++d) {
@@ -391,24 +411,8 @@ __device__ __forceinline__ void operand_coords(prod_operand_t const& o,
         if (s == SRC_MN_TILE) v = (int)mn_elems;
         else if (s >= SRC_KOUTER0) v = (int)pick4(kouter, s - SRC_KOUTER0);
         else if (s >= SRC_OUTER0) v = (int)pick6(outer, s - SRC_OUTER0);
-        c[d] = v;
+        c[d] = v + o.off[d];
     }
-}
-
-// Issues the copies of one operand for one k-iteration.  Several copies per tile only occur for
-// MN-major f16 operands (column blocks of 64 along TMA dim 0, one term).
-__device__ __forceinline__ void
-issue_operand(prod_operand_t const& o, uint32_t n_terms, int const (&c)[5], uint32_t dst, uint32_t bar)
-{
-    if (o.n_boxes == 1) {
-        tma_load5(dst, o.desc0, bar, c[0], c[1], c[2], c[3], c[4]);
-        if (n_terms == 2) tma_load5(dst + o.tile_bytes, o.desc1, bar, c[0], c[1], c[2], c[3], c[4]);
-        return;
-    }
-#pragma unroll
-    for (uint32_t bx = 0; bx < 4; ++bx)
-        if (bx < o.n_boxes)
-            tma_load5(dst + bx * o.box_bytes, o.desc0, bar, c[0] + (int)(bx * o.box_step), c[1], c[2], c[3], c[4]);
 }
 
 template <int KIND, bool PROMOTE, bool BIG> // BIG: the schedule holds 256-row items (p.mh == 2)
@@ -454,12 +458,11 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
-        if (lane == 0) {
+        {
             uint32_t stage = 0, phase = 0;
             bool     ok = true;
-            prod_operand_t const oa = load_operand(p.a, p.tm_a, p.bk_elems);
-            prod_operand_t const ob = load_operand(p.b, p.tm_b, p.bk_elems);
-            uint32_t const n_terms = p.n_terms, stages = p.stages, stage_bytes = p.stage_bytes, bn = p.bn;
+            prod_lane_t const me = make_prod_lane<BIG>(p, (uint32_t)lane, a_region);
+            uint32_t const stages = p.stages, stage_bytes = p.stage_bytes, bn = p.bn;
             uint32_t const k_blocks = p.k_blocks, n_kouter = p.n_kouter;
             uint32_t const kouter_extent[4] = {p.kouter_extent[0], p.kouter_extent[1], p.kouter_extent[2],
                                                p.kouter_extent[3]};
@@ -470,23 +473,23 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
                  tile += gridDim.x, step_tile<BIG>(p, m_tile, n_tile, outer)) {
                 if constexpr (BIG) decode_item<true>(p, tile, m_tile, halves, n_tile, outer);
                 uint32_t const tx_bytes = stage_bytes - ((BIG ? 2u : 1u) - halves) * term_a_bytes;
+                bool const     mine = me.active && me.half < halves; // a 128-row item has no second half
+                uint32_t const mn_elems = me.is_a ? m_tile * BM : n_tile * bn;
                 // odometer over (outer K modes ..., k block): the last entry runs fastest
                 uint32_t kb = 0, kouter[4] = {0, 0, 0, 0};
-                int      ca[5], cb[5];
-                operand_coords(oa, m_tile * BM, outer, kouter, ca);
-                operand_coords(ob, n_tile * bn, outer, kouter, cb);
+                int      c[5];
+                lane_coords(me, mn_elems, outer, kouter, c);
                 for (uint32_t ki = 0; ki < k_iters; ++ki) {
-                    if (!mbar_wait(empty0 + stage * 8u, phase ^ 1, abort_flag, 1)) { ok = false; break; }
+                    // lane 0 waits for the stage and announces the bytes; then every lane issues its copy
                     uint32_t const bar = full0 + stage * 8u;
-                    mbar_arrive_expect_tx(bar, tx_bytes);
-                    uint32_t const stage_base = smem_base + stage * stage_bytes;
-                    issue_operand(oa, n_terms, ca, stage_base, bar);
-                    if (BIG && halves == 2) {
-                        int const ch[5] = {ca[0] + oa.hinc[0], ca[1] + oa.hinc[1], ca[2] + oa.hinc[2], ca[3] + oa.hinc[3],
-                                           ca[4] + oa.hinc[4]};
-                        issue_operand(oa, 1, ch, stage_base + term_a_bytes, bar);
+                    uint32_t       go = 1;
+                    if (lane == 0) {
+                        go = mbar_wait(empty0 + stage * 8u, phase ^ 1, abort_flag, 1) ? 1u : 0u;
+                        if (go) mbar_arrive_expect_tx(bar, tx_bytes);
                     }
-                    issue_operand(ob, n_terms, cb, stage_base + a_region, bar);
+                    go = __shfl_sync(0xffffffffu, go, 0);
+                    if (!go) { ok = false; break; }
+                    if (mine) tma_load5(smem_base + stage * stage_bytes + me.dst_off, me.desc, bar, c[0], c[1], c[2], c[3], c[4]);
                     if (++stage == stages) { stage = 0; phase ^= 1; }
                     if (ki + 1 == k_iters) break; // the next tile computes its own coordinates
                     if (++kb == k_blocks) {
@@ -499,14 +502,10 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
                                 else carry = false;
                             }
                         }
-                        operand_coords(oa, m_tile * BM, outer, kouter, ca);
-                        operand_coords(ob, n_tile * bn, outer, kouter, cb);
+                        lane_coords(me, mn_elems, outer, kouter, c);
                     } else {
 #pragma unroll
-                        for (int d = 0; d < 5; ++d) {
-                            ca[d] += oa.kinc[d];
-                            cb[d] += ob.kinc[d];
-                        }
+                        for (int d = 0; d < 5; ++d) c[d] += me.kinc[d];
                     }
                 }
             }
