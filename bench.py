@@ -385,6 +385,12 @@ def run_gpu(args):
         llama_train = llama_layer_leg(rank, world, dev, fixture="llama7b_train_l4", runs=5)
     except Exception as exc:  # reported, never hidden
         llama_train = {"error": repr(exc)[:300]}
+    # config 5 at the batch it names (8 x 1024 tokens): 117 GB of device memory on one GPU
+    llama_train_full = None
+    try:
+        llama_train_full = llama_layer_leg(rank, world, dev, fixture="llama7b_train_b8s1024_l4", runs=3)
+    except Exception as exc:  # reported, never hidden
+        llama_train_full = {"error": repr(exc)[:300]}
 
     if rank != 0:
         if world > 1:
@@ -425,6 +431,7 @@ def run_gpu(args):
         "classes": classes,
         "llama7b_layer": llama,
         "llama7b_train_4layers": llama_train,
+        "llama7b_train_4layers_b8_s1024": llama_train_full,
         "cpu_baseline": cpu_baseline() if world == 1 else None,
     }
     print(json.dumps(line))
@@ -445,6 +452,14 @@ def llama_layer_leg(rank, world, dev, fixture="llama7b_layer", runs=10):
     if not os.path.exists(path):
         return {"skipped": "no memgraph fixture for %d locations" % world}
     mg = load_memgraph(path)
+    need = int(max(mg["mem_sizes"])) + (8 << 30)
+    free = torch.cuda.mem_get_info(dev)[0]
+    if free < need:
+        return {"skipped": "needs %.0f GB of device memory, %.0f GB free" % (need / 1e9, free / 1e9)}
+    tokens = 2048
+    for t in mg["inputs"]:
+        if t["name"] == "embeddings":
+            tokens = int(t["shape"][0]) * int(t["shape"][1])
     transport = os.environ.get("ES_B200_MOVE_TRANSPORT", "p2p")
     if world > 1:
         try:
@@ -497,17 +512,17 @@ def llama_layer_leg(rank, world, dev, fixture="llama7b_layer", runs=10):
             ms = float(t.item())
         return ms
 
-    out = {"tokens": 2048, "gpus": world, "move_transport": transport, "nodes_this_rank": dict(r.stats),
+    out = {"tokens": tokens, "gpus": world, "move_transport": transport, "nodes_this_rank": dict(r.stats),
            "taskgraph": mg["taskgraph"], "contraction_gflop": mg["taskgraph"]["contraction_flops"] / 1e9}
     ms_eager = timed(lambda: r.run(stream))
-    out["eager"] = {"ms": ms_eager, "tokens/s": 2048 / (ms_eager * 1e-3)}
+    out["eager"] = {"ms": ms_eager, "tokens/s": tokens / (ms_eager * 1e-3)}
     try:
         if transport == "nccl":
             # a process group holding captured NCCL send/recv nodes did not shut down cleanly here
             raise RuntimeError("not captured with the NCCL transport")
         r.capture()
         ms_graph = timed(r.replay)
-        out["cuda_graph"] = {"ms": ms_graph, "tokens/s": 2048 / (ms_graph * 1e-3),
+        out["cuda_graph"] = {"ms": ms_graph, "tokens/s": tokens / (ms_graph * 1e-3),
                              "TFLOP/s": mg["taskgraph"]["contraction_flops"] / (ms_graph * 1e-3) / 1e12}
     except Exception as exc:
         out["cuda_graph"] = {"error": repr(exc)[:200]}
