@@ -111,12 +111,60 @@ def cpu_baseline(budget_s=10.0, rows=1024):
         dt = time.perf_counter() - t0
         if dt >= budget_s or passes >= 200:
             break
-    return {
+    res = {
         "value": cpu_bytes(rows) * passes / dt / 1e9, "unit": "GB/s", "cores": lib.oracle_num_threads(),
         "kind": "port",
         "sample": "%d passes over the first %d of %d rows (same 4 ops, OpenMP over row blocks), %.1f s"
                   % (passes, rows, ROWS, dt),
     }
+    try:
+        res["other_classes"] = cpu_other_classes(lib)
+    except Exception as exc:  # reported, never hidden
+        res["other_classes"] = {"error": repr(exc)[:200]}
+    return res
+
+
+def cpu_other_classes(lib):
+    """The other kernel classes on the host cores, bounded samples: the C1 block contraction
+    (f32 2048^3) through the C port's blocked loops and through torch's CPU sgemm (the
+    closest stand-in here for the cblas_sgemm the reference's executor calls,
+    src/engine/cpu/kernel_executor.cc:1293-1548), and a C3 copy / accumulate touch through
+    the port of execute_touch (src/engine/touch.cc:155-237)."""
+    import torch
+    out = {}
+    p = lambda a: ctypes.c_void_p(a.ctypes.data)
+    rng = np.random.default_rng(1)
+    n = 2048
+    a = rng.uniform(-1, 1, (n, n)).astype(np.float32)
+    b = rng.uniform(-1, 1, (n, n)).astype(np.float32)
+    c = np.empty((n, n), np.float32)
+    rows = 256  # the port's triple loop: a 256-row slab of the block
+    t0 = time.perf_counter()
+    lib.oracle_matmul_f32(ctypes.c_uint64(rows), ctypes.c_uint64(n), ctypes.c_uint64(n), p(c), p(a), p(b))
+    dt = time.perf_counter() - t0
+    out["C1 block ij,jk->ik f32 (port, %d of 2048 rows)" % rows] = {"TFLOP/s": 2.0 * rows * n * n / dt / 1e12}
+    ta, tb = torch.from_numpy(a), torch.from_numpy(b)
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
+    torch.matmul(ta, tb)
+    t0 = time.perf_counter()
+    for _ in range(3):
+        torch.matmul(ta, tb)
+    dt = (time.perf_counter() - t0) / 3
+    out["C1 block ij,jk->ik f32 2048^3 (torch CPU sgemm, stand-in for cblas_sgemm)"] = {
+        "TFLOP/s": 2.0 * n ** 3 / dt / 1e12, "threads": torch.get_num_threads()}
+    # C3 p=2 block: [16,256,16,64] of f16 into a [32,512,32,128] tensor
+    sel = [(16, 32, 0, 16, 16), (256, 512, 0, 256, 256), (16, 32, 0, 16, 16), (64, 128, 0, 64, 64)]
+    dims = (ctypes.c_uint64 * 20)(*[v for d in sel for v in d])
+    src = rng.uniform(-1, 1, 16 * 256 * 16 * 64).astype(np.float16)
+    dst = np.zeros(32 * 512 * 32 * 128, np.float16)
+    for name, castable, factor in (("copy", -1, 2), ("add", 0, 3)):
+        lib.oracle_touch(4, dims, castable, 0, p(dst), p(src))
+        t0 = time.perf_counter()
+        for _ in range(5):
+            lib.oracle_touch(4, dims, castable, 0, p(dst), p(src))
+        dt = (time.perf_counter() - t0) / 5
+        out["touch C3 p=2 f16 %s (port of execute_touch)" % name] = {"GB/s": factor * src.nbytes / dt / 1e9}
+    return out
 
 
 def run_reference_arm(args):
@@ -628,6 +676,39 @@ def other_classes(km, dev, stream):
     big = torch.randn(int(np.prod(full)), dtype=torch.float16, device=dev)
     ms = time_launches(lambda: km(e, stream, dst, [big]), stream)
     out["permute bshd->bhsd f16 [32,512,32,128]"] = {"ms": ms, "GB/s": 2 * big.numel() * 2 / (ms * 1e-3) / 1e9}
+    del big, dst
+    # the f32 variant of the headline workload, [4096,4096], and the fused form of its last two ops
+    # (ab,a->a: sum_b exp(x[a,b] - m[a]), the reference's softmax_v3 reduction) on the f16 tensors
+    def timed_ew(name, e, ins, out_elems, dt, algorithmic_bytes):
+        ws = km.build(e)
+        o = torch.empty(out_elems, dtype=dt, device=dev)
+        w = torch.empty(max(ws or 0, 16), dtype=torch.uint8, device=dev)
+        ms = time_launches(lambda: km(e, stream, o, ins, (w, ws) if ws else None), stream)
+        out[name] = {"ms": ms, "GB/s": algorithmic_bytes / (ms * 1e-3) / 1e9, "kind": km.kernel_info(e).split("|")[0]}
+    r32, c32 = 4096, 4096
+    x32 = torch.randn(r32 * c32, dtype=torch.float32, device=dev)
+    y32 = torch.randn(r32 * c32, dtype=torch.float32, device=dev)
+    m32 = torch.randn(r32, dtype=torch.float32, device=dev)
+    f32 = "f32"
+    timed_ew("C2 f32 [4096,4096] silu(x)*y (64 MB tensors: partly L2-resident)", einsummable_t([r32, c32], [[0, 1], [0, 1]], 2,
+             S.combine(S.make_mul(f32), [S.make_silu(f32), S.make_identity(f32)])), [x32, y32], r32 * c32,
+             torch.float32, 3 * r32 * c32 * 4)
+    timed_ew("C2 f32 [4096,4096] row max (L2-resident)", einsummable_t([r32, c32], [[0, 1]], 1, S.make_identity(f32), "max"),
+             [x32], r32, torch.float32, r32 * c32 * 4 + r32 * 4)
+    timed_ew("C2 f32 [4096,4096] exp(x-rowmax) (partly L2-resident)", einsummable_t([r32, c32], [[0, 1], [0]], 2,
+             S.combine(S.make_exp(f32), [S.make_sub(f32)])), [x32, m32], r32 * c32, torch.float32,
+             2 * r32 * c32 * 4 + r32 * 4)
+    timed_ew("C2 f32 [4096,4096] row sum (L2-resident)", einsummable_t([r32, c32], [[0, 1]], 1, S.make_identity(f32), "add"),
+             [x32], r32, torch.float32, r32 * c32 * 4 + r32 * 4)
+    timed_ew("C2 f32 [4096,4096] fused sum_b exp(x-m) ab,a->a (L2-resident)", einsummable_t([r32, c32], [[0, 1], [0]], 1,
+             S.combine(S.make_exp(f32), [S.make_sub(f32)]), "add"), [x32, m32], r32, torch.float32,
+             r32 * c32 * 4 + 2 * r32 * 4)
+    del x32, y32
+    x16 = torch.randn(ROWS * COLS, dtype=torch.float16, device=dev)
+    m16 = torch.randn(ROWS, dtype=torch.float16, device=dev)
+    timed_ew("C2 f16 [8192,11008] fused sum_b exp(x-m) ab,a->a", einsummable_t([ROWS, COLS], [[0, 1], [0]], 1,
+             S.combine(S.make_exp("f16"), [S.make_sub("f16")]), "add"), [x16, m16], ROWS, torch.float16,
+             ROWS * COLS * 2 + 2 * ROWS * 2)
     return out
 
 
