@@ -484,6 +484,8 @@ int es_b200_describe(const es_einsummable_desc_t* desc, int what, char* buf, int
                 log += log2;
             }
             copy_out(log, buf, buf_len);
+        } else if (what == 4) {
+            copy_out(tc ? cp.info : std::string(), buf, buf_len);
         } else {
             fail(ES_BAD_ARGUMENT, "describe: unknown selector");
         }

@@ -218,7 +218,8 @@ int es_b200_kernel_info(es_b200_t* h, uint64_t kernel_id, char* buf, int buf_len
 /* Host-only helpers (no GPU needed): what build() would generate.  `what`:
  * 0 = merged form "str|join_shape|out_rank|inns", 1 = kernel kind,
  * 2 = generated CUDA source (empty for precompiled kinds),
- * 3 = compile the generated source for sm_100a and return the log. */
+ * 3 = compile the generated source for sm_100a and return the log,
+ * 4 = the tensor-core contraction's plan (tile shape, stages, schedule; empty for other kinds). */
 int es_b200_describe(const es_einsummable_desc_t* desc, int what, char* buf, int buf_len);
 
 /* Simplify a touch (src/einsummable/touch.cc:3-28); returns the new rank in

@@ -150,3 +150,31 @@ def test_kernel_kinds_of_the_llama_layer():
     assert einsummable_t([2048, 4096], [[0, 1], [1]], 2, S.make_mul("f16")).kernel_kind() == "ew_vec"
     assert einsummable_t([4, 512, 32, 64], [[0, 1, 2, 3], [1, 3]], 4, S.make_mul("c64")).kernel_kind() == "ew_vec"
     assert einsummable_t([32, 512, 32, 128], [[0, 2, 1, 3]], 4, S.make_identity("f16")).kernel_kind() == "ew_vec"
+
+
+@pytest.mark.parametrize("spec,extents,expect", [
+    # every row pair is a 256-row item: 128 items for 148 SMs beat two waves of 128-row tiles
+    ("ij,kj->ik", dict(i=2048, j=4096, k=4096), "items256=128,items128=0"),
+    # two full waves of 256-row items, the rest as 128-row items (FFN shape)
+    ("ij,kj->ik", dict(i=2048, j=4096, k=11008), "items256=296,items128=96"),
+    # odd number of 128-row tiles: the last row is scheduled alone
+    ("ij,kj->ik", dict(i=2176, j=1024, k=2816), "items256=88,items128=11"),
+    # too few tiles to gain from larger items: one wave of 128-row tiles
+    ("ij,kj->ik", dict(i=512, j=1024, k=768), None),
+    # two k-blocks per tile (attention scores): epilogue-bound, 128-row tiles
+    ("acbe,adbe->abcd", dict(a=4, b=32, c=512, d=512, e=128), None),
+    # f32 (3xTF32) keeps 128 x 128 tiles
+    ("ij,jk->ik", dict(i=2048, j=2048, k=2048), None),
+])
+def test_contraction_schedule_choice(spec, extents, expect):
+    """The split into 256-row and 128-row work items is made at build time from the shape alone
+    (host code: no GPU needed)."""
+    dtype = "f32" if spec == "ij,jk->ik" else "f16"
+    e = einsummable_t.from_str(spec, extents, scalarop_t.make_mul(dtype), "add")
+    assert e._describe(1).startswith("contraction_tc")
+    info = e._describe(4)
+    assert "bm=128" in info and "stages=" in info
+    if expect is None:
+        assert "items256" not in info, info
+    else:
+        assert expect in info, info
