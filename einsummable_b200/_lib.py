@@ -64,6 +64,7 @@ SYMBOLS = {
     "es_b200_prepare_touch_batch": (_i, [_vp, ctypes.POINTER(es_touch_item_t), _i, _i, _vp, _vp,
                                          ctypes.POINTER(es_touch_batch_t)]),
     "es_b200_launch_prepared_touch_batch": (_i, [_vp, ctypes.POINTER(es_touch_batch_t), _vp]),
+    "es_b200_debug_trace": (_i, [_vp, ctypes.POINTER(ctypes.c_ulonglong), _i, ctypes.POINTER(_i)]),
     "es_b200_fill_constant": (_i, [_vp, _i, _vp, _u64, _vp, _vp]),
     "es_b200_fill_lowertri": (_i, [_vp, _i, _vp, _vp, _u64, _u64, ctypes.c_int64, _vp, _vp]),
     "es_b200_move": (_i, [_vp, _i, _vp, _i, _vp, _u64, _vp]),

@@ -1,6 +1,9 @@
 """Builds libes_b200.so (sm_100a) in-tree with nvcc.
 
-usage: python -m einsummable_b200.build [--force]
+usage: python -m einsummable_b200.build [--force] [--trace]
+
+--trace builds lib/libes_b200_trace.so instead: the same library with the contraction kernel's
+clock trace compiled in (see einsummable_b200/trace.py); the product library is not touched.
 """
 import os
 import subprocess
@@ -25,8 +28,11 @@ def _stale():
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force=False, verbose=False):
-    if not force and not _stale():
+TRACE_LIB = os.path.join(LIB_DIR, "libes_b200_trace.so")
+
+
+def build(force=False, verbose=False, trace=False):
+    if not trace and not force and not _stale():
         return LIB
     os.makedirs(LIB_DIR, exist_ok=True)
     nvcc = os.path.join(CUDA_HOME, "bin", "nvcc")
@@ -38,8 +44,8 @@ def build(force=False, verbose=False):
         "-Xptxas", "-v" if verbose else "-O3",
         "-shared", "-cudart", "static",
         "-I", os.path.join(ROOT, "include"), "-I", CSRC,
-        "-o", LIB,
-    ] + [os.path.join(CSRC, s) for s in SOURCES] + [
+        "-o", TRACE_LIB if trace else LIB,
+    ] + (["-DES_B200_TRACE"] if trace else []) + [os.path.join(CSRC, s) for s in SOURCES] + [
         "-L", os.path.join(CUDA_HOME, "lib64"), "-lnvrtc",
         "-Xlinker", "-rpath," + os.path.join(CUDA_HOME, "lib64"),
     ]
@@ -49,8 +55,8 @@ def build(force=False, verbose=False):
         raise RuntimeError("nvcc failed building libes_b200.so")
     if verbose:
         sys.stderr.write(res.stdout + res.stderr)
-    return LIB
+    return TRACE_LIB if trace else LIB
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, trace="--trace" in sys.argv))

@@ -517,6 +517,18 @@ int es_b200_device_status(es_b200_t* h, unsigned int* error_word)
     });
 }
 
+int es_b200_debug_trace(es_b200_t* h, unsigned long long* out, int n, int* n_out)
+{
+    return guarded([&] {
+        check_handle(h);
+        if (!out || !n_out || n < 0) fail(ES_BAD_ARGUMENT, "null pointer or negative count");
+        set_device(h);
+        int got = read_trace(out, n);
+        if (got < 0) fail(ES_NOT_SUPPORTED, "this library was built without ES_B200_TRACE");
+        *n_out = got;
+    });
+}
+
 int es_b200_flag_signal(es_b200_t* h, void* flag, uint32_t limit_ms, void* stream)
 {
     return guarded([&] {

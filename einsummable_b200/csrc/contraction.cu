@@ -106,6 +106,23 @@ struct alignas(64) tc_params_t {
 
 __device__ unsigned int g_tc_error; // nonzero = a bounded wait expired (code, see below)
 
+// Opt-in clock trace (builds with -DES_B200_TRACE only): CTA 0 records clock64() at the role
+// boundaries of its first events, 8 slots of 1000 entries.
+//   slot 0 / 1: producer before / after the wait for a free stage, per k-iteration
+//               (entries 500..: top of a tile / coordinates ready, per tile)
+//   slot 2 / 3: MMA issuer before / after the wait for a full stage; slot 4: after the stage's commit
+//               (slot 2 entries 500..: producer after the copies of a k-iteration were issued)
+//   slot 5 / 6 / 7: epilogue warp 2 before / after the wait for an accumulator, after releasing it
+#ifdef ES_B200_TRACE
+__device__ unsigned long long g_trace[8000];
+#define ES_TR(slot, idx)                                                                           \
+    do {                                                                                           \
+        if (blockIdx.x == 0 && (idx) < 1000) g_trace[(slot) * 1000 + (idx)] = clock64();            \
+    } while (0)
+#else
+#define ES_TR(slot, idx) do { } while (0)
+#endif
+
 // ------------------------------------------------------------------ PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(void const* p)
 {
@@ -460,6 +477,7 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
         // ------------------------------------------------------------ TMA producer
         {
             uint32_t stage = 0, phase = 0;
+            [[maybe_unused]] uint32_t tr_k = 0, tr_t = 0; // trace indices: k-iterations, tiles
             bool     ok = true;
             prod_lane_t const me = make_prod_lane<BIG>(p, (uint32_t)lane, a_region);
             uint32_t const stages = p.stages, stage_bytes = p.stage_bytes, bn = p.bn;
@@ -471,6 +489,7 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
             if constexpr (!BIG) decode_tile(p, blockIdx.x, m_tile, n_tile, outer);
             for (uint32_t tile = blockIdx.x; tile < p.total_items && ok;
                  tile += gridDim.x, step_tile<BIG>(p, m_tile, n_tile, outer)) {
+                if (lane == 0) ES_TR(0, 500 + tr_t);
                 if constexpr (BIG) decode_item<true>(p, tile, m_tile, halves, n_tile, outer);
                 uint32_t const tx_bytes = stage_bytes - ((BIG ? 2u : 1u) - halves) * term_a_bytes;
                 bool const     mine = me.active && me.half < halves; // a 128-row item has no second half
@@ -479,17 +498,23 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
                 uint32_t kb = 0, kouter[4] = {0, 0, 0, 0};
                 int      c[5];
                 lane_coords(me, mn_elems, outer, kouter, c);
+                if (lane == 0) ES_TR(1, 500 + tr_t);
+                ++tr_t;
                 for (uint32_t ki = 0; ki < k_iters; ++ki) {
                     // lane 0 waits for the stage and announces the bytes; then every lane issues its copy
                     uint32_t const bar = full0 + stage * 8u;
                     uint32_t       go = 1;
                     if (lane == 0) {
+                        ES_TR(0, tr_k);
                         go = mbar_wait(empty0 + stage * 8u, phase ^ 1, abort_flag, 1) ? 1u : 0u;
+                        ES_TR(1, tr_k);
                         if (go) mbar_arrive_expect_tx(bar, tx_bytes);
                     }
                     go = __shfl_sync(0xffffffffu, go, 0);
                     if (!go) { ok = false; break; }
                     if (mine) tma_load5(smem_base + stage * stage_bytes + me.dst_off, me.desc, bar, c[0], c[1], c[2], c[3], c[4]);
+                    if (lane == 0) ES_TR(2, 500 + tr_k);
+                    ++tr_k;
                     if (++stage == stages) { stage = 0; phase ^= 1; }
                     if (ki + 1 == k_iters) break; // the next tile computes its own coordinates
                     if (++kb == k_blocks) {
@@ -514,6 +539,7 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             uint32_t stage = 0, phase = 0, use0 = 0, use1 = 0; // uses of each accumulator slot so far
+            [[maybe_unused]] uint32_t tr_k = 0;
             bool     ok = true;
             constexpr uint32_t NT = PROMOTE ? 3u : 1u; // MMAs per k-step: (lo*hi, hi*lo, hi*hi) or one
             uint64_t const a_hi = ((uint64_t)p.a.desc_hi << 32) | ((uint64_t)p.a.desc_lbo << 16);
@@ -542,7 +568,9 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
                     uint32_t const ki1 = min(ki0 + p.k_chunk, k_iters);
                     for (uint32_t ki = ki0; ki < ki1; ++ki) {
                         uint32_t const s = stage;
+                        ES_TR(2, tr_k);
                         if (!mbar_wait(smem_u32(&ctrl->full[s]), phase, abort_flag, 3)) { ok = false; break; }
+                        ES_TR(3, tr_k);
                         if (++stage == stages) { stage = 0; phase ^= 1; }
                         tc_fence_after();
                         uint32_t const a0 = base_units + s * stage_units;
@@ -573,6 +601,8 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
                             }
                         }
                         umma_commit(smem_u32(&ctrl->empty[s])); // frees the smem stage when these MMAs retire
+                        ES_TR(4, tr_k);
+                        ++tr_k;
                     }
                     if (ok) {
                         umma_commit(smem_u32(&ctrl->tmem_full[slot0]));
@@ -588,6 +618,7 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
         uint32_t const quarter = warp & 3; // TMEM lanes 32*quarter .. +31 belong to this warp
         uint32_t const half = (uint32_t)(warp - 2) >> 2;
         uint32_t use0 = 0, use1 = 0, store_seq = 0; // accumulator slot uses: the MMA issuer's rule
+        [[maybe_unused]] uint32_t tr_u = 0;
         bool     ok = true;
         // PROMOTE: partial sums of each k-chunk are added in registers with
         // round-to-nearest f32 adds.  The tensor core's own accumulation truncates,
@@ -634,7 +665,9 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
                 else if (use0 <= use1) { acc = 0; acc_ph = use0++ & 1; }
                 else { acc = 1; acc_ph = use1++ & 1; }
                 bool const first_chunk = ki0 == 0, last_chunk = ki0 + p.k_chunk >= k_iters;
+                if (warp == 2 && lane == 0) ES_TR(5, tr_u);
                 if (!mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_ph, abort_flag, 4)) { ok = false; break; }
+                if (warp == 2 && lane == 0) ES_TR(6, tr_u);
                 tc_fence_after();
                 uint32_t const trow = tmem_base + ((quarter * 32u) << 16) + acc * p.bn;
                 if constexpr (PROMOTE) {
@@ -746,6 +779,8 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&ctrl->tmem_empty[acc]));
+                if (warp == 2 && lane == 0) ES_TR(7, tr_u);
+                ++tr_u;
             }
           }
         }
@@ -1263,6 +1298,20 @@ void launch_contraction(contraction_plan_t const& plan,
     else if (tp.promote) launch(tc_contraction_kernel<1, true, false>, 1);
     else launch(tc_contraction_kernel<1, false, false>, 2);
     ES_CUDA_CHECK(cudaGetLastError());
+}
+
+int read_trace(unsigned long long* out, int n)
+{
+#ifdef ES_B200_TRACE
+    if (n > 8000) n = 8000;
+    ES_CUDA_CHECK(cudaDeviceSynchronize());
+    ES_CUDA_CHECK(cudaMemcpyFromSymbol(out, g_trace, sizeof(unsigned long long) * (size_t)n));
+    return n;
+#else
+    (void)out;
+    (void)n;
+    return -1;
+#endif
 }
 
 unsigned int read_and_clear_tc_error()

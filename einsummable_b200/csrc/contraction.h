@@ -47,4 +47,8 @@ inline bool contraction_pointers_ok(void const* lhs, void const* rhs)
 // (nonzero = a bounded wait inside a kernel expired).  Synchronises the device.
 unsigned int read_and_clear_tc_error();
 
+// Trace builds (-DES_B200_TRACE): copies the first `n` clock samples of CTA 0 (see contraction.cu);
+// returns the number copied, -1 when the library was built without the trace.
+int read_trace(unsigned long long* out, int n);
+
 } // namespace es

@@ -208,6 +208,14 @@ class kernel_manager_t:
         _lib.check(self._lib.es_b200_device_status(self._h, ctypes.byref(w)))
         return w.value
 
+    def debug_trace(self, n=8000):
+        """Clock samples of the last tensor-core contraction launch (trace builds only, see
+        einsummable_b200/trace.py); raises with ES_NOT_SUPPORTED on the product library."""
+        buf = (ctypes.c_ulonglong * n)()
+        got = ctypes.c_int(0)
+        _lib.check(self._lib.es_b200_debug_trace(self._h, buf, n, ctypes.byref(got)))
+        return list(buf[:got.value])
+
     def counters(self):
         arr = (ctypes.c_uint64 * 4)()
         _lib.check(self._lib.es_b200_query_counters(self._h, arr))

@@ -257,6 +257,13 @@ int es_b200_rowsum_f32_noalloc(es_b200_t*   h,
  * valid.  The reference has no counterpart: its library kernels cannot report. */
 int es_b200_device_status(es_b200_t* h, unsigned int* error_word);
 
+/* Clock trace of the tensor-core contraction kernel (trace builds only: the library compiled
+ * with -DES_B200_TRACE records clock64() at the role boundaries of CTA 0, 8 slots of 1000
+ * entries, see csrc/contraction.cu).  Copies up to `n` samples of the last launch; a normal
+ * build returns ES_NOT_SUPPORTED.  The reference has no counterpart (its timetracker hooks in
+ * src/engine/cpu/kernel_executor.cc:459-591 are host-side and commented out). */
+int es_b200_debug_trace(es_b200_t* h, unsigned long long* out, int n, int* n_out);
+
 /* Launch / byte counters since creation: launches[class], class order =
  * einsummable, touch, fill, move. */
 int es_b200_query_counters(es_b200_t* h, uint64_t launches[4]);

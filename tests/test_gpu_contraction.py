@@ -137,3 +137,12 @@ def test_linearity_at_full_llama_size(km):
     assert km.kernel_info(e).startswith("contraction_tc")
     want = a.reshape(i, j)[:, perm].reshape(-1)
     assert got.tobytes() == want.tobytes()
+
+
+def test_clock_trace_is_absent_from_the_product_library(km):
+    """The kernel's clock trace only exists in the library built with -DES_B200_TRACE
+    (python -m einsummable_b200.build --trace); the product library says so."""
+    from einsummable_b200 import _lib
+    with pytest.raises(_lib.es_error) as exc:
+        km.debug_trace(16)
+    assert "ES_B200_TRACE" in str(exc.value)
