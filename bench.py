@@ -722,6 +722,30 @@ def run_only(args):
     km = es.kernel_manager_t(0)
     stream = torch.cuda.current_stream(dev)
     mul16 = S.make_mul("f16")
+    if args.only == "llama_layer":
+        # the LLaMA-7B-shape layer memgraph (1 location), `steps` eager runs after `warmup`
+        # (profiler launch lists: every node is one or two launches of the library's kernels)
+        from einsummable_b200.memgraph import load_memgraph, memgraph_runner_t
+        mg = load_memgraph(os.path.join(ROOT, "tests", "golden", "graphs", "llama7b_layer_locs1.json.gz"))
+        r = memgraph_runner_t(mg, devices=[0])
+        rng = np.random.default_rng(7)
+        for t in mg["inputs"]:
+            shape, name = t["shape"], t["name"]
+            if name == "freqs_cis":
+                ang = np.outer(np.arange(shape[0]), 1.0 / (10000.0 ** (np.arange(shape[1]) / shape[1])))
+                v = (np.cos(ang) + 1j * np.sin(ang)).astype(np.complex64)
+            elif name.endswith("norm.weight"):
+                v = np.ones(shape, dtype=np.float16)
+            else:
+                v = (rng.standard_normal(shape).astype(np.float32) * 0.02).astype(np.float16)
+            r.set_input(name, v)
+        for _ in range(args.warmup):
+            r.run(stream)
+        torch.cuda.synchronize()
+        ms = time_launches(lambda: r.run(stream), stream, iters=args.steps, warm=0)
+        print(json.dumps({"only": "llama_layer", "ms": ms, "launches_per_run": len(r.program),
+                          "nodes": dict(r.stats), "device_status": r.device_status()}))
+        return
     if args.only == "move":
         # move_t between two GPUs driven by one process (the reference's server model):
         # source buffer on cuda:1, destination on cuda:0, through es_b200_move
@@ -793,7 +817,7 @@ def main():
                     help="rows of the [rows, 11008] tensors (default: the full C2 workload); "
                          "smaller values are for profiler captures only")
     ap.add_argument("--only", default=None,
-                    choices=["gemm_qkv", "gemm_ffn", "gemm_f32", "gemm_nn", "gemm_tn", "attn_scores", "attn_pv", "touch", "permute", "move"],
+                    choices=["llama_layer", "gemm_qkv", "gemm_ffn", "gemm_f32", "gemm_nn", "gemm_tn", "attn_scores", "attn_pv", "touch", "permute", "move"],
                     help="time one other kernel class alone (profiler captures); prints its own small JSON line")
     ap.add_argument("--kernels-only", action="store_true",
                     help="skip the end-to-end, other-class and CPU-baseline legs (profiler captures)")
