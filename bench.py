@@ -520,21 +520,24 @@ def llama_layer_leg(rank, world, dev, fixture="llama7b_layer", runs=10):
     else:
         transport = "local"
         r = memgraph_runner_t(mg, devices=[dev.index])
-    rng = np.random.default_rng(7)
-    for t in mg["inputs"]:
-        shape, name = t["shape"], t["name"]
-        if name == "freqs_cis":
-            seq, half = shape
-            ang = np.outer(np.arange(seq), 1.0 / (10000.0 ** (np.arange(half) / half)))
-            v = (np.cos(ang) + 1j * np.sin(ang)).astype(np.complex64)
-        elif name.endswith("norm.weight"):
-            v = np.ones(shape, dtype=np.float16)
-        elif name == "labels":
-            v = np.zeros(shape, dtype=np.float16)
-            v[np.arange(shape[0]), rng.integers(0, shape[1], shape[0])] = 1.0
-        else:
-            v = (rng.standard_normal(shape).astype(np.float32) * 0.02).astype(np.float16)
-        r.set_input(name, v)
+    def fill_inputs(runner):
+        rng = np.random.default_rng(7)
+        for t in mg["inputs"]:
+            shape, name = t["shape"], t["name"]
+            if name == "freqs_cis":
+                seq, half = shape
+                ang = np.outer(np.arange(seq), 1.0 / (10000.0 ** (np.arange(half) / half)))
+                v = (np.cos(ang) + 1j * np.sin(ang)).astype(np.complex64)
+            elif name.endswith("norm.weight"):
+                v = np.ones(shape, dtype=np.float16)
+            elif name == "labels":
+                v = np.zeros(shape, dtype=np.float16)
+                v[np.arange(shape[0]), rng.integers(0, shape[1], shape[0])] = 1.0
+            else:
+                v = (rng.standard_normal(shape).astype(np.float32) * 0.02).astype(np.float16)
+            runner.set_input(name, v)
+
+    fill_inputs(r)
     stream = torch.cuda.current_stream(dev)
 
     def barrier():
@@ -579,6 +582,23 @@ def llama_layer_leg(rank, world, dev, fixture="llama7b_layer", runs=10):
     r.close()
     del r
     torch.cuda.empty_cache()
+    if world == 1:
+        # the same memgraph with elementwise producers folded into their only reader (fusion across
+        # node boundaries: a rewrite of the graph, not something the reference's engine does)
+        try:
+            rf = memgraph_runner_t(mg, devices=[dev.index], fuse=True)
+            fill_inputs(rf)
+            rf.capture()
+            ms_fused = timed(rf.replay)
+            out["fused_cuda_graph"] = {"ms": ms_fused, "tokens/s": tokens / (ms_fused * 1e-3),
+                                       "nodes_folded": rf.folded, "einsummables": rf.stats["einsummable"],
+                                       "device_status": rf.device_status()}
+            rf.graph = None
+            rf.close()
+            del rf
+            torch.cuda.empty_cache()
+        except Exception as exc:  # reported, never hidden
+            out["fused_cuda_graph"] = {"error": repr(exc)[:200]}
     return out
 
 

@@ -1,0 +1,150 @@
+"""Fusion across node boundaries of a memgraph (one location): an elementwise apply node whose
+result has exactly one reader is folded into that reader, so the intermediate tensor never
+makes its round trip through HBM.
+
+The reference keeps such chains as separate nodes (softmax = 5 nodes, src/einsummable/gwriter.cc:830-855;
+RMSNorm = 8 nodes, llama/modules.cc:126-195) and its kernel manager even splits one node into several
+cuTENSOR calls; here the code generator compiles any scalarop tree, so folding a producer into its
+consumer is a substitution in the join text plus a composition of the index maps.
+
+The pass works on the memgraph as loaded from JSON and returns a new memgraph for in-order execution
+(the runner launches nodes in list order).  A producer A is folded into its reader B when
+  * A is an elementwise einsummable (no aggregation), B an einsummable that is not a plain contraction
+    (those run on the tensor cores with the join x0*x1),
+  * A's result is read by B only, in one input slot, and is not a saved output,
+  * A and B iterate over the same number of points (nothing is recomputed),
+  * nothing between A and B in list order, and not B itself, writes memory A reads (the memgraph
+    reuses memory: B now reads A's inputs later than the reference planned),
+  * the folded node has at most 8 inputs.
+"""
+import copy
+import re
+
+MAX_INNS = 8
+_DSIZE = {"f16": 2, "f32": 4, "f64": 8, "c64": 8}
+_HOLE = re.compile(r"hole\|(f16|f32|f64|c64)@(\d+)")
+
+
+def _prod(v):
+    r = 1
+    for x in v:
+        r *= int(x)
+    return r
+
+
+def _is_elementwise(e):
+    return e["castable"] is None and e["out_rank"] == len(e["join_shape"])
+
+
+def _is_plain_contraction(e):
+    if e["castable"] != "add" or len(e["inns"]) != 2 or e["out_rank"] == len(e["join_shape"]):
+        return False
+    return re.fullmatch(r"\*\[hole\|(f16|f32|f64|c64)@0,hole\|(f16|f32|f64|c64)@1\]", e["join"]) is not None
+
+
+def _overlap(a, b):
+    return a[0] < b[0] + b[1] and b[0] < a[0] + a[1]
+
+
+def _written_region(node):
+    k = node["kind"]
+    if k == "apply":
+        return tuple(node["mems"][0])
+    if k == "constant":
+        f = node["fill"]
+        if f["type"] == "constant":
+            return (node["offset"], int(f["nelem"]) * _DSIZE[f["value"]["dtype"]])
+        return (node["offset"], int(f["nrow"]) * int(f["ncol"]) * _DSIZE[f["lower"]["dtype"]])
+    if k in ("move", "copy"):
+        return (node["dst_offset"], node["size"])
+    return None
+
+
+def compose(a, b, slot):
+    """The einsummable that computes b with its input `slot` replaced by the expression a."""
+    n_a = len(a["inns"])
+    shift = n_a - 1
+
+    def renumber_b(m):
+        i = int(m.group(2))
+        return "hole|%s@%d" % (m.group(1), i if i < slot else i + shift)
+
+    def renumber_a(m):
+        return "hole|%s@%d" % (m.group(1), int(m.group(2)) + slot)
+
+    a_text = _HOLE.sub(renumber_a, a["join"])
+    # substitute first (the slot's hole is unique text "hole|dt@slot"), then renumber the others
+    parts = []
+    pos = 0
+    for m in _HOLE.finditer(b["join"]):
+        parts.append(b["join"][pos:m.start()])
+        parts.append(a_text if int(m.group(2)) == slot else renumber_b(m))
+        pos = m.end()
+    parts.append(b["join"][pos:])
+    via = b["inns"][slot]                      # a's mode m is b's mode via[m]
+    new_inns = b["inns"][:slot] + [[via[m] for m in inn] for inn in a["inns"]] + b["inns"][slot + 1:]
+    return {"join_shape": list(b["join_shape"]), "inns": new_inns, "out_rank": b["out_rank"],
+            "join": "".join(parts), "castable": b["castable"]}
+
+
+def fuse_elementwise_chains(mg):
+    """Returns (new memgraph, number of nodes folded away).  Memgraphs with several locations are
+    returned unchanged: their moves tie the list order to the other ranks'."""
+    if mg["num_locs"] != 1:
+        return mg, 0
+    mg = copy.deepcopy(mg)
+    nodes = mg["nodes"]
+    saved = [(blk["offset"], blk["size"]) for t in mg["outputs"] for blk in t["blocks"]]
+    alive = [True] * len(nodes)
+    folded = 0
+    for ia, a in enumerate(nodes):
+        if a["kind"] != "apply" or "einsummable" not in a or not _is_elementwise(a["einsummable"]):
+            continue
+        out = tuple(a["mems"][0])
+        if any(_overlap(out, s) for s in saved):
+            continue
+        # readers of the result: apply nodes after A that depend on it and read exactly its region
+        readers = []
+        for ib in range(ia + 1, len(nodes)):
+            n = nodes[ib]
+            if not alive[ib] or n["kind"] != "apply" or a["id"] not in n["inns"]:
+                continue
+            if any(tuple(m) == out for m in n["mems"][1:]):
+                readers.append(ib)
+        if len(readers) != 1:
+            continue
+        ib = readers[0]
+        b = nodes[ib]
+        if "einsummable" not in b or _is_plain_contraction(b["einsummable"]):
+            continue
+        slots = [k for k, m in enumerate(b["mems"][1:]) if tuple(m) == out]
+        if len(slots) != 1:
+            continue
+        ea, eb = a["einsummable"], b["einsummable"]
+        if _prod(ea["join_shape"]) != _prod(eb["join_shape"]):
+            continue
+        if len(eb["inns"]) - 1 + len(ea["inns"]) > MAX_INNS:
+            continue
+        a_reads = [tuple(m) for m in a["mems"][1:]]
+        hazard = any(_overlap(tuple(b["mems"][0]), r) for r in a_reads)
+        for ic in range(ia + 1, ib):
+            if hazard:
+                break
+            if not alive[ic]:
+                continue
+            w = _written_region(nodes[ic])
+            if w is not None and any(_overlap(w, r) for r in a_reads):
+                hazard = True
+        if hazard:
+            continue
+        slot = slots[0]
+        b["einsummable"] = compose(ea, eb, slot)
+        b["mems"] = [b["mems"][0]] + b["mems"][1:1 + slot] + a["mems"][1:] + b["mems"][2 + slot:]
+        b["inns"] = sorted(set(i for i in b["inns"] if i != a["id"]) | set(a["inns"]))
+        alive[ia] = False
+        folded += 1
+    # a folded node stays in the list as a bookkeeping stub so that ids keep indexing the list
+    for i, n in enumerate(nodes):
+        if not alive[i]:
+            nodes[i] = {"id": n["id"], "inns": n["inns"], "kind": "alloc", "loc": n["loc"], "folded": True}
+    return mg, folded

@@ -81,11 +81,16 @@ def move_runs(mg):
 
 
 class memgraph_runner_t:
-    def __init__(self, mg, devices=None, rank=None, world=None, transport="nccl", wait_limit_ms=0):
+    def __init__(self, mg, devices=None, rank=None, world=None, transport="nccl", wait_limit_ms=0, fuse=False):
         """transport (one process per GPU only): "nccl" = send/recv pairs; "p2p" = every
         location buffer lives in symmetric memory, the destination rank pulls the bytes over
         NVLink with an SM copy kernel, and the two ranks hand-shake through bounded flag
         kernels (data ready / copy finished)."""
+        self.folded = 0
+        if fuse:
+            # elementwise producers folded into their only reader (one location only, see fuse.py)
+            from .fuse import fuse_elementwise_chains
+            mg, self.folded = fuse_elementwise_chains(mg)
         self.mg = mg
         self.num_locs = mg["num_locs"]
         self.distributed = rank is not None

@@ -129,3 +129,52 @@ def test_llama7b_layer_runs_and_is_finite():
     print(kinds)
     assert kinds.get("contraction_tc_f16", 0) >= 10   # every contraction of the layer is on the tensor cores
     r.close()
+
+
+@pytest.mark.parametrize("name", ["llama_tiny_locs1", "llama_train_tiny_locs1"])
+def test_fused_memgraphs_match_reference(name):
+    """Elementwise producers folded into their only reader (einsummable_b200/fuse.py): every fused
+    join goes through the same code generator; results against the reference interpreter's."""
+    mg = load_memgraph(graph_path(name))
+    r = memgraph_runner_t(mg, fuse=True)
+    assert r.folded > 0
+    for k, v in inputs_of(name).items():
+        r.set_input(k, v)
+    r.run()
+    torch.cuda.synchronize()
+    assert r.device_status() == 0
+    for k, ref in outputs_of(name).items():
+        got = r.get_output(k)
+        scale = np.abs(ref.astype(np.float64)).max()
+        err = np.abs(got.astype(np.float64) - ref.astype(np.float64)).max()
+        assert err <= (2e-2 if ref.dtype == np.float16 else 1e-4) * scale, (name, k, err, scale)
+    r.close()
+
+
+def test_llama7b_layer_fused_agrees_with_unfused():
+    mg = load_memgraph(os.path.join(GRAPHS, "llama7b_layer_locs1.json.gz"))
+    outs = []
+    for fuse in (False, True):
+        r = memgraph_runner_t(mg, fuse=fuse)
+        rng = np.random.default_rng(0)
+        for t in mg["inputs"]:
+            shape, name = t["shape"], t["name"]
+            if name == "freqs_cis":
+                seq, half = shape
+                ang = np.outer(np.arange(seq), 1.0 / (10000.0 ** (np.arange(half) / half)))
+                v = (np.cos(ang) + 1j * np.sin(ang)).astype(np.complex64)
+            elif name.endswith("norm.weight"):
+                v = np.ones(shape, dtype=np.float16)
+            else:
+                v = (rng.standard_normal(shape).astype(np.float32) * 0.02).astype(np.float16)
+            r.set_input(name, v)
+        r.run()
+        torch.cuda.synchronize()
+        assert r.device_status() == 0
+        outs.append(r.get_output("scores").astype(np.float64))
+        if fuse:
+            assert r.folded >= 15
+        r.close()
+    scale = np.abs(outs[0]).max()
+    # f16 graph: the folded intermediates are no longer rounded to f16 (1e-2 of the output scale)
+    assert np.abs(outs[0] - outs[1]).max() <= 1e-2 * scale

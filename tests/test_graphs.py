@@ -118,3 +118,43 @@ def test_move_runs_cut_groups_the_same_way_on_every_rank(name):
     for n in moves:
         for j in move_ancestors(n["id"], set()):
             assert runs[j] != runs[n["id"]]
+
+
+def test_compose_substitutes_and_renumbers():
+    from einsummable_b200.fuse import compose
+    a = {"join_shape": [4, 8], "inns": [[0, 1], [1]], "out_rank": 2,
+         "join": "+[hole|f32@0,*[constant{f32|-1},hole|f32@1]]", "castable": None}      # x[a,b] - m[b]
+    b = {"join_shape": [8, 4], "inns": [[1, 0], [0, 1]], "out_rank": 1,                   # sum_b y[a',b'] * A^T
+         "join": "*[hole|f32@1,exp[hole|f32@0]]", "castable": "add"}
+    c = compose(a, b, 0)
+    # a's modes (0, 1) are b's modes (1, 0); b's other input moves behind a's two inputs
+    assert c["inns"] == [[1, 0], [0], [0, 1]]
+    assert c["join"] == "*[hole|f32@2,exp[+[hole|f32@0,*[constant{f32|-1},hole|f32@1]]]]"
+    assert c["castable"] == "add" and c["out_rank"] == 1 and c["join_shape"] == [8, 4]
+
+
+@pytest.mark.parametrize("name", ["llama_tiny_locs1", "llama_train_tiny_locs1", "c1_n64_locs1"])
+def test_fused_memgraph_still_matches_reference(name):
+    """Folding elementwise producers into their only reader must not change the results beyond the
+    rounding of the intermediates that are no longer written (none in f32 beyond reassociation)."""
+    from einsummable_b200.fuse import fuse_elementwise_chains
+    mg = load(name)
+    fused, n = fuse_elementwise_chains(mg)
+    assert n > 0 or name.startswith("c1")
+    assert len(fused["nodes"]) == len(mg["nodes"])          # ids keep indexing the list
+    for mode in ("interp", "executor"):
+        bufs = O.memgraph_place_inputs(fused, inputs_of(name))
+        O.run_memgraph(fused, bufs, mode)
+        got = O.memgraph_collect_outputs(fused, bufs)
+        for k, want in outputs_of(name).items():
+            scale = np.abs(want.astype(np.float64)).max()
+            err = np.abs(got[k].astype(np.float64) - want.astype(np.float64)).max()
+            tol = 2e-2 if want.dtype == np.float16 else 1e-4
+            assert err <= tol * scale, (name, mode, k, err, scale)
+
+
+def test_fusion_leaves_partitioned_memgraphs_alone():
+    from einsummable_b200.fuse import fuse_elementwise_chains
+    mg = load("llama_tiny_locs2")
+    fused, n = fuse_elementwise_chains(mg)
+    assert n == 0 and fused is mg
