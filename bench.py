@@ -583,7 +583,7 @@ def llama_layer_leg(rank, world, dev, fixture="llama7b_layer", runs=10):
     del r
     torch.cuda.empty_cache()
     if world == 1:
-        # the same memgraph with elementwise producers folded into their only reader (fusion across
+        # the same memgraph with elementwise producers folded into their readers (fusion across
         # node boundaries: a rewrite of the graph, not something the reference's engine does)
         try:
             rf = memgraph_runner_t(mg, devices=[dev.index], fuse=True)

@@ -1,5 +1,5 @@
-"""Fusion across node boundaries of a memgraph (one location): an elementwise apply node whose
-result has exactly one reader is folded into that reader, so the intermediate tensor never
+"""Fusion across node boundaries of a memgraph (one location): an elementwise apply node is
+folded into the nodes that read its result, so the intermediate tensor never
 makes its round trip through HBM.
 
 The reference keeps such chains as separate nodes (softmax = 5 nodes, src/einsummable/gwriter.cc:830-855;
@@ -11,7 +11,9 @@ The pass works on the memgraph as loaded from JSON and returns a new memgraph fo
 (the runner launches nodes in list order).  A producer A is folded into its reader B when
   * A is an elementwise einsummable (no aggregation), B an einsummable that is not a plain contraction
     (those run on the tensor cores with the join x0*x1),
-  * A's result is read by B only, in one input slot, and is not a saved output,
+  * every reader of A's result qualifies (then A is folded into each of them: evaluating a
+    memory-bound expression once per reader moves fewer bytes than writing and re-reading it),
+    reads it in one input slot, and the result is not a saved output,
   * A and B iterate over the same number of points (nothing is recomputed),
   * nothing between A and B in list order, and not B itself, writes memory A reads (the memgraph
     reuses memory: B now reads A's inputs later than the reference planned),
@@ -111,36 +113,48 @@ def fuse_elementwise_chains(mg):
                 continue
             if any(tuple(m) == out for m in n["mems"][1:]):
                 readers.append(ib)
-        if len(readers) != 1:
+        if not readers:
             continue
-        ib = readers[0]
-        b = nodes[ib]
-        if "einsummable" not in b or _is_plain_contraction(b["einsummable"]):
-            continue
-        slots = [k for k, m in enumerate(b["mems"][1:]) if tuple(m) == out]
-        if len(slots) != 1:
-            continue
-        ea, eb = a["einsummable"], b["einsummable"]
-        if _prod(ea["join_shape"]) != _prod(eb["join_shape"]):
-            continue
-        if len(eb["inns"]) - 1 + len(ea["inns"]) > MAX_INNS:
-            continue
+        ea = a["einsummable"]
         a_reads = [tuple(m) for m in a["mems"][1:]]
-        hazard = any(_overlap(tuple(b["mems"][0]), r) for r in a_reads)
-        for ic in range(ia + 1, ib):
-            if hazard:
+        # with R readers the producer is evaluated R times instead of once; in bytes that is
+        # R * in(A) against in(A) + (R + 1) * out(A) before, nearly always less (kernels of this
+        # kind are bound by memory, not by the arithmetic)
+        in_bytes = sum(m[1] for m in a_reads)
+        n_r = len(readers)
+        if (n_r - 1) * in_bytes > (n_r + 1) * out[1]:
+            continue
+        plans = []
+        for ib in readers:
+            b = nodes[ib]
+            if "einsummable" not in b or _is_plain_contraction(b["einsummable"]):
                 break
+            slots = [k for k, m in enumerate(b["mems"][1:]) if tuple(m) == out]
+            eb = b["einsummable"]
+            if len(slots) != 1 or _prod(ea["join_shape"]) != _prod(eb["join_shape"]):
+                break
+            if len(eb["inns"]) - 1 + len(ea["inns"]) > MAX_INNS:
+                break
+            if any(_overlap(tuple(b["mems"][0]), r) for r in a_reads):
+                break
+            plans.append((ib, slots[0]))
+        if len(plans) != n_r:
+            continue
+        hazard = False
+        for ic in range(ia + 1, readers[-1]):
             if not alive[ic]:
                 continue
             w = _written_region(nodes[ic])
             if w is not None and any(_overlap(w, r) for r in a_reads):
                 hazard = True
+                break
         if hazard:
             continue
-        slot = slots[0]
-        b["einsummable"] = compose(ea, eb, slot)
-        b["mems"] = [b["mems"][0]] + b["mems"][1:1 + slot] + a["mems"][1:] + b["mems"][2 + slot:]
-        b["inns"] = sorted(set(i for i in b["inns"] if i != a["id"]) | set(a["inns"]))
+        for ib, slot in plans:
+            b = nodes[ib]
+            b["einsummable"] = compose(ea, b["einsummable"], slot)
+            b["mems"] = [b["mems"][0]] + b["mems"][1:1 + slot] + a["mems"][1:] + b["mems"][2 + slot:]
+            b["inns"] = sorted(set(i for i in b["inns"] if i != a["id"]) | set(a["inns"]))
         alive[ia] = False
         folded += 1
     # a folded node stays in the list as a bookkeeping stub so that ids keep indexing the list

@@ -88,7 +88,7 @@ class memgraph_runner_t:
         kernels (data ready / copy finished)."""
         self.folded = 0
         if fuse:
-            # elementwise producers folded into their only reader (one location only, see fuse.py)
+            # elementwise producers folded into their readers (one location only, see fuse.py)
             from .fuse import fuse_elementwise_chains
             mg, self.folded = fuse_elementwise_chains(mg)
         self.mg = mg

@@ -133,7 +133,7 @@ def test_llama7b_layer_runs_and_is_finite():
 
 @pytest.mark.parametrize("name", ["llama_tiny_locs1", "llama_train_tiny_locs1"])
 def test_fused_memgraphs_match_reference(name):
-    """Elementwise producers folded into their only reader (einsummable_b200/fuse.py): every fused
+    """Elementwise producers folded into their readers (einsummable_b200/fuse.py): every fused
     join goes through the same code generator; results against the reference interpreter's."""
     mg = load_memgraph(graph_path(name))
     r = memgraph_runner_t(mg, fuse=True)

@@ -135,7 +135,7 @@ def test_compose_substitutes_and_renumbers():
 
 @pytest.mark.parametrize("name", ["llama_tiny_locs1", "llama_train_tiny_locs1", "c1_n64_locs1"])
 def test_fused_memgraph_still_matches_reference(name):
-    """Folding elementwise producers into their only reader must not change the results beyond the
+    """Folding elementwise producers into their readers must not change the results beyond the
     rounding of the intermediates that are no longer written (none in f32 beyond reassociation)."""
     from einsummable_b200.fuse import fuse_elementwise_chains
     mg = load(name)
