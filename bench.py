@@ -436,7 +436,10 @@ def run_gpu(args):
     # config 5 at the batch it names (8 x 1024 tokens): 117 GB of device memory on one GPU
     llama_train_full = None
     try:
-        llama_train_full = llama_layer_leg(rank, world, dev, fixture="llama7b_train_b8s1024_l4", runs=3)
+        if world == 1 or os.environ.get("ES_B200_BENCH_C5_FULL") == "1":
+            llama_train_full = llama_layer_leg(rank, world, dev, fixture="llama7b_train_b8s1024_l4", runs=3)
+        else:
+            llama_train_full = {"skipped": "8 x 1024 tokens on several GPUs: set ES_B200_BENCH_C5_FULL=1"}
     except Exception as exc:  # reported, never hidden
         llama_train_full = {"error": repr(exc)[:300]}
 
@@ -742,12 +745,12 @@ def run_only(args):
     km = es.kernel_manager_t(0)
     stream = torch.cuda.current_stream(dev)
     mul16 = S.make_mul("f16")
-    if args.only == "llama_layer":
+    if args.only in ("llama_layer", "llama_layer_fused"):
         # the LLaMA-7B-shape layer memgraph (1 location), `steps` eager runs after `warmup`
         # (profiler launch lists: every node is one or two launches of the library's kernels)
         from einsummable_b200.memgraph import load_memgraph, memgraph_runner_t
         mg = load_memgraph(os.path.join(ROOT, "tests", "golden", "graphs", "llama7b_layer_locs1.json.gz"))
-        r = memgraph_runner_t(mg, devices=[0])
+        r = memgraph_runner_t(mg, devices=[0], fuse=args.only.endswith("fused"))
         rng = np.random.default_rng(7)
         for t in mg["inputs"]:
             shape, name = t["shape"], t["name"]
@@ -763,7 +766,7 @@ def run_only(args):
             r.run(stream)
         torch.cuda.synchronize()
         ms = time_launches(lambda: r.run(stream), stream, iters=args.steps, warm=0)
-        print(json.dumps({"only": "llama_layer", "ms": ms, "launches_per_run": len(r.program),
+        print(json.dumps({"only": args.only, "ms": ms, "launches_per_run": len(r.program), "nodes_folded": r.folded,
                           "nodes": dict(r.stats), "device_status": r.device_status()}))
         return
     if args.only == "move":
@@ -837,7 +840,7 @@ def main():
                     help="rows of the [rows, 11008] tensors (default: the full C2 workload); "
                          "smaller values are for profiler captures only")
     ap.add_argument("--only", default=None,
-                    choices=["llama_layer", "gemm_qkv", "gemm_ffn", "gemm_f32", "gemm_nn", "gemm_tn", "attn_scores", "attn_pv", "touch", "permute", "move"],
+                    choices=["llama_layer", "llama_layer_fused", "gemm_qkv", "gemm_ffn", "gemm_f32", "gemm_nn", "gemm_tn", "attn_scores", "attn_pv", "touch", "permute", "move"],
                     help="time one other kernel class alone (profiler captures); prints its own small JSON line")
     ap.add_argument("--kernels-only", action="store_true",
                     help="skip the end-to-end, other-class and CPU-baseline legs (profiler captures)")

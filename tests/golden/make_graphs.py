@@ -153,14 +153,18 @@ def main():
             arrays["%s/out/%s" % (name, k)] = v
         print(name, mg["taskgraph"], "loss", outs["loss"])
 
-    # config 5, LLaMA-7B shape (graph only): 4 layers forward + backward + update, f16, B=4, S=512
+    # config 5, LLaMA-7B shape (graph only): 4 layers forward + backward + update, f16, at B=4, S=512 and at
+    # the batch the config names, B=8, S=1024 (117 GB on one location; 8 locations: 58747 nodes, 35 minutes)
     force = "--force" in sys.argv[1:]
-    for n_layers, nlocs in ((1, 1), (4, 1), (4, 2), (4, 4), (4, 8)):
+    for n_layers, nlocs, batch, seq in ((1, 1, 4, 512), (4, 1, 4, 512), (4, 2, 4, 512), (4, 4, 4, 512),
+                                        (4, 8, 4, 512), (4, 1, 8, 1024), (4, 8, 8, 1024)):
         name = "llama7b_train_l%d_locs%d" % (n_layers, nlocs)
+        if (batch, seq) != (4, 512):
+            name = "llama7b_train_b%ds%d_l%d_locs%d" % (batch, seq, n_layers, nlocs)
         if os.path.exists(os.path.join(OUT, name + ".json.gz")) and not force:
             print(name, "kept")
             continue
-        h = ok(L.ref_graph_build_llama_train(u64(4096), u64(32), u64(256), u64(32000), n_layers, u64(4), u64(512),
+        h = ok(L.ref_graph_build_llama_train(u64(4096), u64(32), u64(256), u64(32000), n_layers, u64(batch), u64(seq),
                                              nlocs, 0, ctypes.c_double(1e-3), 0))
         mg = write_json(h, name, True)
         print(name, mg["taskgraph"], "nodes", len(mg["nodes"]))
