@@ -483,6 +483,9 @@ def run_gpu(args):
         "per_kernel": {name: {"ms": t, "GB/s": b / (t * 1e-3) / 1e9, "frac_of_" + peak_kind: b / (t * 1e-3) / 1e9 / peak}
                        for name, t, b in zip(["silu_mul", "rowmax", "exp_sub", "rowsum"], per_kernel_ms,
                                              [BYTES_SILU_MUL, BYTES_ROWMAX, BYTES_EXP_SUB, BYTES_ROWSUM])},
+        "per_kernel_note": "CUDA-event intervals between the kernels of one step: a reduction's interval also carries "
+                           "the write-back of the 180 MB the kernel before it wrote (L2 holds 126 MB), so its own "
+                           "rate reads low and the elementwise kernel's high; the step total is what is exact",
         "classes": classes,
         "llama7b_layer": llama,
         "llama7b_train_4layers": llama_train,
