@@ -752,11 +752,12 @@ def run_only(args):
     km = es.kernel_manager_t(0)
     stream = torch.cuda.current_stream(dev)
     mul16 = S.make_mul("f16")
-    if args.only in ("llama_layer", "llama_layer_fused"):
+    if args.only in ("llama_layer", "llama_layer_fused", "llama_train", "llama_train_fused"):
         # the LLaMA-7B-shape layer memgraph (1 location), `steps` eager runs after `warmup`
         # (profiler launch lists: every node is one or two launches of the library's kernels)
         from einsummable_b200.memgraph import load_memgraph, memgraph_runner_t
-        mg = load_memgraph(os.path.join(ROOT, "tests", "golden", "graphs", "llama7b_layer_locs1.json.gz"))
+        fixture = "llama7b_layer_locs1" if args.only.startswith("llama_layer") else "llama7b_train_l4_locs1"
+        mg = load_memgraph(os.path.join(ROOT, "tests", "golden", "graphs", fixture + ".json.gz"))
         r = memgraph_runner_t(mg, devices=[0], fuse=args.only.endswith("fused"))
         rng = np.random.default_rng(7)
         for t in mg["inputs"]:
@@ -766,6 +767,9 @@ def run_only(args):
                 v = (np.cos(ang) + 1j * np.sin(ang)).astype(np.complex64)
             elif name.endswith("norm.weight"):
                 v = np.ones(shape, dtype=np.float16)
+            elif name == "labels":
+                v = np.zeros(shape, dtype=np.float16)
+                v[np.arange(shape[0]), rng.integers(0, shape[1], shape[0])] = 1.0
             else:
                 v = (rng.standard_normal(shape).astype(np.float32) * 0.02).astype(np.float16)
             r.set_input(name, v)
@@ -847,7 +851,7 @@ def main():
                     help="rows of the [rows, 11008] tensors (default: the full C2 workload); "
                          "smaller values are for profiler captures only")
     ap.add_argument("--only", default=None,
-                    choices=["llama_layer", "llama_layer_fused", "gemm_qkv", "gemm_ffn", "gemm_f32", "gemm_nn", "gemm_tn", "attn_scores", "attn_pv", "touch", "permute", "move"],
+                    choices=["llama_layer", "llama_layer_fused", "llama_train", "llama_train_fused", "gemm_qkv", "gemm_ffn", "gemm_f32", "gemm_nn", "gemm_tn", "attn_scores", "attn_pv", "touch", "permute", "move"],
                     help="time one other kernel class alone (profiler captures); prints its own small JSON line")
     ap.add_argument("--kernels-only", action="store_true",
                     help="skip the end-to-end, other-class and CPU-baseline legs (profiler captures)")

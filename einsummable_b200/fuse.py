@@ -35,7 +35,8 @@ def _prod(v):
 
 
 def _is_elementwise(e):
-    return e["castable"] is None and e["out_rank"] == len(e["join_shape"])
+    # no aggregated mode: a castable on such a node has nothing to combine
+    return e["out_rank"] == len(e["join_shape"])
 
 
 def _is_plain_contraction(e):
