@@ -592,11 +592,16 @@ def llama_layer_leg(rank, world, dev, fixture="llama7b_layer", runs=10):
     r.close()
     del r
     torch.cuda.empty_cache()
-    if world == 1:
+    fused_multi = os.environ.get("ES_B200_BENCH_FUSED_MULTI", "1" if world <= 2 else "0") == "1"
+    if transport != "nccl" and (world == 1 or fused_multi):
         # the same memgraph with elementwise producers folded into their readers (fusion across
-        # node boundaries: a rewrite of the graph, not something the reference's engine does)
+        # node boundaries: a rewrite of the graph, not something the reference's engine does);
+        # on more than two GPUs only when ES_B200_BENCH_FUSED_MULTI=1
         try:
-            rf = memgraph_runner_t(mg, devices=[dev.index], fuse=True)
+            if world == 1:
+                rf = memgraph_runner_t(mg, devices=[dev.index], fuse=True)
+            else:
+                rf = memgraph_runner_t(mg, rank=rank, world=world, transport=transport, fuse=True)
             fill_inputs(rf)
             rf.capture()
             ms_fused = timed(rf.replay)

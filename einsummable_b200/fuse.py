@@ -49,17 +49,22 @@ def _overlap(a, b):
     return a[0] < b[0] + b[1] and b[0] < a[0] + a[1]
 
 
-def _written_region(node):
+def _written_region(node, loc):
+    """The (offset, size) a node writes in location `loc`'s memory, or None."""
     k = node["kind"]
     if k == "apply":
-        return tuple(node["mems"][0])
+        return tuple(node["mems"][0]) if node["loc"] == loc else None
     if k == "constant":
+        if node["loc"] != loc:
+            return None
         f = node["fill"]
         if f["type"] == "constant":
             return (node["offset"], int(f["nelem"]) * _DSIZE[f["value"]["dtype"]])
         return (node["offset"], int(f["nrow"]) * int(f["ncol"]) * _DSIZE[f["lower"]["dtype"]])
-    if k in ("move", "copy"):
-        return (node["dst_offset"], node["size"])
+    if k == "move":   # the destination rank pulls the bytes at the move's place in its own order
+        return (node["dst_offset"], node["size"]) if node["dst_loc"] == loc else None
+    if k == "copy":
+        return (node["dst_offset"], node["size"]) if node["loc"] == loc else None
     return None
 
 
@@ -91,30 +96,34 @@ def compose(a, b, slot):
 
 
 def fuse_elementwise_chains(mg):
-    """Returns (new memgraph, number of nodes folded away).  Memgraphs with several locations are
-    returned unchanged: their moves tie the list order to the other ranks'."""
-    if mg["num_locs"] != 1:
-        return mg, 0
+    """Returns (new memgraph, number of nodes folded away).  With several locations the same rules
+    apply inside each location (every rank must fold the same way, which it does: the pass only
+    reads the graph); a result that a move ships to another location is never folded."""
     mg = copy.deepcopy(mg)
     nodes = mg["nodes"]
-    saved = [(blk["offset"], blk["size"]) for t in mg["outputs"] for blk in t["blocks"]]
+    saved = [(blk["loc"], blk["offset"], blk["size"]) for t in mg["outputs"] for blk in t["blocks"]]
     alive = [True] * len(nodes)
     folded = 0
     for ia, a in enumerate(nodes):
         if a["kind"] != "apply" or "einsummable" not in a or not _is_elementwise(a["einsummable"]):
             continue
         out = tuple(a["mems"][0])
-        if any(_overlap(out, s) for s in saved):
+        loc = a["loc"]
+        if any(s[0] == loc and _overlap(out, s[1:]) for s in saved):
             continue
         # readers of the result: apply nodes after A that depend on it and read exactly its region
         readers = []
+        shipped = False
         for ib in range(ia + 1, len(nodes)):
             n = nodes[ib]
-            if not alive[ib] or n["kind"] != "apply" or a["id"] not in n["inns"]:
+            if not alive[ib] or a["id"] not in n["inns"]:
                 continue
-            if any(tuple(m) == out for m in n["mems"][1:]):
+            if n["kind"] in ("move", "copy"):
+                shipped = True      # another location (or a copy) reads the materialised tensor
+                break
+            if n["kind"] == "apply" and n["loc"] == loc and any(tuple(m) == out for m in n["mems"][1:]):
                 readers.append(ib)
-        if not readers:
+        if shipped or not readers:
             continue
         ea = a["einsummable"]
         a_reads = [tuple(m) for m in a["mems"][1:]]
@@ -145,7 +154,7 @@ def fuse_elementwise_chains(mg):
         for ic in range(ia + 1, readers[-1]):
             if not alive[ic]:
                 continue
-            w = _written_region(nodes[ic])
+            w = _written_region(nodes[ic], loc)
             if w is not None and any(_overlap(w, r) for r in a_reads):
                 hazard = True
                 break

@@ -42,6 +42,14 @@ def test_two_ranks_llama_tiny(transport):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("name", ["llama_tiny_locs2", "llama_train_tiny_locs2"])
+def test_two_ranks_fused(name):
+    """Elementwise nodes folded into their readers inside each location (every rank folds the same
+    way); the moves and their hand-shakes are those of the unfused graph."""
+    run_workers(2, name, "p2p", "fuse", "capture")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_two_ranks_c1(tmp_path):
     run_workers(2, "c1_n64_locs2", "p2p")
 
