@@ -165,3 +165,55 @@ def test_fusion_never_folds_a_tensor_that_a_move_ships():
             assert not (set(node["inns"]) & folded)
     # the moves themselves are untouched, so every rank still sees the same exchange steps
     assert [x for x in fused["nodes"] if x["kind"] == "move"] == [x for x in mg["nodes"] if x["kind"] == "move"]
+
+
+def _mini(nodes, outputs=()):
+    """A hand-made one-location memgraph: only what the fusion pass reads."""
+    return {"num_locs": 1, "mem_sizes": [1 << 20], "taskgraph": {}, "inputs": [],
+            "outputs": [{"blocks": [{"loc": 0, "offset": o, "size": s}]} for o, s in outputs], "nodes": nodes}
+
+
+def _ew(i, inns, out, reads, join="hole|f32@0", n=64, castable=None, rank2=False):
+    shape = [8, 8] if rank2 else [n]
+    idx = [0, 1] if rank2 else [0]
+    return {"id": i, "inns": inns, "kind": "apply", "loc": 0, "group": -1,
+            "mems": [list(out)] + [list(r) for r in reads],
+            "einsummable": {"join_shape": shape, "inns": [idx for _ in reads], "out_rank": len(shape),
+                            "join": join, "castable": castable}}
+
+
+def test_fusion_hazards_on_hand_made_graphs():
+    from einsummable_b200.fuse import fuse_elementwise_chains
+    X, A, B, C = (0, 256), (256, 256), (512, 256), (768, 256)
+    sq = "power{2}[hole|f32@0]"
+    exp = "exp[hole|f32@0]"
+    # plain chain: exp(x^2) in one node
+    mg = _mini([_ew(0, [], A, [X], sq), _ew(1, [0], B, [A], exp)], outputs=[B])
+    f, n = fuse_elementwise_chains(mg)
+    assert n == 1 and f["nodes"][1]["einsummable"]["join"] == "exp[power{2}[hole|f32@0]]"
+    assert f["nodes"][1]["mems"] == [list(B), list(X)] and f["nodes"][0].get("folded")
+    # the producer's result is itself saved: it has to be written
+    assert fuse_elementwise_chains(_mini([_ew(0, [], A, [X], sq), _ew(1, [0], B, [A], exp)], outputs=[A, B]))[1] == 0
+    # a node between the two overwrites what the producer read: the reader cannot read it later
+    clobber = _ew(1, [], X, [C], sq)
+    assert fuse_elementwise_chains(_mini([_ew(0, [], A, [X], sq), clobber, _ew(2, [0], B, [A], exp)], outputs=[B]))[1] == 0
+    # the reader's own output lies on the producer's input
+    assert fuse_elementwise_chains(_mini([_ew(0, [], A, [X], sq), _ew(1, [0], X, [A], exp)], outputs=[X]))[1] == 0
+    # the reader uses the result in two slots
+    two = _ew(1, [0], B, [A, A], "*[hole|f32@0,hole|f32@1]")
+    assert fuse_elementwise_chains(_mini([_ew(0, [], A, [X], sq), two], outputs=[B]))[1] == 0
+    # a plain contraction keeps its operands materialised (it runs on the tensor cores)
+    mm = {"id": 1, "inns": [0], "kind": "apply", "loc": 0, "group": -1, "mems": [list(B), list(A), list(C)],
+          "einsummable": {"join_shape": [8, 8, 8], "inns": [[0, 2], [2, 1]], "out_rank": 2,
+                          "join": "*[hole|f32@0,hole|f32@1]", "castable": "add"}}
+    assert fuse_elementwise_chains(_mini([_ew(0, [], A, [X], sq, rank2=True), mm], outputs=[B]))[1] == 0
+    # two readers: folded into both, evaluated twice
+    r1, r2 = _ew(1, [0], B, [A], exp), _ew(2, [0], C, [A], "log[hole|f32@0]")
+    f, n = fuse_elementwise_chains(_mini([_ew(0, [], A, [X], sq), r1, r2], outputs=[B, C]))
+    assert n == 1 and [x["mems"][1] for x in f["nodes"][1:]] == [list(X), list(X)]
+    # a reduction as the reader keeps its castable and output rank
+    red = {"id": 1, "inns": [0], "kind": "apply", "loc": 0, "group": -1, "mems": [[2048, 32], list(A)],
+           "einsummable": {"join_shape": [8, 8], "inns": [[0, 1]], "out_rank": 1, "join": "hole|f32@0", "castable": "add"}}
+    f, n = fuse_elementwise_chains(_mini([_ew(0, [], A, [X], sq, rank2=True), red], outputs=[(2048, 32)]))
+    assert n == 1 and f["nodes"][1]["einsummable"] == {"join_shape": [8, 8], "inns": [[0, 1]], "out_rank": 1,
+                                                       "join": sq, "castable": "add"}
