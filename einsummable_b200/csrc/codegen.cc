@@ -590,14 +590,17 @@ plan_t gen_red_row(ctx_t const& c, bool force_scalar)
     c.signature(s, "es_red_row_k0", 256);
     if (G == 32) {
         s.add("  const int lane = threadIdx.x & 31;");
-        s.add("  const %s row = (%s)blockIdx.x * %du + (threadIdx.x >> 5);", c.idx(), c.idx(),
+        // CTAs take the rows from the last to the first: a reduction usually reads what the kernel
+        // before it just wrote front to back, and the tail of that tensor is what the 126 MB L2 still
+        // holds; the CTAs that start first find it there instead of evicting it with the head
+        s.add("  const %s row = (%s)(gridDim.x - 1u - blockIdx.x) * %du + (threadIdx.x >> 5);", c.idx(), c.idx(),
               rows_per_cta);
         s.add("  if (row >= %s) return;", c.lit(NO).c_str());
         s.add("  const %s p_begin = 0, p_end = %s;", c.idx(), c.lit(AV).c_str());
     } else {
         s.add("  const int lane = threadIdx.x;");
         if (S == 1) {
-            s.add("  const %s row = blockIdx.x;", c.idx());
+            s.add("  const %s row = gridDim.x - 1u - blockIdx.x;  // last rows first, see above", c.idx());
             s.add("  const %s p_begin = 0, p_end = %s;", c.idx(), c.lit(AV).c_str());
         } else {
             s.add("  const %s row = blockIdx.x / %s;", c.idx(), c.lit(S).c_str());
