@@ -178,3 +178,32 @@ def test_contraction_schedule_choice(spec, extents, expect):
         assert "items256" not in info, info
     else:
         assert expect in info, info
+
+
+def test_multiply_high_division_is_exact_below_2_31():
+    """The tile decode of the contraction kernel and the index decode of the touch kernel divide by
+    fixed divisors with q = umulhi(n, m) >> s, l = ceil(log2 d), m = ceil(2^(31+l) / d), s = l - 1
+    (csrc/contraction.cu make_fd, csrc/kernels.cu make_fastdiv).  The claim: exact for every
+    numerator below 2^31.  Checked here on the arithmetic itself, at the edges and at random."""
+    import random
+
+    def make(d):
+        if d <= 1:
+            return None
+        l = (d - 1).bit_length()
+        m = ((1 << (31 + l)) + d - 1) // d
+        assert m < (1 << 32)
+        return m, l - 1
+
+    def div(n, d, f):
+        return n if f is None else ((n * f[0]) >> 32) >> f[1]
+
+    rng = random.Random(5)
+    divisors = [1, 2, 3, 5, 7, 43, 148, 250, 344, 1000, 11008, 32000, (1 << 16) - 1, (1 << 16) + 1, (1 << 30) - 1,
+                (1 << 30) + 1, (1 << 31) - 1] + [rng.randrange(1, 1 << 31) for _ in range(300)]
+    for d in divisors:
+        f = make(d)
+        edge = [0, 1, d - 1, d, d + 1, 2 * d - 1, 2 * d, (1 << 31) - 1, ((1 << 31) - 1) // d * d, ((1 << 31) - 1) // d * d - 1]
+        for n in edge + [rng.randrange(0, 1 << 31) for _ in range(200)]:
+            if 0 <= n < (1 << 31):
+                assert div(n, d, f) == n // d, (n, d)
