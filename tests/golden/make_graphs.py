@@ -5,8 +5,11 @@ the reference sources by oracle/Makefile; see oracle/ref_graphs.cc).
 
 For every case: the memgraph as JSON (what the reference's graph -> taskgraph ->
 memgraph pipeline emits for that graph and placement).  For the small cases also
-seeded inputs and the outputs of the reference's reference_compute_memgraph on
-them (graphs.npz).  Runs only where the reference tree exists.
+seeded inputs and the outputs of the reference's interpreter on them (graphs.npz):
+oracle/ref_graphs.cc walks the memgraph in order with the reference's own
+reference_einsummable / reference_touch / reference_fill, because
+reference_compute_memgraph itself rejects constant nodes.  Runs only where the
+reference tree exists.
 
 The full-size training graphs take the reference's autoplacer and memgraph
 compiler up to half an hour each (8 locations: 49003 memgraph nodes), so an
