@@ -24,6 +24,7 @@
 #include "src/autoplace/alocate.h"
 #include "llama/builder.h"
 #include "llama/modules.h"
+#include "src/misc/update.h"
 
 #include <fstream>
 
@@ -37,6 +38,7 @@ struct built_graph_t {
     map<int, mem_t>          inn_mem, save_mem;
     memgraph_t               memgraph;
     map<int, string>         names; // graph id -> name (weights etc.)
+    map<string, scalar_t>    vars;  // scalar variables of the updater, substituted where a node is used
 };
 
 vector<built_graph_t*> g_graphs;
@@ -216,7 +218,8 @@ int ref_graph_build_llama_train(uint64_t dim,
                                 int      nlocs,
                                 int      dtype_code,
                                 double   learning_rate,
-                                int      save_grads)
+                                int      save_grads,
+                                int      updater)
 {
     G_BEGIN
     dtype_t dtype = dtype_code == 0 ? dtype_t::f16 : dtype_t::f32;
@@ -264,6 +267,39 @@ int ref_graph_build_llama_train(uint64_t dim,
         vector<int> weight_ids = vector_from_each_method(ws, int, get_id);
         vector<int> grad_ids = vector_from_each_method(grads, int, get_id);
         b->graph = writer.get_graph();
+        if (updater == 1) {
+            // the reference trainer's AdamW (src/misc/update.cc:100-189) with f32 as its minimum
+            // precision, its state tensors m and v as extra inputs, and the scalar variables of
+            // iteration 1 (update_vars, :74-98) substituted wherever a node is written or interpreted
+            updater_desc_t          desc{dtype, updater_desc_t::adamw_t{.min_precision = dtype_t::f32}};
+            vector<tuple<int, int>> old_news;
+            auto inits = update_weights(desc, b->graph, old_news, weight_ids, grad_ids);
+            b->vars["beta1"] = scalar_t(dtype, "0.9");
+            b->vars["beta2"] = scalar_t(dtype, "0.999");
+            b->vars["eta"] = scalar_t(dtype, write_with_ss(learning_rate));
+            update_vars(desc, 1, b->vars);
+            map<int, string> wname;
+            for (size_t i = 0; i != weight_ids.size(); ++i) wname[weight_ids[i]] = wnames[i];
+            int n_state = 0;
+            for (auto const& [old_id, new_id] : old_news) {
+                b->graph.nodes[new_id].op.set_save(true);
+                if (wname.count(old_id)) {
+                    b->names[new_id] = "new." + wname.at(old_id);
+                } else {
+                    // m and v come in pairs per weight, in the order update_weights created them
+                    string which = (n_state % 2 == 0) ? "m." : "v.";
+                    b->names[old_id] = which + wnames[n_state / 2];
+                    b->names[new_id] = "new." + which + wnames[n_state / 2];
+                    ++n_state;
+                }
+            }
+            if (save_grads) {
+                for (size_t i = 0; i != weight_ids.size(); ++i) {
+                    b->graph.nodes[grad_ids[i]].op.set_save(true);
+                    b->names[grad_ids[i]] = "grad." + wnames[i];
+                }
+            }
+        } else {
         scalarop_t update = scalarop_t::combine(
             scalarop_t::make_sub(dtype),
             {scalarop_t::make_identity(dtype),
@@ -279,6 +315,7 @@ int ref_graph_build_llama_train(uint64_t dim,
                 b->graph.nodes[grad_ids[i]].op.set_save(true);
                 b->names[grad_ids[i]] = "grad." + wnames[i];
             }
+        }
         }
     }
     b->placements = autoplace01(b->graph, autoplace_config_t::make_default01(nlocs, 1));
@@ -381,7 +418,7 @@ int ref_graph_write_json(int h, char const* path)
             }
             out << "]";
             if (a.is_einsummable()) {
-                auto const& e = a.get_einsummable();
+                einsummable_t const e = a.get_einsummable().replace_scalar_variables(b.vars);
                 out << ",\"einsummable\":{\"join_shape\":" << jvec(e.join_shape) << ",\"inns\":[";
                 for (size_t i = 0; i != e.inns.size(); ++i) {
                     out << (i ? "," : "") << jvec(e.inns[i]);
@@ -454,7 +491,7 @@ int ref_graph_run(int h, void** loc_buffers)
                 return dbuffer_t(d, make_buffer_reference(at(apply.loc, apply.mems[i].offset), apply.mems[i].size));
             };
             if (apply.is_einsummable()) {
-                auto const&       e = apply.get_einsummable();
+                einsummable_t const e = apply.get_einsummable().replace_scalar_variables(b.vars);
                 vector<dbuffer_t> inns;
                 for (int i = 1; i != apply.mems.size(); ++i) {
                     inns.push_back(buf(i, e.inn_dtype(i - 1)));

@@ -142,13 +142,37 @@ def main():
     # the gradients themselves are saved so that the comparison is not swamped by the weights
     for nlocs in (1, 2):
         h = ok(L.ref_graph_build_llama_train(u64(64), u64(2), u64(32), u64(128), 1, u64(2), u64(16), nlocs, 1,
-                                             ctypes.c_double(0.01), 1))
+                                             ctypes.c_double(0.01), 1, 0))
         name = "llama_train_tiny_locs%d" % nlocs
         mg = write_json(h, name, True)
         ins = llama_inputs(mg, np.random.default_rng(3), 0.3)
         labels = np.zeros((2, 128), dtype=np.float32)
         labels[0, 5] = labels[1, 77] = 1.0
         ins["labels"] = labels
+        outs = run_reference(h, mg, ins)
+        for k, v in ins.items():
+            arrays["%s/in/%s" % (name, k)] = v
+        for k, v in outs.items():
+            arrays["%s/out/%s" % (name, k)] = v
+        print(name, mg["taskgraph"], "loss", outs["loss"])
+
+    # config 5, tiny, with the reference trainer's own AdamW updater (src/misc/update.cc:100-189; f32, its
+    # scalar variables of iteration 1 substituted): weights, first and second moments all updated
+    for nlocs in (1, 2):
+        h = ok(L.ref_graph_build_llama_train(u64(64), u64(2), u64(32), u64(128), 1, u64(2), u64(16), nlocs, 1,
+                                             ctypes.c_double(0.01), 1, 1))
+        name = "llama_train_adamw_tiny_locs%d" % nlocs
+        mg = write_json(h, name, True)
+        rng = np.random.default_rng(4)
+        ins = llama_inputs(mg, rng, 0.3)
+        labels = np.zeros((2, 128), dtype=np.float32)
+        labels[0, 9] = labels[1, 100] = 1.0
+        ins["labels"] = labels
+        for t in mg["inputs"]:                  # optimizer state: small positive second moments
+            if t["name"].startswith("m."):
+                ins[t["name"]] = (rng.standard_normal(t["shape"]) * 1e-3).astype(np.float32)
+            elif t["name"].startswith("v."):
+                ins[t["name"]] = (rng.uniform(1e-6, 1e-5, t["shape"])).astype(np.float32)
         outs = run_reference(h, mg, ins)
         for k, v in ins.items():
             arrays["%s/in/%s" % (name, k)] = v
@@ -168,7 +192,7 @@ def main():
             print(name, "kept")
             continue
         h = ok(L.ref_graph_build_llama_train(u64(4096), u64(32), u64(256), u64(32000), n_layers, u64(batch), u64(seq),
-                                             nlocs, 0, ctypes.c_double(1e-3), 0))
+                                             nlocs, 0, ctypes.c_double(1e-3), 0, 0))
         mg = write_json(h, name, True)
         print(name, mg["taskgraph"], "nodes", len(mg["nodes"]))
 

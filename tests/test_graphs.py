@@ -12,7 +12,8 @@ from conftest import GOLDEN_DIR
 GRAPHS = os.path.join(GOLDEN_DIR, "graphs")
 ARR = np.load(os.path.join(GRAPHS, "graphs.npz"))
 SMALL = ["c1_n64_locs1", "c1_n64_locs2", "llama_tiny_locs1", "llama_tiny_locs2", "llama_tiny_locs4",
-         "llama_train_tiny_locs1", "llama_train_tiny_locs2"]
+         "llama_train_tiny_locs1", "llama_train_tiny_locs2", "llama_train_adamw_tiny_locs1",
+         "llama_train_adamw_tiny_locs2"]
 
 
 def load(name):
@@ -48,6 +49,11 @@ def test_oracle_memgraph_interp_matches_reference(name):
         err = np.abs(g.astype(np.float64) - want.astype(np.float64)).max()
         # f16 trees with exp / pow differ from half.hpp in the last place here and there
         tol = 4e-3 if want.dtype == np.float16 else 1e-6
+        if name.startswith("llama_train"):
+            # numpy's exp / log / power differ from libm's in the last place of f32; the backward
+            # pass carries that into gradients that are small differences of larger terms (the
+            # attention gradients of these fixtures are 1e-9 .. 1e-12)
+            tol = 2e-5
         assert err <= tol * scale, (name, k, err, scale)
 
 
@@ -134,7 +140,8 @@ def test_compose_substitutes_and_renumbers():
 
 
 @pytest.mark.parametrize("name", ["llama_tiny_locs1", "llama_train_tiny_locs1", "c1_n64_locs1", "llama_tiny_locs2",
-                                  "llama_tiny_locs4", "llama_train_tiny_locs2"])
+                                  "llama_tiny_locs4", "llama_train_tiny_locs2", "llama_train_adamw_tiny_locs1",
+                                  "llama_train_adamw_tiny_locs2"])
 def test_fused_memgraph_still_matches_reference(name):
     """Folding elementwise producers into their readers must not change the results beyond the
     rounding of the intermediates that are no longer written (none in f32 beyond reassociation)."""
