@@ -219,7 +219,8 @@ int ref_graph_build_llama_train(uint64_t dim,
                                 int      dtype_code,
                                 double   learning_rate,
                                 int      save_grads,
-                                int      updater)
+                                int      updater,
+                                int      lora_rank)
 {
     G_BEGIN
     dtype_t dtype = dtype_code == 0 ? dtype_t::f16 : dtype_t::f32;
@@ -234,7 +235,9 @@ int ref_graph_build_llama_train(uint64_t dim,
     auto* b = new built_graph_t();
     {
         graph_writer_t writer;
-        transformer_t  model(&writer, args, 0);
+        // lora_rank > 0: the reference trainer's set-up (llama/gpu_train.cc:164,236-252): only the
+        // low-rank adapters are trained, the base weights are inputs that are saved as they are
+        transformer_t  model(&writer, args, 0, lora_rank > 0 ? optional<int>(lora_rank) : std::nullopt);
         tensor_t       embeddings = writer.input(full_shape_t(
             {full_dim_t::singleton(args.batch_size), full_dim_t::singleton(seqlen), args.full_dim()}));
         tensor_t predictions = model.forward(embeddings);
@@ -255,9 +258,12 @@ int ref_graph_build_llama_train(uint64_t dim,
         vector<tensor_t> ws;
         vector<string>   wnames;
         for (auto [name, tensor] : model.weight_map()) {
+            b->names[tensor.get_id()] = name;
+            if (lora_rank > 0 && name.find("lora") == string::npos) {
+                continue; // a frozen base weight
+            }
             ws.push_back(tensor);
             wnames.push_back(name);
-            b->names[tensor.get_id()] = name;
         }
         vector<tensor_t> grads = writer.backprop(loss, ws);
         b->names[embeddings.get_id()] = "embeddings";

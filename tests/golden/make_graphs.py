@@ -142,7 +142,7 @@ def main():
     # the gradients themselves are saved so that the comparison is not swamped by the weights
     for nlocs in (1, 2):
         h = ok(L.ref_graph_build_llama_train(u64(64), u64(2), u64(32), u64(128), 1, u64(2), u64(16), nlocs, 1,
-                                             ctypes.c_double(0.01), 1, 0))
+                                             ctypes.c_double(0.01), 1, 0, 0))
         name = "llama_train_tiny_locs%d" % nlocs
         mg = write_json(h, name, True)
         ins = llama_inputs(mg, np.random.default_rng(3), 0.3)
@@ -160,7 +160,7 @@ def main():
     # scalar variables of iteration 1 substituted): weights, first and second moments all updated
     for nlocs in (1, 2):
         h = ok(L.ref_graph_build_llama_train(u64(64), u64(2), u64(32), u64(128), 1, u64(2), u64(16), nlocs, 1,
-                                             ctypes.c_double(0.01), 1, 1))
+                                             ctypes.c_double(0.01), 1, 1, 0))
         name = "llama_train_adamw_tiny_locs%d" % nlocs
         mg = write_json(h, name, True)
         rng = np.random.default_rng(4)
@@ -180,6 +180,23 @@ def main():
             arrays["%s/out/%s" % (name, k)] = v
         print(name, mg["taskgraph"], "loss", outs["loss"])
 
+    # config 5, tiny, the reference trainer's set-up: rank-4 LoRA adapters trained, base weights frozen
+    for nlocs in (1, 2):
+        h = ok(L.ref_graph_build_llama_train(u64(64), u64(2), u64(32), u64(128), 1, u64(2), u64(16), nlocs, 1,
+                                             ctypes.c_double(0.01), 1, 0, 4))
+        name = "llama_train_lora_tiny_locs%d" % nlocs
+        mg = write_json(h, name, True)
+        ins = llama_inputs(mg, np.random.default_rng(6), 0.3)
+        labels = np.zeros((2, 128), dtype=np.float32)
+        labels[0, 3] = labels[1, 64] = 1.0
+        ins["labels"] = labels
+        outs = run_reference(h, mg, ins)
+        for k, v in ins.items():
+            arrays["%s/in/%s" % (name, k)] = v
+        for k, v in outs.items():
+            arrays["%s/out/%s" % (name, k)] = v
+        print(name, mg["taskgraph"], "loss", outs["loss"], [t["name"] for t in mg["outputs"]][:6])
+
     # config 5, LLaMA-7B shape (graph only): 4 layers forward + backward + update, f16, at B=4, S=512 and at
     # the batch the config names, B=8, S=1024 (117 GB on one location; 8 locations: 58747 nodes, 35 minutes)
     force = "--force" in sys.argv[1:]
@@ -192,7 +209,7 @@ def main():
             print(name, "kept")
             continue
         h = ok(L.ref_graph_build_llama_train(u64(4096), u64(32), u64(256), u64(32000), n_layers, u64(batch), u64(seq),
-                                             nlocs, 0, ctypes.c_double(1e-3), 0, 0))
+                                             nlocs, 0, ctypes.c_double(1e-3), 0, 0, 0))
         mg = write_json(h, name, True)
         print(name, mg["taskgraph"], "nodes", len(mg["nodes"]))
 

@@ -21,7 +21,7 @@ GRAPHS = os.path.join(GOLDEN_DIR, "graphs")
 ARR = np.load(os.path.join(GRAPHS, "graphs.npz"))
 SMALL = ["c1_n64_locs1", "c1_n64_locs2", "llama_tiny_locs1", "llama_tiny_locs2", "llama_tiny_locs4",
          "llama_train_tiny_locs1", "llama_train_tiny_locs2", "llama_train_adamw_tiny_locs1",
-         "llama_train_adamw_tiny_locs2"]
+         "llama_train_adamw_tiny_locs2", "llama_train_lora_tiny_locs1", "llama_train_lora_tiny_locs2"]
 
 
 def graph_path(name):
@@ -132,7 +132,8 @@ def test_llama7b_layer_runs_and_is_finite():
     r.close()
 
 
-@pytest.mark.parametrize("name", ["llama_tiny_locs1", "llama_train_tiny_locs1", "llama_train_adamw_tiny_locs1"])
+@pytest.mark.parametrize("name", ["llama_tiny_locs1", "llama_train_tiny_locs1", "llama_train_adamw_tiny_locs1",
+                                  "llama_train_lora_tiny_locs1"])
 def test_fused_memgraphs_match_reference(name):
     """Elementwise producers folded into their readers (einsummable_b200/fuse.py): every fused
     join goes through the same code generator; results against the reference interpreter's."""

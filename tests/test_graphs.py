@@ -13,7 +13,7 @@ GRAPHS = os.path.join(GOLDEN_DIR, "graphs")
 ARR = np.load(os.path.join(GRAPHS, "graphs.npz"))
 SMALL = ["c1_n64_locs1", "c1_n64_locs2", "llama_tiny_locs1", "llama_tiny_locs2", "llama_tiny_locs4",
          "llama_train_tiny_locs1", "llama_train_tiny_locs2", "llama_train_adamw_tiny_locs1",
-         "llama_train_adamw_tiny_locs2"]
+         "llama_train_adamw_tiny_locs2", "llama_train_lora_tiny_locs1", "llama_train_lora_tiny_locs2"]
 
 
 def load(name):
@@ -141,7 +141,8 @@ def test_compose_substitutes_and_renumbers():
 
 @pytest.mark.parametrize("name", ["llama_tiny_locs1", "llama_train_tiny_locs1", "c1_n64_locs1", "llama_tiny_locs2",
                                   "llama_tiny_locs4", "llama_train_tiny_locs2", "llama_train_adamw_tiny_locs1",
-                                  "llama_train_adamw_tiny_locs2"])
+                                  "llama_train_adamw_tiny_locs2", "llama_train_lora_tiny_locs1",
+                                  "llama_train_lora_tiny_locs2"])
 def test_fused_memgraph_still_matches_reference(name):
     """Folding elementwise producers into their readers must not change the results beyond the
     rounding of the intermediates that are no longer written (none in f32 beyond reassociation)."""
