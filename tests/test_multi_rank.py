@@ -67,3 +67,33 @@ def test_reference_arm_only_rank0_prints(tmp_path):
     import json
     line = json.loads(res.stdout.strip().splitlines()[-1])
     assert line["impl"] == "reference" and line["cpu_baseline"]["kind"] == "port" and line["value"] > 0
+
+
+def _run_cpu_workers(nproc, name, *extra):
+    worker = os.path.join(ROOT, "tests", "multi_worker_cpu.py")
+    port = str(free_port())
+    res = subprocess.run(
+        [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=%d" % nproc,
+         "--master-addr", "127.0.0.1", "--master-port", port, worker, name] + list(extra),
+        capture_output=True, text=True, timeout=300, env=dict(os.environ, OMP_NUM_THREADS="1"))
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
+    import json
+    out = json.loads([l for l in res.stdout.splitlines() if l.startswith("{")][-1])
+    assert out["ok"] and out["world"] == nproc
+    return out
+
+
+def test_partitioned_memgraph_over_two_gloo_ranks():
+    """One process per location, moves as grouped send / recv pairs cut by move_runs (the logic of
+    the GPU runner's NCCL transport), results against the reference interpreter's."""
+    _run_cpu_workers(2, "llama_tiny_locs2")
+
+
+def test_partitioned_memgraph_over_four_gloo_ranks():
+    """The four-location graph is the one whose groups, cut per rank instead of from the global
+    order, made the ranks wait on each other for ever."""
+    _run_cpu_workers(4, "llama_tiny_locs4")
+
+
+def test_folded_partitioned_training_graph_over_two_gloo_ranks():
+    _run_cpu_workers(2, "llama_train_tiny_locs2", "fuse")
