@@ -46,12 +46,18 @@ class es_touch_batch_t(ctypes.Structure):
                 ("pad", ctypes.c_int32), ("max_slots", ctypes.c_uint64), ("items_dev", ctypes.c_void_p)]
 
 
+class es_pull_item_t(ctypes.Structure):
+    _fields_ = [("src", ctypes.c_void_p), ("dst", ctypes.c_void_p), ("bytes", ctypes.c_uint64),
+                ("ready_flag", ctypes.c_void_p), ("done_flag", ctypes.c_void_p)]
+
+
 LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libes_b200.so")
 
 # every symbol include/es_b200.h declares: name -> (restype, argtypes)
 _vp, _u64, _i, _cp = ctypes.c_void_p, ctypes.c_uint64, ctypes.c_int, ctypes.c_char_p
 _desc_p = ctypes.POINTER(es_einsummable_desc_t)
 _td_p = ctypes.POINTER(es_touchdim_t)
+_ip = ctypes.POINTER(ctypes.c_int)
 SYMBOLS = {
     "es_b200_create": (_i, [_i, ctypes.POINTER(_vp)]),
     "es_b200_destroy": (_i, [_vp]),
@@ -77,6 +83,27 @@ SYMBOLS = {
     "es_b200_rowsum_f32_noalloc": (_i, [_vp, _vp, _vp, _u64, _u64, _vp]),
     "es_b200_device_status": (_i, [_vp, ctypes.POINTER(ctypes.c_uint)]),
     "es_b200_query_counters": (_i, [_vp, ctypes.POINTER(_u64)]),
+    "es_b200_query_work": (_i, [_vp, ctypes.POINTER(_u64), ctypes.POINTER(_u64)]),
+    "es_b200_program_create": (_i, [_vp, ctypes.POINTER(_vp)]),
+    "es_b200_program_destroy": (_i, [_vp]),
+    "es_b200_program_add_einsummable": (_i, [_vp, _u64, _vp, ctypes.POINTER(_vp), _i, _ip, _i, _ip]),
+    "es_b200_program_add_touch": (_i, [_vp, _td_p, _i, _i, _i, _vp, _vp, _ip, _i, _ip]),
+    "es_b200_program_add_touch_batch": (_i, [_vp, ctypes.POINTER(es_touch_item_t), _i, _i, _ip, _i, _ip]),
+    "es_b200_program_add_fill_constant": (_i, [_vp, _i, _vp, _u64, _vp, _ip, _i, _ip]),
+    "es_b200_program_add_fill_lowertri": (_i, [_vp, _i, _vp, _vp, _u64, _u64, ctypes.c_int64, _vp, _ip, _i, _ip]),
+    "es_b200_program_add_copy": (_i, [_vp, _vp, _vp, _u64, _ip, _i, _ip]),
+    "es_b200_program_add_signal": (_i, [_vp, ctypes.POINTER(_vp), _i, _ip, _i, _ip]),
+    "es_b200_program_add_pull": (_i, [_vp, ctypes.POINTER(es_pull_item_t), _i, _ip, _i, _ip]),
+    "es_b200_program_add_wait": (_i, [_vp, ctypes.POINTER(_vp), _i, _ip, _i, _ip]),
+    "es_b200_program_finalize": (_i, [_vp, _i, ctypes.POINTER(_u64)]),
+    "es_b200_program_set_workspace": (_i, [_vp, _vp, _u64]),
+    "es_b200_program_set_wait_limit": (_i, [_vp, ctypes.c_uint32]),
+    "es_b200_program_launch": (_i, [_vp, _vp]),
+    "es_b200_program_launch_timed": (_i, [_vp, _vp, ctypes.POINTER(ctypes.c_float), _i]),
+    "es_b200_program_instantiate": (_i, [_vp]),
+    "es_b200_program_replay": (_i, [_vp, _vp]),
+    "es_b200_program_reset_epoch": (_i, [_vp]),
+    "es_b200_program_describe": (_i, [_vp, _cp, _i, _ip]),
     "es_b200_last_error": (_cp, []),
     "es_b200_version": (_cp, []),
 }

@@ -16,6 +16,7 @@
 #include "jit.h"
 #include "handle.h"
 #include "kernels.h"
+#include "exchange.h"
 
 namespace es {
 
@@ -86,6 +87,97 @@ void copy_out(std::string const& s, char* buf, int buf_len)
 
 } // namespace
 
+namespace es {
+
+// A fallback plan may only run with the workspace the caller was told about.
+static void check_fallback_workspace(plan_t const& plan, void* workspace, uint64_t workspace_bytes)
+{
+    if (plan.workspace_bytes == 0) return;
+    if (!workspace || workspace_bytes < plan.workspace_bytes)
+        fail(ES_WORKSPACE_TOO_SMALL, "einsummable launch: the kernel for these (unaligned) pointers needs " +
+                                         std::to_string(plan.workspace_bytes) + " bytes of workspace");
+}
+
+void launch_built(es_b200*           h,
+                  uint64_t           kernel_id,
+                  cudaStream_t       stream,
+                  void*              out,
+                  void const* const* inns,
+                  int                n_inn,
+                  void*              workspace,
+                  uint64_t           workspace_bytes)
+{
+    built_kernel_t* k = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(h->build_mutex);
+        if (kernel_id >= h->kernels.size()) fail(ES_NOT_BUILT, "kernel id was never built");
+        k = h->kernels[kernel_id].get();
+    }
+    if (n_inn != (int)k->e.inns.size())
+        fail(ES_BAD_ARGUMENT, "einsummable launch: wrong number of inputs");
+    if (!out || !inns) fail(ES_BAD_ARGUMENT, "einsummable launch: null pointer");
+    for (int i = 0; i != n_inn; ++i)
+        if (!inns[i]) fail(ES_BAD_ARGUMENT, "einsummable launch: null input pointer");
+    if (k->workspace_bytes > 0) {
+        if (!workspace) fail(ES_WORKSPACE_TOO_SMALL, "einsummable launch: workspace required");
+        if (workspace_bytes < k->workspace_bytes)
+            fail(ES_WORKSPACE_TOO_SMALL,
+                 "einsummable launch: workspace of " + std::to_string(workspace_bytes) +
+                     " bytes, need " + std::to_string(k->workspace_bytes));
+        if (reinterpret_cast<uintptr_t>(workspace) & 15)
+            fail(ES_BAD_ARGUMENT, "einsummable launch: workspace must be 16-byte aligned");
+    }
+    set_device(h);
+    if (k->contraction && contraction_pointers_ok(inns[0], inns[1])) {
+        launch_contraction(*k->contraction, stream, out, inns[0], inns[1], workspace);
+        h->counters[0] += k->contraction->n_launches;
+        h->work_bytes[0] += k->algorithmic_bytes;
+        h->work_flops += k->algorithmic_flops;
+        return;
+    }
+    if (k->contraction) {
+        // operands not 16-byte aligned: TMA cannot address them; use the
+        // generated SIMT kernel, built on first need
+        std::lock_guard<std::mutex> lock(h->build_mutex);
+        if (k->functions.empty()) {
+            k->plan = plan_pointwise(k->e, false);
+            load_functions(k->plan, k->module, k->functions);
+        }
+    }
+    plan_t const*             plan = &k->plan;
+    std::vector<void*> const* fns = &k->functions;
+    if (plan->align > 1 && !pointers_aligned(out, inns, n_inn, plan->align)) {
+        std::lock_guard<std::mutex> lock(h->build_mutex);
+        if (!k->scalar_plan) {
+            auto sp = std::make_unique<plan_t>(plan_pointwise(k->e, true));
+            load_functions(*sp, k->scalar_module, k->scalar_functions);
+            k->scalar_plan = std::move(sp);
+        }
+        plan = k->scalar_plan.get();
+        fns = &k->scalar_functions;
+    }
+    if (plan != &k->plan || k->contraction) check_fallback_workspace(*plan, workspace, workspace_bytes);
+    void* args[ES_MAX_INNS + 2];
+    void* out_v = out;
+    void* in_v[ES_MAX_INNS];
+    void* ws_v = workspace;
+    args[0] = &out_v;
+    for (int i = 0; i != n_inn; ++i) {
+        in_v[i] = const_cast<void*>(inns[i]);
+        args[1 + i] = &in_v[i];
+    }
+    args[1 + n_inn] = &ws_v;
+    for (size_t i = 0; i != plan->launches.size(); ++i) {
+        launch_t const& l = plan->launches[i];
+        launch_function((*fns)[i], l.grid, l.block, l.smem, stream, args);
+    }
+    h->counters[0] += plan->launches.size();
+    h->work_bytes[0] += k->algorithmic_bytes;
+    h->work_flops += k->algorithmic_flops;
+}
+
+} // namespace es
+
 extern "C" {
 
 const char* es_b200_last_error(void)
@@ -117,6 +209,8 @@ int es_b200_create(int device, es_b200_t** out)
         auto* h = new es_b200;
         h->device = device;
         for (auto& c : h->counters) c = 0;
+        for (auto& c : h->work_bytes) c = 0;
+        h->work_flops = 0;
         *out = h;
     });
 }
@@ -171,6 +265,9 @@ int es_b200_build_einsummable(es_b200_t*                   h,
                     load_functions(pp, cp->pre_modules.back(), cp->pre_functions.back());
                 }
                 k->contraction = std::move(cp);
+                // unaligned operands run the generated SIMT kernel instead (built on first need);
+                // its workspace must be part of what build reports
+                k->workspace_bytes = std::max(k->workspace_bytes, plan_pointwise(e, false).workspace_bytes);
             }
         }
         if (!k->contraction) {
@@ -179,6 +276,10 @@ int es_b200_build_einsummable(es_b200_t*                   h,
             k->workspace_bytes = k->plan.workspace_bytes;
             load_functions(k->plan, k->module, k->functions);
         }
+        // the scalar twin (pointers below the vector alignment) may split differently
+        k->workspace_bytes = std::max(k->workspace_bytes, plan_pointwise(e, true).workspace_bytes);
+        k->algorithmic_bytes = e.algorithmic_bytes();
+        k->algorithmic_flops = e.is_contraction() ? e.algorithmic_flops() : 0;
         uint64_t id = h->kernels.size();
         h->kernels.push_back(std::move(k));
         h->by_key[key] = id;
@@ -209,71 +310,7 @@ int es_b200_launch_einsummable(es_b200_t*         h,
 {
     return guarded([&] {
         check_handle(h);
-        built_kernel_t* k = nullptr;
-        {
-            std::lock_guard<std::mutex> lock(h->build_mutex);
-            if (kernel_id >= h->kernels.size()) fail(ES_NOT_BUILT, "kernel id was never built");
-            k = h->kernels[kernel_id].get();
-        }
-        if (n_inn != (int)k->e.inns.size())
-            fail(ES_BAD_ARGUMENT, "einsummable launch: wrong number of inputs");
-        if (!out || !inns) fail(ES_BAD_ARGUMENT, "einsummable launch: null pointer");
-        for (int i = 0; i != n_inn; ++i)
-            if (!inns[i]) fail(ES_BAD_ARGUMENT, "einsummable launch: null input pointer");
-        if (k->workspace_bytes > 0) {
-            if (!workspace) fail(ES_WORKSPACE_TOO_SMALL, "einsummable launch: workspace required");
-            if (workspace_bytes < k->workspace_bytes)
-                fail(ES_WORKSPACE_TOO_SMALL,
-                     "einsummable launch: workspace of " + std::to_string(workspace_bytes) +
-                         " bytes, need " + std::to_string(k->workspace_bytes));
-            if (reinterpret_cast<uintptr_t>(workspace) & 15)
-                fail(ES_BAD_ARGUMENT, "einsummable launch: workspace must be 16-byte aligned");
-        }
-        set_device(h);
-        if (k->contraction && contraction_pointers_ok(inns[0], inns[1])) {
-            launch_contraction(*k->contraction, (cudaStream_t)stream, out, inns[0], inns[1],
-                               workspace);
-            h->counters[0] += k->contraction->n_launches;
-            return;
-        }
-        if (k->contraction && k->functions.empty()) {
-            // operands not 16-byte aligned: TMA cannot address them; use the
-            // generated SIMT kernel, built on first need
-            std::lock_guard<std::mutex> lock(h->build_mutex);
-            if (k->functions.empty()) {
-                k->plan = plan_pointwise(k->e, false);
-                load_functions(k->plan, k->module, k->functions);
-            }
-        }
-        plan_t const*             plan = &k->plan;
-        std::vector<void*> const* fns = &k->functions;
-        if (plan->align > 1 && !pointers_aligned(out, inns, n_inn, plan->align)) {
-            std::lock_guard<std::mutex> lock(h->build_mutex);
-            if (!k->scalar_plan) {
-                auto sp = std::make_unique<plan_t>(plan_pointwise(k->e, true));
-                if (sp->workspace_bytes > k->workspace_bytes)
-                    fail(ES_NOT_SUPPORTED, "unaligned launch needs more workspace than build reported");
-                load_functions(*sp, k->scalar_module, k->scalar_functions);
-                k->scalar_plan = std::move(sp);
-            }
-            plan = k->scalar_plan.get();
-            fns = &k->scalar_functions;
-        }
-        void* args[ES_MAX_INNS + 2];
-        void* out_v = out;
-        void* in_v[ES_MAX_INNS];
-        void* ws_v = workspace;
-        args[0] = &out_v;
-        for (int i = 0; i != n_inn; ++i) {
-            in_v[i] = const_cast<void*>(inns[i]);
-            args[1 + i] = &in_v[i];
-        }
-        args[1 + n_inn] = &ws_v;
-        for (size_t i = 0; i != plan->launches.size(); ++i) {
-            launch_t const& l = plan->launches[i];
-            launch_function((*fns)[i], l.grid, l.block, l.smem, stream, args);
-        }
-        h->counters[0] += plan->launches.size();
+        es::launch_built(h, kernel_id, (cudaStream_t)stream, out, inns, n_inn, workspace, workspace_bytes);
     });
 }
 
@@ -293,6 +330,9 @@ int es_b200_launch_touch(es_b200_t*           h,
         set_device(h);
         launch_touch(a, w, dtype, (cudaStream_t)stream);
         h->counters[1] += 1;
+        uint64_t n = dtype_size(dtype);
+        for (int i = 0; i != rank; ++i) n *= dims[i].size;
+        h->work_bytes[1] += n * (castable == ES_CASTABLE_NONE ? 2 : 3);
     });
 }
 
@@ -375,6 +415,7 @@ int es_b200_fill_constant(
         set_device(h);
         launch_fill_constant(dtype, value8, nelem, (cudaStream_t)stream, out);
         h->counters[2] += 1;
+        h->work_bytes[2] += nelem * dtype_size(dtype);
     });
 }
 
@@ -394,6 +435,7 @@ int es_b200_fill_lowertri(es_b200_t*  h,
         set_device(h);
         launch_fill_lowertri(dtype, lower8, upper8, nrow, ncol, start, (cudaStream_t)stream, out);
         h->counters[2] += 1;
+        h->work_bytes[2] += nrow * ncol * dtype_size(dtype);
     });
 }
 
@@ -444,6 +486,7 @@ int es_b200_move(es_b200_t*  h,
                                               (cudaStream_t)stream));
         }
         h->counters[3] += 1;
+        h->work_bytes[3] += bytes;
     });
 }
 
@@ -513,7 +556,8 @@ int es_b200_device_status(es_b200_t* h, unsigned int* error_word)
         ES_CUDA_CHECK(cudaDeviceSynchronize());
         unsigned int tc = read_and_clear_tc_error();
         unsigned int fl = read_and_clear_flag_error();
-        *error_word = tc | (fl << 8);
+        unsigned int ex = read_and_clear_exchange_error();
+        *error_word = tc | ((fl ? fl : ex) << 8);
     });
 }
 
@@ -558,6 +602,7 @@ int es_b200_pull(es_b200_t* h, const void* src, void* dst, uint64_t bytes, void*
         set_device(h);
         launch_pull_copy(src, dst, bytes, (cudaStream_t)stream);
         h->counters[3] += 1;
+        h->work_bytes[3] += bytes;
     });
 }
 
@@ -567,6 +612,16 @@ int es_b200_query_counters(es_b200_t* h, uint64_t launches[4])
         check_handle(h);
         if (!launches) fail(ES_BAD_ARGUMENT, "null pointer");
         for (int i = 0; i != 4; ++i) launches[i] = h->counters[i];
+    });
+}
+
+int es_b200_query_work(es_b200_t* h, uint64_t bytes[4], uint64_t* contraction_flops)
+{
+    return guarded([&] {
+        check_handle(h);
+        if (!bytes || !contraction_flops) fail(ES_BAD_ARGUMENT, "null pointer");
+        for (int i = 0; i != 4; ++i) bytes[i] = h->work_bytes[i];
+        *contraction_flops = h->work_flops;
     });
 }
 

@@ -130,6 +130,13 @@ bool einsum_t::is_contraction() const
            castable == ES_CASTABLE_ADD && join.is_mul();
 }
 
+uint64_t einsum_t::algorithmic_bytes() const
+{
+    uint64_t b = out_nelem() * dtype_size(out_dtype());
+    for (int k = 0; k != (int)inns.size(); ++k) b += inn_nelem(k) * dtype_size(inn_dtype(k));
+    return b;
+}
+
 bool einsum_t::is_straight_elementwise() const
 {
     if (has_aggregation()) return false;

@@ -43,6 +43,11 @@ struct einsum_t {
     uint64_t inn_nelem(int k) const;
     uint64_t join_nelem() const;
 
+    // Algorithmic work of one launch: every input read once at its own size plus the output
+    // written once; 2 * prod(join_shape) multiply-adds for a contraction.
+    uint64_t algorithmic_bytes() const;
+    uint64_t algorithmic_flops() const { return 2 * join_nelem(); }
+
     // Element stride of every join mode inside input k (0 where the input does
     // not have the mode) and inside the output (0 for aggregated modes).
     std::vector<uint64_t> inn_strides(int k) const;

@@ -7,14 +7,19 @@ RMSNorm = 8 nodes, llama/modules.cc:126-195) and its kernel manager even splits 
 cuTENSOR calls; here the code generator compiles any scalarop tree, so folding a producer into its
 consumer is a substitution in the join text plus a composition of the index maps.
 
-The pass works on the memgraph as loaded from JSON and returns a new memgraph for in-order execution
-(the runner launches nodes in list order).  A producer A is folded into its reader B when
+The pass works on the memgraph as loaded from JSON and returns a new memgraph that is valid both for
+in-order execution and for dependency-ordered execution: a reader that now reads A's inputs takes over
+A's dependencies, and every later node that writes into memory A read (the memgraph reuses freed memory,
+and the `del` that freed it only knew A as a reader) is made to depend on the readers.
+A producer A is folded into its reader B when
   * A is an elementwise einsummable (no aggregation), B an einsummable that is not a plain contraction
     (those run on the tensor cores with the join x0*x1),
   * every reader of A's result qualifies (then A is folded into each of them: evaluating a
     memory-bound expression once per reader moves fewer bytes than writing and re-reading it),
     reads it in one input slot, and the result is not a saved output,
-  * A and B iterate over the same number of points (nothing is recomputed),
+  * A and B iterate over the same number of points (nothing is recomputed), B reads A's result with
+    exactly the shape and dtype A wrote it in (the taskgraph lets a node view the same bytes under
+    another shape or dtype, src/einsummable/taskgraph.cc:765-793: such readers are left alone),
   * nothing between A and B in list order, and not B itself, writes memory A reads (the memgraph
     reuses memory: B now reads A's inputs later than the reference planned),
   * the folded node has at most 8 inputs.
@@ -66,6 +71,19 @@ def _written_region(node, loc):
     if k == "copy":
         return (node["dst_offset"], node["size"]) if node["loc"] == loc else None
     return None
+
+
+def _hole_dtype(join, slot):
+    for m in _HOLE.finditer(join):
+        if int(m.group(2)) == slot:
+            return m.group(1)
+    return None
+
+
+def _out_dtype(join):
+    """Dtype of the join's root node, by the reference's typing rules."""
+    from .scalarop import scalarop_t
+    return scalarop_t(join).out_dtype()
 
 
 def compose(a, b, slot):
@@ -143,6 +161,11 @@ def fuse_elementwise_chains(mg):
             eb = b["einsummable"]
             if len(slots) != 1 or _prod(ea["join_shape"]) != _prod(eb["join_shape"]):
                 break
+            via = eb["inns"][slots[0]]
+            if [int(ea["join_shape"][m]) for m in range(ea["out_rank"])] != [int(eb["join_shape"][v]) for v in via]:
+                break       # the reader views the bytes under another shape
+            if _out_dtype(ea["join"]) != _hole_dtype(eb["join"], slots[0]):
+                break       # ... or another dtype
             if len(eb["inns"]) - 1 + len(ea["inns"]) > MAX_INNS:
                 break
             if any(_overlap(tuple(b["mems"][0]), r) for r in a_reads):
@@ -165,6 +188,14 @@ def fuse_elementwise_chains(mg):
             b["einsummable"] = compose(ea, b["einsummable"], slot)
             b["mems"] = [b["mems"][0]] + b["mems"][1:1 + slot] + a["mems"][1:] + b["mems"][2 + slot:]
             b["inns"] = sorted(set(i for i in b["inns"] if i != a["id"]) | set(a["inns"]))
+        # later writers into memory A read must now also wait for the readers
+        reader_ids = [nodes[ib]["id"] for ib, _ in plans]
+        for ic in range(readers[-1] + 1, len(nodes)):
+            if not alive[ic]:
+                continue
+            w = _written_region(nodes[ic], loc)
+            if w is not None and any(_overlap(w, r) for r in a_reads):
+                nodes[ic]["inns"] = sorted(set(nodes[ic]["inns"]) | set(reader_ids))
         alive[ia] = False
         folded += 1
     # a folded node stays in the list as a bookkeeping stub so that ids keep indexing the list

@@ -15,7 +15,14 @@ Two placements of the locations:
   * single process: every location is a buffer on a device this process can see
     (several locations may share one GPU);
   * one process per GPU (torchrun): rank r owns location r; a move between
-    locations is an NCCL send/recv pair issued in node order on both sides.
+    locations is an exchange over peer-mapped memory (or an NCCL send/recv pair).
+
+Two schedules:
+  * "dag" (default): the nodes become a program of the library's executor
+    (program.py): every op waits for exactly the ops it depends on -- the
+    memgraph's own edges, looked through its bookkeeping nodes -- on several
+    lanes, and the whole run replays as one CUDA graph;
+  * "list": one stream, the memgraph's node order (what the NCCL transport uses).
 """
 import gzip
 import json
@@ -25,6 +32,7 @@ import torch
 
 from .einsummable import einsummable_t, fill_t, touch_t
 from .kernel_manager import kernel_manager_t
+from .program import program_t
 from .scalarop import DTYPE_SIZE
 
 NP_DTYPE = {"f16": np.float16, "f32": np.float32, "f64": np.float64, "c64": np.complex64}
@@ -79,13 +87,155 @@ def move_runs(mg):
             runs[node["id"]] = run_id
     return runs
 
+BOOKKEEPING = ("alloc", "del", "inputmem", "partialize")
+
+
+def _sides(node):
+    if node["kind"] == "move":
+        return (node["src_loc"], node["dst_loc"])
+    return (node["loc"],)
+
+
+def schedule_units(mg, owned, exchange):
+    """The launchable units of the locations in `owned`, in the memgraph's node order, each with
+    the units it depends on.
+
+    owned: the locations this process drives.  exchange: True when a move between two locations
+    is an exchange between two processes (one process per GPU) -- the source rank gets a
+    `signal` unit, the destination rank a `pull` unit, and whatever later reuses the source's
+    memory a `wait` unit for the destination's acknowledgement; False when this process drives
+    both sides and the move is a plain copy.
+
+    Dependencies are the memgraph's edges looked through its bookkeeping nodes (alloc, del,
+    inputmem, partialize: src/einsummable/memgraph.h:189-309 -- they launch nothing but carry
+    the "this memory is free again" ordering).  The incoming moves of one run (move_runs) form
+    one pull unit and are served by one launch; the outgoing moves of a run that wait for the
+    same producers share a signal unit.  Touches of one group are chained in node order, the
+    first being the copy (src/engine/gpu/exec_graph.cc:167-172,368-378).
+
+    Units are dicts: kind in {einsummable, touch, constant, copy, signal, pull, wait}, `deps`
+    (indices of earlier units), `node` or `moves` (memgraph node ids)."""
+    nodes = mg["nodes"]
+    owned = set(owned)
+    runs = move_runs(mg)
+    run_members = {}
+    for nid in sorted(runs):
+        run_members.setdefault(runs[nid], []).append(nid)
+
+    def is_cross(n):
+        return exchange and n["kind"] == "move" and n["src_loc"] != n["dst_loc"]
+
+    # real nodes a bookkeeping node stands for (nodes are in topological order)
+    closure = {}
+    for n in nodes:
+        if n["kind"] in BOOKKEEPING:
+            acc = set()
+            for i in n["inns"]:
+                acc |= closure[i] if nodes[i]["kind"] in BOOKKEEPING else {i}
+            closure[n["id"]] = frozenset(acc)
+
+    units, unit_of, waited, group_last = [], {}, {}, {}
+
+    def raw_deps(n, side=None):
+        acc = set()
+        for i in n["inns"]:
+            dep = nodes[i]
+            if side is not None and side not in _sides(dep):
+                continue
+            acc |= closure[i] if dep["kind"] in BOOKKEEPING else {i}
+        return acc
+
+    def resolve(raw):
+        """Unit indices for a set of real node ids; may emit one wait unit in front."""
+        deps, tokens = set(), []
+        for r in sorted(raw):
+            dep = nodes[r]
+            if is_cross(dep):
+                if dep["dst_loc"] in owned:
+                    deps.add(unit_of[r])
+                elif dep["src_loc"] in owned:
+                    if r in waited:
+                        deps.add(waited[r])
+                    else:
+                        tokens.append(r)
+            elif r in unit_of:
+                deps.add(unit_of[r])
+        if tokens:
+            units.append({"kind": "wait", "moves": tokens, "deps": []})
+            for t in tokens:
+                waited[t] = len(units) - 1
+            deps.add(len(units) - 1)
+        return sorted(deps)
+
+    def emit(unit):
+        units.append(unit)
+        return len(units) - 1
+
+    for n in nodes:
+        kind, nid = n["kind"], n["id"]
+        if kind in BOOKKEEPING:
+            continue
+        if kind == "move" and is_cross(n):
+            run = run_members[runs[nid]]
+            if n["dst_loc"] in owned and nid not in unit_of:
+                members = [m for m in run if nodes[m]["dst_loc"] in owned and nodes[m]["dst_loc"] == n["dst_loc"]
+                           and is_cross(nodes[m])]
+                raw = set()
+                for m in members:
+                    raw |= raw_deps(nodes[m], nodes[m]["dst_loc"])
+                idx = emit({"kind": "pull", "moves": members, "deps": resolve(raw), "loc": n["dst_loc"]})
+                for m in members:
+                    unit_of[m] = idx
+            if n["src_loc"] in owned and ("signal", nid) not in unit_of:
+                members = [m for m in run if nodes[m]["src_loc"] == n["src_loc"] and is_cross(nodes[m])]
+                by_deps = {}
+                for m in members:
+                    by_deps.setdefault(tuple(resolve(raw_deps(nodes[m], n["src_loc"]))), []).append(m)
+                for deps, ms in by_deps.items():
+                    idx = emit({"kind": "signal", "moves": ms, "deps": list(deps), "loc": n["src_loc"]})
+                    for m in ms:
+                        unit_of[("signal", m)] = idx
+            continue
+        loc = n["dst_loc"] if kind == "move" else n["loc"]
+        if loc not in owned or (kind == "move" and n["src_loc"] not in owned):
+            continue
+        deps = resolve(raw_deps(n))
+        if kind == "apply" and "touch" in n:
+            first = True
+            if n["group"] >= 0:
+                key = (loc, n["group"])
+                first = key not in group_last
+                if not first:
+                    deps = sorted(set(deps) | {group_last[key]})
+            idx = emit({"kind": "touch", "node": nid, "deps": deps, "first": first, "loc": loc})
+            if n["group"] >= 0:
+                group_last[(loc, n["group"])] = idx
+        elif kind == "apply":
+            idx = emit({"kind": "einsummable", "node": nid, "deps": deps, "loc": loc})
+        elif kind == "constant":
+            idx = emit({"kind": "constant", "node": nid, "deps": deps, "loc": loc})
+        elif kind in ("move", "copy"):
+            idx = emit({"kind": "copy", "node": nid, "deps": deps, "loc": loc})
+        else:
+            raise ValueError("unknown memgraph node kind %r" % kind)
+        unit_of[nid] = idx
+    # sources nobody on this rank reused: the next run may overwrite them, so the run ends by
+    # collecting their acknowledgements
+    rest = [n["id"] for n in nodes if is_cross(n) and n["src_loc"] in owned and n["id"] not in waited]
+    if rest:
+        units.append({"kind": "wait", "moves": rest, "deps": []})
+    return units
+
 
 class memgraph_runner_t:
-    def __init__(self, mg, devices=None, rank=None, world=None, transport="nccl", wait_limit_ms=0, fuse=False):
+    def __init__(self, mg, devices=None, rank=None, world=None, transport="nccl", wait_limit_ms=0, fuse=False,
+                 schedule="dag", max_lanes=0):
         """transport (one process per GPU only): "nccl" = send/recv pairs; "p2p" = every
         location buffer lives in symmetric memory, the destination rank pulls the bytes over
         NVLink with an SM copy kernel, and the two ranks hand-shake through bounded flag
-        kernels (data ready / copy finished)."""
+        kernels (data ready / copy finished).
+        schedule: "dag" = the library's program executor (dependency-ordered lanes, see the
+        module text); "list" = one stream in node order.  The NCCL transport always runs as a list."""
         self.folded = 0
         if fuse:
             # elementwise producers folded into their readers (one location only, see fuse.py)
@@ -95,6 +245,11 @@ class memgraph_runner_t:
         self.num_locs = mg["num_locs"]
         self.distributed = rank is not None
         self.transport = transport if self.distributed else "local"
+        self.schedule = "list" if self.transport == "nccl" else schedule
+        if self.schedule not in ("dag", "list"):
+            raise ValueError("schedule must be 'dag' or 'list'")
+        self.max_lanes = max_lanes
+        self.prog = None
         self.wait_limit_ms = wait_limit_ms
         if self.distributed:
             if world != self.num_locs:
@@ -105,6 +260,9 @@ class memgraph_runner_t:
         else:
             devices = devices or [0] * self.num_locs
             self.devices = {loc: devices[loc] for loc in range(self.num_locs)}
+            if len(set(self.devices.values())) > 1:
+                # one process driving several GPUs: the moves synchronise the devices on the host
+                self.schedule = "list"
         self.kms = {}
         for loc, dev in self.devices.items():
             if dev not in self.kms:
@@ -116,9 +274,17 @@ class memgraph_runner_t:
             for loc, dev in self.devices.items():
                 size = int(mg["mem_sizes"][loc]) + 256
                 self.buffers[loc] = torch.zeros(size, dtype=torch.uint8, device="cuda:%d" % dev)
-        self._prepare()
+        if self.schedule == "dag":
+            self._build_program()
+        else:
+            self._prepare()
 
     def _alloc_symmetric(self):
+        import os
+        # plain peer mappings only: the exchange uses peer loads and flags, never the NVLink
+        # multicast object symmetric memory would otherwise bind the buffer to (a rank that
+        # exits while bound to one disturbs its peers)
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed as dist
         import torch.distributed._symmetric_memory as symm_mem
         self.cross_moves = [n["id"] for n in self.mg["nodes"] if n["kind"] == "move" and n["src_loc"] != n["dst_loc"]]
@@ -149,7 +315,105 @@ class memgraph_runner_t:
     def ptr(self, loc, offset):
         return self.buffers[loc].data_ptr() + int(offset)
 
-    # ------------------------------------------------------------------ build
+
+    # ------------------------------------------------------------------ build (dag)
+    def _build_program(self):
+        """Translates schedule_units into ops of the library's program executor."""
+        nodes = self.mg["nodes"]
+        self.units = schedule_units(self.mg, set(self.devices), self.transport == "p2p")
+        dev = next(iter(self.devices.values()))
+        km = self.kms[dev]
+        prog = program_t(km)
+        self.stats = {"einsummable": 0, "touch": 0, "move": 0, "fill": 0, "move_bytes": 0}
+        self.unit_labels = []
+        for u in self.units:
+            kind, deps = u["kind"], u["deps"]
+            if kind == "einsummable":
+                node = nodes[u["node"]]
+                d = node["einsummable"]
+                e = einsummable_t(d["join_shape"], d["inns"], d["out_rank"], d["join"], d["castable"])
+                if km.build(e) is None:
+                    raise RuntimeError("build returned nullopt for %r" % (e,))
+                loc = node["loc"]
+                offs = [m[0] for m in node["mems"]]
+                prog.add_einsummable(km._built(e)[0], self.ptr(loc, offs[0]), [self.ptr(loc, o) for o in offs[1:]], deps)
+                self.stats["einsummable"] += 1
+                kk = km.kernel_info(e).split("|")[0]
+                self.unit_labels.append(("contraction" if kk.startswith("contraction") else
+                                         ("reduction" if e.has_aggregation() else "elementwise"), repr(e)))
+            elif kind == "touch":
+                node = nodes[u["node"]]
+                d = node["touch"]
+                t = touch_t(d["selection"], d["castable"], d["dtype"])
+                loc = node["loc"]
+                offs = [m[0] for m in node["mems"]]
+                prog.add_touch(t, None if u["first"] else d["castable"], self.ptr(loc, offs[0]), self.ptr(loc, offs[1]), deps)
+                self.stats["touch"] += 1
+                self.unit_labels.append(("touch", "%s %s" % (d["castable"], d["dtype"])))
+            elif kind == "constant":
+                node = nodes[u["node"]]
+                f = node["fill"]
+                out = self.ptr(node["loc"], node["offset"])
+                if f["type"] == "constant":
+                    dt = f["value"]["dtype"]
+                    prog.add_fill_constant(fill_t.constant_t(_scalar_from_raw(f["value"]["raw"], dt), [f["nelem"]], dt),
+                                           out, deps)
+                else:
+                    dt = f["lower"]["dtype"]
+                    prog.add_fill_lowertri(fill_t.lowertri_t(_scalar_from_raw(f["lower"]["raw"], dt),
+                                                             _scalar_from_raw(f["upper"]["raw"], dt),
+                                                             f["nrow"], f["ncol"], f["start"], dt), out, deps)
+                self.stats["fill"] += 1
+                self.unit_labels.append(("fill", f["type"]))
+            elif kind == "copy":
+                node = nodes[u["node"]]
+                if node["kind"] == "move":
+                    s_loc, d_loc = node["src_loc"], node["dst_loc"]
+                else:
+                    s_loc = d_loc = node["loc"]
+                prog.add_copy(self.ptr(s_loc, node["src_offset"]), self.ptr(d_loc, node["dst_offset"]), node["size"], deps)
+                self.stats["move"] += 1
+                self.stats["move_bytes"] += node["size"]
+                self.unit_labels.append(("copy", str(node["size"])))
+            elif kind == "signal":
+                prog.add_signal([self._flag_ptr(nodes[m]["dst_loc"], 0, self.move_index[m]) for m in u["moves"]], deps)
+                self.stats["move"] += len(u["moves"])
+                self.stats["move_bytes"] += sum(nodes[m]["size"] for m in u["moves"])
+                self.unit_labels.append(("signal", str(len(u["moves"]))))
+            elif kind == "pull":
+                items = []
+                for m in u["moves"]:
+                    node = nodes[m]
+                    k = self.move_index[m]
+                    items.append((self.peer_base[node["src_loc"]] + node["src_offset"],
+                                  self.ptr(node["dst_loc"], node["dst_offset"]), node["size"],
+                                  self._flag_ptr(node["dst_loc"], 0, k), self._flag_ptr(node["src_loc"], 1, k)))
+                prog.add_pull(items, deps)
+                self.stats["move"] += len(items)
+                self.stats["move_bytes"] += sum(it[2] for it in items)
+                self.unit_labels.append(("pull", "%d moves %d bytes" % (len(items), sum(it[2] for it in items))))
+            elif kind == "wait":
+                prog.add_wait([self._flag_ptr(nodes[m]["src_loc"], 1, self.move_index[m]) for m in u["moves"]], deps)
+                self.unit_labels.append(("wait", str(len(u["moves"]))))
+            else:
+                raise ValueError(kind)
+        need = prog.finalize(self.max_lanes)
+        self.workspace = {dev: (torch.empty(max(need, 256), dtype=torch.uint8, device="cuda:%d" % dev), need)}
+        prog.set_workspace(self.workspace[dev][0], max(need, 256))
+        if self.wait_limit_ms:
+            prog.set_wait_limit(self.wait_limit_ms)
+        self.prog = prog
+        self.program = self.units
+
+    def profile(self, stream=None):
+        """One run with a CUDA event pair around every op: [(class, label, milliseconds)].  For pull
+        and wait ops the time includes waiting for the peer."""
+        if self.prog is None:
+            raise RuntimeError("profile needs the dag schedule")
+        ms = self.prog.launch_timed(stream if stream is not None else torch.cuda.current_stream())
+        return [(lab[0], lab[1], t) for lab, t in zip(self.unit_labels, ms)]
+
+    # ------------------------------------------------------------------ build (list)
     def _prepare(self):
         self.program = []
         ws_need = {loc: 0 for loc in self.devices}
@@ -296,6 +560,9 @@ class memgraph_runner_t:
         current stream of the first device)."""
         if stream is None:
             stream = torch.cuda.current_stream(next(iter(self.devices.values())))
+        if self.prog is not None:
+            self.prog.launch(stream)
+            return
         groups_touched = set()
         for op in self.program:
             kind = op[0]
@@ -371,18 +638,48 @@ class memgraph_runner_t:
         self.run()
         for dev in set(self.devices.values()):
             torch.cuda.synchronize(dev)
+        if self.prog is not None:
+            self.prog.instantiate()
+            self.graph = self.prog
+            return self.prog
+        if len(set(self.devices.values())) > 1:
+            raise RuntimeError("capture: one process driving several GPUs runs as a list and is not captured")
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
             self.run(torch.cuda.current_stream())
         self.graph = g
         return g
 
-    def replay(self):
-        self.graph.replay()
+    def replay(self, stream=None):
+        if self.prog is not None:
+            self.prog.replay(stream if stream is not None else torch.cuda.current_stream())
+        else:
+            self.graph.replay()
+
+    def kernel_kinds(self):
+        """How many einsummable ops run as which kernel kind (contraction_tc_f16, ew_vec, red_row, ...)."""
+        kinds = {}
+        if self.prog is not None:
+            for u in self.units:
+                if u["kind"] == "einsummable":
+                    node = self.mg["nodes"][u["node"]]
+                    d = node["einsummable"]
+                    e = einsummable_t(d["join_shape"], d["inns"], d["out_rank"], d["join"], d["castable"])
+                    k = self.km(node["loc"]).kernel_info(e).split("|")[0]
+                    kinds[k] = kinds.get(k, 0) + 1
+        else:
+            for op in self.program:
+                if op[0] == "einsummable":
+                    k = self.km(op[1]).kernel_info(op[2]).split("|")[0]
+                    kinds[k] = kinds.get(k, 0) + 1
+        return kinds
 
     def device_status(self):
         return max(km.device_status() for km in self.kms.values())
 
     def close(self):
+        if self.prog is not None:
+            self.prog.close()
+            self.prog = None
         for km in self.kms.values():
             km.close()

@@ -264,9 +264,115 @@ int es_b200_device_status(es_b200_t* h, unsigned int* error_word);
  * src/engine/cpu/kernel_executor.cc:459-591 are host-side and commented out). */
 int es_b200_debug_trace(es_b200_t* h, unsigned long long* out, int n, int* n_out);
 
-/* Launch / byte counters since creation: launches[class], class order =
- * einsummable, touch, fill, move. */
+/* Launch counters since creation: launches[class], class order =
+ * einsummable, touch, fill, move.  The reference has no counterpart (its counters are the
+ * commented-out timetracker hooks of src/engine/cpu/kernel_executor.cc:459-591). */
 int es_b200_query_counters(es_b200_t* h, uint64_t launches[4]);
+
+/* Algorithmic work launched since creation, per class in the same order: bytes every launch
+ * must move (inputs once + output once; touch copy 2x, accumulate 3x the region; fills and
+ * moves their size) and the multiply-add flops of the contractions (2 * prod(join_shape), the
+ * reference counts prod(join_shape): src/einsummable/taskgraph.cc:2262-2271). */
+int es_b200_query_work(es_b200_t* h, uint64_t bytes[4], uint64_t* contraction_flops);
+
+/* ---------------------------------------------------------------------------------------------
+ * Program: the nodes of one memgraph that run on this GPU, as a static schedule.
+ *
+ * Stands in for make_gpu_exec_graph + exec_state_t::event_loop
+ * (src/engine/gpu/exec_graph.cc:37-256, src/engine/exec_state.cc:110-219): there every node is
+ * launched from the host when the stream callbacks of its dependencies have fired
+ * (cudaStreamAddCallback, src/engine/gpu/exec_graph.cc:318-332; at most 5 streams per device,
+ * src/server/gpu/server.h:81).  Here every op names the earlier ops it depends on, finalize
+ * assigns the ops to lanes (CUDA streams) joined by events, and a launch issues the whole
+ * schedule without returning to the host; instantiate captures it into one CUDA graph.
+ *
+ * Ops are added in an order in which every dependency comes first (the memgraph's node order
+ * is one, src/einsummable/memgraph.h:167-173); `deps` holds indices of earlier ops, *op_index
+ * receives the new op's index.  Pointers are device pointers owned by the caller and must stay
+ * valid while the program exists.  A program is used from one host thread, one launch at a time.
+ *
+ * Exchange between processes that each drive one GPU (no counterpart in the reference, whose
+ * one process copies between its GPUs directly, src/engine/gpu/exec_graph.cc:406-467): flags
+ * are zero-initialised 32-bit words both GPUs can address.  Every run of a program increments
+ * the program's own run counter; `signal` stores it into flags in the peers' memory, `pull`
+ * waits for its local ready flag to reach it, copies over NVLink and then stores it into the
+ * done flag in the source rank's memory, `wait` waits for local (done) flags to reach it.
+ * All ranks must therefore run their programs the same number of times.  Ops that wait for a
+ * peer (pull, wait) are issued on one lane in program order: add them in the same global order
+ * on every rank.  Waits are bounded (es_b200_program_set_wait_limit, default 2000 ms): on
+ * expiry the kernel records a code in bits 8..15 of es_b200_device_status (3 = pull, 4 = wait)
+ * and the schedule carries on; nothing traps. */
+typedef struct es_b200_program es_b200_program_t;
+
+typedef struct {
+    const void* src;        /* peer-mapped source, 16-byte aligned */
+    void*       dst;        /* local destination, 16-byte aligned */
+    uint64_t    bytes;
+    void*       ready_flag; /* local flag: raised by the source rank's signal */
+    void*       done_flag;  /* flag in the source rank's memory: raised after the copy */
+} es_pull_item_t;
+
+/* h may be NULL: the program can then be filled, finalized and described (host only, for
+ * inspecting the schedule) but not launched. */
+int es_b200_program_create(es_b200_t* h, es_b200_program_t** out);
+int es_b200_program_destroy(es_b200_program_t* p);
+
+/* gpu_einsummable_t::launch (src/engine/gpu/exec_graph.cc:277-335); kernel_id from
+ * es_b200_build_einsummable; the workspace comes from es_b200_program_set_workspace. */
+int es_b200_program_add_einsummable(es_b200_program_t* p, uint64_t kernel_id, void* out,
+                                    const void* const* inns, int n_inn,
+                                    const int* deps, int n_deps, int* op_index);
+/* gpu_touch_t::launch (src/engine/gpu/exec_graph.cc:354-404).  The caller resolves the
+ * first-touch-of-a-group-is-a-copy rule (:167-172, 368-378) by passing the castable to use
+ * and by making the touches of one group depend on one another. */
+int es_b200_program_add_touch(es_b200_program_t* p, const es_touchdim_t* dims, int rank, int castable,
+                              int dtype, void* out, const void* inn,
+                              const int* deps, int n_deps, int* op_index);
+/* Many touches of one dtype whose destinations do not overlap, as one launch. */
+int es_b200_program_add_touch_batch(es_b200_program_t* p, const es_touch_item_t* items, int n, int dtype,
+                                    const int* deps, int n_deps, int* op_index);
+/* gpu_constant_t / gpu_lowerTri_t::launch (src/engine/gpu/exec_graph.cc:623,675). */
+int es_b200_program_add_fill_constant(es_b200_program_t* p, int dtype, const void* value8, uint64_t nelem,
+                                      void* out, const int* deps, int n_deps, int* op_index);
+int es_b200_program_add_fill_lowertri(es_b200_program_t* p, int dtype, const void* lower8, const void* upper8,
+                                      uint64_t nrow, uint64_t ncol, int64_t start, void* out,
+                                      const int* deps, int n_deps, int* op_index);
+/* gpu_copy_t::launch for a move or copy inside this GPU (src/engine/gpu/exec_graph.cc:406-467). */
+int es_b200_program_add_copy(es_b200_program_t* p, const void* src, void* dst, uint64_t bytes,
+                             const int* deps, int n_deps, int* op_index);
+int es_b200_program_add_signal(es_b200_program_t* p, void* const* flags, int n,
+                               const int* deps, int n_deps, int* op_index);
+int es_b200_program_add_pull(es_b200_program_t* p, const es_pull_item_t* items, int n,
+                             const int* deps, int n_deps, int* op_index);
+int es_b200_program_add_wait(es_b200_program_t* p, void* const* flags, int n,
+                             const int* deps, int n_deps, int* op_index);
+
+/* Computes the schedule (max_lanes compute lanes, 0 = 8; plus the exchange lane when the
+ * program has pull / wait ops), creates streams and events and uploads the descriptor arrays.
+ * *workspace_bytes = what es_b200_program_set_workspace must be given (each lane has its own
+ * slice, as gpu_workspace_manager_t lends one workspace per node in flight,
+ * src/engine/gpu/workspace.cc:49-91). */
+int es_b200_program_finalize(es_b200_program_t* p, int max_lanes, uint64_t* workspace_bytes);
+int es_b200_program_set_workspace(es_b200_program_t* p, void* workspace, uint64_t bytes);
+int es_b200_program_set_wait_limit(es_b200_program_t* p, uint32_t limit_ms);
+
+/* One run, asynchronous: everything is ordered after the work already on `stream`, and
+ * `stream` continues only when every op has finished. */
+int es_b200_program_launch(es_b200_program_t* p, void* stream);
+/* The same with a CUDA event pair around every op; synchronises `stream` and returns the
+ * milliseconds each op held its lane (for pull / wait ops this includes the time spent
+ * waiting for the peer). */
+int es_b200_program_launch_timed(es_b200_program_t* p, void* stream, float* ms_per_op, int n);
+/* Captures one run into a CUDA graph (run the program once before, so that everything is
+ * loaded); replay launches that graph on `stream`. */
+int es_b200_program_instantiate(es_b200_program_t* p);
+int es_b200_program_replay(es_b200_program_t* p, void* stream);
+/* Synchronises the device and sets the run counter back to zero (flags are the caller's to
+ * clear); all ranks do this together, between runs. */
+int es_b200_program_reset_epoch(es_b200_program_t* p);
+/* The schedule as JSON: lanes, per op its kind, lane, dependencies and the events it waits for.
+ * With buf == NULL only *needed (bytes incl. the terminator) is returned. */
+int es_b200_program_describe(es_b200_program_t* p, char* buf, int buf_len, int* needed);
 
 const char* es_b200_last_error(void);
 const char* es_b200_version(void);

@@ -39,11 +39,15 @@ def outputs_of(name):
     return {k[len(pre):]: ARR[k] for k in ARR.files if k.startswith(pre)}
 
 
+@pytest.mark.parametrize("schedule", ["dag", "list"])
 @pytest.mark.parametrize("name", SMALL)
-def test_small_memgraphs_match_oracle_and_reference(name):
+def test_small_memgraphs_match_oracle_and_reference(name, schedule):
+    """schedule "dag": the library's program executor (dependency-ordered lanes); "list": one
+    stream in node order."""
     mg = load_memgraph(graph_path(name))
     ins = inputs_of(name)
-    r = memgraph_runner_t(mg)
+    r = memgraph_runner_t(mg, schedule=schedule)
+    assert (r.prog is not None) == (schedule == "dag")
     for k, v in ins.items():
         r.set_input(k, v)
     r.run()
@@ -69,6 +73,20 @@ def test_small_memgraphs_match_oracle_and_reference(name):
     torch.cuda.synchronize()
     for k, v in first.items():
         assert r.get_output(k).tobytes() == v.tobytes()
+    # and so does the replay of the run captured as one CUDA graph
+    r.capture()
+    r.replay()
+    r.replay()
+    torch.cuda.synchronize()
+    assert r.device_status() == 0
+    for k, v in first.items():
+        assert r.get_output(k).tobytes() == v.tobytes()
+    if schedule == "dag":
+        prof = r.profile()
+        torch.cuda.synchronize()
+        assert len(prof) == len(r.units) and all(t >= 0 for _, _, t in prof)
+        for k, v in first.items():
+            assert r.get_output(k).tobytes() == v.tobytes()
     r.close()
 
 
@@ -122,11 +140,7 @@ def test_llama7b_layer_runs_and_is_finite():
     r.run()
     torch.cuda.synchronize()
     assert r.get_output("scores").tobytes() == first.tobytes()
-    kinds = {}
-    for op in r.program:
-        if op[0] == "einsummable":
-            k = r.km(op[1]).kernel_info(op[2]).split("|")[0]
-            kinds[k] = kinds.get(k, 0) + 1
+    kinds = r.kernel_kinds()
     print(kinds)
     assert kinds.get("contraction_tc_f16", 0) >= 10   # every contraction of the layer is on the tensor cores
     r.close()

@@ -1,0 +1,295 @@
+"""The dependency-ordered schedule of the memgraph runner, checked on CPU.
+
+schedule_units (einsummable_b200/memgraph.py) turns a memgraph into units with dependencies; the
+library's program executor (es_b200_program_*, created here without a device: planning only)
+assigns them to lanes and decides which events each op waits for.  Checked on the real plans:
+
+  * every dependency of every op is implied by lane order plus the events it waits for;
+  * no two ops of one process that touch overlapping memory (at least one writing) are left
+    unordered -- i.e. the memgraph's edges, looked through its bookkeeping nodes, carry every
+    hazard, including the reuse of freed memory;
+  * exchange between ranks: a source region is not written between its `signal` and the
+    acknowledgement `wait`; simulated over repeated runs with the kernels' semantics (run
+    counters in the flags, pull/wait ops on one in-order lane) no rank ever blocks for good, and
+    every pull reads what the source rank signalled in that very run.
+"""
+import os
+
+import pytest
+
+from conftest import GOLDEN_DIR
+from einsummable_b200 import memgraph as M
+from einsummable_b200.einsummable import touch_t
+from einsummable_b200.program import program_t
+
+GRAPHS = os.path.join(GOLDEN_DIR, "graphs")
+BASE = 1 << 40          # made-up buffer addresses, one range per location
+FLAGS = 1 << 36         # offset of the flag words inside a location's range
+
+
+def load(name):
+    path = os.path.join(GRAPHS, name + ".json")
+    return M.load_memgraph(path if os.path.exists(path) else path + ".gz")
+
+
+def ptr(loc, off):
+    return (loc + 1) * BASE + off
+
+
+def plan(mg, owned, exchange, max_lanes=8):
+    """(units, described schedule) of the program a runner would build for `owned`."""
+    nodes = mg["nodes"]
+    units = M.schedule_units(mg, owned, exchange)
+    cross = [n["id"] for n in nodes if n["kind"] == "move" and n["src_loc"] != n["dst_loc"]]
+    index = {m: k for k, m in enumerate(cross)}
+
+    def flag(loc, kind, m):
+        return ptr(loc, FLAGS + 4 * (kind * len(cross) + index[m]))
+
+    prog = program_t(None)
+    for u in units:
+        k, deps = u["kind"], u["deps"]
+        if k == "einsummable":
+            n = nodes[u["node"]]
+            offs = [m[0] for m in n["mems"]]
+            prog.add_einsummable(0, ptr(n["loc"], offs[0]), [ptr(n["loc"], o) for o in offs[1:]], deps)
+        elif k == "touch":
+            n = nodes[u["node"]]
+            d = n["touch"]
+            t = touch_t(d["selection"], d["castable"], d["dtype"])
+            prog.add_touch(t, None if u["first"] else d["castable"], ptr(n["loc"], n["mems"][0][0]),
+                           ptr(n["loc"], n["mems"][1][0]), deps)
+        elif k == "constant":
+            n = nodes[u["node"]]
+            prog.add_copy(ptr(n["loc"], 0), ptr(n["loc"], n["offset"]), 16, deps)   # stand-in op, same deps
+        elif k == "copy":
+            n = nodes[u["node"]]
+            s, d = (n["src_loc"], n["dst_loc"]) if n["kind"] == "move" else (n["loc"], n["loc"])
+            prog.add_copy(ptr(s, n["src_offset"]), ptr(d, n["dst_offset"]), n["size"], deps)
+        elif k == "signal":
+            prog.add_signal([flag(nodes[m]["dst_loc"], 0, m) for m in u["moves"]], deps)
+        elif k == "pull":
+            prog.add_pull([(ptr(nodes[m]["src_loc"], nodes[m]["src_offset"]),
+                            ptr(nodes[m]["dst_loc"], nodes[m]["dst_offset"]), nodes[m]["size"],
+                            flag(nodes[m]["dst_loc"], 0, m), flag(nodes[m]["src_loc"], 1, m)) for m in u["moves"]], deps)
+        elif k == "wait":
+            prog.add_wait([flag(nodes[m]["src_loc"], 1, m) for m in u["moves"]], deps)
+    prog.finalize(max_lanes)
+    d = prog.describe()
+    prog.close()
+    assert len(d["ops"]) == len(units)
+    return units, d
+
+
+def happens_before(d):
+    """hb[i] = bitset of the ops known to be complete when op i starts."""
+    ops = d["ops"]
+    last, hb = {}, []
+    for i, op in enumerate(ops):
+        acc = 0
+        pred = ([last[op["lane"]]] if op["lane"] in last else []) + op["wait_on"]
+        for p in pred:
+            assert p < i
+            acc |= hb[p] | (1 << p)
+        hb.append(acc)
+        last[op["lane"]] = i
+    return hb
+
+
+def regions(mg, u):
+    """(reads, writes) of a unit: lists of (loc, lo, hi, box) with box = (tensor key, per-dim
+    (offset, size)) for a touch's destination so that touches of disjoint blocks of one tensor
+    do not count as a conflict."""
+    nodes = mg["nodes"]
+    k = u["kind"]
+    if k == "einsummable":
+        n = nodes[u["node"]]
+        mems = n["mems"]
+        return ([(n["loc"], m[0], m[0] + m[1], None) for m in mems[1:]],
+                [(n["loc"], mems[0][0], mems[0][0] + mems[0][1], None)])
+    if k == "touch":
+        n = nodes[u["node"]]
+        mems, sel = n["mems"], n["touch"]["selection"]
+        box = ((n["loc"], mems[0][0], tuple(s[1] for s in sel)), tuple((s[3], s[4]) for s in sel))
+        out = (n["loc"], mems[0][0], mems[0][0] + mems[0][1], box)
+        reads = [(n["loc"], mems[1][0], mems[1][0] + mems[1][1], None)]
+        if not u["first"]:
+            reads.append(out)
+        return reads, [out]
+    if k == "constant":
+        n = nodes[u["node"]]
+        f = n["fill"]
+        size = {"f16": 2, "f32": 4, "f64": 8, "c64": 8}[(f.get("value") or f["lower"])["dtype"]]
+        nelem = f["nelem"] if f["type"] == "constant" else f["nrow"] * f["ncol"]
+        return [], [(n["loc"], n["offset"], n["offset"] + nelem * size, None)]
+    if k == "copy":
+        n = nodes[u["node"]]
+        s, d = (n["src_loc"], n["dst_loc"]) if n["kind"] == "move" else (n["loc"], n["loc"])
+        return ([(s, n["src_offset"], n["src_offset"] + n["size"], None)],
+                [(d, n["dst_offset"], n["dst_offset"] + n["size"], None)])
+    if k == "pull":
+        return [], [(nodes[m]["dst_loc"], nodes[m]["dst_offset"], nodes[m]["dst_offset"] + nodes[m]["size"], None)
+                    for m in u["moves"]]
+    if k == "signal":   # the peer reads the sources from now on
+        return [(nodes[m]["src_loc"], nodes[m]["src_offset"], nodes[m]["src_offset"] + nodes[m]["size"], None)
+                for m in u["moves"]], []
+    return [], []
+
+
+def overlap(a, b):
+    if a[0] != b[0] or not (a[1] < b[2] and b[1] < a[2]):
+        return False
+    if a[3] is not None and b[3] is not None and a[3][0] == b[3][0]:
+        return all(x[0] < y[0] + y[1] and y[0] < x[0] + x[1] for x, y in zip(a[3][1], b[3][1]))
+    return True
+
+
+def check_plan(mg, units, d):
+    hb = happens_before(d)
+    ops = d["ops"]
+    for i, op in enumerate(ops):
+        for dep in op["deps"]:
+            assert hb[i] >> dep & 1, "op %d starts without its dependency %d" % (i, dep)
+    rw = [regions(mg, u) for u in units]
+    for j in range(len(units)):
+        for i in range(j):
+            if hb[j] >> i & 1:
+                continue
+            (ri, wi), (rj, wj) = rw[i], rw[j]
+            for w in wi:
+                for x in rj + wj:
+                    assert not overlap(w, x), ("unordered hazard", i, units[i], j, units[j])
+            for w in wj:
+                for x in ri:
+                    assert not overlap(w, x), ("unordered hazard", i, units[i], j, units[j])
+    return hb
+
+
+SMALL = [("c1_n64_locs2", 2), ("llama_tiny_locs2", 2), ("llama_tiny_locs4", 4), ("llama_train_tiny_locs2", 2),
+         ("llama_train_adamw_tiny_locs2", 2)]
+LARGE = [("llama7b_layer_locs1", 1), ("llama7b_layer_locs2", 2), ("llama7b_layer_locs4", 4), ("llama7b_layer_locs8", 8)]
+
+
+@pytest.mark.parametrize("name,world", SMALL + LARGE)
+@pytest.mark.parametrize("lanes", [1, 8])
+def test_single_process_schedule_has_no_unordered_hazard(name, world, lanes):
+    mg = load(name)
+    units, d = plan(mg, set(range(world)), False, lanes)
+    assert d["n_lanes"] <= lanes
+    check_plan(mg, units, d)
+
+
+@pytest.mark.parametrize("name,world", SMALL + LARGE[1:])
+def test_per_rank_schedules_order_every_hazard_and_protect_sources(name, world):
+    mg = load(name)
+    nodes = mg["nodes"]
+    for rank in range(world):
+        units, d = plan(mg, {rank}, True)
+        hb = check_plan(mg, units, d)
+        # pull / wait ops share lane 0, everything else runs elsewhere
+        for u, op in zip(units, d["ops"]):
+            assert (op["lane"] == 0) == (u["kind"] in ("pull", "wait")), (u, op)
+        # a source region: written only before its signal or after the acknowledgement
+        sig, ack = {}, {}
+        for i, u in enumerate(units):
+            if u["kind"] == "signal":
+                sig.update({m: i for m in u["moves"]})
+            elif u["kind"] == "wait":
+                ack.update({m: i for m in u["moves"]})
+        assert set(sig) == set(ack) == {n["id"] for n in nodes if n["kind"] == "move"
+                                        and n["src_loc"] == rank and n["dst_loc"] != rank}
+        rw = [regions(mg, u) for u in units]
+        for m, s in sig.items():
+            src = (rank, nodes[m]["src_offset"], nodes[m]["src_offset"] + nodes[m]["size"], None)
+            for i, (_, writes) in enumerate(rw):
+                if i == s or not any(overlap(src, w) for w in writes):
+                    continue
+                assert (hb[s] >> i & 1) or (hb[i] >> ack[m] & 1) or i == ack[m], \
+                    ("source of move %d written while a peer may read it" % m, units[i])
+
+
+@pytest.mark.parametrize("name,world", SMALL + LARGE[1:])
+def test_exchange_never_blocks_over_repeated_runs(name, world):
+    """All ranks' programs executed together with the kernels' semantics: an op starts when the
+    op before it on its lane and the ops it waits for have finished; a pull finishes when every
+    member's ready flag has reached the rank's run number and then raises the done flags; a wait
+    finishes when its done flags have.  Also: a pull only ever sees a flag of its own run."""
+    mg = load(name)
+    nodes = mg["nodes"]
+    plans = [plan(mg, {r}, True) for r in range(world)]
+    ready, done = {}, {}
+    for run in range(1, 4):
+        finished = [set() for _ in range(world)]
+        heads = []
+        for r in range(world):
+            lanes = {}
+            for i, op in enumerate(plans[r][1]["ops"]):
+                lanes.setdefault(op["lane"], []).append(i)
+            heads.append(lanes)
+        remaining = sum(len(p[0]) for p in plans)
+        while remaining:
+            progressed = False
+            for r in range(world):
+                units, d = plans[r]
+                for lane, queue in heads[r].items():
+                    while queue:
+                        i = queue[0]
+                        if not all(w in finished[r] for w in d["ops"][i]["wait_on"]):
+                            break
+                        u = units[i]
+                        if u["kind"] == "pull":
+                            if not all(ready.get(m, 0) >= run for m in u["moves"]):
+                                break
+                            assert all(ready[m] == run for m in u["moves"]), "a pull saw a flag of another run"
+                            for m in u["moves"]:
+                                done[m] = run
+                        elif u["kind"] == "wait":
+                            if not all(done.get(m, 0) >= run for m in u["moves"]):
+                                break
+                        elif u["kind"] == "signal":
+                            for m in u["moves"]:
+                                assert ready.get(m, 0) == run - 1
+                                ready[m] = run
+                        finished[r].add(i)
+                        queue.pop(0)
+                        remaining -= 1
+                        progressed = True
+            assert progressed, "every rank is blocked in run %d" % run
+        n_cross = sum(1 for n in nodes if n["kind"] == "move" and n["src_loc"] != n["dst_loc"])
+        assert len(ready) == len(done) == n_cross and set(ready.values()) == set(done.values()) == {run}
+
+
+def test_exchange_ops_come_in_the_same_global_order_on_every_rank():
+    """pull and wait units are keyed by the memgraph node that needs them; every rank lists its
+    own in increasing key order (what makes the single in-order exchange lane safe)."""
+    mg = load("llama7b_layer_locs8")
+    for rank in range(8):
+        units = M.schedule_units(mg, {rank}, True)
+        keys = [min(u["moves"]) for u in units if u["kind"] == "pull"]
+        assert keys == sorted(keys)
+        # the incoming moves of one run share a unit; units never mix runs
+        runs = M.move_runs(mg)
+        for u in units:
+            if u["kind"] == "pull":
+                assert len({runs[m] for m in u["moves"]}) == 1
+
+
+def test_program_rejects_bad_input():
+    from einsummable_b200 import _lib
+    p = program_t(None)
+    a = p.add_copy(BASE, BASE + 4096, 64)
+    with pytest.raises(_lib.es_error):
+        p.add_copy(BASE, BASE + 4096, 64, deps=[5])          # not an earlier op
+    with pytest.raises(_lib.es_error):
+        p.add_pull([(BASE + 8, BASE + 4096, 64, BASE + 64, BASE + 68)])   # unaligned source
+    with pytest.raises(_lib.es_error):
+        p.launch()                                            # not finalized
+    p.add_copy(BASE, BASE + 8192, 64, deps=[a])
+    p.finalize(4)
+    with pytest.raises(_lib.es_error):
+        p.launch()                                            # planning only: no device
+    with pytest.raises(_lib.es_error):
+        p.add_copy(BASE, BASE + 4096, 64)                     # already finalized
+    d = p.describe()
+    assert [op["lane"] for op in d["ops"]] == [0, 0] and d["ops"][1]["wait_on"] == []
+    p.close()
