@@ -225,3 +225,29 @@ def test_fusion_hazards_on_hand_made_graphs():
     f, n = fuse_elementwise_chains(_mini([_ew(0, [], A, [X], sq, rank2=True), red], outputs=[(2048, 32)]))
     assert n == 1 and f["nodes"][1]["einsummable"] == {"join_shape": [8, 8], "inns": [[0, 1]], "out_rank": 1,
                                                        "join": sq, "castable": "add"}
+
+
+def test_fusion_leaves_readers_that_view_the_bytes_differently():
+    """The taskgraph lets a node read the same bytes under another shape (squeeze) or dtype (a
+    complex view of float pairs), src/einsummable/taskgraph.cc:765-793: a producer is never folded
+    into such a reader, and a later writer into memory the folded producer read waits for the reader."""
+    from einsummable_b200.fuse import fuse_elementwise_chains
+    X, A, B, C = (0, 256), (256, 256), (512, 256), (768, 256)
+    sq = "power{2}[hole|f32@0]"
+    # producer writes [64]; the reader takes the same 256 bytes as [8, 8]
+    reader = _ew(1, [0], B, [A], "exp[hole|f32@0]", rank2=True)
+    assert fuse_elementwise_chains(_mini([_ew(0, [], A, [X], sq), reader], outputs=[B]))[1] == 0
+    # ... and the other way round (more modes in the producer than in the reader's slot)
+    reader = _ew(1, [0], B, [A], "exp[hole|f32@0]")
+    assert fuse_elementwise_chains(_mini([_ew(0, [], A, [X], sq, rank2=True), reader], outputs=[B]))[1] == 0
+    # producer writes 64 f32; the reader takes them as 32 c64
+    cview = _ew(1, [0], B, [A], "conj[hole|c64@0]", n=32)
+    assert fuse_elementwise_chains(_mini([_ew(0, [], A, [X], sq), cview], outputs=[B]))[1] == 0
+    # producer converts to f16, the reader's hole is f32 over half as many... same count, other dtype
+    conv = _ew(0, [], A, [X], "to_f16[hole|f32@0]")
+    assert fuse_elementwise_chains(_mini([conv, _ew(1, [0], B, [A], "exp[hole|f32@0]")], outputs=[B]))[1] == 0
+    # same shape and dtype: folded, and the later writer into X now depends on the reader
+    writer = _ew(2, [], X, [C], sq)
+    f, n = fuse_elementwise_chains(_mini([_ew(0, [], A, [X], sq), _ew(1, [0], B, [A], "exp[hole|f32@0]"), writer],
+                                         outputs=[B]))
+    assert n == 1 and f["nodes"][2]["inns"] == [1]

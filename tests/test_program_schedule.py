@@ -179,6 +179,21 @@ def test_single_process_schedule_has_no_unordered_hazard(name, world, lanes):
     check_plan(mg, units, d)
 
 
+@pytest.mark.parametrize("name,world", SMALL + LARGE)
+def test_folded_graphs_stay_hazard_free_under_dependency_order(name, world):
+    """The fold pass moves reads (a reader now reads its folded producer's inputs): later writers
+    into that memory must have been made to wait for the reader."""
+    from einsummable_b200.fuse import fuse_elementwise_chains
+    mg, folded = fuse_elementwise_chains(load(name))
+    if not name.startswith("c1"):
+        assert folded > 0
+    units, d = plan(mg, set(range(world)), False, 8)
+    check_plan(mg, units, d)
+    for rank in range(world if world > 1 else 0):
+        units, d = plan(mg, {rank}, True)
+        check_plan(mg, units, d)
+
+
 @pytest.mark.parametrize("name,world", SMALL + LARGE[1:])
 def test_per_rank_schedules_order_every_hazard_and_protect_sources(name, world):
     mg = load(name)
