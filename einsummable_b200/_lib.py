@@ -102,6 +102,7 @@ SYMBOLS = {
     "es_b200_program_launch_timed": (_i, [_vp, _vp, ctypes.POINTER(ctypes.c_float), _i]),
     "es_b200_program_instantiate": (_i, [_vp]),
     "es_b200_program_replay": (_i, [_vp, _vp]),
+    "es_b200_program_replay_timed": (_i, [_vp, _vp, ctypes.POINTER(ctypes.c_ulonglong), _i]),
     "es_b200_program_reset_epoch": (_i, [_vp]),
     "es_b200_program_describe": (_i, [_vp, _cp, _i, _ip]),
     "es_b200_last_error": (_cp, []),

@@ -49,6 +49,15 @@ __device__ __forceinline__ bool spin_until(uint32_t const* flag, uint32_t epoch,
     return true;
 }
 
+__global__ void stamp_kernel(unsigned long long* slot)
+{
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        *slot = t;
+    }
+}
+
 __global__ void epoch_bump_kernel(uint32_t* epoch)
 {
     if (blockIdx.x == 0 && threadIdx.x == 0) *epoch = *epoch + 1;
@@ -135,6 +144,12 @@ uint32_t pull_ctas_for(uint64_t bytes)
     // direction while leaving the SMs to the compute kernels that run beside the pull
     uint64_t c = (bytes + 32767) / 32768;
     return (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>(c, 48));
+}
+
+void launch_stamp(unsigned long long* slot_dev, cudaStream_t s)
+{
+    stamp_kernel<<<1, 32, 0, s>>>(slot_dev);
+    ES_CUDA_CHECK(cudaGetLastError());
 }
 
 void launch_epoch_bump(uint32_t* epoch_dev, cudaStream_t s)

@@ -19,6 +19,8 @@ struct pull_item_t {
 
 uint32_t pull_ctas_for(uint64_t bytes);
 
+// Stores the GPU's nanosecond timer into *slot_dev (profiling runs of a program).
+void launch_stamp(unsigned long long* slot_dev, cudaStream_t s);
 void launch_epoch_bump(uint32_t* epoch_dev, cudaStream_t s);
 void launch_signal_many(uint32_t* const* flags_dev, int n, uint32_t const* epoch_dev, cudaStream_t s);
 void launch_wait_many(uint32_t* const* flags_dev, int n, uint32_t const* epoch_dev, uint32_t limit_ms, cudaStream_t s);

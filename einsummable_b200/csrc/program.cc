@@ -103,6 +103,9 @@ struct es_b200_program {
     cudaGraph_t               graph = nullptr;
     cudaGraphExec_t           exec = nullptr;
     std::vector<cudaEvent_t>  t0, t1; // timing events (launch_timed)
+    cudaGraph_t               graph_timed = nullptr; // the run with a time stamp before and after every op
+    cudaGraphExec_t           exec_timed = nullptr;
+    unsigned long long*       stamps_dev = nullptr;  // [2 * n_ops + 2]
 };
 
 namespace {
@@ -217,6 +220,12 @@ void free_device_side(es_b200_program* p)
 {
     if (p->exec) cudaGraphExecDestroy(p->exec);
     if (p->graph) cudaGraphDestroy(p->graph);
+    if (p->exec_timed) cudaGraphExecDestroy(p->exec_timed);
+    if (p->graph_timed) cudaGraphDestroy(p->graph_timed);
+    if (p->stamps_dev) cudaFree(p->stamps_dev);
+    p->exec_timed = nullptr;
+    p->graph_timed = nullptr;
+    p->stamps_dev = nullptr;
     if (p->capture_stream) cudaStreamDestroy(p->capture_stream);
     for (auto e : p->events) cudaEventDestroy(e);
     for (auto e : p->join_ev) cudaEventDestroy(e);
@@ -325,13 +334,18 @@ void launch_op(es_b200_program* p, op_t const& op, cudaStream_t s)
 
 // One run: fork from `stream` into the lanes, issue every op on its lane behind the events of
 // its dependencies, join back into `stream`.  Nothing synchronises with the host.
-void launch_all(es_b200_program* p, cudaStream_t stream, bool timed)
+enum { RUN_PLAIN = 0, RUN_EVENTS = 1, RUN_STAMPS = 2 };
+
+void launch_all(es_b200_program* p, cudaStream_t stream, int mode)
 {
+    bool const timed = mode == RUN_EVENTS;
+    bool const stamps = mode == RUN_STAMPS;
     if (!p->h) fail(ES_BAD_ARGUMENT, "program: created without a device (planning only)");
     if (p->ws_total > 0 && (!p->ws_base || p->ws_bytes < p->ws_total))
         fail(ES_WORKSPACE_TOO_SMALL, "program: workspace of " + std::to_string(p->ws_total) + " bytes required");
     ES_CUDA_CHECK(cudaSetDevice(p->h->device));
     launch_epoch_bump(p->epoch_dev, stream);
+    if (stamps) launch_stamp(p->stamps_dev + 2 * p->ops.size(), stream);
     ES_CUDA_CHECK(cudaEventRecord(p->fork_ev, stream));
     for (int l = 0; l != p->n_lanes; ++l)
         if (p->lane_last[l] >= 0) ES_CUDA_CHECK(cudaStreamWaitEvent(p->lanes[l], p->fork_ev, 0));
@@ -340,7 +354,9 @@ void launch_all(es_b200_program* p, cudaStream_t stream, bool timed)
         cudaStream_t s = p->lanes[op.lane];
         for (int d : op.wait_on) ES_CUDA_CHECK(cudaStreamWaitEvent(s, p->events[p->event_of[d]], 0));
         if (timed) ES_CUDA_CHECK(cudaEventRecord(p->t0[i], s));
+        if (stamps) launch_stamp(p->stamps_dev + 2 * i, s);
         launch_op(p, op, s);
+        if (stamps) launch_stamp(p->stamps_dev + 2 * i + 1, s);
         if (timed) ES_CUDA_CHECK(cudaEventRecord(p->t1[i], s));
         if (op.record) ES_CUDA_CHECK(cudaEventRecord(p->events[p->event_of[i]], s));
     }
@@ -349,6 +365,26 @@ void launch_all(es_b200_program* p, cudaStream_t stream, bool timed)
         ES_CUDA_CHECK(cudaEventRecord(p->join_ev[l], p->lanes[l]));
         ES_CUDA_CHECK(cudaStreamWaitEvent(stream, p->join_ev[l], 0));
     }
+    if (stamps) launch_stamp(p->stamps_dev + 2 * p->ops.size() + 1, stream);
+}
+
+cudaGraphExec_t capture(es_b200_program* p, int mode, cudaGraph_t* graph_out)
+{
+    if (!p->capture_stream) ES_CUDA_CHECK(cudaStreamCreateWithFlags(&p->capture_stream, cudaStreamNonBlocking));
+    ES_CUDA_CHECK(cudaStreamBeginCapture(p->capture_stream, cudaStreamCaptureModeThreadLocal));
+    try {
+        launch_all(p, p->capture_stream, mode);
+    } catch (...) {
+        cudaGraph_t broken = nullptr;
+        cudaStreamEndCapture(p->capture_stream, &broken);
+        if (broken) cudaGraphDestroy(broken);
+        cudaGetLastError();
+        throw;
+    }
+    ES_CUDA_CHECK(cudaStreamEndCapture(p->capture_stream, graph_out));
+    cudaGraphExec_t exec = nullptr;
+    ES_CUDA_CHECK(cudaGraphInstantiate(&exec, *graph_out, 0));
+    return exec;
 }
 
 template <typename F> int guarded(F&& f)
@@ -689,7 +725,7 @@ int es_b200_program_launch(es_b200_program_t* p, void* stream)
 {
     return guarded([&] {
         check_program(p, true);
-        launch_all(p, (cudaStream_t)stream, false);
+        launch_all(p, (cudaStream_t)stream, RUN_PLAIN);
     });
 }
 
@@ -706,7 +742,7 @@ int es_b200_program_launch_timed(es_b200_program_t* p, void* stream, float* ms_p
             for (auto& e : p->t0) ES_CUDA_CHECK(cudaEventCreate(&e));
             for (auto& e : p->t1) ES_CUDA_CHECK(cudaEventCreate(&e));
         }
-        launch_all(p, (cudaStream_t)stream, true);
+        launch_all(p, (cudaStream_t)stream, RUN_EVENTS);
         ES_CUDA_CHECK(cudaStreamSynchronize((cudaStream_t)stream));
         for (size_t i = 0; i != p->ops.size(); ++i)
             ES_CUDA_CHECK(cudaEventElapsedTime(&ms_per_op[i], p->t0[i], p->t1[i]));
@@ -727,20 +763,26 @@ int es_b200_program_instantiate(es_b200_program_t* p)
             cudaGraphDestroy(p->graph);
             p->graph = nullptr;
         }
-        if (!p->capture_stream)
-            ES_CUDA_CHECK(cudaStreamCreateWithFlags(&p->capture_stream, cudaStreamNonBlocking));
-        ES_CUDA_CHECK(cudaStreamBeginCapture(p->capture_stream, cudaStreamCaptureModeThreadLocal));
-        try {
-            launch_all(p, p->capture_stream, false);
-        } catch (...) {
-            cudaGraph_t broken = nullptr;
-            cudaStreamEndCapture(p->capture_stream, &broken);
-            if (broken) cudaGraphDestroy(broken);
-            cudaGetLastError();
-            throw;
+        p->exec = capture(p, RUN_PLAIN, &p->graph);
+    });
+}
+
+int es_b200_program_replay_timed(es_b200_program_t* p, void* stream, unsigned long long* ns, int n)
+{
+    return guarded([&] {
+        check_program(p, true);
+        if (!p->h) fail(ES_BAD_ARGUMENT, "program: created without a device (planning only)");
+        int need = 2 * (int)p->ops.size() + 2;
+        if (!ns || n < need) fail(ES_BAD_ARGUMENT, "program: time stamp array too small");
+        ES_CUDA_CHECK(cudaSetDevice(p->h->device));
+        if (!p->exec_timed) {
+            ES_CUDA_CHECK(cudaMalloc(&p->stamps_dev, sizeof(unsigned long long) * need));
+            ES_CUDA_CHECK(cudaMemset(p->stamps_dev, 0, sizeof(unsigned long long) * need));
+            p->exec_timed = capture(p, RUN_STAMPS, &p->graph_timed);
         }
-        ES_CUDA_CHECK(cudaStreamEndCapture(p->capture_stream, &p->graph));
-        ES_CUDA_CHECK(cudaGraphInstantiate(&p->exec, p->graph, 0));
+        ES_CUDA_CHECK(cudaGraphLaunch(p->exec_timed, (cudaStream_t)stream));
+        ES_CUDA_CHECK(cudaStreamSynchronize((cudaStream_t)stream));
+        ES_CUDA_CHECK(cudaMemcpy(ns, p->stamps_dev, sizeof(unsigned long long) * need, cudaMemcpyDeviceToHost));
     });
 }
 

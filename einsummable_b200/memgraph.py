@@ -226,10 +226,125 @@ def schedule_units(mg, owned, exchange):
         units.append({"kind": "wait", "moves": rest, "deps": []})
     return units
 
+_DSIZE = {"f16": 2, "f32": 4, "f64": 8, "c64": 8}
+
+
+def unit_cost_us(mg, u):
+    """(latency_us, work_us, server) of a unit for the schedule simulation: a fixed launch latency that
+    overlaps with anything, and work that occupies a server -- "gpu" (HBM / tensor time, from the
+    unit's algorithmic bytes and flops at round B200 rates) or "link" (NVLink into this GPU)."""
+    nodes = mg["nodes"]
+    k = u["kind"]
+    if k == "einsummable":
+        n = nodes[u["node"]]
+        e = n["einsummable"]
+        nbytes = sum(m[1] for m in n["mems"])
+        if (len(e["inns"]) == 2 and e["castable"] == "add" and e["out_rank"] < len(e["join_shape"])
+                and e["join"].startswith("*[hole")):
+            flops = 2.0
+            for d in e["join_shape"]:
+                flops *= d
+            return 5.0, max(flops / 1.25e9, nbytes / 5.0e6), "gpu"
+        return 2.5, nbytes / 5.5e6, "gpu"
+    if k == "touch":
+        n = nodes[u["node"]]
+        return 2.5, n["mems"][1][1] * (2 if u["first"] else 3) / 4.5e6, "gpu"
+    if k == "constant":
+        return 2.5, 0.5, "gpu"
+    if k == "copy":
+        return 2.5, 2 * nodes[u["node"]]["size"] / 4.5e6, "gpu"
+    if k == "signal":
+        return 3.0, 0.0, None
+    if k == "pull":
+        return 3.0, sum(nodes[m]["size"] for m in u["moves"]) / 0.65e6, "link"
+    if k == "wait":
+        return 2.0, 0.0, None
+    raise ValueError(k)
+
+
+def simulate_schedule(mg, units_by_rank):
+    """Start and finish time (us) of every unit of every rank under a simple machine model: a unit
+    becomes ready when its dependencies -- and, for a pull, the source ranks' signals; for a wait, the
+    destination ranks' pulls -- have finished; ready units are served first come first served; each
+    rank's GPU and each rank's incoming link do one unit's work at a time, launch latencies overlap.
+    Deterministic (ties by rank and index), so every rank that runs it gets the same answer.
+    Returns {(rank, index): (start, finish)}."""
+    import heapq
+    sig_of, pull_of = {}, {}
+    for r, units in enumerate(units_by_rank):
+        for i, u in enumerate(units):
+            if u["kind"] == "signal":
+                for m in u["moves"]:
+                    sig_of[m] = (r, i)
+            elif u["kind"] == "pull":
+                for m in u["moves"]:
+                    pull_of[m] = (r, i)
+    preds, succs, cost = {}, {}, {}
+    for r, units in enumerate(units_by_rank):
+        for i, u in enumerate(units):
+            p = [(r, d) for d in u["deps"]]
+            if u["kind"] == "pull":
+                p += [sig_of[m] for m in u["moves"]]
+            elif u["kind"] == "wait":
+                p += [pull_of[m] for m in u["moves"]]
+            preds[(r, i)] = p
+            cost[(r, i)] = unit_cost_us(mg, u)
+            for q in p:
+                succs.setdefault(q, []).append((r, i))
+    left = {k: len(p) for k, p in preds.items()}
+    ready_at = {k: 0.0 for k in preds}
+    heap = [(0.0, k) for k, n in left.items() if n == 0]
+    heapq.heapify(heap)
+    free = {}
+    times = {}
+    while heap:
+        t, k = heapq.heappop(heap)
+        lat, work, server = cost[k]
+        begin = t + lat
+        if server is not None and work > 0:
+            begin = max(begin, free.get((k[0], server), 0.0))
+            free[(k[0], server)] = begin + work
+        fin = begin + work
+        times[k] = (t, fin)
+        for c in succs.get(k, ()):
+            # a flag takes about 2 us to cross NVLink
+            ready_at[c] = max(ready_at[c], fin + (2.0 if c[0] != k[0] else 0.0))
+            left[c] -= 1
+            if left[c] == 0:
+                heapq.heappush(heap, (ready_at[c], c))
+    if len(times) != len(preds):
+        raise RuntimeError("simulate_schedule: the units of the ranks wait for one another in a cycle")
+    return times
+
+
+def order_units_by_simulation(mg, world, rank):
+    """The units of `rank` (schedule_units) reordered by their simulated start time, dependencies
+    renumbered.  Every rank simulates all ranks, so the ranks agree on when each exchange is expected:
+    the pull / wait ops, which share one in-order lane, are then served in the order in which their
+    data is expected to be ready instead of the memgraph's node order.  The order stays a valid one
+    on every rank and across ranks: along every dependency, also those that cross ranks, the
+    simulated start times strictly increase."""
+    all_units = [schedule_units(mg, {r}, True) for r in range(world)]
+    times = simulate_schedule(mg, all_units)
+    units = all_units[rank]
+    # the closing wait (acknowledgements nobody on this rank needs during the run) stays last
+    closing = len(units) - 1 if units and units[-1]["kind"] == "wait" and not any(
+        len(units) - 1 in u["deps"] for u in units) else -1
+    order = sorted(range(len(units)), key=lambda i: (i == closing, times[(rank, i)][0], i))
+    new_index = {old: new for new, old in enumerate(order)}
+    out = []
+    for old in order:
+        u = dict(units[old])
+        u["deps"] = sorted(new_index[d] for d in u["deps"])
+        assert all(d < len(out) for d in u["deps"])
+        u["sim_start_us"], u["sim_finish_us"] = times[(rank, old)]
+        out.append(u)
+    return out
+
 
 class memgraph_runner_t:
     def __init__(self, mg, devices=None, rank=None, world=None, transport="nccl", wait_limit_ms=0, fuse=False,
-                 schedule="dag", max_lanes=0):
+                 schedule="dag", max_lanes=0, order="simulated"):
         """transport (one process per GPU only): "nccl" = send/recv pairs; "p2p" = every
         location buffer lives in symmetric memory, the destination rank pulls the bytes over
         NVLink with an SM copy kernel, and the two ranks hand-shake through bounded flag
@@ -249,6 +364,9 @@ class memgraph_runner_t:
         if self.schedule not in ("dag", "list"):
             raise ValueError("schedule must be 'dag' or 'list'")
         self.max_lanes = max_lanes
+        # order of the ops of one process per GPU: "simulated" = by the start times of a simulation of
+        # all ranks (order_units_by_simulation), "memgraph" = the memgraph's node order
+        self.order = order
         self.prog = None
         self.wait_limit_ms = wait_limit_ms
         if self.distributed:
@@ -320,7 +438,10 @@ class memgraph_runner_t:
     def _build_program(self):
         """Translates schedule_units into ops of the library's program executor."""
         nodes = self.mg["nodes"]
-        self.units = schedule_units(self.mg, set(self.devices), self.transport == "p2p")
+        if self.transport == "p2p" and self.order == "simulated":
+            self.units = order_units_by_simulation(self.mg, self.num_locs, self.rank)
+        else:
+            self.units = schedule_units(self.mg, set(self.devices), self.transport == "p2p")
         dev = next(iter(self.devices.values()))
         km = self.kms[dev]
         prog = program_t(km)
@@ -412,6 +533,66 @@ class memgraph_runner_t:
             raise RuntimeError("profile needs the dag schedule")
         ms = self.prog.launch_timed(stream if stream is not None else torch.cuda.current_stream())
         return [(lab[0], lab[1], t) for lab, t in zip(self.unit_labels, ms)]
+
+    def timeline(self, stream=None):
+        """One replay of the captured run with the GPU's nanosecond timer read before and after every
+        op: ([(class, label, start_us, end_us)], run_us), times relative to the start of the run.  An
+        op's start is when its lane was free and its dependencies had finished."""
+        if self.prog is None:
+            raise RuntimeError("timeline needs the dag schedule")
+        spans, (t0, t1) = self.prog.replay_timed(stream if stream is not None else torch.cuda.current_stream())
+        return ([(lab[0], lab[1], (a - t0) / 1e3, (b - t0) / 1e3) for lab, (a, b) in zip(self.unit_labels, spans)],
+                (t1 - t0) / 1e3)
+
+    def timeline_summary(self, tl, run_us, top=12):
+        """Text summary of a timeline: time per class, how long no compute op was running, and the
+        chain of ops that determined the end of the run (each with the gap since its predecessor)."""
+        by = {}
+        for c, _, a, b in tl:
+            v = by.setdefault(c, [0, 0.0])
+            v[0] += 1
+            v[1] += b - a
+        spin = ("pull", "wait")
+        iv = sorted((a, b) for c, _, a, b in tl if c not in spin)
+        busy, cur_a, cur_b = 0.0, None, None
+        for a, b in iv:
+            if cur_b is None or a > cur_b:
+                if cur_b is not None:
+                    busy += cur_b - cur_a
+                cur_a, cur_b = a, b
+            else:
+                cur_b = max(cur_b, b)
+        if cur_b is not None:
+            busy += cur_b - cur_a
+        lines = ["run %.1f us; compute lanes busy (union) %.1f us, idle %.1f us" % (run_us, busy, run_us - busy),
+                 "per class (ops / summed lane time us): " +
+                 "  ".join("%s %d/%.0f" % (k, v[0], v[1]) for k, v in sorted(by.items()))]
+        # critical chain
+        lane_prev, last = {}, {}
+        d = self.prog.describe()["ops"]
+        for i, op in enumerate(d):
+            lane_prev[i] = last.get(op["lane"])
+            last[op["lane"]] = i
+        i = max(range(len(tl)), key=lambda k: tl[k][3])
+        chain = []
+        while i is not None:
+            preds = list(self.units[i]["deps"]) + ([lane_prev[i]] if lane_prev[i] is not None else [])
+            p = max(preds, key=lambda k: tl[k][3]) if preds else None
+            chain.append((i, tl[i][2] - (tl[p][3] if p is not None else 0.0)))
+            i = p
+        chain.reverse()
+        lines.append("critical chain: %d ops; per class (ops / us on the chain, gaps included):" % len(chain))
+        cc = {}
+        for i, gap in chain:
+            v = cc.setdefault(tl[i][0], [0, 0.0, 0.0])
+            v[0] += 1
+            v[1] += tl[i][3] - tl[i][2]
+            v[2] += max(gap, 0.0)
+        lines.append("  " + "  ".join("%s %d/%.0f (+%.0f gaps)" % (k, v[0], v[1], v[2]) for k, v in sorted(cc.items())))
+        for i, gap in sorted(chain, key=lambda x: -(tl[x[0]][3] - tl[x[0]][2] + max(x[1], 0)))[:top]:
+            lines.append("  at %7.1f us: %-11s %6.1f us (gap %5.1f)  %s" % (tl[i][2], tl[i][0], tl[i][3] - tl[i][2], gap,
+                                                                       tl[i][1][:90]))
+        return "\n".join(lines)
 
     # ------------------------------------------------------------------ build (list)
     def _prepare(self):

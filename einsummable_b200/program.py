@@ -162,6 +162,14 @@ class program_t:
     def replay(self, stream=None):
         _lib.check(self._lib.es_b200_program_replay(self._p, _stream(stream)))
 
+    def replay_timed(self, stream=None):
+        """One replay with the GPU's nanosecond timer read before and after every op: returns
+        ([(start_ns, end_ns) per op], (run_begin_ns, run_end_ns))."""
+        n = 2 * self.n_ops + 2
+        ns = (ctypes.c_ulonglong * n)()
+        _lib.check(self._lib.es_b200_program_replay_timed(self._p, _stream(stream), ns, n))
+        return [(ns[2 * i], ns[2 * i + 1]) for i in range(self.n_ops)], (ns[n - 2], ns[n - 1])
+
     def reset_epoch(self):
         _lib.check(self._lib.es_b200_program_reset_epoch(self._p))
 

@@ -367,6 +367,11 @@ int es_b200_program_launch_timed(es_b200_program_t* p, void* stream, float* ms_p
  * loaded); replay launches that graph on `stream`. */
 int es_b200_program_instantiate(es_b200_program_t* p);
 int es_b200_program_replay(es_b200_program_t* p, void* stream);
+/* One replay of the run captured with a time stamp (the GPU's nanosecond timer) before and
+ * after every op: ns[2*i], ns[2*i+1] = when op i could start on its lane and when it had
+ * finished; ns[2*n_ops], ns[2*n_ops+1] = begin and end of the run.  Synchronises `stream`.
+ * The first call captures that second graph (run the program once before). */
+int es_b200_program_replay_timed(es_b200_program_t* p, void* stream, unsigned long long* ns, int n);
 /* Synchronises the device and sets the run counter back to zero (flags are the caller's to
  * clear); all ranks do this together, between runs. */
 int es_b200_program_reset_epoch(es_b200_program_t* p);

@@ -36,10 +36,15 @@ def ptr(loc, off):
     return (loc + 1) * BASE + off
 
 
-def plan(mg, owned, exchange, max_lanes=8):
-    """(units, described schedule) of the program a runner would build for `owned`."""
+def plan(mg, owned, exchange, max_lanes=8, order="memgraph"):
+    """(units, described schedule) of the program a runner would build for `owned`; order
+    "simulated": the units of one rank sorted by the start times of the all-rank simulation."""
     nodes = mg["nodes"]
-    units = M.schedule_units(mg, owned, exchange)
+    if order == "simulated":
+        (rank,) = owned
+        units = M.order_units_by_simulation(mg, mg["num_locs"], rank)
+    else:
+        units = M.schedule_units(mg, owned, exchange)
     cross = [n["id"] for n in nodes if n["kind"] == "move" and n["src_loc"] != n["dst_loc"]]
     index = {m: k for k, m in enumerate(cross)}
 
@@ -194,12 +199,13 @@ def test_folded_graphs_stay_hazard_free_under_dependency_order(name, world):
         check_plan(mg, units, d)
 
 
+@pytest.mark.parametrize("order", ["memgraph", "simulated"])
 @pytest.mark.parametrize("name,world", SMALL + LARGE[1:])
-def test_per_rank_schedules_order_every_hazard_and_protect_sources(name, world):
+def test_per_rank_schedules_order_every_hazard_and_protect_sources(name, world, order):
     mg = load(name)
     nodes = mg["nodes"]
     for rank in range(world):
-        units, d = plan(mg, {rank}, True)
+        units, d = plan(mg, {rank}, True, order=order)
         hb = check_plan(mg, units, d)
         # pull / wait ops share lane 0, everything else runs elsewhere
         for u, op in zip(units, d["ops"]):
@@ -223,15 +229,16 @@ def test_per_rank_schedules_order_every_hazard_and_protect_sources(name, world):
                     ("source of move %d written while a peer may read it" % m, units[i])
 
 
+@pytest.mark.parametrize("order", ["memgraph", "simulated"])
 @pytest.mark.parametrize("name,world", SMALL + LARGE[1:])
-def test_exchange_never_blocks_over_repeated_runs(name, world):
+def test_exchange_never_blocks_over_repeated_runs(name, world, order):
     """All ranks' programs executed together with the kernels' semantics: an op starts when the
     op before it on its lane and the ops it waits for have finished; a pull finishes when every
     member's ready flag has reached the rank's run number and then raises the done flags; a wait
     finishes when its done flags have.  Also: a pull only ever sees a flag of its own run."""
     mg = load(name)
     nodes = mg["nodes"]
-    plans = [plan(mg, {r}, True) for r in range(world)]
+    plans = [plan(mg, {r}, True, order=order) for r in range(world)]
     ready, done = {}, {}
     for run in range(1, 4):
         finished = [set() for _ in range(world)]
@@ -287,6 +294,38 @@ def test_exchange_ops_come_in_the_same_global_order_on_every_rank():
         for u in units:
             if u["kind"] == "pull":
                 assert len({runs[m] for m in u["moves"]}) == 1
+
+
+def test_simulated_order_is_the_same_on_every_rank_and_increases_along_dependencies():
+    """Every rank simulates all ranks and must get the same times; along every dependency --
+    local, signal -> pull, pull -> wait -- the simulated start time strictly increases, which is
+    what makes one in-order exchange lane per rank safe under that order."""
+    mg = load("llama7b_layer_locs4")
+    all_units = [M.schedule_units(mg, {r}, True) for r in range(4)]
+    times = M.simulate_schedule(mg, all_units)
+    assert times == M.simulate_schedule(mg, [M.schedule_units(mg, {r}, True) for r in range(4)])
+    sig, pull = {}, {}
+    for r, units in enumerate(all_units):
+        for i, u in enumerate(units):
+            if u["kind"] == "signal":
+                sig.update({m: (r, i) for m in u["moves"]})
+            if u["kind"] == "pull":
+                pull.update({m: (r, i) for m in u["moves"]})
+    for r, units in enumerate(all_units):
+        for i, u in enumerate(units):
+            before = [(r, d) for d in u["deps"]]
+            if u["kind"] == "pull":
+                before += [sig[m] for m in u["moves"]]
+            if u["kind"] == "wait":
+                before += [pull[m] for m in u["moves"]]
+            for b in before:
+                assert times[b][0] < times[b][1] <= times[(r, i)][0]
+    for rank in range(4):
+        units = M.order_units_by_simulation(mg, 4, rank)
+        assert sorted(u["kind"] for u in units) == sorted(u["kind"] for u in all_units[rank])
+        assert units[-1]["kind"] == "wait"
+        starts = [u["sim_start_us"] for u in units[:-1]]
+        assert starts == sorted(starts)
 
 
 def test_program_rejects_bad_input():
