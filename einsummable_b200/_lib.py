@@ -98,6 +98,7 @@ SYMBOLS = {
     "es_b200_program_finalize": (_i, [_vp, _i, ctypes.POINTER(_u64)]),
     "es_b200_program_set_workspace": (_i, [_vp, _vp, _u64]),
     "es_b200_program_set_wait_limit": (_i, [_vp, ctypes.c_uint32]),
+    "es_b200_program_set_exchange_lanes": (_i, [_vp, _i]),
     "es_b200_program_launch": (_i, [_vp, _vp]),
     "es_b200_program_launch_timed": (_i, [_vp, _vp, ctypes.POINTER(ctypes.c_float), _i]),
     "es_b200_program_instantiate": (_i, [_vp]),

@@ -9,10 +9,17 @@
 // an op waits for exactly the ops it depends on, nothing returns to the host between ops, and the
 // whole schedule can be captured into one CUDA graph and replayed.
 //
-// Lanes.  Ops that spin on a flag another GPU raises (pull, wait) all go to lane 0, in program
-// order, so that at most one kernel per GPU is ever waiting for a peer and the order in which the
-// ranks serve their exchanges is the same everywhere (the memgraph's node order): the earliest
-// unfinished exchange can always proceed, whatever the other lanes do.  Every other op continues
+// Lanes.  Ops that spin on a flag another GPU raises (pull, wait) go to an exchange lane of
+// their own (optionally a few: round robin in program order, so each of these lanes is in program
+// order) and no other op is ever queued behind them.  The ranks list their exchange ops in one global order
+// along which every dependency -- also those that cross ranks -- points forward; the earliest
+// unfinished exchange op is therefore always at the head of its lane with everything it needs
+// finished or running, and can proceed whatever the other lanes wait for.  (This relies on what
+// every kernel that waits for a peer GPU relies on: kernels of different streams whose
+// dependencies are met get to run beside a kernel that spins.  Every wait is bounded, so a
+// platform where that failed would report an error word, not hang.  With one exchange lane this
+// has held in every run; with four, launched eagerly on more streams than the device has
+// hardware queues, bounded waits did run out on 8 GPUs -- hence the default of one.)  Every other op continues
 // the lane of one of its dependencies when that dependency is the lane's last op, and otherwise
 // takes the lane that has been idle longest.
 #include <cuda_runtime.h>
@@ -85,6 +92,8 @@ struct es_b200_program {
     bool                     finalized = false;
     int                      n_lanes = 0;
     bool                     has_spin = false;
+    int                      exchange_lanes = 1; // lanes shared by the ops that wait for a peer
+    int                      n_exchange = 0;     // how many of them the schedule uses
     uint32_t                 limit_ms = 0;
     std::vector<cudaStream_t> lanes;
     std::vector<cudaEvent_t>  events; // one per op that some other lane waits for
@@ -149,8 +158,10 @@ void schedule(es_b200_program* p, int max_lanes)
     int   n = (int)ops.size();
     p->has_spin = false;
     for (auto const& op : ops) p->has_spin = p->has_spin || is_spin(op);
-    int first_compute = p->has_spin ? 1 : 0;
+    int first_compute = p->has_spin ? std::max(p->exchange_lanes, 1) : 0;
     int n_lanes = std::max(max_lanes, 1) + first_compute;
+    int n_spin = 0;
+    p->n_exchange = first_compute;
     std::vector<int> tail(n_lanes, -1);
     // known[l][m]: the highest op index of lane m known to be complete when lane l's next op starts
     std::vector<std::vector<int>> known(n_lanes, std::vector<int>(n_lanes, -1));
@@ -160,7 +171,7 @@ void schedule(es_b200_program* p, int max_lanes)
         op_t& op = ops[i];
         int   lane = -1;
         if (is_spin(op)) {
-            lane = 0;
+            lane = n_spin++ % first_compute; // round robin, so that every exchange lane is in program order
         } else {
             int best = -1;
             for (int d : op.deps) {
@@ -713,6 +724,15 @@ int es_b200_program_set_workspace(es_b200_program_t* p, void* workspace, uint64_
     });
 }
 
+int es_b200_program_set_exchange_lanes(es_b200_program_t* p, int lanes)
+{
+    return guarded([&] {
+        check_program(p, false);
+        if (lanes < 1 || lanes > 4) fail(ES_BAD_ARGUMENT, "program: 1 to 4 exchange lanes");
+        p->exchange_lanes = lanes;
+    });
+}
+
 int es_b200_program_set_wait_limit(es_b200_program_t* p, uint32_t limit_ms)
 {
     return guarded([&] {
@@ -813,7 +833,7 @@ int es_b200_program_describe(es_b200_program_t* p, char* buf, int buf_len, int* 
     return guarded([&] {
         check_program(p, true);
         std::ostringstream os;
-        os << "{\"n_lanes\": " << p->n_lanes << ", \"workspace_bytes\": " << p->ws_total << ", \"ops\": [";
+        os << "{\"n_lanes\": " << p->n_lanes << ", \"n_exchange_lanes\": " << p->n_exchange << ", \"workspace_bytes\": " << p->ws_total << ", \"ops\": [";
         for (size_t i = 0; i != p->ops.size(); ++i) {
             op_t const& op = p->ops[i];
             os << (i ? ", " : "") << "{\"kind\": \"" << OP_NAMES[op.kind] << "\", \"lane\": " << op.lane

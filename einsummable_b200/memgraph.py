@@ -344,7 +344,7 @@ def order_units_by_simulation(mg, world, rank):
 
 class memgraph_runner_t:
     def __init__(self, mg, devices=None, rank=None, world=None, transport="nccl", wait_limit_ms=0, fuse=False,
-                 schedule="dag", max_lanes=0, order="simulated"):
+                 schedule="dag", max_lanes=0, order="simulated", exchange_lanes=1):
         """transport (one process per GPU only): "nccl" = send/recv pairs; "p2p" = every
         location buffer lives in symmetric memory, the destination rank pulls the bytes over
         NVLink with an SM copy kernel, and the two ranks hand-shake through bounded flag
@@ -364,6 +364,7 @@ class memgraph_runner_t:
         if self.schedule not in ("dag", "list"):
             raise ValueError("schedule must be 'dag' or 'list'")
         self.max_lanes = max_lanes
+        self.exchange_lanes = exchange_lanes
         # order of the ops of one process per GPU: "simulated" = by the start times of a simulation of
         # all ranks (order_units_by_simulation), "memgraph" = the memgraph's node order
         self.order = order
@@ -518,6 +519,7 @@ class memgraph_runner_t:
                 self.unit_labels.append(("wait", str(len(u["moves"]))))
             else:
                 raise ValueError(kind)
+        prog.set_exchange_lanes(self.exchange_lanes)
         need = prog.finalize(self.max_lanes)
         self.workspace = {dev: (torch.empty(max(need, 256), dtype=torch.uint8, device="cuda:%d" % dev), need)}
         prog.set_workspace(self.workspace[dev][0], max(need, 256))

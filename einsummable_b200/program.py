@@ -144,6 +144,10 @@ class program_t:
         self._keep.append(workspace)
         _lib.check(self._lib.es_b200_program_set_workspace(self._p, _ptr(workspace), int(nbytes)))
 
+    def set_exchange_lanes(self, lanes):
+        """Before finalize: the number of lanes the pull / wait ops share (1..4, default 1)."""
+        _lib.check(self._lib.es_b200_program_set_exchange_lanes(self._p, int(lanes)))
+
     def set_wait_limit(self, limit_ms):
         _lib.check(self._lib.es_b200_program_set_wait_limit(self._p, int(limit_ms)))
 

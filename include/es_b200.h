@@ -298,8 +298,8 @@ int es_b200_query_work(es_b200_t* h, uint64_t bytes[4], uint64_t* contraction_fl
  * waits for its local ready flag to reach it, copies over NVLink and then stores it into the
  * done flag in the source rank's memory, `wait` waits for local (done) flags to reach it.
  * All ranks must therefore run their programs the same number of times.  Ops that wait for a
- * peer (pull, wait) are issued on one lane in program order: add them in the same global order
- * on every rank.  Waits are bounded (es_b200_program_set_wait_limit, default 2000 ms): on
+ * peer (pull, wait) are issued on a few lanes of their own, each in program order: add them in
+ * one global order on every rank, along which every dependency points forward.  Waits are bounded (es_b200_program_set_wait_limit, default 2000 ms): on
  * expiry the kernel records a code in bits 8..15 of es_b200_device_status (3 = pull, 4 = wait)
  * and the schedule carries on; nothing traps. */
 typedef struct es_b200_program es_b200_program_t;
@@ -355,6 +355,11 @@ int es_b200_program_add_wait(es_b200_program_t* p, void* const* flags, int n,
 int es_b200_program_finalize(es_b200_program_t* p, int max_lanes, uint64_t* workspace_bytes);
 int es_b200_program_set_workspace(es_b200_program_t* p, void* workspace, uint64_t bytes);
 int es_b200_program_set_wait_limit(es_b200_program_t* p, uint32_t limit_ms);
+/* Before finalize: how many lanes the pull / wait ops share (1..4, default 1; round robin in
+ * program order).  More lanes let exchanges that arrive out of the expected order overtake, but
+ * put more kernels that spin on a peer's flag in flight at once: with 4, launched eagerly on more
+ * streams than the GPU has hardware queues, bounded waits have run out on an 8-GPU box. */
+int es_b200_program_set_exchange_lanes(es_b200_program_t* p, int lanes);
 
 /* One run, asynchronous: everything is ordered after the work already on `stream`, and
  * `stream` continues only when every op has finished. */

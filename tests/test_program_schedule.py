@@ -36,7 +36,7 @@ def ptr(loc, off):
     return (loc + 1) * BASE + off
 
 
-def plan(mg, owned, exchange, max_lanes=8, order="memgraph"):
+def plan(mg, owned, exchange, max_lanes=8, order="memgraph", exchange_lanes=1):
     """(units, described schedule) of the program a runner would build for `owned`; order
     "simulated": the units of one rank sorted by the start times of the all-rank simulation."""
     nodes = mg["nodes"]
@@ -79,6 +79,7 @@ def plan(mg, owned, exchange, max_lanes=8, order="memgraph"):
                             flag(nodes[m]["dst_loc"], 0, m), flag(nodes[m]["src_loc"], 1, m)) for m in u["moves"]], deps)
         elif k == "wait":
             prog.add_wait([flag(nodes[m]["src_loc"], 1, m) for m in u["moves"]], deps)
+    prog.set_exchange_lanes(exchange_lanes)
     prog.finalize(max_lanes)
     d = prog.describe()
     prog.close()
@@ -207,7 +208,8 @@ def test_per_rank_schedules_order_every_hazard_and_protect_sources(name, world, 
     for rank in range(world):
         units, d = plan(mg, {rank}, True, order=order)
         hb = check_plan(mg, units, d)
-        # pull / wait ops share lane 0, everything else runs elsewhere
+        # pull / wait ops have the exchange lanes to themselves
+        assert d["n_exchange_lanes"] == 1
         for u, op in zip(units, d["ops"]):
             assert (op["lane"] == 0) == (u["kind"] in ("pull", "wait")), (u, op)
         # a source region: written only before its signal or after the acknowledgement
@@ -229,16 +231,17 @@ def test_per_rank_schedules_order_every_hazard_and_protect_sources(name, world, 
                     ("source of move %d written while a peer may read it" % m, units[i])
 
 
+@pytest.mark.parametrize("exchange_lanes", [1, 4])
 @pytest.mark.parametrize("order", ["memgraph", "simulated"])
 @pytest.mark.parametrize("name,world", SMALL + LARGE[1:])
-def test_exchange_never_blocks_over_repeated_runs(name, world, order):
+def test_exchange_never_blocks_over_repeated_runs(name, world, order, exchange_lanes):
     """All ranks' programs executed together with the kernels' semantics: an op starts when the
     op before it on its lane and the ops it waits for have finished; a pull finishes when every
     member's ready flag has reached the rank's run number and then raises the done flags; a wait
     finishes when its done flags have.  Also: a pull only ever sees a flag of its own run."""
     mg = load(name)
     nodes = mg["nodes"]
-    plans = [plan(mg, {r}, True, order=order) for r in range(world)]
+    plans = [plan(mg, {r}, True, order=order, exchange_lanes=exchange_lanes) for r in range(world)]
     ready, done = {}, {}
     for run in range(1, 4):
         finished = [set() for _ in range(world)]
@@ -345,5 +348,5 @@ def test_program_rejects_bad_input():
     with pytest.raises(_lib.es_error):
         p.add_copy(BASE, BASE + 4096, 64)                     # already finalized
     d = p.describe()
-    assert [op["lane"] for op in d["ops"]] == [0, 0] and d["ops"][1]["wait_on"] == []
+    assert [op["lane"] for op in d["ops"]] == [0, 0] and d["ops"][1]["wait_on"] == [] and d["n_exchange_lanes"] == 0
     p.close()
