@@ -88,6 +88,7 @@ SYMBOLS = {
     "es_b200_program_destroy": (_i, [_vp]),
     "es_b200_program_add_einsummable": (_i, [_vp, _u64, _vp, ctypes.POINTER(_vp), _i, _ip, _i, _ip]),
     "es_b200_program_add_touch": (_i, [_vp, _td_p, _i, _i, _i, _vp, _vp, _ip, _i, _ip]),
+    "es_b200_program_add_remote_touch": (_i, [_vp, _td_p, _i, _i, _i, _vp, _vp, _vp, _ip, _i, _ip]),
     "es_b200_program_add_touch_batch": (_i, [_vp, ctypes.POINTER(es_touch_item_t), _i, _i, _ip, _i, _ip]),
     "es_b200_program_add_fill_constant": (_i, [_vp, _i, _vp, _u64, _vp, _ip, _i, _ip]),
     "es_b200_program_add_fill_lowertri": (_i, [_vp, _i, _vp, _vp, _u64, _u64, ctypes.c_int64, _vp, _ip, _i, _ip]),

@@ -6,11 +6,11 @@
 // run increments it.  A flag is a 32-bit word both GPUs can address, zero-initialised, and only
 // ever holds the epoch of the last run in which it was raised:
 //   signal : stores this rank's epoch into the peers' flags (system-scope release; no waiting)
-//   pull   : per move, waits (bounded) until the local "ready" flag has reached this rank's epoch,
-//            copies the bytes from the peer-mapped source into local memory with 128-bit loads,
-//            and the last CTA of the move stores the epoch into the "done" flag in the source
-//            rank's memory
 //   wait   : waits (bounded) until every listed local flag has reached this rank's epoch
+//   pull   : per move, copies the bytes from the peer-mapped source into local memory with 128-bit
+//            loads, and the last CTA of the move stores the epoch into the "done" flag in the source
+//            rank's memory; with a "ready" flag given it first waits (bounded) for that flag itself
+//   (a touch whose input is peer-mapped acknowledges through the same "done" flag: kernels.cu)
 // All ranks run the same number of runs, so their epochs agree.  A wait that exceeds its limit
 // records an error code and carries on; nothing traps and no wait is unbounded.
 #include <cuda_runtime.h>
@@ -93,7 +93,8 @@ __global__ void __launch_bounds__(256) pull_batch_kernel(pull_item_t const* __re
     __shared__ int ok;
     uint32_t const e = *epoch;
     if (threadIdx.x == 0) {
-        bool got = spin_until(it.ready, e, limit_cycles);
+        // ready == null: a wait op in front of this pull has already seen the flag
+        bool got = it.ready == nullptr || spin_until(it.ready, e, limit_cycles);
         if (!got) atomicCAS(&g_exchange_error, 0u, 3u);
         ok = got ? 1 : 0;
     }
@@ -124,7 +125,6 @@ __global__ void __launch_bounds__(256) pull_batch_kernel(pull_item_t const* __re
         uint32_t old = atomicAdd(&counters[blockIdx.y], 1u);
         if (old == it.n_ctas - 1) {
             counters[blockIdx.y] = 0; // ready for the next run
-            __threadfence_system();
             st_release_sys(it.done, e);
         }
     }

@@ -216,6 +216,19 @@ __global__ void __launch_bounds__(TOUCH_BLOCK) touch_kernel(const __grid_constan
 {
     uint32_t slot0 = blockIdx.x * (TOUCH_BLOCK * TOUCH_UNROLL) + threadIdx.x;
     touch_dispatch<W, DT>(a, slot0, TOUCH_BLOCK);
+    if (a.done != nullptr) {
+        // input read from a peer GPU: tell it when the last CTA has finished reading
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence();
+            uint32_t old = atomicAdd(a.counter, 1u);
+            if (old == gridDim.x - 1) {
+                *a.counter = 0;
+                uint32_t e = *a.epoch;
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.done), "r"(e) : "memory");
+            }
+        }
+    }
 }
 
 // many touches; blockIdx.y selects the descriptor in device memory

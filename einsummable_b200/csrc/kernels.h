@@ -31,6 +31,11 @@ struct touch_args_t {
     uint64_t    total_slots;              // n_rows * segs_per_row << seg_shift  (< 2^31)
     int32_t     castable;
     int32_t     pad;
+    // A touch that reads a peer GPU's memory (`inn` peer-mapped) acknowledges the read: the last
+    // CTA to finish stores *epoch into *done (a flag in the source GPU's memory).  Null otherwise.
+    uint32_t*       done;
+    uint32_t*       counter; // CTAs finished so far; returns to zero
+    uint32_t const* epoch;
 };
 
 // Host: simplify (src/einsummable/touch.cc:3-28) + bounds checks + lowering.

@@ -143,7 +143,11 @@ int add_op(es_b200_program* p, op_t&& op, int const* deps, int n_deps, int* inde
 
 bool is_spin(op_t const& op)
 {
-    return op.kind == OP_PULL || op.kind == OP_WAIT;
+    if (op.kind == OP_WAIT) return true;
+    if (op.kind == OP_PULL)
+        for (auto const& it : op.pulls)
+            if (it.ready) return true;
+    return false;
 }
 
 uint64_t round_up(uint64_t v, uint64_t a)
@@ -277,6 +281,8 @@ void upload(es_b200_program* p)
             op.dev_off2 = place(nullptr, op.pulls.size() * sizeof(uint32_t));
         } else if (op.kind == OP_TOUCH_BATCH) {
             op.dev_off = place(op.batch.data(), op.batch.size() * sizeof(touch_args_t));
+        } else if (op.kind == OP_TOUCH && op.touch.done) {
+            op.dev_off = place(nullptr, sizeof(uint32_t));
         }
     }
     p->dev_bytes = round_up(host.size(), 256);
@@ -284,6 +290,12 @@ void upload(es_b200_program* p)
     ES_CUDA_CHECK(cudaMalloc(&p->dev_buf, p->dev_bytes));
     ES_CUDA_CHECK(cudaMemcpy(p->dev_buf, host.data(), p->dev_bytes, cudaMemcpyHostToDevice));
     p->epoch_dev = reinterpret_cast<uint32_t*>(p->dev_buf);
+    for (auto& op : ops) {
+        if (op.kind == OP_TOUCH && op.touch.done) {
+            op.touch.counter = reinterpret_cast<uint32_t*>(p->dev_buf + op.dev_off);
+            op.touch.epoch = p->epoch_dev;
+        }
+    }
 }
 
 void launch_op(es_b200_program* p, op_t const& op, cudaStream_t s)
@@ -495,6 +507,34 @@ int es_b200_program_add_touch(es_b200_program_t*   p,
     });
 }
 
+int es_b200_program_add_remote_touch(es_b200_program_t*   p,
+                                     const es_touchdim_t* dims,
+                                     int                  rank,
+                                     int                  castable,
+                                     int                  dtype,
+                                     void*                out,
+                                     const void*          inn_peer,
+                                     void*                done_flag,
+                                     const int*           deps,
+                                     int                  n_deps,
+                                     int*                 op_index)
+{
+    return guarded([&] {
+        check_program(p, false);
+        if (!done_flag || (reinterpret_cast<uintptr_t>(done_flag) & 3))
+            fail(ES_BAD_ARGUMENT, "program remote touch: null or unaligned flag");
+        op_t op;
+        op.kind = OP_TOUCH;
+        op.dtype = dtype;
+        op.touch_width = prepare_touch(dims, rank, castable, dtype, out, inn_peer, op.touch);
+        op.touch.done = static_cast<uint32_t*>(done_flag);
+        uint64_t n = dtype_size(dtype);
+        for (int i = 0; i != rank; ++i) n *= dims[i].size;
+        op.work_bytes = n * (castable == ES_CASTABLE_NONE ? 2 : 3);
+        add_op(p, std::move(op), deps, n_deps, op_index);
+    });
+}
+
 int es_b200_program_add_fill_constant(es_b200_program_t* p,
                                       int                dtype,
                                       const void*        value8,
@@ -624,8 +664,7 @@ int es_b200_program_add_pull(es_b200_program_t*    p,
         op.max_ctas = 1;
         for (int i = 0; i != n; ++i) {
             es_pull_item_t const& it = items[i];
-            if (!it.src || !it.dst || !it.ready_flag || !it.done_flag)
-                fail(ES_BAD_ARGUMENT, "program pull: null pointer");
+            if (!it.src || !it.dst || !it.done_flag) fail(ES_BAD_ARGUMENT, "program pull: null pointer");
             if ((reinterpret_cast<uintptr_t>(it.src) | reinterpret_cast<uintptr_t>(it.dst)) & 15)
                 fail(ES_BAD_ARGUMENT, "program pull: source and destination must be 16-byte aligned");
             if ((reinterpret_cast<uintptr_t>(it.ready_flag) | reinterpret_cast<uintptr_t>(it.done_flag)) & 3)

@@ -102,19 +102,21 @@ def schedule_units(mg, owned, exchange):
 
     owned: the locations this process drives.  exchange: True when a move between two locations
     is an exchange between two processes (one process per GPU) -- the source rank gets a
-    `signal` unit, the destination rank a `pull` unit, and whatever later reuses the source's
-    memory a `wait` unit for the destination's acknowledgement; False when this process drives
-    both sides and the move is a plain copy.
+    `signal` unit; the destination rank an `await` unit (waits for the signal) followed by a
+    `pull` unit (copies the bytes over and acknowledges), or, when the moved block is read by
+    exactly one touch, by that touch as an `rtouch` unit that reads the peer's memory directly;
+    and whatever later reuses the source's memory a `wait` unit for the acknowledgement.
+    False when this process drives both sides and the move is a plain copy.
 
     Dependencies are the memgraph's edges looked through its bookkeeping nodes (alloc, del,
     inputmem, partialize: src/einsummable/memgraph.h:189-309 -- they launch nothing but carry
-    the "this memory is free again" ordering).  The incoming moves of one run (move_runs) form
-    one pull unit and are served by one launch; the outgoing moves of a run that wait for the
-    same producers share a signal unit.  Touches of one group are chained in node order, the
+    the "this memory is free again" ordering).  The incoming moves of one run (move_runs) share
+    an await unit and a pull unit, each one launch; the outgoing moves of a run that wait for
+    the same producers share a signal unit.  Touches of one group are chained in node order, the
     first being the copy (src/engine/gpu/exec_graph.cc:167-172,368-378).
 
-    Units are dicts: kind in {einsummable, touch, constant, copy, signal, pull, wait}, `deps`
-    (indices of earlier units), `node` or `moves` (memgraph node ids)."""
+    Units are dicts: kind in {einsummable, touch, rtouch, constant, copy, signal, await, pull,
+    wait}, `deps` (indices of earlier units), `node` and / or `moves` (memgraph node ids)."""
     nodes = mg["nodes"]
     owned = set(owned)
     runs = move_runs(mg)
@@ -135,6 +137,26 @@ def schedule_units(mg, owned, exchange):
             closure[n["id"]] = frozenset(acc)
 
     units, unit_of, waited, group_last = [], {}, {}, {}
+
+    # incoming moves whose bytes are read by exactly one touch: the touch reads them in place
+    remote_touch = {}
+    if exchange:
+        users = {}
+        for n in nodes:
+            if n["kind"] in BOOKKEEPING:
+                continue
+            for i in n["inns"]:
+                if is_cross(nodes[i]):
+                    users.setdefault(i, []).append(n["id"])
+        for m, us in users.items():
+            mv = nodes[m]
+            if len(us) == 1 and mv["dst_loc"] in owned:
+                t = nodes[us[0]]
+                if (t["kind"] == "apply" and "touch" in t and t["loc"] == mv["dst_loc"]
+                        and list(t["mems"][1]) == [mv["dst_offset"], mv["size"]]
+                        and sum(1 for i in t["inns"] if is_cross(nodes[i])) == 1):
+                    remote_touch[m] = t["id"]
+    touch_move = {t: m for m, t in remote_touch.items()}
 
     def raw_deps(n, side=None):
         acc = set()
@@ -180,12 +202,18 @@ def schedule_units(mg, owned, exchange):
             if n["dst_loc"] in owned and nid not in unit_of:
                 members = [m for m in run if nodes[m]["dst_loc"] in owned and nodes[m]["dst_loc"] == n["dst_loc"]
                            and is_cross(nodes[m])]
-                raw = set()
+                aw = emit({"kind": "await", "moves": members, "deps": [], "loc": n["dst_loc"]})
+                copied = [m for m in members if m not in remote_touch]
                 for m in members:
-                    raw |= raw_deps(nodes[m], nodes[m]["dst_loc"])
-                idx = emit({"kind": "pull", "moves": members, "deps": resolve(raw), "loc": n["dst_loc"]})
-                for m in members:
-                    unit_of[m] = idx
+                    unit_of[m] = aw
+                if copied:
+                    raw = set()
+                    for m in copied:
+                        raw |= raw_deps(nodes[m], nodes[m]["dst_loc"])
+                    deps = resolve(raw)      # may put a wait unit in front
+                    idx = emit({"kind": "pull", "moves": copied, "deps": sorted(set(deps) | {aw}), "loc": n["dst_loc"]})
+                    for m in copied:
+                        unit_of[m] = idx
             if n["src_loc"] in owned and ("signal", nid) not in unit_of:
                 members = [m for m in run if nodes[m]["src_loc"] == n["src_loc"] and is_cross(nodes[m])]
                 by_deps = {}
@@ -207,7 +235,11 @@ def schedule_units(mg, owned, exchange):
                 first = key not in group_last
                 if not first:
                     deps = sorted(set(deps) | {group_last[key]})
-            idx = emit({"kind": "touch", "node": nid, "deps": deps, "first": first, "loc": loc})
+            if nid in touch_move:
+                idx = emit({"kind": "rtouch", "node": nid, "moves": [touch_move[nid]], "deps": deps, "first": first,
+                            "loc": loc})
+            else:
+                idx = emit({"kind": "touch", "node": nid, "deps": deps, "first": first, "loc": loc})
             if n["group"] >= 0:
                 group_last[(loc, n["group"])] = idx
         elif kind == "apply":
@@ -249,6 +281,10 @@ def unit_cost_us(mg, u):
     if k == "touch":
         n = nodes[u["node"]]
         return 2.5, n["mems"][1][1] * (2 if u["first"] else 3) / 4.5e6, "gpu"
+    if k == "rtouch":
+        return 6.0, nodes[u["node"]]["mems"][1][1] / 0.65e6, "link"
+    if k == "await":
+        return 3.0, 0.0, None
     if k == "constant":
         return 2.5, 0.5, "gpu"
     if k == "copy":
@@ -256,7 +292,7 @@ def unit_cost_us(mg, u):
     if k == "signal":
         return 3.0, 0.0, None
     if k == "pull":
-        return 3.0, sum(nodes[m]["size"] for m in u["moves"]) / 0.65e6, "link"
+        return 6.0, sum(nodes[m]["size"] for m in u["moves"]) / 0.65e6, "link"
     if k == "wait":
         return 2.0, 0.0, None
     raise ValueError(k)
@@ -264,8 +300,8 @@ def unit_cost_us(mg, u):
 
 def simulate_schedule(mg, units_by_rank):
     """Start and finish time (us) of every unit of every rank under a simple machine model: a unit
-    becomes ready when its dependencies -- and, for a pull, the source ranks' signals; for a wait, the
-    destination ranks' pulls -- have finished; ready units are served first come first served; each
+    becomes ready when its dependencies -- and, for an await, the source ranks' signals; for a wait, the
+    destination ranks' pulls or remote touches -- have finished; ready units are served first come first served; each
     rank's GPU and each rank's incoming link do one unit's work at a time, launch latencies overlap.
     Deterministic (ties by rank and index), so every rank that runs it gets the same answer.
     Returns {(rank, index): (start, finish)}."""
@@ -276,14 +312,14 @@ def simulate_schedule(mg, units_by_rank):
             if u["kind"] == "signal":
                 for m in u["moves"]:
                     sig_of[m] = (r, i)
-            elif u["kind"] == "pull":
+            elif u["kind"] in ("pull", "rtouch"):
                 for m in u["moves"]:
                     pull_of[m] = (r, i)
     preds, succs, cost = {}, {}, {}
     for r, units in enumerate(units_by_rank):
         for i, u in enumerate(units):
             p = [(r, d) for d in u["deps"]]
-            if u["kind"] == "pull":
+            if u["kind"] == "await":
                 p += [sig_of[m] for m in u["moves"]]
             elif u["kind"] == "wait":
                 p += [pull_of[m] for m in u["moves"]]
@@ -463,15 +499,24 @@ class memgraph_runner_t:
                 kk = km.kernel_info(e).split("|")[0]
                 self.unit_labels.append(("contraction" if kk.startswith("contraction") else
                                          ("reduction" if e.has_aggregation() else "elementwise"), repr(e)))
-            elif kind == "touch":
+            elif kind in ("touch", "rtouch"):
                 node = nodes[u["node"]]
                 d = node["touch"]
                 t = touch_t(d["selection"], d["castable"], d["dtype"])
                 loc = node["loc"]
                 offs = [m[0] for m in node["mems"]]
-                prog.add_touch(t, None if u["first"] else d["castable"], self.ptr(loc, offs[0]), self.ptr(loc, offs[1]), deps)
+                if kind == "rtouch":
+                    mv = nodes[u["moves"][0]]
+                    prog.add_touch(t, None if u["first"] else d["castable"], self.ptr(loc, offs[0]),
+                                   self.peer_base[mv["src_loc"]] + mv["src_offset"], deps,
+                                   done_flag=self._flag_ptr(mv["src_loc"], 1, self.move_index[mv["id"]]))
+                    self.stats["move"] += 1
+                    self.stats["move_bytes"] += mv["size"]
+                else:
+                    prog.add_touch(t, None if u["first"] else d["castable"], self.ptr(loc, offs[0]),
+                                   self.ptr(loc, offs[1]), deps)
                 self.stats["touch"] += 1
-                self.unit_labels.append(("touch", "%s %s" % (d["castable"], d["dtype"])))
+                self.unit_labels.append((kind, "%s %s %d bytes" % (d["castable"], d["dtype"], node["mems"][1][1])))
             elif kind == "constant":
                 node = nodes[u["node"]]
                 f = node["fill"]
@@ -509,11 +554,14 @@ class memgraph_runner_t:
                     k = self.move_index[m]
                     items.append((self.peer_base[node["src_loc"]] + node["src_offset"],
                                   self.ptr(node["dst_loc"], node["dst_offset"]), node["size"],
-                                  self._flag_ptr(node["dst_loc"], 0, k), self._flag_ptr(node["src_loc"], 1, k)))
+                                  None, self._flag_ptr(node["src_loc"], 1, k)))
                 prog.add_pull(items, deps)
                 self.stats["move"] += len(items)
                 self.stats["move_bytes"] += sum(it[2] for it in items)
                 self.unit_labels.append(("pull", "%d moves %d bytes" % (len(items), sum(it[2] for it in items))))
+            elif kind == "await":
+                prog.add_wait([self._flag_ptr(nodes[m]["dst_loc"], 0, self.move_index[m]) for m in u["moves"]], deps)
+                self.unit_labels.append(("await", str(len(u["moves"]))))
             elif kind == "wait":
                 prog.add_wait([self._flag_ptr(nodes[m]["src_loc"], 1, self.move_index[m]) for m in u["moves"]], deps)
                 self.unit_labels.append(("wait", str(len(u["moves"]))))
@@ -529,8 +577,8 @@ class memgraph_runner_t:
         self.program = self.units
 
     def profile(self, stream=None):
-        """One run with a CUDA event pair around every op: [(class, label, milliseconds)].  For pull
-        and wait ops the time includes waiting for the peer."""
+        """One run with a CUDA event pair around every op: [(class, label, milliseconds)].  For await
+        and wait ops the time is time spent waiting for the peer."""
         if self.prog is None:
             raise RuntimeError("profile needs the dag schedule")
         ms = self.prog.launch_timed(stream if stream is not None else torch.cuda.current_stream())
@@ -554,7 +602,7 @@ class memgraph_runner_t:
             v = by.setdefault(c, [0, 0.0])
             v[0] += 1
             v[1] += b - a
-        spin = ("pull", "wait")
+        spin = ("await", "wait")
         iv = sorted((a, b) for c, _, a, b in tl if c not in spin)
         busy, cur_a, cur_b = 0.0, None, None
         for a, b in iv:

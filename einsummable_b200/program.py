@@ -58,9 +58,16 @@ class program_t:
             self._p, int(kernel_id), _ptr(out), arr, len(inns), d, nd, ctypes.byref(idx)))
         return self._added(idx)
 
-    def add_touch(self, t, castable, out, inn, deps=()):
+    def add_touch(self, t, castable, out, inn, deps=(), done_flag=None):
+        """done_flag given: `inn` is peer-mapped memory (a move consumed in place); the last CTA
+        raises the flag in the source rank's memory once the input has been read."""
         d, nd = _deps(deps)
         idx = ctypes.c_int(-1)
+        if done_flag is not None:
+            _lib.check(self._lib.es_b200_program_add_remote_touch(
+                self._p, t.c_dims(), len(t.selection), CASTABLE_CODE[castable], DTYPE_CODE[t.dtype],
+                _ptr(out), _ptr(inn), int(done_flag), d, nd, ctypes.byref(idx)))
+            return self._added(idx)
         _lib.check(self._lib.es_b200_program_add_touch(
             self._p, t.c_dims(), len(t.selection), CASTABLE_CODE[castable], DTYPE_CODE[t.dtype],
             _ptr(out), _ptr(inn), d, nd, ctypes.byref(idx)))
@@ -125,10 +132,10 @@ class program_t:
         return self._flag_op(self._lib.es_b200_program_add_wait, flags, deps)
 
     def add_pull(self, items, deps=()):
-        """items: (src, dst, nbytes, ready_flag, done_flag) per move; one launch for all."""
+        """items: (src, dst, nbytes, ready_flag or None, done_flag) per move; one launch for all."""
         arr = (_lib.es_pull_item_t * len(items))()
         for i, (src, dst, nbytes, ready, done) in enumerate(items):
-            arr[i] = _lib.es_pull_item_t(int(src), int(dst), int(nbytes), int(ready), int(done))
+            arr[i] = _lib.es_pull_item_t(int(src), int(dst), int(nbytes), int(ready) if ready else None, int(done))
         d, nd = _deps(deps)
         idx = ctypes.c_int(-1)
         _lib.check(self._lib.es_b200_program_add_pull(self._p, arr, len(items), d, nd, ctypes.byref(idx)))

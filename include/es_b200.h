@@ -294,9 +294,10 @@ int es_b200_query_work(es_b200_t* h, uint64_t bytes[4], uint64_t* contraction_fl
  * Exchange between processes that each drive one GPU (no counterpart in the reference, whose
  * one process copies between its GPUs directly, src/engine/gpu/exec_graph.cc:406-467): flags
  * are zero-initialised 32-bit words both GPUs can address.  Every run of a program increments
- * the program's own run counter; `signal` stores it into flags in the peers' memory, `pull`
- * waits for its local ready flag to reach it, copies over NVLink and then stores it into the
- * done flag in the source rank's memory, `wait` waits for local (done) flags to reach it.
+ * the program's own run counter; `signal` stores it into flags in the peers' memory, `wait`
+ * waits for local flags (a move's ready flag, or the done flags of moves this rank sent) to
+ * reach it, `pull` copies over NVLink and then stores it into the done flag in the source
+ * rank's memory (a remote touch does the same after reading its input).
  * All ranks must therefore run their programs the same number of times.  Ops that wait for a
  * peer (pull, wait) are issued on a few lanes of their own, each in program order: add them in
  * one global order on every rank, along which every dependency points forward.  Waits are bounded (es_b200_program_set_wait_limit, default 2000 ms): on
@@ -308,7 +309,9 @@ typedef struct {
     const void* src;        /* peer-mapped source, 16-byte aligned */
     void*       dst;        /* local destination, 16-byte aligned */
     uint64_t    bytes;
-    void*       ready_flag; /* local flag: raised by the source rank's signal */
+    void*       ready_flag; /* local flag raised by the source rank's signal; NULL when a wait op
+                               the pull depends on has already waited for it (then the pull itself
+                               does not wait for a peer and runs on any lane) */
     void*       done_flag;  /* flag in the source rank's memory: raised after the copy */
 } es_pull_item_t;
 
@@ -328,6 +331,13 @@ int es_b200_program_add_einsummable(es_b200_program_t* p, uint64_t kernel_id, vo
 int es_b200_program_add_touch(es_b200_program_t* p, const es_touchdim_t* dims, int rank, int castable,
                               int dtype, void* out, const void* inn,
                               const int* deps, int n_deps, int* op_index);
+/* A touch whose input lies in a peer GPU's memory (move_t followed by the touch that consumes it,
+ * src/engine/gpu/exec_graph.cc:354-467, as one kernel: the bytes cross NVLink once, straight into
+ * the region they belong to).  A wait op among `deps` must have seen the move's ready flag; the
+ * last CTA raises `done_flag` (in the source rank's memory) when the input has been read. */
+int es_b200_program_add_remote_touch(es_b200_program_t* p, const es_touchdim_t* dims, int rank, int castable,
+                                     int dtype, void* out, const void* inn_peer, void* done_flag,
+                                     const int* deps, int n_deps, int* op_index);
 /* Many touches of one dtype whose destinations do not overlap, as one launch. */
 int es_b200_program_add_touch_batch(es_b200_program_t* p, const es_touch_item_t* items, int n, int dtype,
                                     const int* deps, int n_deps, int* op_index);

@@ -10,8 +10,8 @@ assigns them to lanes and decides which events each op waits for.  Checked on th
     hazard, including the reuse of freed memory;
   * exchange between ranks: a source region is not written between its `signal` and the
     acknowledgement `wait`; simulated over repeated runs with the kernels' semantics (run
-    counters in the flags, pull/wait ops on one in-order lane) no rank ever blocks for good, and
-    every pull reads what the source rank signalled in that very run.
+    counters in the flags, the ops that wait for a peer on one in-order lane) no rank ever blocks
+    for good, and every pull or in-place touch reads what the source rank signalled in that very run.
 """
 import os
 
@@ -58,12 +58,17 @@ def plan(mg, owned, exchange, max_lanes=8, order="memgraph", exchange_lanes=1):
             n = nodes[u["node"]]
             offs = [m[0] for m in n["mems"]]
             prog.add_einsummable(0, ptr(n["loc"], offs[0]), [ptr(n["loc"], o) for o in offs[1:]], deps)
-        elif k == "touch":
+        elif k in ("touch", "rtouch"):
             n = nodes[u["node"]]
             d = n["touch"]
             t = touch_t(d["selection"], d["castable"], d["dtype"])
-            prog.add_touch(t, None if u["first"] else d["castable"], ptr(n["loc"], n["mems"][0][0]),
-                           ptr(n["loc"], n["mems"][1][0]), deps)
+            if k == "rtouch":
+                m = nodes[u["moves"][0]]
+                prog.add_touch(t, None if u["first"] else d["castable"], ptr(n["loc"], n["mems"][0][0]),
+                               ptr(m["src_loc"], m["src_offset"]), deps, done_flag=flag(m["src_loc"], 1, m["id"]))
+            else:
+                prog.add_touch(t, None if u["first"] else d["castable"], ptr(n["loc"], n["mems"][0][0]),
+                               ptr(n["loc"], n["mems"][1][0]), deps)
         elif k == "constant":
             n = nodes[u["node"]]
             prog.add_copy(ptr(n["loc"], 0), ptr(n["loc"], n["offset"]), 16, deps)   # stand-in op, same deps
@@ -73,10 +78,12 @@ def plan(mg, owned, exchange, max_lanes=8, order="memgraph", exchange_lanes=1):
             prog.add_copy(ptr(s, n["src_offset"]), ptr(d, n["dst_offset"]), n["size"], deps)
         elif k == "signal":
             prog.add_signal([flag(nodes[m]["dst_loc"], 0, m) for m in u["moves"]], deps)
+        elif k == "await":
+            prog.add_wait([flag(nodes[m]["dst_loc"], 0, m) for m in u["moves"]], deps)
         elif k == "pull":
             prog.add_pull([(ptr(nodes[m]["src_loc"], nodes[m]["src_offset"]),
                             ptr(nodes[m]["dst_loc"], nodes[m]["dst_offset"]), nodes[m]["size"],
-                            flag(nodes[m]["dst_loc"], 0, m), flag(nodes[m]["src_loc"], 1, m)) for m in u["moves"]], deps)
+                            None, flag(nodes[m]["src_loc"], 1, m)) for m in u["moves"]], deps)
         elif k == "wait":
             prog.add_wait([flag(nodes[m]["src_loc"], 1, m) for m in u["moves"]], deps)
     prog.set_exchange_lanes(exchange_lanes)
@@ -113,12 +120,13 @@ def regions(mg, u):
         mems = n["mems"]
         return ([(n["loc"], m[0], m[0] + m[1], None) for m in mems[1:]],
                 [(n["loc"], mems[0][0], mems[0][0] + mems[0][1], None)])
-    if k == "touch":
+    if k in ("touch", "rtouch"):
         n = nodes[u["node"]]
         mems, sel = n["mems"], n["touch"]["selection"]
         box = ((n["loc"], mems[0][0], tuple(s[1] for s in sel)), tuple((s[3], s[4]) for s in sel))
         out = (n["loc"], mems[0][0], mems[0][0] + mems[0][1], box)
-        reads = [(n["loc"], mems[1][0], mems[1][0] + mems[1][1], None)]
+        # an rtouch reads the source rank's memory (guarded by the signal / acknowledgement pair)
+        reads = [(n["loc"], mems[1][0], mems[1][0] + mems[1][1], None)] if k == "touch" else []
         if not u["first"]:
             reads.append(out)
         return reads, [out]
@@ -208,10 +216,10 @@ def test_per_rank_schedules_order_every_hazard_and_protect_sources(name, world, 
     for rank in range(world):
         units, d = plan(mg, {rank}, True, order=order)
         hb = check_plan(mg, units, d)
-        # pull / wait ops have the exchange lanes to themselves
+        # the ops that wait for a peer have the exchange lane to themselves
         assert d["n_exchange_lanes"] == 1
         for u, op in zip(units, d["ops"]):
-            assert (op["lane"] == 0) == (u["kind"] in ("pull", "wait")), (u, op)
+            assert (op["lane"] == 0) == (u["kind"] in ("await", "wait")), (u, op)
         # a source region: written only before its signal or after the acknowledgement
         sig, ack = {}, {}
         for i, u in enumerate(units):
@@ -262,10 +270,12 @@ def test_exchange_never_blocks_over_repeated_runs(name, world, order, exchange_l
                         if not all(w in finished[r] for w in d["ops"][i]["wait_on"]):
                             break
                         u = units[i]
-                        if u["kind"] == "pull":
+                        if u["kind"] == "await":
                             if not all(ready.get(m, 0) >= run for m in u["moves"]):
                                 break
-                            assert all(ready[m] == run for m in u["moves"]), "a pull saw a flag of another run"
+                            assert all(ready[m] == run for m in u["moves"]), "an await saw a flag of another run"
+                        elif u["kind"] in ("pull", "rtouch"):
+                            assert all(ready.get(m, 0) == run for m in u["moves"]), "bytes read before their signal"
                             for m in u["moves"]:
                                 done[m] = run
                         elif u["kind"] == "wait":
@@ -290,13 +300,18 @@ def test_exchange_ops_come_in_the_same_global_order_on_every_rank():
     mg = load("llama7b_layer_locs8")
     for rank in range(8):
         units = M.schedule_units(mg, {rank}, True)
-        keys = [min(u["moves"]) for u in units if u["kind"] == "pull"]
+        keys = [min(u["moves"]) for u in units if u["kind"] == "await"]
         assert keys == sorted(keys)
         # the incoming moves of one run share a unit; units never mix runs
         runs = M.move_runs(mg)
         for u in units:
-            if u["kind"] == "pull":
+            if u["kind"] in ("await", "pull"):
                 assert len({runs[m] for m in u["moves"]}) == 1
+        # every incoming move is read exactly once: by a pull or by a touch in place
+        read = [m for u in units if u["kind"] in ("pull", "rtouch") for m in u["moves"]]
+        assert sorted(read) == sorted(n["id"] for n in mg["nodes"] if n["kind"] == "move"
+                                      and n["dst_loc"] == rank and n["src_loc"] != rank)
+        assert sum(1 for u in units if u["kind"] == "rtouch") >= 10
 
 
 def test_simulated_order_is_the_same_on_every_rank_and_increases_along_dependencies():
@@ -312,12 +327,12 @@ def test_simulated_order_is_the_same_on_every_rank_and_increases_along_dependenc
         for i, u in enumerate(units):
             if u["kind"] == "signal":
                 sig.update({m: (r, i) for m in u["moves"]})
-            if u["kind"] == "pull":
+            if u["kind"] in ("pull", "rtouch"):
                 pull.update({m: (r, i) for m in u["moves"]})
     for r, units in enumerate(all_units):
         for i, u in enumerate(units):
             before = [(r, d) for d in u["deps"]]
-            if u["kind"] == "pull":
+            if u["kind"] == "await":
                 before += [sig[m] for m in u["moves"]]
             if u["kind"] == "wait":
                 before += [pull[m] for m in u["moves"]]
