@@ -1,20 +1,20 @@
 #!/usr/bin/env python3
-"""Benchmark of the memgraph apply-node kernels on B200.
+"""Benchmark of the B200 execution path for einsummable's memgraph apply nodes.
 
-Workload (N=1): BASELINE config 2 -- f16 tensors x, y of shape [8192, 11008]
-~ N(0,1); one step = one pass of the four einsummables over them, launched
-through the C ABI on one stream:
-    (i)   a,a->a    silu(x) * y
-    (ii)  ab->a     castable max            (row max of x)
-    (iii) ab,a->ab  exp(x - rowmax)
-    (iv)  ab->a     castable add            (row sum of (iii))
-Metric: algorithmic GB/s (inputs + outputs of every op, broadcast inputs at
-their own size) over the whole step.  Under torchrun every rank runs the same
-workload on its own GPU (the path shards by blocks with no data-path
-collective), value = bytes of all ranks / max-over-ranks device time.
+Headline (every N): the LLaMA-7B-shape transformer layer of BASELINE config 4 -- batch 4 x seq 512 =
+2048 tokens, f16, seeded synthetic weights ~ N(0, 0.02) -- executed from the memgraph the reference's
+own compilers produce for N locations (autoplace01), one process per GPU, moves over peer memory.
+One step = one run of that graph (one CUDA-graph replay of the dependency-ordered schedule).
+Metric: tokens/s = 2048 * steps / max-over-ranks device time; "scaling": "strong" (the same layer at
+every N).  The saved `scores` of the timed configuration are checked against the CPU oracle's.
 
-Prints ONE JSON line on rank 0.  `--impl reference` times the CPU restatement of
-the reference's CPU kernels (oracle/es_oracle.c) on the host cores instead.
+Also in the line: `e2e` (the step's input copied from pinned host memory and the result copied back
+inside the timed region), `roofline` of the step's largest kernel plus one fraction per kernel class,
+the BASELINE config 2 step (elementwise + reductions, GB/s), config 5 training graphs, and at N=1 the
+CPU baseline.  `--impl reference` runs the same layer on the host cores through oracle/cpu_engine.py,
+a restatement of the reference's CPU engine (its MKL executor cannot be built here).
+
+Prints ONE JSON line on rank 0.
 """
 import argparse
 import ctypes
@@ -60,6 +60,16 @@ def set_rows(rows):
     WORKLOAD = "REDUCED (profiling only) f16 [%d,11008]: silu(x)*y; rowmax; exp(x-rowmax); rowsum" % rows
 
 
+def measured_peaks_all():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "kind": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "kind": "fallback"}
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -99,29 +109,59 @@ def cpu_buffers(rows, seed=0):
     return (x, y, np.empty_like(x), np.empty(rows, np.float16), np.empty_like(x), np.empty(rows, np.float16))
 
 
-def cpu_baseline(budget_s=10.0, rows=1024):
-    lib = load_cpu_oracle()
-    bufs = cpu_buffers(rows)
-    cpu_pass(lib, rows, *bufs)  # warm
+def cpu_layer_engine():
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    from cpu_engine import cpu_engine_t
+    mg = load_layer_graph(1)
+    eng = cpu_engine_t(mg, accumulate="f32", threads=os.cpu_count() or 1)
+    for k, v in layer_inputs(mg).items():
+        eng.set_input(k, v)
+    return eng
+
+
+CPU_SAMPLE = ("each step = the whole 1-location layer memgraph (2048 tokens) on the host cores: torch CPU einsum as the "
+              "stand-in for cblas_sgemm, elementwise / reductions / touches with the reference CPU executor's conventions, "
+              "nodes in memgraph order, every kernel on all cores")
+
+
+def cpu_baseline(budget_s=15.0):
+    """The same layer on this box's host cores (oracle/cpu_engine.py), a bounded number of passes."""
+    eng = cpu_layer_engine()
+    eng.run()
     t0 = time.perf_counter()
     passes = 0
     while True:
-        cpu_pass(lib, rows, *bufs)
+        eng.run()
         passes += 1
         dt = time.perf_counter() - t0
-        if dt >= budget_s or passes >= 200:
+        if dt >= budget_s or passes >= 20:
             break
-    res = {
-        "value": cpu_bytes(rows) * passes / dt / 1e9, "unit": "GB/s", "cores": lib.oracle_num_threads(),
-        "kind": "port",
-        "sample": "%d passes over the first %d of %d rows (same 4 ops, OpenMP over row blocks), %.1f s"
-                  % (passes, rows, ROWS, dt),
-    }
+    res = {"value": LAYER_TOKENS * passes / dt, "unit": "tokens/s", "cores": eng.threads, "kind": "port",
+           "sample": "%d passes, %.1f s; %s" % (passes, dt, CPU_SAMPLE),
+           "contraction_TFLOP/s": eng.flops / (dt / passes) / 1e12}
     try:
-        res["other_classes"] = cpu_other_classes(lib)
+        lib = load_cpu_oracle()
+        other = cpu_other_classes(lib)
+        sys.stderr.write("CPU port, other classes:\n%s\n" % json.dumps(other, indent=1))
+        res["c2_step_GB/s"] = cpu_c2(lib)
     except Exception as exc:  # reported, never hidden
-        res["other_classes"] = {"error": repr(exc)[:200]}
+        res["other_error"] = repr(exc)[:200]
     return res
+
+
+def cpu_c2(lib, budget_s=4.0):
+    """BASELINE config 2 (all 8192 rows) through the C port's loops on the host cores."""
+    bufs = cpu_buffers(ROWS)
+    cpu_pass(lib, ROWS, *bufs)
+    t0 = time.perf_counter()
+    passes = 0
+    while True:
+        cpu_pass(lib, ROWS, *bufs)
+        passes += 1
+        dt = time.perf_counter() - t0
+        if dt >= budget_s:
+            break
+    return round(cpu_bytes(ROWS) * passes / dt / 1e9, 2)
 
 
 def cpu_other_classes(lib):
@@ -168,32 +208,33 @@ def cpu_other_classes(lib):
 
 
 def run_reference_arm(args):
-    """The reference's CPU implementation of the path on the host cores.  The
-    reference's MKL executor cannot be built here (no MKL; merge-conflict markers
-    in src/engine/cpu/kernel_executor.cc:1323-1445), so this is the C port of its
-    loops; each step is one pass over a bounded sample of the workload."""
+    """The reference's CPU implementation of the path on the host cores, same workload as the GPU
+    arm: the whole layer memgraph per step.  The reference's MKL executor cannot be built here (no
+    MKL; merge-conflict markers in src/engine/cpu/kernel_executor.cc:1323-1445), so this is the
+    restatement in oracle/cpu_engine.py.  Under torchrun rank 0 alone runs it."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    rows = 1024
-    lib = load_cpu_oracle()
-    bufs = cpu_buffers(rows)
-    for _ in range(args.warmup):
-        cpu_pass(lib, rows, *bufs)
+    eng = cpu_layer_engine()          # sets the thread count explicitly (torchrun exports OMP_NUM_THREADS=1)
+    for _ in range(max(1, min(args.warmup, 2))):
+        eng.run()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        cpu_pass(lib, rows, *bufs)
+        eng.run()
     dt = time.perf_counter() - t0
-    value = cpu_bytes(rows) * args.steps / dt / 1e9
-    cores = lib.oracle_num_threads()
-    sample = "each step = one pass over the first %d of %d rows (same 4 ops)" % (rows, ROWS)
+    value = LAYER_TOKENS * args.steps / dt
+    want = golden_scores()
+    got = eng.get_output("scores").astype(np.float64)
+    parity = None if want is None else float(np.abs(got - want).max() / np.abs(want).max())
     print(json.dumps({
-        "impl": "reference", "metric": "elementwise+reduction algorithmic GB/s", "value": value, "unit": "GB/s",
+        "impl": "reference", "metric": "LLaMA-7B layer tokens/s", "value": value, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "sample": sample},
-        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
-        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32 math on f16 tensors",
+        "data": "synthetic",
+        "config": {"workload": LAYER_WORKLOAD, "tokens_per_step": LAYER_TOKENS, "sample": CPU_SAMPLE},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": eng.threads, "kind": "port", "sample": CPU_SAMPLE},
+        "parity": {"max_abs_err_over_max_abs_vs_f64_oracle": parity},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
 
@@ -257,21 +298,336 @@ class ClockSampler:
 # --------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------
+LAYER_FIXTURE = "llama7b_layer"
+LAYER_WORKLOAD = ("C4 LLaMA-7B-shape transformer layer forward (dim 4096, 32 heads x 128, FFN 11008 SwiGLU, RMSNorm, "
+                  "RoPE, causal attention, last-token vocabulary projection), batch 4 x seq 512 = 2048 tokens, f16, "
+                  "the reference's memgraph for N locations (autoplace01)")
+LAYER_TOKENS = 2048
+
+
+def layer_inputs(mg):
+    """Seeded synthetic inputs of the layer graph (the same on every rank and in the golden fixture)."""
+    from einsummable_b200.memgraph import synthetic_llama_inputs
+    return synthetic_llama_inputs(mg, seed=7)
+
+
+def load_layer_graph(world, fixture=LAYER_FIXTURE):
+    from einsummable_b200.memgraph import load_memgraph
+    path = os.path.join(ROOT, "tests", "golden", "graphs", "%s_locs%d.json.gz" % (fixture, world))
+    if not os.path.exists(path):
+        raise RuntimeError("no memgraph fixture of %s for %d locations" % (fixture, world))
+    return load_memgraph(path)
+
+
+def golden_scores():
+    """`scores` of the layer for layer_inputs(), computed once by the CPU oracle with f64 accumulation
+    (tests/golden/make_c4_full.py) and committed; None when the fixture is missing."""
+    path = os.path.join(ROOT, "tests", "golden", "c4_full.npz")
+    if not os.path.exists(path):
+        return None
+    return np.load(path)["scores"].astype(np.float64)
+
+
+class Ranks:
+    """torch.distributed plumbing of the bench: barrier, max over ranks, sum of a result."""
+    def __init__(self):
+        import torch
+        self.torch = torch
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        # the exchange uses plain peer loads and flags: no NVLink multicast objects, neither NCCL's nor
+        # symmetric memory's (a rank that dies while bound to one disturbs the others)
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        torch.cuda.set_device(self.local)
+        self.dev = torch.device("cuda", self.local)
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.init_process_group("nccl", device_id=self.dev)
+            self.dist = dist
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize(self.dev)
+
+    def max(self, v):
+        if self.world == 1:
+            return v
+        t = self.torch.tensor([v], dtype=self.torch.float64, device=self.dev)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def sum_array(self, a):
+        if self.world == 1:
+            return a
+        t = self.torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(self.dev)
+        self.dist.all_reduce(t)
+        return t.cpu().numpy()
+
+    def close(self):
+        if self.world > 1:
+            self.dist.barrier()
+            self.dist.destroy_process_group()
+
+
+def timed_steps(rk, stream, fn, steps):
+    """ms per step of `steps` calls of fn: CUDA events on the launching stream, a barrier and a
+    synchronise on both sides, max over ranks."""
+    torch = rk.torch
+    rk.barrier()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record(stream)
+    for _ in range(steps):
+        fn()
+    e.record(stream)
+    rk.barrier()
+    return rk.max(s.elapsed_time(e)) / steps
+
+
+def make_runner(rk, mg, fuse, **kw):
+    from einsummable_b200.memgraph import memgraph_runner_t
+    if rk.world > 1:
+        transport = os.environ.get("ES_B200_MOVE_TRANSPORT", "p2p")
+        return memgraph_runner_t(mg, rank=rk.rank, world=rk.world, transport=transport, fuse=fuse,
+                                 wait_limit_ms=int(os.environ.get("ES_B200_WAIT_LIMIT_MS", "2000")), **kw)
+    return memgraph_runner_t(mg, devices=[rk.local], fuse=fuse, **kw)
+
+
+def parity_of(rk, runner, want):
+    """The saved `scores` of all ranks summed (every block has one owner) against the oracle's."""
+    got = rk.sum_array(runner.get_output("scores").astype(np.float32)).astype(np.float64)
+    if want is None:
+        return {"ok": None, "note": "tests/golden/c4_full.npz missing"}
+    scale = float(np.abs(want).max())
+    err = float(np.abs(got - want).max())
+    return {"max_abs_err_over_max_abs": err / scale, "tolerance": 1e-2, "ok": bool(err <= 1e-2 * scale),
+            "against": "CPU oracle, f64-accumulated contractions, same seeded inputs (tests/golden/c4_full.npz)"}
+
+
 def run_gpu(args):
     import torch
     import einsummable_b200 as es
-    from einsummable_b200 import einsummable_t, scalarop_t as S, touch_t
+    rk = Ranks()
+    rank, world, dev = rk.rank, rk.world, rk.dev
+    stream = torch.cuda.current_stream(dev)
+    warmup = max(args.warmup, 3)
+    peaks = measured_peaks_all()
+    want = golden_scores()
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    km = es.kernel_manager_t(local)  # raises if the CUDA library or device is missing
+    # ---------------- headline: the layer graph for `world` locations, one process per GPU ----------------
+    mg = load_layer_graph(world)
+    inputs = layer_inputs(mg)
+    r = make_runner(rk, mg, fuse=True)
+    for k, v in inputs.items():
+        r.set_input(k, v)
+    c0 = r.km(rank if world > 1 else 0).counters()
+    r.run(stream)
+    torch.cuda.synchronize(dev)
+    c1 = r.km(rank if world > 1 else 0).counters()
+    launches_per_step = int(sum(c1[k] - c0[k] for k in c0))
+    ms_eager = timed_steps(rk, stream, lambda: r.run(stream), 5)
+    r.capture()
+    for _ in range(warmup):
+        r.replay(stream)
+    sampler = ClockSampler(rk.local)
+    if rank == 0:
+        sampler.start()
+    t_begin = time.perf_counter()
+    ms = timed_steps(rk, stream, lambda: r.replay(stream), args.steps)
+    t_end = time.perf_counter()
+    clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
+    status = int(rk.max(r.device_status()))
+    parity = parity_of(rk, r, want)
 
+    # the dominant kernel inside the step: the GPU's own timer read before and after every op of one replay
+    tl, run_us = r.timeline(stream)
+    dom = None
+    for (cls, label, a, b), u in zip(tl, r.units):
+        if cls == "contraction":
+            node = mg["nodes"][u["node"]]
+            flops = 2.0 * float(np.prod(node["einsummable"]["join_shape"]))
+            if dom is None or flops > dom["flops"]:
+                dom = {"flops": flops, "us": b - a, "label": label}
+    by_class = {}
+    for cls, _, a, b in tl:
+        by_class[cls] = by_class.get(cls, 0.0) + (b - a)
+
+    # ---------------- end to end: the step's input from pinned host memory, its result back to the host ----------------
+    e2e = e2e_layer(rk, r, mg, inputs, stream, min(max(args.steps, 4), 50))
+
+    # ---------------- the graph as the reference compiled it (nothing folded), and the old list schedule ----------------
+    variants = {}
+    r.close()
+    del r
+    torch.cuda.empty_cache()
+    for name, kw in (("as_compiled", dict(fuse=False)),
+                     ("as_compiled_list_schedule", dict(fuse=False, schedule="list"))):
+        try:
+            if name.endswith("list_schedule") and os.environ.get("ES_B200_BENCH_LIST", "1") == "0":
+                continue
+            rv = make_runner(rk, mg, **kw)
+            for k, v in inputs.items():
+                rv.set_input(k, v)
+            rv.capture()
+            for _ in range(3):
+                rv.replay() if kw.get("schedule") == "list" else rv.replay(stream)
+            msv = timed_steps(rk, stream, (lambda: rv.replay()) if kw.get("schedule") == "list" else (lambda: rv.replay(stream)),
+                              min(args.steps, 50))
+            variants[name] = {"ms": round(msv, 4), "tokens/s": round(LAYER_TOKENS / (msv * 1e-3)),
+                              "parity_ok": parity_of(rk, rv, want)["ok"], "device_status": int(rk.max(rv.device_status()))}
+            rv.graph = None
+            rv.close()
+            del rv
+            torch.cuda.empty_cache()
+        except Exception as exc:  # reported, never hidden
+            variants[name] = {"error": repr(exc)[:200]}
+
+    # ---------------- other legs: rank 0's kernel classes (N=1), the C2 step, config 5 ----------------
+    classes, c2 = {}, None
+    km = es.kernel_manager_t(rk.local)
+    if world == 1:
+        try:
+            c2 = c2_step_leg(km, dev, stream, peaks)
+            classes = class_fractions(other_classes(km, dev, stream), c2, peaks)
+        except Exception as exc:  # reported, never hidden
+            classes = {"error": repr(exc)[:200]}
+        torch.cuda.empty_cache()
+    train = {}
+    if os.environ.get("ES_B200_BENCH_TRAIN", "1") != "0":
+        for name, fixture, runs in (("c5_shape_4layers_2048tok", "llama7b_train_l4", 5),
+                                    ("c5_4layers_8192tok", "llama7b_train_b8s1024_l4", 3)):
+            try:
+                train[name] = train_leg(rk, fixture, runs, stream)
+            except Exception as exc:  # reported, never hidden
+                train[name] = {"error": repr(exc)[:200]}
+    km.close()
+
+    if rank != 0:
+        rk.close()
+        return
+    peak_tc = peaks["bf16_tflops_sustained"]
+    achieved = dom["flops"] / (dom["us"] * 1e-6) / 1e12 if dom else None
+    line = {
+        "metric": "LLaMA-7B layer tokens/s", "value": LAYER_TOKENS / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": LAYER_WORKLOAD, "tokens_per_step": LAYER_TOKENS,
+                   "l2": "weights (405 MB) and activations exceed the 126 MB L2; no flush",
+                   "execution": "one CUDA-graph replay per step (dependency-ordered lanes), elementwise chains "
+                                "folded into their readers; eager %.3f ms" % ms_eager,
+                   "contraction_gflop_per_step": mg["taskgraph"]["contraction_flops"] / 1e9,
+                   "moves_per_step": mg["taskgraph"].get("move"), "move_bytes_per_step": mg["taskgraph"].get("move_bytes"),
+                   "variants": variants},
+        "clocks": clocks,
+        "parity": parity,
+        "device_status": status,
+        "e2e": e2e,
+        "gpu_launches": launches_per_step * args.steps,
+        "roofline": {"bound": "tensor", "kernel": "tcgen05 contraction, largest of the step: " + (dom["label"][:80] if dom else "?"),
+                     "achieved": achieved, "peak": peak_tc, "unit": "TFLOP/s", "frac": achieved / peak_tc if achieved else None,
+                     "peak_kind": peaks["kind"] + " (cuBLAS bf16, sustained: the kernel is timed inside the step)",
+                     "duration_us": dom["us"] if dom else None,
+                     "duration_by": "GPU timer read before and after the op inside one replay of the step's graph",
+                     "traffic": ffn_traffic(dom), "algorithmic_flops_per_launch": dom["flops"] if dom else None,
+                     "step_us_by_class": {k: round(v, 1) for k, v in sorted(by_class.items())},
+                     "classes": classes},
+        "c2_step": c2,
+        "train": train,
+        "cpu_baseline": cpu_baseline() if world == 1 else None,
+    }
+    print(json.dumps(line))
+    rk.close()
+
+
+def ffn_traffic(dom):
+    """dram__bytes_read.sum + dram__bytes_write.sum of one launch of the step's largest contraction, from
+    the committed ncu summary (profiles/traffic.json: kernel label -> bytes); None when not captured."""
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    if dom is None or not os.path.exists(path):
+        return None
+    with open(path) as f:
+        table = json.load(f)
+    for key, val in table.items():
+        if key in dom["label"]:
+            return val
+    return None
+
+
+def e2e_layer(rk, r, mg, inputs, stream, steps):
+    """tokens/s through the public call with host buffers: every step copies the step's input (the
+    token embeddings; the weights are the resident model) from pinned host memory into the location
+    buffers, replays the graph and reads the result (`scores`) back into pinned host memory."""
+    torch = rk.torch
+    name = "embeddings" if any(t["name"] == "embeddings" for t in mg["inputs"]) else mg["inputs"][0]["name"]
+    up = r.stage_input(name, inputs[name])
+    down = r.stage_output("scores")
+    h2d = sum(h.numel() * h.element_size() for h, _ in up)
+    d2h = sum(h.numel() * h.element_size() for h, _ in down)
+
+    def step():
+        for h, d in up:
+            d.copy_(h, non_blocking=True)
+        r.replay(stream)
+        for h, d in down:
+            h.copy_(d, non_blocking=True)
+    for _ in range(3):
+        step()
+    ms = timed_steps(rk, stream, step, steps)
+    tot_h2d, tot_d2h = sum_int(rk, h2d), sum_int(rk, d2h)
+    return {"value": LAYER_TOKENS / (ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": tot_h2d,
+            "d2h_bytes_per_step": tot_d2h, "ms_per_step": ms, "steps": steps,
+            "what": "input `%s` from pinned host memory every step, result `scores` back to pinned host memory; "
+                    "weights stay resident" % name}
+
+
+def sum_int(rk, v):
+    if rk.world == 1:
+        return v
+    t = rk.torch.tensor([float(v)], dtype=rk.torch.float64, device=rk.dev)
+    rk.dist.all_reduce(t)
+    return int(t.item())
+
+
+def train_leg(rk, fixture, runs, stream):
+    """Config 5: four layers forward, the log-softmax loss, backward and the weight update as the
+    reference's trainer builds them (llama/gpu_train.cc:154-322); tokens/s of the CUDA-graph replay."""
+    torch = rk.torch
+    path = os.path.join(ROOT, "tests", "golden", "graphs", "%s_locs%d.json.gz" % (fixture, rk.world))
+    if not os.path.exists(path):
+        return {"skipped": "no memgraph fixture for %d locations" % rk.world}
+    from einsummable_b200.memgraph import load_memgraph
+    mg = load_memgraph(path)
+    need = int(max(mg["mem_sizes"])) + (8 << 30)
+    free = torch.cuda.mem_get_info(rk.dev)[0]
+    if free < need:
+        return {"skipped": "needs %.0f GB of device memory, %.0f GB free" % (need / 1e9, free / 1e9)}
+    tokens = 2048
+    for t in mg["inputs"]:
+        if t["name"] == "embeddings":
+            tokens = int(t["shape"][0]) * int(t["shape"][1])
+    r = make_runner(rk, mg, fuse=True)
+    for k, v in layer_inputs(mg).items():
+        r.set_input(k, v)
+    r.capture()
+    r.replay(stream)
+    ms = timed_steps(rk, stream, lambda: r.replay(stream), runs)
+    out = {"tokens": tokens, "ms": round(ms, 3), "tokens/s": round(tokens / (ms * 1e-3)),
+           "contraction_TFLOP/s": round(mg["taskgraph"]["contraction_flops"] / (ms * 1e-3) / 1e12, 1),
+           "nodes_folded": r.folded, "device_status": int(rk.max(r.device_status()))}
+    r.graph = None
+    r.close()
+    del r
+    torch.cuda.empty_cache()
+    return out
+
+
+def c2_step_leg(km, dev, stream, peaks, steps=20):
+    """BASELINE config 2: f16 [8192,11008] ~ N(0,1); silu(x)*y, row max, exp(x - rowmax), row sum through
+    the C ABI on one stream; algorithmic GB/s of the step and of each kernel (CUDA events between them)."""
+    import torch
+    from einsummable_b200 import einsummable_t, scalarop_t as S
     f16 = "f16"
     e_silu = einsummable_t([ROWS, COLS], [[0, 1], [0, 1]], 2,
                            S.combine(S.make_mul(f16), [S.make_silu(f16), S.make_identity(f16)]))
@@ -282,338 +638,63 @@ def run_gpu(args):
     ws_bytes = max(km.build(e) for e in ops)
     ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
     wsarg = (ws, ws_bytes) if ws_bytes else None
-
     g = torch.Generator(device=dev)
-    g.manual_seed(1234 + rank)
+    g.manual_seed(1234)
     x = torch.randn(N, dtype=torch.float16, device=dev, generator=g)
     y = torch.randn(N, dtype=torch.float16, device=dev, generator=g)
     o_silu = torch.empty(N, dtype=torch.float16, device=dev)
     o_max = torch.empty(ROWS, dtype=torch.float16, device=dev)
     o_exp = torch.empty(N, dtype=torch.float16, device=dev)
     o_sum = torch.empty(ROWS, dtype=torch.float16, device=dev)
-    stream = torch.cuda.current_stream(dev)
 
-    def step(events=None):
-        if events is not None:
-            events[0].record(stream)
-        km(e_silu, stream, o_silu, [x, y], wsarg)
-        if events is not None:
-            events[1].record(stream)
-        km(e_max, stream, o_max, [x], wsarg)
-        if events is not None:
-            events[2].record(stream)
-        km(e_exp, stream, o_exp, [x, o_max], wsarg)
-        if events is not None:
-            events[3].record(stream)
-        km(e_sum, stream, o_sum, [o_exp], wsarg)
-        if events is not None:
-            events[4].record(stream)
-
-    def barrier():
-        if world > 1:
-            import torch.distributed as dist
-            dist.barrier()
-        torch.cuda.synchronize(dev)
-
-    for _ in range(max(args.warmup, 3)):
+    def step(ev=None):
+        calls = ((e_silu, o_silu, [x, y]), (e_max, o_max, [x]), (e_exp, o_exp, [x, o_max]), (e_sum, o_sum, [o_exp]))
+        for i, (e, o, ins) in enumerate(calls):
+            if ev is not None:
+                ev[i].record(stream)
+            km(e, stream, o, ins, wsarg)
+        if ev is not None:
+            ev[4].record(stream)
+    for _ in range(3):
         step()
-    barrier()
-
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(args.steps)]
-    c0 = km.counters()
-    barrier()
-    t_begin = time.perf_counter()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record(stream)
-    for k in range(args.steps):
-        step(ev[k])
-    end.record(stream)
-    barrier()
-    t_end = time.perf_counter()
-    c1 = km.counters()
-    clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
-    ms = start.elapsed_time(end)
-    if world > 1:
-        import torch.distributed as dist
-        t = torch.tensor([ms], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    per_kernel_ms = [float(np.mean([ev[k][i].elapsed_time(ev[k][i + 1]) for k in range(args.steps)]))
-                     for i in range(4)]
-    launches = sum(c1[k] - c0[k] for k in c0)
-
-    if args.kernels_only:
-        if rank == 0:
-            print(json.dumps({"metric": "elementwise+reduction algorithmic GB/s (kernels only)",
-                              "value": BYTES_STEP * world * args.steps / (ms * 1e-3) / 1e9, "unit": "GB/s",
-                              "config": {"workload": WORKLOAD}, "ms_per_step": ms / args.steps,
-                              "per_kernel_ms": per_kernel_ms, "gpu_launches": int(launches)}))
-        if world > 1:
-            import torch.distributed as dist
-            dist.destroy_process_group()
-        return
-
-    # ---- end to end: host buffers in, results back on the host, every step ----
-    # Every step copies its own inputs from pinned host memory and its results back.  The copies
-    # of neighbouring steps overlap the kernels on separate streams (double-buffered device
-    # inputs and outputs): H2D of step i+1 and D2H of step i-1 run while step i computes.
-    hx = torch.randn(N, dtype=torch.float16).pin_memory()
-    hy = torch.randn(N, dtype=torch.float16).pin_memory()
-    h_silu = torch.empty(N, dtype=torch.float16).pin_memory()
-    h_max = torch.empty(ROWS, dtype=torch.float16).pin_memory()
-    h_sum = torch.empty(ROWS, dtype=torch.float16).pin_memory()
-    xs, ys = [x, torch.empty_like(x)], [y, torch.empty_like(y)]
-    o_silus = [o_silu, torch.empty_like(o_silu)]
-    o_maxs, o_sums = [o_max, torch.empty_like(o_max)], [o_sum, torch.empty_like(o_sum)]
-    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-    ev_in = [torch.cuda.Event() for _ in range(2)]      # inputs of buffer b have landed
-    ev_done = [torch.cuda.Event() for _ in range(2)]    # kernels reading buffer b have finished
-    ev_out = [torch.cuda.Event() for _ in range(2)]     # results of buffer b are on the host
-
-    def e2e_step(i):
-        b = i & 1
-        with torch.cuda.stream(s_in):
-            s_in.wait_event(ev_done[b])                 # the step that last used these buffers is done
-            xs[b].copy_(hx, non_blocking=True)
-            ys[b].copy_(hy, non_blocking=True)
-            ev_in[b].record(s_in)
-        stream.wait_event(ev_in[b])
-        stream.wait_event(ev_out[b])                    # previous results of this buffer were read out
-        km(e_silu, stream, o_silus[b], [xs[b], ys[b]], wsarg)
-        km(e_max, stream, o_maxs[b], [xs[b]], wsarg)
-        km(e_exp, stream, o_exp, [xs[b], o_maxs[b]], wsarg)
-        km(e_sum, stream, o_sums[b], [o_exp], wsarg)
-        ev_done[b].record(stream)
-        with torch.cuda.stream(s_out):
-            s_out.wait_event(ev_done[b])
-            h_silu.copy_(o_silus[b], non_blocking=True)
-            h_max.copy_(o_maxs[b], non_blocking=True)
-            h_sum.copy_(o_sums[b], non_blocking=True)
-            ev_out[b].record(s_out)
-
-    e2e_steps = max(4, min(args.steps, 10))
-    for b in range(2):
-        ev_done[b].record(stream)
-        ev_out[b].record(stream)
-    e2e_step(0)
-    e2e_step(1)
-    barrier()
-    s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s2.record(stream)
-    s_in.wait_event(s2)
-    for i in range(e2e_steps):
-        e2e_step(i)
-    stream.wait_stream(s_out)
-    stream.wait_stream(s_in)
-    e2.record(stream)
-    barrier()
-    e2e_ms = s2.elapsed_time(e2)
-    if world > 1:
-        import torch.distributed as dist
-        t = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
-    # the end-to-end result must be the same bits as the device-resident one for the same inputs
-    x.copy_(hx)
-    y.copy_(hy)
-    step()
     torch.cuda.synchronize(dev)
-    e2e_ok = bool(torch.equal(o_silu.cpu(), h_silu) and torch.equal(o_sum.cpu(), h_sum))
-
-    # ---- other kernel classes of the metric (outside the timed region above; rank 0 only).  They
-    # are kernels timed alone, so they run here, before the long graph legs heat the GPU into its
-    # power cap: their fractions are quoted against the burst peak ----
-    classes = {}
-    if rank == 0:
-        try:
-            classes = other_classes(km, dev, stream)
-        except Exception as exc:  # reported, never hidden
-            classes = {"error": repr(exc)}
-        torch.cuda.empty_cache()
-
-    # ---- configs 4 and 5: LLaMA-7B-shape graphs, the reference's own memgraphs for `world` GPUs ----
-    llama, llama_train = None, None
-    try:
-        llama = llama_layer_leg(rank, world, dev)
-    except Exception as exc:  # reported, never hidden
-        llama = {"error": repr(exc)[:300]}
-    try:
-        llama_train = llama_layer_leg(rank, world, dev, fixture="llama7b_train_l4", runs=5)
-    except Exception as exc:  # reported, never hidden
-        llama_train = {"error": repr(exc)[:300]}
-    # config 5 at the batch it names (8 x 1024 tokens): 117 GB of device memory on one GPU
-    llama_train_full = None
-    try:
-        if os.environ.get("ES_B200_BENCH_C5_FULL", "1") != "0":
-            llama_train_full = llama_layer_leg(rank, world, dev, fixture="llama7b_train_b8s1024_l4", runs=3)
-        else:
-            llama_train_full = {"skipped": "ES_B200_BENCH_C5_FULL=0"}
-    except Exception as exc:  # reported, never hidden
-        llama_train_full = {"error": repr(exc)[:300]}
-
-    if rank != 0:
-        if world > 1:
-            import torch.distributed as dist
-            dist.destroy_process_group()
-        return
-
-    peak, peak_kind = measured_peaks()
-    achieved = BYTES_SILU_MUL / (per_kernel_ms[0] * 1e-3) / 1e9
-    line = {
-        "metric": "elementwise+reduction algorithmic GB/s", "value": BYTES_STEP * world * args.steps / (ms * 1e-3) / 1e9,
-        "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "l2": "inputs larger than L2 (3 x 180 MB per op); no flush",
-                   "algorithmic_bytes_per_step": BYTES_STEP,
-                   "kernels": dict(zip(["silu_mul", "rowmax", "exp_sub", "rowsum"],
-                                       [km.kernel_info(e).split("|")[0] for e in ops]))},
-        "clocks": clocks,
-        "e2e": {"value": BYTES_STEP * world * e2e_steps / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
-                "h2d_bytes_per_step": 2 * N * 2, "d2h_bytes_per_step": N * 2 + 2 * ROWS * 2,
-                "ms_per_step": e2e_ms / e2e_steps, "results_match_device_run": e2e_ok,
-                "overlap": "copies of neighbouring steps overlap the kernels (3 streams, double buffering)"},
-        "gpu_launches": int(launches),
-        "roofline": {"bound": "hbm", "kernel": "silu(x)*y a,a->a f16 (generated ew_vec)", "achieved": achieved,
-                     "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
-                     "traffic": SILU_MUL_DRAM_TRAFFIC if ROWS == 8192 else None, "algorithmic_bytes_per_launch": BYTES_SILU_MUL},
-        "per_kernel": {name: {"ms": t, "GB/s": b / (t * 1e-3) / 1e9, "frac_of_" + peak_kind: b / (t * 1e-3) / 1e9 / peak}
-                       for name, t, b in zip(["silu_mul", "rowmax", "exp_sub", "rowsum"], per_kernel_ms,
-                                             [BYTES_SILU_MUL, BYTES_ROWMAX, BYTES_EXP_SUB, BYTES_ROWSUM])},
-        "per_kernel_note": "CUDA-event intervals between the kernels of one step: a reduction's interval also carries "
-                           "the write-back of the 180 MB the kernel before it wrote (L2 holds 126 MB), so its own "
-                           "rate reads low and the elementwise kernel's high; the step total is what is exact",
-        "classes": classes,
-        "llama7b_layer": llama,
-        "llama7b_train_4layers": llama_train,
-        "llama7b_train_4layers_b8_s1024": llama_train_full,
-        "cpu_baseline": cpu_baseline() if world == 1 else None,
-    }
-    print(json.dumps(line))
-    if world > 1:
-        import torch.distributed as dist
-        dist.destroy_process_group()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(steps)]
+    for k in range(steps):
+        step(ev[k])
+    torch.cuda.synchronize(dev)
+    per = [float(np.mean([ev[k][i].elapsed_time(ev[k][i + 1]) for k in range(steps)])) for i in range(4)]
+    ms = float(np.mean([ev[k][0].elapsed_time(ev[k][4]) for k in range(steps)]))
+    peak = peaks["hbm_gbs"]
+    names = ["silu_mul", "rowmax", "exp_sub", "rowsum"]
+    nbytes = [BYTES_SILU_MUL, BYTES_ROWMAX, BYTES_EXP_SUB, BYTES_ROWSUM]
+    return {"workload": WORKLOAD, "ms_per_step": round(ms, 4), "GB/s": round(BYTES_STEP / (ms * 1e-3) / 1e9, 1),
+            "frac_of_hbm_peak": round(BYTES_STEP / (ms * 1e-3) / 1e9 / peak, 3),
+            "per_kernel_frac": {n: round(b / (t * 1e-3) / 1e9 / peak, 3) for n, t, b in zip(names, per, nbytes)},
+            "silu_mul_dram_traffic_per_launch": SILU_MUL_DRAM_TRAFFIC if ROWS == 8192 else None,
+            "kernels": dict(zip(names, [km.kernel_info(e).split("|")[0] for e in ops]))}
 
 
-def llama_layer_leg(rank, world, dev, fixture="llama7b_layer", runs=10):
-    """tokens/s of a LLaMA-7B-shape graph (dim 4096, 32 heads, FFN 11008, B=4, S=512, f16) executed
-    from the memgraph the reference's compilers produce for `world` locations, one process per GPU,
-    moves over peer memory (or NCCL send/recv).  `llama7b_layer`: one transformer layer forward plus
-    final norm and last-token vocabulary projection.  `llama7b_train_l4`: four layers forward, the
-    log-softmax loss, backward and the vanilla weight update.  Synthetic N(0, 0.02) weights."""
-    import torch
-    from einsummable_b200.memgraph import load_memgraph, memgraph_runner_t
-    path = os.path.join(ROOT, "tests", "golden", "graphs", "%s_locs%d.json.gz" % (fixture, world))
-    if not os.path.exists(path):
-        return {"skipped": "no memgraph fixture for %d locations" % world}
-    mg = load_memgraph(path)
-    need = int(max(mg["mem_sizes"])) + (8 << 30)
-    free = torch.cuda.mem_get_info(dev)[0]
-    if free < need:
-        return {"skipped": "needs %.0f GB of device memory, %.0f GB free" % (need / 1e9, free / 1e9)}
-    tokens = 2048
-    for t in mg["inputs"]:
-        if t["name"] == "embeddings":
-            tokens = int(t["shape"][0]) * int(t["shape"][1])
-    transport = os.environ.get("ES_B200_MOVE_TRANSPORT", "p2p")
-    if world > 1:
-        try:
-            r = memgraph_runner_t(mg, rank=rank, world=world, transport=transport)
-        except Exception as exc:
-            # symmetric memory could not be set up on this box: every rank fails the same way
-            sys.stderr.write("p2p transport unavailable (%r); using NCCL send/recv\n" % (exc,))
-            transport = "nccl"
-            r = memgraph_runner_t(mg, rank=rank, world=world, transport="nccl")
-    else:
-        transport = "local"
-        r = memgraph_runner_t(mg, devices=[dev.index])
-    def fill_inputs(runner):
-        rng = np.random.default_rng(7)
-        for t in mg["inputs"]:
-            shape, name = t["shape"], t["name"]
-            if name == "freqs_cis":
-                seq, half = shape
-                ang = np.outer(np.arange(seq), 1.0 / (10000.0 ** (np.arange(half) / half)))
-                v = (np.cos(ang) + 1j * np.sin(ang)).astype(np.complex64)
-            elif name.endswith("norm.weight"):
-                v = np.ones(shape, dtype=np.float16)
-            elif name == "labels":
-                v = np.zeros(shape, dtype=np.float16)
-                v[np.arange(shape[0]), rng.integers(0, shape[1], shape[0])] = 1.0
-            else:
-                v = (rng.standard_normal(shape).astype(np.float32) * 0.02).astype(np.float16)
-            runner.set_input(name, v)
-
-    fill_inputs(r)
-    stream = torch.cuda.current_stream(dev)
-
-    def barrier():
-        if world > 1:
-            import torch.distributed as dist
-            dist.barrier()
-        torch.cuda.synchronize(dev)
-
-    def timed(fn):
-        fn()
-        barrier()
-        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s.record(stream)
-        for _ in range(runs):
-            fn()
-        e.record(stream)
-        barrier()
-        ms = s.elapsed_time(e) / runs
-        if world > 1:
-            import torch.distributed as dist
-            t = torch.tensor([ms], dtype=torch.float64, device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
-
-    out = {"tokens": tokens, "gpus": world, "move_transport": transport, "nodes_this_rank": dict(r.stats),
-           "taskgraph": mg["taskgraph"], "contraction_gflop": mg["taskgraph"]["contraction_flops"] / 1e9}
-    ms_eager = timed(lambda: r.run(stream))
-    out["eager"] = {"ms": ms_eager, "tokens/s": tokens / (ms_eager * 1e-3)}
-    try:
-        if transport == "nccl":
-            # a process group holding captured NCCL send/recv nodes did not shut down cleanly here
-            raise RuntimeError("not captured with the NCCL transport")
-        r.capture()
-        ms_graph = timed(r.replay)
-        out["cuda_graph"] = {"ms": ms_graph, "tokens/s": tokens / (ms_graph * 1e-3),
-                             "TFLOP/s": mg["taskgraph"]["contraction_flops"] / (ms_graph * 1e-3) / 1e12}
-    except Exception as exc:
-        out["cuda_graph"] = {"error": repr(exc)[:200]}
-    out["device_status"] = r.device_status()
-    r.graph = None
-    r.close()
-    del r
-    torch.cuda.empty_cache()
-    fused_multi = os.environ.get("ES_B200_BENCH_FUSED_MULTI", "1" if world <= 2 else "0") == "1"
-    if transport != "nccl" and (world == 1 or fused_multi):
-        # the same memgraph with elementwise producers folded into their readers (fusion across
-        # node boundaries: a rewrite of the graph, not something the reference's engine does);
-        # on more than two GPUs only when ES_B200_BENCH_FUSED_MULTI=1
-        try:
-            if world == 1:
-                rf = memgraph_runner_t(mg, devices=[dev.index], fuse=True)
-            else:
-                rf = memgraph_runner_t(mg, rank=rank, world=world, transport=transport, fuse=True)
-            fill_inputs(rf)
-            rf.capture()
-            ms_fused = timed(rf.replay)
-            out["fused_cuda_graph"] = {"ms": ms_fused, "tokens/s": tokens / (ms_fused * 1e-3),
-                                       "nodes_folded": rf.folded, "einsummables": rf.stats["einsummable"],
-                                       "device_status": rf.device_status()}
-            rf.graph = None
-            rf.close()
-            del rf
-            torch.cuda.empty_cache()
-        except Exception as exc:  # reported, never hidden
-            out["fused_cuda_graph"] = {"error": repr(exc)[:200]}
+def class_fractions(classes, c2, peaks):
+    """{kernel class: fraction of its roofline} for the JSON line (the full per-case numbers go to stderr)."""
+    sys.stderr.write("kernel classes (timed alone, 20 launches, CUDA events):\n%s\n" % json.dumps(classes, indent=1))
+    tc, hbm = peaks["bf16_tflops"], peaks["hbm_gbs"]
+    out = {}
+    for name, v in classes.items():
+        if "TFLOP/s" in v and "attn" not in name:
+            f = v["TFLOP/s"] / (tc / 2 if "f32" in name else tc)
+            key = "contraction f32 3xTF32 (of half the bf16 peak, counting 1 of the 3 MMAs)" if "f32" in name else "contraction f16"
+            out[key] = round(max(out.get(key, 0.0), f), 3)
+        elif "attn" in name:
+            out["attention contraction (HBM bound) " + name.split()[1]] = round(v["GB/s"] / hbm, 3)
+        elif name.startswith("touch C3 sweep"):
+            key = "touch batched " + ("add" if " add " in name else "copy")
+            out[key] = round(max(out.get(key, 0.0), v["GB/s"] / hbm), 3)
+        elif name.startswith("permute"):
+            out["permutation"] = round(v["GB/s"] / hbm, 3)
+    if c2:
+        out["elementwise (C2 silu*y, exp(x-max))"] = max(c2["per_kernel_frac"]["silu_mul"], c2["per_kernel_frac"]["exp_sub"])
+        out["reduction (C2 row max / row sum, inside the step)"] = max(c2["per_kernel_frac"]["rowmax"], c2["per_kernel_frac"]["rowsum"])
+        out["C2 step of 4 kernels"] = c2["frac_of_hbm_peak"]
     return out
 
 
@@ -849,7 +930,7 @@ def run_only(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=ROWS,

@@ -44,6 +44,30 @@ def load_memgraph(path):
         return json.load(f)
 
 
+def synthetic_llama_inputs(mg, seed=7):
+    """Seeded synthetic inputs for the LLaMA-shape memgraph fixtures, by input name: weights and
+    embeddings ~ N(0, 0.02) rounded to f16, norm weights 1, `freqs_cis` the rotary table, `labels`
+    one-hot rows.  The graph's inputs come in the same order whatever the number of locations, so
+    every partitioning of one graph gets the same tensors."""
+    rng = np.random.default_rng(seed)
+    out = {}
+    for t in mg["inputs"]:
+        shape, name = t["shape"], t["name"]
+        if name == "freqs_cis":
+            seq, half = shape
+            ang = np.outer(np.arange(seq), 1.0 / (10000.0 ** (np.arange(half) / half)))
+            v = (np.cos(ang) + 1j * np.sin(ang)).astype(np.complex64)
+        elif name.endswith("norm.weight"):
+            v = np.ones(shape, dtype=NP_DTYPE[t["dtype"]])
+        elif name == "labels":
+            v = np.zeros(shape, dtype=NP_DTYPE[t["dtype"]])
+            v[np.arange(shape[0]), rng.integers(0, shape[1], shape[0])] = 1.0
+        else:
+            v = (rng.standard_normal(shape).astype(np.float32) * 0.02).astype(np.float16).astype(NP_DTYPE[t["dtype"]])
+        out[name] = v
+    return out
+
+
 def _scalar_from_raw(raw, dtype):
     b = bytes(raw[:DTYPE_SIZE[dtype]])
     return np.frombuffer(b, dtype=NP_DTYPE[dtype])[0]
@@ -784,6 +808,32 @@ class memgraph_runner_t:
             raw = self.buffers[blk["loc"]][blk["offset"]:blk["offset"] + blk["size"]].cpu().numpy()
             out[sl] = raw.view(NP_DTYPE[t["dtype"]]).reshape(out[sl].shape)
         return out
+
+    def stage_input(self, key, array):
+        """Pinned host copies of this process's blocks of input `key`, each with the device slice it
+        belongs to: [(host tensor, device tensor)].  `device.copy_(host, non_blocking=True)` on the
+        stream of the run then is the host-to-device copy of that input."""
+        t = self._tensor_desc("inputs", key)
+        a = np.ascontiguousarray(array, dtype=NP_DTYPE[t["dtype"]]).reshape(t["shape"])
+        pairs = []
+        for blk, sl in zip(t["blocks"], _blocks_of(t["shape"], t["partdims"])):
+            if not self.owns(blk["loc"]):
+                continue
+            raw = np.ascontiguousarray(a[sl]).view(np.uint8).reshape(-1)
+            host = torch.from_numpy(raw.copy()).pin_memory()
+            pairs.append((host, self.buffers[blk["loc"]][blk["offset"]:blk["offset"] + blk["size"]]))
+        return pairs
+
+    def stage_output(self, key):
+        """Pinned host buffers for this process's blocks of saved tensor `key`: [(host, device)]."""
+        t = self._tensor_desc("outputs", key)
+        pairs = []
+        for blk in t["blocks"]:
+            if not self.owns(blk["loc"]):
+                continue
+            host = torch.empty(blk["size"], dtype=torch.uint8).pin_memory()
+            pairs.append((host, self.buffers[blk["loc"]][blk["offset"]:blk["offset"] + blk["size"]]))
+        return pairs
 
     # ------------------------------------------------------------------ run
     def run(self, stream=None):

@@ -111,38 +111,57 @@ def test_c1_full_size(nlocs):
     r.close()
 
 
-def test_llama7b_layer_runs_and_is_finite():
-    """Config 4 at full size on one GPU: every node of the reference's memgraph builds
-    and runs; the result is finite and reproducible (values are checked at the tiny
-    size above, where the reference's interpreter can run)."""
-    mg = load_memgraph(os.path.join(GRAPHS, "llama7b_layer_locs1.json.gz"))
-    r = memgraph_runner_t(mg)
-    rng = np.random.default_rng(0)
-    for t in mg["inputs"]:
-        shape, name = t["shape"], t["name"]
-        if name == "freqs_cis":
-            seq, half = shape
-            ang = np.outer(np.arange(seq), 1.0 / (10000.0 ** (np.arange(half) / half)))
-            v = (np.cos(ang) + 1j * np.sin(ang)).astype(np.complex64)
-        elif name.endswith("norm.weight"):
-            v = np.ones(shape, dtype=np.float16)
-        elif name == "embeddings":
-            v = (rng.standard_normal(shape) * 0.02).astype(np.float16)
-        else:
-            v = (rng.standard_normal(shape).astype(np.float32) * 0.02).astype(np.float16)
-        r.set_input(name, v)
+FULL = np.load(os.path.join(GOLDEN_DIR, "c4_full.npz"))
+
+
+@pytest.mark.parametrize("nlocs,fuse", [(1, False), (1, True), (8, False), (8, True)])
+def test_llama7b_layer_full_size_against_the_cpu_oracle(nlocs, fuse):
+    """Config 4 at full size (2048 tokens, dim 4096, FFN 11008, vocabulary 32000): the reference's
+    memgraph for 1 and for 8 locations (all on this GPU), as compiled and with elementwise chains
+    folded, against the scores of the CPU oracle with f64-accumulated contractions
+    (tests/golden/make_c4_full.py).  f16 tolerance 1e-2 of the largest score."""
+    from einsummable_b200.memgraph import synthetic_llama_inputs
+    mg = load_memgraph(os.path.join(GRAPHS, "llama7b_layer_locs%d.json.gz" % nlocs))
+    r = memgraph_runner_t(mg, fuse=fuse)
+    for k, v in synthetic_llama_inputs(mg, seed=7).items():
+        r.set_input(k, v)
     r.run()
     torch.cuda.synchronize()
     assert r.device_status() == 0
-    out = r.get_output("scores")
-    assert out.shape == (4, 32000) and np.isfinite(out.astype(np.float32)).all() and np.abs(out).max() > 0
-    first = out.copy()
+    got = r.get_output("scores").astype(np.float64)
+    want = FULL["scores"].astype(np.float64)
+    assert got.shape == (4, 32000)
+    scale = np.abs(want).max()
+    err = np.abs(got - want).max()
+    print("nlocs", nlocs, "fuse", fuse, "max err / max |score| = %.2e" % (err / scale))
+    assert err <= 1e-2 * scale
+    first = got.copy()
+    r.capture()
+    r.replay()
+    torch.cuda.synchronize()
+    assert r.get_output("scores").astype(np.float64).tobytes() == first.tobytes()
+    if nlocs == 1 and not fuse:
+        kinds = r.kernel_kinds()
+        print(kinds)
+        assert kinds.get("contraction_tc_f16", 0) >= 10   # every contraction of the layer is on the tensor cores
+    r.close()
+
+
+@pytest.mark.parametrize("fuse", [False, True])
+def test_llama7b_training_graph_full_size_loss(fuse):
+    """Config 5's shape at 2048 tokens (4 layers forward, loss, backward, update; 512 einsummables):
+    the per-sequence loss against the CPU oracle's."""
+    from einsummable_b200.memgraph import synthetic_llama_inputs
+    mg = load_memgraph(os.path.join(GRAPHS, "llama7b_train_l4_locs1.json.gz"))
+    r = memgraph_runner_t(mg, fuse=fuse)
+    for k, v in synthetic_llama_inputs(mg, seed=7).items():
+        r.set_input(k, v)
     r.run()
     torch.cuda.synchronize()
-    assert r.get_output("scores").tobytes() == first.tobytes()
-    kinds = r.kernel_kinds()
-    print(kinds)
-    assert kinds.get("contraction_tc_f16", 0) >= 10   # every contraction of the layer is on the tensor cores
+    assert r.device_status() == 0
+    got = r.get_output("loss").astype(np.float64).reshape(-1)
+    want = FULL["train/loss"]
+    assert np.abs(got - want).max() <= 1e-2 * np.abs(want).max(), (got, want)
     r.close()
 
 

@@ -251,3 +251,33 @@ def test_fusion_leaves_readers_that_view_the_bytes_differently():
     f, n = fuse_elementwise_chains(_mini([_ew(0, [], A, [X], sq), _ew(1, [0], B, [A], "exp[hole|f32@0]"), writer],
                                          outputs=[B]))
     assert n == 1 and f["nodes"][2]["inns"] == [1]
+
+
+@pytest.mark.parametrize("accumulate", ["f32", "f64"])
+@pytest.mark.parametrize("name", ["c1_n64_locs2", "llama_tiny_locs1", "llama_tiny_locs4", "llama_train_tiny_locs2",
+                                  "llama_train_adamw_tiny_locs1", "llama_train_lora_tiny_locs2"])
+def test_cpu_engine_matches_reference(name, accumulate):
+    """oracle/cpu_engine.py (the timed CPU baseline and the full-size oracle) against the reference
+    interpreter's results on the graphs small enough for the interpreter, same tolerances as the GPU runner."""
+    from cpu_engine import cpu_engine_t
+    mg = load(name)
+    eng = cpu_engine_t(mg, accumulate=accumulate, threads=2)
+    for k, v in inputs_of(name).items():
+        eng.set_input(k, v)
+    eng.run()
+    for k, ref in outputs_of(name).items():
+        got = eng.get_output(k)
+        scale = np.abs(ref.astype(np.float64)).max()
+        err = np.abs(got.astype(np.float64) - ref.astype(np.float64)).max()
+        tol = 2e-2 if ref.dtype == np.float16 else (1e-4 if name.startswith("llama_train") else 1e-5)
+        assert err <= tol * scale, (name, k, err, scale)
+    eng.run()       # groups reset per run
+    for k, ref in outputs_of(name).items():
+        assert np.isfinite(eng.get_output(k).astype(np.float64)).all()
+
+
+def test_full_size_fixture_is_present_and_sane():
+    z = np.load(os.path.join(GOLDEN_DIR, "c4_full.npz"))
+    assert z["scores"].shape == (4, 32000) and z["scores"].dtype == np.float16
+    assert np.isfinite(z["scores"].astype(np.float32)).all() and np.abs(z["scores"]).max() > 1
+    assert z["train/loss"].shape == (4,) and np.isfinite(z["train/loss"]).all()
