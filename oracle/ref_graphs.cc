@@ -130,6 +130,12 @@ void tensor_json(std::ostream& out, built_graph_t const& b, int gid, vtensor_t<i
 
 } // namespace
 
+// for oracle/ref_engine_run.cc, which hands the memgraph to the reference's own GPU engine
+memgraph_t const& ref_graph_memgraph(int h)
+{
+    return g_graphs.at(h)->memgraph;
+}
+
 extern "C" {
 
 char const* ref_graph_last_error()

@@ -1,0 +1,80 @@
+"""The reference's own GPU engine on the boundary.
+
+oracle/_ref/engine_parity (built by oracle/Makefile where the reference tree is present; the
+binary travels with the working tree) is the reference's exec graph, exec nodes, stream pool,
+workspace / group / buffer managers and event loop -- src/engine/exec_graph.cc, exec_state.cc,
+gpu/exec_graph.cc, ... compiled unchanged -- linked with the drop-in kernel_manager_t instead of
+the reference's cuTENSOR one.  It builds the memgraph in-process with the reference's compilers,
+runs exec_state_t::event_loop on it and hands back the location buffer; the saved tensors are
+compared with what the reference's interpreter computed for the same inputs (tests/golden/graphs)."""
+import json
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+import es_oracle as O
+from conftest import GOLDEN_DIR, ROOT
+
+pytestmark = pytest.mark.gpu
+BIN = os.path.join(ROOT, "oracle", "_ref", "engine_parity")
+ARR = np.load(os.path.join(GOLDEN_DIR, "graphs", "graphs.npz"))
+
+CASES = [
+    ("c1_n64_locs1", "c1:64:2:1"),
+    ("llama_tiny_locs1", "llama:64:2:32:128:1:2:16:0"),
+]
+
+
+def run_engine(spec, tmp_path, inputs=None, iters=2):
+    if not os.path.exists(BIN):
+        pytest.skip("oracle/_ref/engine_parity is not built (needs the reference tree at build time)")
+    # first call: only to learn the layout the reference's compilers chose (memgraph.json)
+    if inputs is not None:
+        res = subprocess.run([BIN, spec, str(tmp_path), "0"], capture_output=True, text=True, timeout=600)
+        assert res.returncode == 0, res.stderr[-2000:]
+        with open(tmp_path / "memgraph.json") as f:
+            mg = json.load(f)
+        bufs = O.memgraph_place_inputs(mg, inputs)
+        bufs[0][:int(mg["mem_sizes"][0])].tofile(tmp_path / "in.bin")
+    res = subprocess.run([BIN, spec, str(tmp_path), str(iters)], capture_output=True, text=True, timeout=900)
+    assert res.returncode == 0, res.stderr[-2000:]
+    with open(tmp_path / "memgraph.json") as f:
+        mg = json.load(f)
+    info = json.loads(res.stdout.strip().splitlines()[-1])
+    out = np.fromfile(tmp_path / "out.bin", dtype=np.uint8)
+    return mg, info, out
+
+
+@pytest.mark.parametrize("name,spec", CASES)
+def test_reference_engine_runs_memgraphs_on_the_drop_in(name, spec, tmp_path):
+    pre = name + "/in/"
+    inputs = {k[len(pre):]: ARR[k] for k in ARR.files if k.startswith(pre)}
+    mg, info, out = run_engine(spec, tmp_path, inputs)
+    assert mg["num_locs"] == 1 and info["exec_nodes"] == len(mg["nodes"])
+    got = O.memgraph_collect_outputs(mg, [np.concatenate([out, np.zeros(256, np.uint8)])])
+    pre = name + "/out/"
+    checked = 0
+    for k in ARR.files:
+        if not k.startswith(pre):
+            continue
+        ref = ARR[k]
+        g = got[k[len(pre):]]
+        scale = np.abs(ref.astype(np.float64)).max()
+        err = np.abs(g.astype(np.float64) - ref.astype(np.float64)).max()
+        assert err <= (2e-2 if ref.dtype == np.float16 else 1e-5) * scale, (name, k, err, scale)
+        checked += 1
+    assert checked >= 1
+    print(name, info)
+
+
+def test_reference_engine_llama7b_layer_times(tmp_path):
+    """The LLaMA-7B-shape layer (config 4) through the reference's event loop (one
+    cudaStreamAddCallback round trip per node, 5 streams): every node builds and runs; the time per
+    event loop is printed next to what the library's own schedule needs (see bench.py)."""
+    mg, info, out = run_engine("llama:4096:32:256:32000:1:4:512:0", tmp_path, None, iters=5)
+    assert info["exec_nodes"] == len(mg["nodes"])
+    loops = info["event_loop_ms"]
+    print("reference engine on the drop-in, LLaMA-7B layer: build %.0f ms, event loops %s ms" % (info["build_ms"], loops))
+    assert min(loops) < 50.0
