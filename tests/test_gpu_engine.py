@@ -42,7 +42,7 @@ def run_engine(spec, tmp_path, inputs=None, iters=2):
     assert res.returncode == 0, res.stderr[-2000:]
     with open(tmp_path / "memgraph.json") as f:
         mg = json.load(f)
-    info = json.loads(res.stdout.strip().splitlines()[-1])
+    info = json.loads([l for l in res.stdout.splitlines() if l.startswith("{")][-1])   # the engine prints, too
     out = np.fromfile(tmp_path / "out.bin", dtype=np.uint8)
     return mg, info, out
 
