@@ -93,6 +93,16 @@ SYMBOLS = {
     "es_b200_program_add_fill_constant": (_i, [_vp, _i, _vp, _u64, _vp, _ip, _i, _ip]),
     "es_b200_program_add_fill_lowertri": (_i, [_vp, _i, _vp, _vp, _u64, _u64, ctypes.c_int64, _vp, _ip, _i, _ip]),
     "es_b200_program_add_copy": (_i, [_vp, _vp, _vp, _u64, _ip, _i, _ip]),
+    "es_b200_program_add_evict": (_i, [_vp, _vp, _vp, _u64, _ip, _i, _ip]),
+    "es_b200_program_add_load": (_i, [_vp, _vp, _vp, _u64, _ip, _i, _ip]),
+    "es_b200_storage_create": (_i, [_u64, _i, ctypes.POINTER(_vp)]),
+    "es_b200_storage_destroy": (_i, [_vp]),
+    "es_b200_storage_write": (_i, [_vp, _i, _vp, _u64]),
+    "es_b200_storage_read": (_i, [_vp, _i, _vp, _u64]),
+    "es_b200_storage_remove": (_i, [_vp, _i]),
+    "es_b200_storage_reference": (_i, [_vp, _i, ctypes.POINTER(_vp), ctypes.POINTER(_u64)]),
+    "es_b200_evict": (_i, [_vp, _vp, _i, _vp, _u64, _vp]),
+    "es_b200_load": (_i, [_vp, _vp, _i, _vp, _u64, _vp]),
     "es_b200_program_add_signal": (_i, [_vp, ctypes.POINTER(_vp), _i, _ip, _i, _ip]),
     "es_b200_program_add_pull": (_i, [_vp, ctypes.POINTER(es_pull_item_t), _i, _ip, _i, _ip]),
     "es_b200_program_add_wait": (_i, [_vp, ctypes.POINTER(_vp), _i, _ip, _i, _ip]),

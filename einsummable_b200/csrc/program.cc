@@ -49,11 +49,14 @@ enum op_kind_t {
     OP_SIGNAL = 5,
     OP_PULL = 6,
     OP_WAIT = 7,
-    OP_TOUCH_BATCH = 8
+    OP_TOUCH_BATCH = 8,
+    OP_EVICT = 9,
+    OP_LOAD = 10
 };
 
 char const* const OP_NAMES[] = {"einsummable", "touch", "fill_constant", "fill_lowertri", "copy",
-                                "signal",      "pull",  "wait",          "touch_batch"};
+                                "signal",      "pull",  "wait",          "touch_batch",   "evict",
+                                "load"};
 
 struct op_t {
     int              kind = 0;
@@ -334,6 +337,16 @@ void launch_op(es_b200_program* p, op_t const& op, cudaStream_t s)
             h->counters[3] += 1;
             h->work_bytes[3] += op.bytes;
             break;
+        case OP_EVICT:
+            ES_CUDA_CHECK(cudaMemcpyAsync(op.out, op.src, op.bytes, cudaMemcpyDeviceToHost, s));
+            h->counters[3] += 1;
+            h->work_bytes[3] += op.bytes;
+            break;
+        case OP_LOAD:
+            ES_CUDA_CHECK(cudaMemcpyAsync(op.out, op.src, op.bytes, cudaMemcpyHostToDevice, s));
+            h->counters[3] += 1;
+            h->work_bytes[3] += op.bytes;
+            break;
         case OP_SIGNAL:
             launch_signal_many(reinterpret_cast<uint32_t* const*>(p->dev_buf + op.dev_off), (int)op.flags.size(),
                                p->epoch_dev, s);
@@ -605,6 +618,34 @@ int es_b200_program_add_copy(es_b200_program_t* p,
         op.bytes = bytes;
         add_op(p, std::move(op), deps, n_deps, op_index);
     });
+}
+
+static int add_host_copy(es_b200_program_t* p, int kind, const void* src, void* dst, uint64_t bytes,
+                         const int* deps, int n_deps, int* op_index)
+{
+    return guarded([&] {
+        check_program(p, false);
+        if (!src || !dst) fail(ES_BAD_ARGUMENT, "program evict / load: null pointer");
+        op_t op;
+        op.kind = kind;
+        op.src = src;
+        op.out = dst;
+        op.bytes = bytes;
+        op.work_bytes = bytes;
+        add_op(p, std::move(op), deps, n_deps, op_index);
+    });
+}
+
+int es_b200_program_add_evict(es_b200_program_t* p, const void* dev_src, void* host_dst, uint64_t bytes,
+                              const int* deps, int n_deps, int* op_index)
+{
+    return add_host_copy(p, OP_EVICT, dev_src, host_dst, bytes, deps, n_deps, op_index);
+}
+
+int es_b200_program_add_load(es_b200_program_t* p, const void* host_src, void* dev_dst, uint64_t bytes,
+                             const int* deps, int n_deps, int* op_index)
+{
+    return add_host_copy(p, OP_LOAD, host_src, dev_dst, bytes, deps, n_deps, op_index);
 }
 
 int es_b200_program_add_signal(es_b200_program_t* p,

@@ -70,6 +70,8 @@ def _written_region(node, loc):
         return (node["dst_offset"], node["size"]) if node["dst_loc"] == loc else None
     if k == "copy":
         return (node["dst_offset"], node["size"]) if node["loc"] == loc else None
+    if k == "load":
+        return (node["offset"], node["size"]) if node["loc"] == loc else None
     return None
 
 
@@ -119,7 +121,8 @@ def fuse_elementwise_chains(mg):
     reads the graph); a result that a move ships to another location is never folded."""
     mg = copy.deepcopy(mg)
     nodes = mg["nodes"]
-    saved = [(blk["loc"], blk["offset"], blk["size"]) for t in mg["outputs"] for blk in t["blocks"]]
+    # (saved blocks that end up in storage have no memory region to protect)
+    saved = [(blk["loc"], blk["offset"], blk["size"]) for t in mg["outputs"] for blk in t["blocks"] if "offset" in blk]
     alive = [True] * len(nodes)
     folded = 0
     for ia, a in enumerate(nodes):
@@ -136,8 +139,8 @@ def fuse_elementwise_chains(mg):
             n = nodes[ib]
             if not alive[ib] or a["id"] not in n["inns"]:
                 continue
-            if n["kind"] in ("move", "copy"):
-                shipped = True      # another location (or a copy) reads the materialised tensor
+            if n["kind"] in ("move", "copy", "evict"):
+                shipped = True      # another location (or a copy, or the storage) reads the materialised tensor
                 break
             if n["kind"] == "apply" and n["loc"] == loc and any(tuple(m) == out for m in n["mems"][1:]):
                 readers.append(ib)

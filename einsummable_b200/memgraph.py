@@ -88,7 +88,7 @@ def move_runs(mg):
     may post its members of a run as one NCCL group.  The numbering uses the whole graph only:
     every rank cuts its groups at the same places.  (Groups that straddle a cut on one rank but
     not on its peer can wait on each other for ever.)"""
-    bookkeeping = ("alloc", "del", "inputmem", "partialize")
+    bookkeeping = BOOKKEEPING
     moved_from = {}
     runs = {}
     run_id, members = 0, set()
@@ -111,7 +111,7 @@ def move_runs(mg):
             runs[node["id"]] = run_id
     return runs
 
-BOOKKEEPING = ("alloc", "del", "inputmem", "partialize")
+BOOKKEEPING = ("alloc", "del", "inputmem", "inputsto", "partialize")
 
 
 def _sides(node):
@@ -207,7 +207,10 @@ def schedule_units(mg, owned, exchange):
             elif r in unit_of:
                 deps.add(unit_of[r])
         if tokens:
-            units.append({"kind": "wait", "moves": tokens, "deps": []})
+            # (the acknowledgement can only follow this rank's own signal; naming that edge keeps
+            # "ordered after the wait" meaning "ordered after the signal" for whoever reads the plan)
+            units.append({"kind": "wait", "moves": tokens,
+                          "deps": sorted({unit_of[("signal", t)] for t in tokens if ("signal", t) in unit_of})})
             for t in tokens:
                 waited[t] = len(units) - 1
             deps.add(len(units) - 1)
@@ -272,6 +275,8 @@ def schedule_units(mg, owned, exchange):
             idx = emit({"kind": "constant", "node": nid, "deps": deps, "loc": loc})
         elif kind in ("move", "copy"):
             idx = emit({"kind": "copy", "node": nid, "deps": deps, "loc": loc})
+        elif kind in ("evict", "load"):
+            idx = emit({"kind": kind, "node": nid, "deps": deps, "loc": loc})
         else:
             raise ValueError("unknown memgraph node kind %r" % kind)
         unit_of[nid] = idx
@@ -279,7 +284,8 @@ def schedule_units(mg, owned, exchange):
     # collecting their acknowledgements
     rest = [n["id"] for n in nodes if is_cross(n) and n["src_loc"] in owned and n["id"] not in waited]
     if rest:
-        units.append({"kind": "wait", "moves": rest, "deps": []})
+        units.append({"kind": "wait", "moves": rest,
+                      "deps": sorted({unit_of[("signal", t)] for t in rest if ("signal", t) in unit_of})})
     return units
 
 _DSIZE = {"f16": 2, "f32": 4, "f64": 8, "c64": 8}
@@ -313,6 +319,8 @@ def unit_cost_us(mg, u):
         return 2.5, 0.5, "gpu"
     if k == "copy":
         return 2.5, 2 * nodes[u["node"]]["size"] / 4.5e6, "gpu"
+    if k in ("evict", "load"):
+        return 4.0, nodes[u["node"]]["size"] / 0.05e6, "pcie"
     if k == "signal":
         return 3.0, 0.0, None
     if k == "pull":
@@ -388,8 +396,7 @@ def order_units_by_simulation(mg, world, rank):
     times = simulate_schedule(mg, all_units)
     units = all_units[rank]
     # the closing wait (acknowledgements nobody on this rank needs during the run) stays last
-    closing = len(units) - 1 if units and units[-1]["kind"] == "wait" and not any(
-        len(units) - 1 in u["deps"] for u in units) else -1
+    closing = len(units) - 1 if units and units[-1]["kind"] == "wait" else -1
     order = sorted(range(len(units)), key=lambda i: (i == closing, times[(rank, i)][0], i))
     new_index = {old: new for new, old in enumerate(order)}
     out = []
@@ -453,10 +460,31 @@ class memgraph_runner_t:
             for loc, dev in self.devices.items():
                 size = int(mg["mem_sizes"][loc]) + 256
                 self.buffers[loc] = torch.zeros(size, dtype=torch.uint8, device="cuda:%d" % dev)
+        self._alloc_storage()
         if self.schedule == "dag":
             self._build_program()
         else:
+            if self.sto_slot:
+                raise RuntimeError("memgraphs with storage (evict / load) run with the dag schedule only")
             self._prepare()
+
+    def _alloc_storage(self):
+        """Memgraphs compiled under a memory limit: one pinned host arena per process, a fixed block
+        in it for every storage id of this process's locations (ids are unique within a run:
+        src/einsummable/memgraph.h:311-316), so evict / load are plain copies in the static schedule."""
+        self.sto_slot = {}
+        off = 0
+        for n in self.mg["nodes"]:
+            if n["kind"] in ("inputsto", "evict") and self.owns(n["loc"]):
+                key = (n["storage_loc"], n["storage_id"])
+                if key not in self.sto_slot:
+                    self.sto_slot[key] = (off, int(n["size"]))
+                    off += (int(n["size"]) + 255) // 256 * 256
+        self.sto_host = torch.zeros(max(off, 256), dtype=torch.uint8).pin_memory() if off else None
+
+    def _sto_view(self, key):
+        off, size = self.sto_slot[key]
+        return self.sto_host[off:off + size]
 
     def _alloc_symmetric(self):
         import os
@@ -566,6 +594,17 @@ class memgraph_runner_t:
                 self.stats["move"] += 1
                 self.stats["move_bytes"] += node["size"]
                 self.unit_labels.append(("copy", str(node["size"])))
+            elif kind in ("evict", "load"):
+                node = nodes[u["node"]]
+                host = self._sto_view((node["storage_loc"], node["storage_id"]))
+                dev_ptr = self.ptr(node["loc"], node["offset"])
+                if kind == "evict":
+                    prog.add_evict(dev_ptr, host.data_ptr(), node["size"], deps)
+                else:
+                    prog.add_load(host.data_ptr(), dev_ptr, node["size"], deps)
+                self.stats["move"] += 1
+                self.stats["move_bytes"] += node["size"]
+                self.unit_labels.append((kind, "%d bytes" % node["size"]))
             elif kind == "signal":
                 prog.add_signal([self._flag_ptr(nodes[m]["dst_loc"], 0, self.move_index[m]) for m in u["moves"]], deps)
                 self.stats["move"] += len(u["moves"])
@@ -796,6 +835,9 @@ class memgraph_runner_t:
                 continue
             raw = np.ascontiguousarray(a[sl]).view(np.uint8).reshape(-1)
             assert raw.size == blk["size"], (raw.size, blk)
+            if "sto_id" in blk:       # this block starts out in storage
+                self._sto_view((blk["sto_loc"], blk["sto_id"])).copy_(torch.from_numpy(raw))
+                continue
             self.buffers[blk["loc"]][blk["offset"]:blk["offset"] + blk["size"]].copy_(torch.from_numpy(raw))
 
     def get_output(self, key):
@@ -805,7 +847,10 @@ class memgraph_runner_t:
         for blk, sl in zip(t["blocks"], _blocks_of(t["shape"], t["partdims"])):
             if not self.owns(blk["loc"]):
                 continue
-            raw = self.buffers[blk["loc"]][blk["offset"]:blk["offset"] + blk["size"]].cpu().numpy()
+            if "sto_id" in blk:       # the saved block ended up in storage (synchronise before reading)
+                raw = self._sto_view((blk["sto_loc"], blk["sto_id"])).numpy().copy()
+            else:
+                raw = self.buffers[blk["loc"]][blk["offset"]:blk["offset"] + blk["size"]].cpu().numpy()
             out[sl] = raw.view(NP_DTYPE[t["dtype"]]).reshape(out[sl].shape)
         return out
 

@@ -116,6 +116,22 @@ class program_t:
                                                       ctypes.byref(idx)))
         return self._added(idx)
 
+    def add_evict(self, dev_src, host_dst, nbytes, deps=()):
+        """evict_t: device memory -> the storage id's (pinned) host block."""
+        d, nd = _deps(deps)
+        idx = ctypes.c_int(-1)
+        _lib.check(self._lib.es_b200_program_add_evict(self._p, _ptr(dev_src), _ptr(host_dst), int(nbytes), d, nd,
+                                                       ctypes.byref(idx)))
+        return self._added(idx)
+
+    def add_load(self, host_src, dev_dst, nbytes, deps=()):
+        """load_t: the storage id's host block -> device memory."""
+        d, nd = _deps(deps)
+        idx = ctypes.c_int(-1)
+        _lib.check(self._lib.es_b200_program_add_load(self._p, _ptr(host_src), _ptr(dev_dst), int(nbytes), d, nd,
+                                                      ctypes.byref(idx)))
+        return self._added(idx)
+
     def _flag_op(self, fn, flags, deps):
         arr = (ctypes.c_void_p * len(flags))(*[int(f) for f in flags])
         d, nd = _deps(deps)

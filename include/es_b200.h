@@ -197,6 +197,24 @@ int es_b200_move(es_b200_t*  h,
                  uint64_t    bytes,
                  void*       stream);
 
+/* Host storage for evicted tensors: gpu_storage_t (src/engine/gpu/storage.h:20-86, storage.cc:4-29:
+ * one pinned, portable host allocation of the whole storage size; write-combined there, optional
+ * here because saved tensors that end up in storage are read back by the host).  Every storage id
+ * owns one block.  write / read / remove / reference are the host-side members of the same names. */
+typedef struct es_b200_storage es_b200_storage_t;
+int es_b200_storage_create(uint64_t bytes, int write_combined, es_b200_storage_t** out);
+int es_b200_storage_destroy(es_b200_storage_t* s);
+int es_b200_storage_write(es_b200_storage_t* s, int id, const void* host_src, uint64_t bytes);
+int es_b200_storage_read(es_b200_storage_t* s, int id, void* host_dst, uint64_t bytes);
+int es_b200_storage_remove(es_b200_storage_t* s, int id);
+int es_b200_storage_reference(es_b200_storage_t* s, int id, void** host_ptr, uint64_t* bytes);
+/* gpu_evict_t::launch (src/engine/gpu/exec_graph.cc:469-515): reserve `id` and copy `bytes` from
+ * device memory into it, asynchronously on `stream`.
+ * gpu_load_t::launch (:517-577): copy the id's bytes back to device memory on `stream`; the id
+ * leaves the storage at once and its block is reused once that copy has finished. */
+int es_b200_evict(es_b200_t* h, es_b200_storage_t* s, int id, const void* dev_src, uint64_t bytes, void* stream);
+int es_b200_load(es_b200_t* h, es_b200_storage_t* s, int id, void* dev_dst, uint64_t bytes, void* stream);
+
 /* move_t between two processes that each drive one GPU (the reference drives all
  * GPUs of a box from one process and needs no hand-shake: src/engine/gpu/exec_graph.cc:406-467;
  * these three calls have no counterpart there).  `flag` is a zero-initialised 32-bit word
@@ -349,6 +367,12 @@ int es_b200_program_add_fill_lowertri(es_b200_program_t* p, int dtype, const voi
                                       const int* deps, int n_deps, int* op_index);
 /* gpu_copy_t::launch for a move or copy inside this GPU (src/engine/gpu/exec_graph.cc:406-467). */
 int es_b200_program_add_copy(es_b200_program_t* p, const void* src, void* dst, uint64_t bytes,
+                             const int* deps, int n_deps, int* op_index);
+/* evict_t / load_t of a static schedule: the host block of every storage id is fixed by the caller
+ * (pinned memory, e.g. es_b200_storage_reference), the op is the one cudaMemcpyAsync. */
+int es_b200_program_add_evict(es_b200_program_t* p, const void* dev_src, void* host_dst, uint64_t bytes,
+                              const int* deps, int n_deps, int* op_index);
+int es_b200_program_add_load(es_b200_program_t* p, const void* host_src, void* dev_dst, uint64_t bytes,
                              const int* deps, int n_deps, int* op_index);
 int es_b200_program_add_signal(es_b200_program_t* p, void* const* flags, int n,
                                const int* deps, int n_deps, int* op_index);

@@ -37,6 +37,10 @@ struct built_graph_t {
     taskgraph_t              taskgraph;
     map<int, mem_t>          inn_mem, save_mem;
     memgraph_t               memgraph;
+    // with storage (evict / load): where every input / saved block lives, memory or storage
+    bool                       has_storage = false;
+    map<int, memstoloc_t>      inn_msl, save_msl;
+    vector<map<int, buffer_t>> sto;   // storage contents around ref_graph_run_storage
     map<int, string>         names; // graph id -> name (weights etc.)
     map<string, scalar_t>    vars;  // scalar variables of the updater, substituted where a node is used
 };
@@ -55,6 +59,30 @@ int finish(built_graph_t* b)
     b->inn_mem = inn_mem;
     b->save_mem = save_mem;
     b->memgraph = mg;
+    g_graphs.push_back(b);
+    return int(g_graphs.size()) - 1;
+}
+
+// The same with a memory limit per location: memgraph_t::make (src/einsummable/memgraph.h:158-164)
+// evicts to and loads from one storage per location when the tensors do not fit
+// (as exps/reference.cc:89-211 test_make_memgraph_with_evict sets it up).
+int finish_with_storage(built_graph_t* b, uint64_t mem_limit)
+{
+    auto [inn_tids, save_tids, tg] = taskgraph_t::make(b->graph, b->placements);
+    b->inn_tids = inn_tids;
+    b->save_tids = save_tids;
+    b->taskgraph = tg;
+    int              nlocs = tg.num_locs();
+    vector<int>      which_storage(nlocs);
+    vector<uint64_t> mem_sizes(nlocs, mem_limit);
+    std::iota(which_storage.begin(), which_storage.end(), 0);
+    auto [inn_msl, save_msl, mg] = memgraph_t::make(b->taskgraph, which_storage, mem_sizes, {},
+                                                    allocator_settings_t::gpu_alignment_settings());
+    b->has_storage = true;
+    b->inn_msl = inn_msl;
+    b->save_msl = save_msl;
+    b->memgraph = mg;
+    b->sto.resize(nlocs);
     g_graphs.push_back(b);
     return int(g_graphs.size()) - 1;
 }
@@ -121,6 +149,19 @@ void tensor_json(std::ostream& out, built_graph_t const& b, int gid, vtensor_t<i
     auto const& vec = tids.get();
     for (size_t i = 0; i != vec.size(); ++i) {
         int          tid = vec[i];
+        if (b.has_storage) {
+            memstoloc_t const& msl = (&mems == &b.inn_mem ? b.inn_msl : b.save_msl).at(tid);
+            uint64_t           size = b.taskgraph.nodes[tid].op.out_size();
+            if (msl.is_memloc()) {
+                auto const& m = msl.get_memloc();
+                out << (i ? "," : "") << "{\"loc\":" << m.loc << ",\"offset\":" << m.offset << ",\"size\":" << m.size << "}";
+            } else {
+                auto const& st = msl.get_stoloc();
+                out << (i ? "," : "") << "{\"loc\":" << b.taskgraph.out_loc(tid) << ",\"sto_loc\":" << st.loc
+                    << ",\"sto_id\":" << st.id << ",\"size\":" << size << "}";
+            }
+            continue;
+        }
         mem_t const& m = mems.at(tid);
         out << (i ? "," : "") << "{\"loc\":" << b.taskgraph.out_loc(tid) << ",\"offset\":" << m.offset
             << ",\"size\":" << m.size << "}";
@@ -335,6 +376,69 @@ int ref_graph_build_llama_train(uint64_t dim,
     G_END
 }
 
+// config 1 with a memory limit per location: the memgraph evicts to / loads from storage
+int ref_graph_build_c1_evict(uint64_t n, int n_split, int nlocs, int dtype_code, uint64_t mem_limit)
+{
+    G_BEGIN
+    dtype_t     dtype = dtype_code == 0 ? dtype_t::f16 : dtype_t::f32;
+    partdim_t   pd = partdim_t::split(n, n_split);
+    partition_t part2({pd, pd});
+    partition_t part3({pd, pd, pd});
+    graph_constructor_t g;
+    int lhs = g.insert_input(part2, dtype);
+    int rhs = g.insert_input(part2, dtype);
+    int join = g.insert_einsummable(part3, einsummable_t::from_matmul(n, n, n, dtype), {lhs, rhs});
+    int out = g.insert_formation(part2, join, true);
+    auto* b = new built_graph_t();
+    b->graph = g.graph;
+    vector<partition_t> parts = vector_from_each_member(g.get_placements(), partition_t, partition);
+    b->placements = alocate01(b->graph, parts, nlocs, 100);
+    b->names[lhs] = "lhs";
+    b->names[rhs] = "rhs";
+    b->names[out] = "out";
+    return finish_with_storage(b, mem_limit);
+    G_END
+}
+
+// Storage contents of a graph built with a memory limit: written before, read after
+// ref_graph_run_storage, which is the reference's own reference_compute_memgraph with storage
+// (src/einsummable/reference.cc:191-307).
+int ref_graph_sto_write(int h, int sto_loc, int sto_id, void const* data, uint64_t size)
+{
+    G_BEGIN
+    built_graph_t& b = *g_graphs.at(h);
+    buffer_t       buf = make_buffer(size);
+    std::copy((uint8_t const*)data, (uint8_t const*)data + size, buf->data);
+    b.sto.at(sto_loc)[sto_id] = buf;
+    return 0;
+    G_END
+}
+
+int ref_graph_sto_read(int h, int sto_loc, int sto_id, void* data, uint64_t size)
+{
+    G_BEGIN
+    built_graph_t& b = *g_graphs.at(h);
+    buffer_t       buf = b.sto.at(sto_loc).at(sto_id);
+    if (buf->size != size) throw std::runtime_error("storage block has another size");
+    std::copy(buf->data, buf->data + size, (uint8_t*)data);
+    return 0;
+    G_END
+}
+
+int ref_graph_run_storage(int h, void** loc_buffers)
+{
+    G_BEGIN
+    built_graph_t&   b = *g_graphs.at(h);
+    vector<buffer_t> locs;
+    auto             sizes = b.memgraph.mem_sizes();
+    for (size_t i = 0; i != sizes.size(); ++i) {
+        locs.push_back(make_buffer_reference((uint8_t*)loc_buffers[i], sizes[i]));
+    }
+    reference_compute_memgraph(b.memgraph, locs, b.sto);
+    return 0;
+    G_END
+}
+
 int ref_graph_num_locs(int h)
 {
     return g_graphs.at(h)->memgraph.num_compute_locs;
@@ -466,8 +570,20 @@ int ref_graph_write_json(int h, char const* path)
         } else if (op.is_del()) {
             auto const& x = op.get_del();
             out << ",\"kind\":\"del\",\"loc\":" << x.loc;
+        } else if (op.is_inputsto()) {
+            auto const& x = op.get_inputsto();
+            out << ",\"kind\":\"inputsto\",\"loc\":" << x.storage_loc << ",\"storage_loc\":" << x.storage_loc
+                << ",\"storage_id\":" << x.storage_id << ",\"size\":" << x.size;
+        } else if (op.is_evict()) {
+            auto const& x = op.get_evict();
+            out << ",\"kind\":\"evict\",\"loc\":" << x.src.loc << ",\"offset\":" << x.src.offset << ",\"size\":" << x.src.size
+                << ",\"storage_loc\":" << x.dst.loc << ",\"storage_id\":" << x.dst.id;
+        } else if (op.is_load()) {
+            auto const& x = op.get_load();
+            out << ",\"kind\":\"load\",\"loc\":" << x.dst.loc << ",\"offset\":" << x.dst.offset << ",\"size\":" << x.dst.size
+                << ",\"storage_loc\":" << x.src.loc << ",\"storage_id\":" << x.src.id;
         } else {
-            throw std::runtime_error("memgraph node kind not expected without storage");
+            throw std::runtime_error("unknown memgraph node kind");
         }
         out << "}";
     }

@@ -213,3 +213,79 @@ def test_llama7b_layer_fused_agrees_with_unfused():
     scale = np.abs(outs[0]).max()
     # f16 graph: the folded intermediates are no longer rounded to f16 (1e-2 of the output scale)
     assert np.abs(outs[0] - outs[1]).max() <= 1e-2 * scale
+
+
+EVICT = np.load(os.path.join(GRAPHS, "graphs_evict.npz"))
+
+
+@pytest.mark.parametrize("name", ["c1_n64_evict_locs1", "c1_n64_evict_locs2"])
+def test_memgraphs_with_evict_and_load(name):
+    """Memgraphs the reference compiled under a memory limit: 40 evicts, 50 loads and 20 inputs that
+    start out in storage.  Every storage id has a fixed block of one pinned host arena; evict / load
+    are copy ops of the dependency-ordered schedule.  Against the reference's
+    reference_compute_memgraph with storage."""
+    mg = load_memgraph(graph_path(name))
+    r = memgraph_runner_t(mg)
+    assert sum(1 for u in r.units if u["kind"] == "evict") > 30 and sum(1 for u in r.units if u["kind"] == "load") > 40
+    pre = name + "/in/"
+    for k in EVICT.files:
+        if k.startswith(pre):
+            r.set_input(k[len(pre):], EVICT[k])
+    ref = EVICT[name + "/out/out"]
+    for attempt in range(2):
+        r.run()
+        torch.cuda.synchronize()
+        assert r.device_status() == 0
+        got = r.get_output("out")
+        assert np.abs(got.astype(np.float64) - ref.astype(np.float64)).max() <= 1e-5 * np.abs(ref).max()
+        # inputs that started in storage were consumed (loaded and overwritten): put them back for the next run
+        for k in EVICT.files:
+            if k.startswith(pre):
+                r.set_input(k[len(pre):], EVICT[k])
+    r.capture()
+    r.replay()
+    torch.cuda.synchronize()
+    got = r.get_output("out")
+    assert np.abs(got.astype(np.float64) - ref.astype(np.float64)).max() <= 1e-5 * np.abs(ref).max()
+    r.close()
+
+
+def test_storage_evict_load_through_the_c_abi():
+    """es_b200_storage_* / es_b200_evict / es_b200_load: the dynamic form (ids reserved and released
+    at run time, as gpu_storage_t does).  Bit-exact round trips, id reuse after a load, errors."""
+    import ctypes
+    import einsummable_b200 as es
+    from einsummable_b200 import _lib
+    lib = _lib.load()
+    km = es.kernel_manager_t(0)
+    sto = ctypes.c_void_p()
+    _lib.check(lib.es_b200_storage_create(1 << 20, 0, ctypes.byref(sto)))
+    x = torch.randn(65536, device="cuda:0")          # 256 KiB
+    y = torch.zeros_like(x)
+    stream = torch.cuda.current_stream().cuda_stream
+    for rep in range(8):                              # 8 x 256 KiB through a 1 MiB arena: blocks must be reused
+        _lib.check(lib.es_b200_evict(km._h, sto, 7, x.data_ptr(), x.numel() * 4, stream))
+        _lib.check(lib.es_b200_evict(km._h, sto, 8 + rep, x.data_ptr(), 1024, stream))
+        _lib.check(lib.es_b200_load(km._h, sto, 7, y.data_ptr(), y.numel() * 4, stream))
+        torch.cuda.synchronize()
+        assert torch.equal(x, y)
+        y.zero_()
+        host = np.zeros(256, np.float32)
+        _lib.check(lib.es_b200_storage_read(sto, 8 + rep, host.ctypes.data_as(ctypes.c_void_p), 1024))
+        assert host.tobytes() == x[:256].cpu().numpy().tobytes()
+        _lib.check(lib.es_b200_storage_remove(sto, 8 + rep))
+    # host-side write, then load
+    w = np.arange(1024, dtype=np.float32)
+    _lib.check(lib.es_b200_storage_write(sto, 3, w.ctypes.data_as(ctypes.c_void_p), 4096))
+    _lib.check(lib.es_b200_load(km._h, sto, 3, y.data_ptr(), 4096, stream))
+    torch.cuda.synchronize()
+    assert y[:1024].cpu().numpy().tobytes() == w.tobytes()
+    # errors: unknown id, id in use, wrong size, out of space
+    assert lib.es_b200_load(km._h, sto, 3, y.data_ptr(), 4096, stream) == _lib.ES_BAD_ARGUMENT
+    _lib.check(lib.es_b200_evict(km._h, sto, 5, x.data_ptr(), 1024, stream))
+    assert lib.es_b200_evict(km._h, sto, 5, x.data_ptr(), 1024, stream) == _lib.ES_BAD_ARGUMENT
+    assert lib.es_b200_load(km._h, sto, 5, y.data_ptr(), 2048, stream) == _lib.ES_BAD_ARGUMENT
+    assert lib.es_b200_evict(km._h, sto, 6, x.data_ptr(), 2 << 20, stream) == _lib.ES_WORKSPACE_TOO_SMALL
+    torch.cuda.synchronize()
+    _lib.check(lib.es_b200_storage_destroy(sto))
+    km.close()

@@ -281,3 +281,24 @@ def test_full_size_fixture_is_present_and_sane():
     assert z["scores"].shape == (4, 32000) and z["scores"].dtype == np.float16
     assert np.isfinite(z["scores"].astype(np.float32)).all() and np.abs(z["scores"]).max() > 1
     assert z["train/loss"].shape == (4,) and np.isfinite(z["train/loss"]).all()
+
+
+EVICT = np.load(os.path.join(GRAPHS, "graphs_evict.npz"))
+
+
+@pytest.mark.parametrize("name", ["c1_n64_evict_locs1", "c1_n64_evict_locs2"])
+def test_oracle_runs_memgraphs_with_evict_and_load(name):
+    """Memgraphs the reference compiled under a memory limit (evict / load nodes, inputs that start
+    out in storage): the oracle's interpreter against the reference's reference_compute_memgraph
+    with storage, bit for bit in interp mode."""
+    mg = load(name)
+    kinds = {n["kind"] for n in mg["nodes"]}
+    assert {"evict", "load", "inputsto"} <= kinds
+    pre = name + "/in/"
+    ins = {k[len(pre):]: EVICT[k] for k in EVICT.files if k.startswith(pre)}
+    storage = {}
+    bufs = O.memgraph_place_inputs(mg, ins, storage)
+    O.run_memgraph(mg, bufs, "interp", storage=storage)
+    got = O.memgraph_collect_outputs(mg, bufs, storage)
+    ref = EVICT[name + "/out/out"]
+    assert got["out"].tobytes() == ref.tobytes()

@@ -76,6 +76,13 @@ def plan(mg, owned, exchange, max_lanes=8, order="memgraph", exchange_lanes=1):
             n = nodes[u["node"]]
             s, d = (n["src_loc"], n["dst_loc"]) if n["kind"] == "move" else (n["loc"], n["loc"])
             prog.add_copy(ptr(s, n["src_offset"]), ptr(d, n["dst_offset"]), n["size"], deps)
+        elif k in ("evict", "load"):
+            n = nodes[u["node"]]
+            host = (1 << 50) + 4096 * n["storage_id"]
+            if k == "evict":
+                prog.add_evict(ptr(n["loc"], n["offset"]), host, n["size"], deps)
+            else:
+                prog.add_load(host, ptr(n["loc"], n["offset"]), n["size"], deps)
         elif k == "signal":
             prog.add_signal([flag(nodes[m]["dst_loc"], 0, m) for m in u["moves"]], deps)
         elif k == "await":
@@ -141,6 +148,11 @@ def regions(mg, u):
         s, d = (n["src_loc"], n["dst_loc"]) if n["kind"] == "move" else (n["loc"], n["loc"])
         return ([(s, n["src_offset"], n["src_offset"] + n["size"], None)],
                 [(d, n["dst_offset"], n["dst_offset"] + n["size"], None)])
+    if k in ("evict", "load"):      # the storage id's host block stands in as a region of its own
+        n = nodes[u["node"]]
+        dev = (n["loc"], n["offset"], n["offset"] + n["size"], None)
+        sto = (("sto", n["storage_loc"]), n["storage_id"], n["storage_id"] + 1, None)
+        return ([dev], [sto]) if k == "evict" else ([sto], [dev])
     if k == "pull":
         return [], [(nodes[m]["dst_loc"], nodes[m]["dst_offset"], nodes[m]["dst_offset"] + nodes[m]["size"], None)
                     for m in u["moves"]]
@@ -179,7 +191,7 @@ def check_plan(mg, units, d):
     return hb
 
 
-SMALL = [("c1_n64_locs2", 2), ("llama_tiny_locs2", 2), ("llama_tiny_locs4", 4), ("llama_train_tiny_locs2", 2),
+SMALL = [("c1_n64_evict_locs1", 1), ("c1_n64_evict_locs2", 2), ("c1_n64_locs2", 2), ("llama_tiny_locs2", 2), ("llama_tiny_locs4", 4), ("llama_train_tiny_locs2", 2),
          ("llama_train_adamw_tiny_locs2", 2)]
 LARGE = [("llama7b_layer_locs1", 1), ("llama7b_layer_locs2", 2), ("llama7b_layer_locs4", 4), ("llama7b_layer_locs8", 8)]
 
@@ -209,7 +221,7 @@ def test_folded_graphs_stay_hazard_free_under_dependency_order(name, world):
 
 
 @pytest.mark.parametrize("order", ["memgraph", "simulated"])
-@pytest.mark.parametrize("name,world", SMALL + LARGE[1:])
+@pytest.mark.parametrize("name,world", SMALL[1:] + LARGE[1:])
 def test_per_rank_schedules_order_every_hazard_and_protect_sources(name, world, order):
     mg = load(name)
     nodes = mg["nodes"]
@@ -241,7 +253,7 @@ def test_per_rank_schedules_order_every_hazard_and_protect_sources(name, world, 
 
 @pytest.mark.parametrize("exchange_lanes", [1, 4])
 @pytest.mark.parametrize("order", ["memgraph", "simulated"])
-@pytest.mark.parametrize("name,world", SMALL + LARGE[1:])
+@pytest.mark.parametrize("name,world", SMALL[1:] + LARGE[1:])
 def test_exchange_never_blocks_over_repeated_runs(name, world, order, exchange_lanes):
     """All ranks' programs executed together with the kernels' semantics: an op starts when the
     op before it on its lane and the ops it waits for have finished; a pull finishes when every
