@@ -117,6 +117,11 @@ SYMBOLS = {
     "es_b200_program_replay_timed": (_i, [_vp, _vp, ctypes.POINTER(ctypes.c_ulonglong), _i]),
     "es_b200_program_reset_epoch": (_i, [_vp]),
     "es_b200_program_describe": (_i, [_vp, _cp, _i, _ip]),
+    "es_b200_wire_to_json": (_i, [_cp, _vp, _u64, _vp, _u64, ctypes.POINTER(_u64)]),
+    "es_b200_wire_from_json": (_i, [_cp, _cp, _vp, _u64, ctypes.POINTER(_u64)]),
+    "es_b200_weight_file_list": (_i, [_cp, _vp, _u64, ctypes.POINTER(_u64), _i, ctypes.POINTER(_i)]),
+    "es_b200_weight_file_read": (_i, [_cp, _cp, _vp, _u64, ctypes.POINTER(_u64)]),
+    "es_b200_weight_file_append": (_i, [_cp, _cp, _vp, _u64]),
     "es_b200_last_error": (_cp, []),
     "es_b200_version": (_cp, []),
 }

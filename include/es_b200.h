@@ -418,6 +418,28 @@ int es_b200_program_reset_epoch(es_b200_program_t* p);
  * With buf == NULL only *needed (bytes incl. the terminator) is returned. */
 int es_b200_program_describe(es_b200_program_t* p, char* buf, int buf_len, int* needed);
 
+/* ---------------------------------------------------------------------------------------------
+ * Interchange formats (host only, no GPU needed).
+ *
+ * The protobuf messages of src/proto/einsummable.proto:5-320 that carry graphs between processes
+ * (memgraph_t::to_wire / from_wire, src/einsummable/memgraph.cc:258-380, src/server/mg_base.cc:118;
+ * likewise taskgraph_t, einsummable_t, touch_t, fill_t, partition_t, placement_t): `message` is the
+ * message name ("MemGraph", "TaskGraph", "Einsummable", ...); the JSON side uses the .proto's field
+ * names, repeated fields as arrays, absent optional fields left out.  With buf == NULL only
+ * *needed is returned.  to_json output is NUL-terminated; from_json output is the raw bytes. */
+int es_b200_wire_to_json(const char* message, const void* bytes, uint64_t n, char* buf, uint64_t buf_len,
+                         uint64_t* needed);
+int es_b200_wire_from_json(const char* message, const char* json, void* buf, uint64_t buf_len, uint64_t* needed);
+
+/* The weight file of llama/from_pth2.py:27-35, read by llama/reader.cc:42-110: records of a 50-byte
+ * space-padded tensor name, an int64 element count and that many f16 values.
+ * list: '\n'-separated names into `names`, element counts into nelems[0..max_records), *count records.
+ * read: the named tensor's f16 values into dst (dst == NULL: only *nelem).  append: one more record. */
+int es_b200_weight_file_list(const char* path, char* names, uint64_t names_len, uint64_t* nelems, int max_records,
+                             int* count);
+int es_b200_weight_file_read(const char* path, const char* tensor_name, void* dst, uint64_t dst_bytes, uint64_t* nelem);
+int es_b200_weight_file_append(const char* path, const char* tensor_name, const void* f16_data, uint64_t nelem);
+
 const char* es_b200_last_error(void);
 const char* es_b200_version(void);
 

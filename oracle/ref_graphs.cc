@@ -131,7 +131,8 @@ string scalar_json(scalar_t const& s)
     for (int i = 0; i != int(dtype_size(s.dtype)); ++i) {
         b[i] = s.data[i]; // bytes past the dtype's size are not part of the value
     }
-    return "{\"dtype\":" + jstr(write_with_ss(s.dtype)) + ",\"raw\":" + jvec(b) + "}";
+    // "text": the form the protobuf messages carry (fill_t::to_proto, src/einsummable/fill.cc:97-118)
+    return "{\"dtype\":" + jstr(write_with_ss(s.dtype)) + ",\"raw\":" + jvec(b) + ",\"text\":" + jstr(write_with_ss(s)) + "}";
 }
 
 void tensor_json(std::ostream& out, built_graph_t const& b, int gid, vtensor_t<int> const& tids,
@@ -461,7 +462,8 @@ int ref_graph_write_json(int h, char const* path)
     built_graph_t const& b = *g_graphs.at(h);
     memgraph_t const&    mg = b.memgraph;
     std::ofstream        out(path);
-    out << "{\"num_locs\":" << mg.num_compute_locs << ",\"mem_sizes\":" << jvec(mg.mem_sizes());
+    out << "{\"num_locs\":" << mg.num_compute_locs << ",\"num_storage_locs\":" << mg.num_storage_locs
+        << ",\"storage_locs\":" << jvec(mg.storage_locs) << ",\"mem_sizes\":" << jvec(mg.mem_sizes());
     // statistics of the taskgraph
     {
         int      n_apply = 0, n_move = 0, n_partialize = 0;
@@ -563,13 +565,13 @@ int ref_graph_write_json(int h, char const* path)
                 << ",\"src_offset\":" << c.src_offset << ",\"dst_offset\":" << c.dst_offset;
         } else if (op.is_partialize()) {
             auto const& x = op.get_partialize();
-            out << ",\"kind\":\"partialize\",\"loc\":" << x.loc;
+            out << ",\"kind\":\"partialize\",\"loc\":" << x.loc << ",\"offset\":" << x.offset << ",\"size\":" << x.size;
         } else if (op.is_alloc()) {
             auto const& x = op.get_alloc();
-            out << ",\"kind\":\"alloc\",\"loc\":" << x.loc;
+            out << ",\"kind\":\"alloc\",\"loc\":" << x.loc << ",\"offset\":" << x.offset << ",\"size\":" << x.size;
         } else if (op.is_del()) {
             auto const& x = op.get_del();
-            out << ",\"kind\":\"del\",\"loc\":" << x.loc;
+            out << ",\"kind\":\"del\",\"loc\":" << x.loc << ",\"offset\":" << x.offset << ",\"size\":" << x.size;
         } else if (op.is_inputsto()) {
             auto const& x = op.get_inputsto();
             out << ",\"kind\":\"inputsto\",\"loc\":" << x.storage_loc << ",\"storage_loc\":" << x.storage_loc
