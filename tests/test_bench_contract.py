@@ -8,18 +8,24 @@ from conftest import ROOT
 
 
 def test_reference_arm_prints_one_json_line_with_the_contract_keys():
+    # torchrun exports OMP_NUM_THREADS=1 to its workers: the arm must set its thread count itself
+    env = dict(os.environ, OMP_NUM_THREADS="1")
     res = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "2",
-                          "--warmup", "1"], capture_output=True, text=True, timeout=300, cwd=ROOT)
+                          "--warmup", "1"], capture_output=True, text=True, timeout=600, cwd=ROOT, env=env)
     assert res.returncode == 0, res.stderr[-2000:]
     lines = [l for l in res.stdout.splitlines() if l.startswith("{")]
     assert len(lines) == 1
     d = json.loads(lines[0])
-    assert d["impl"] == "reference" and d["unit"] == "GB/s" and d["higher_is_better"] is True
+    assert d["impl"] == "reference" and d["unit"] == "tokens/s" and d["higher_is_better"] is True
+    assert d["metric"] == "LLaMA-7B layer tokens/s" and d["scaling"] == "strong"
     assert d["steps"] == 2 and d["warmup"] == 1 and d["n_gpus"] == 1 and d["value"] > 0
-    assert d["cpu_baseline"]["kind"] in ("port", "reference") and d["cpu_baseline"]["cores"] >= 1
+    assert d["cpu_baseline"]["kind"] in ("port", "reference")
+    assert d["cpu_baseline"]["cores"] == (os.cpu_count() or 1)
     assert d["cpu_baseline"]["value"] == d["value"] and d["cpu_baseline"]["sample"]
-    assert d["e2e"] == {"value": d["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
-    assert "workload" in d["config"]
+    assert d["e2e"] == {"value": d["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    assert "workload" in d["config"] and d["config"]["tokens_per_step"] == 2048
+    # the same full-size layer as the GPU arm, and the right answer
+    assert d["parity"]["max_abs_err_over_max_abs_vs_f64_oracle"] <= 1e-2
 
 
 def test_other_ranks_of_the_reference_arm_exit_without_work():

@@ -377,3 +377,64 @@ def test_program_rejects_bad_input():
     d = p.describe()
     assert [op["lane"] for op in d["ops"]] == [0, 0] and d["ops"][1]["wait_on"] == [] and d["n_exchange_lanes"] == 0
     p.close()
+
+
+def _run_units_on_cpu(mg, units, order, inputs):
+    """The units executed by the numpy oracle in the given order (the first-touch rule resolved
+    statically, as the runner does): what any execution that respects only `deps` may compute."""
+    import es_oracle as O
+    nodes = mg["nodes"]
+    storage = {}
+    bufs = O.memgraph_place_inputs(mg, inputs, storage)
+    for i in order:
+        u = units[i]
+        n = dict(nodes[u["node"]])
+        if u["kind"] == "touch":
+            n["group"] = -1 if u["first"] else 1
+            O.run_memgraph({"nodes": [n]}, bufs, "interp", groups_touched=set() if u["first"] else {1}, storage=storage)
+        else:
+            O.run_memgraph({"nodes": [n]}, bufs, "interp", storage=storage)
+    return O.memgraph_collect_outputs(mg, bufs, storage)
+
+
+@pytest.mark.parametrize("name", ["c1_n64_evict_locs1", "c1_n64_evict_locs2", "c1_n64_locs2", "llama_tiny_locs2",
+                                  "llama_train_tiny_locs2"])
+def test_any_order_that_respects_the_dependencies_gives_the_reference_result(name):
+    """The units of a memgraph (all locations in one process) run by the oracle in random topological
+    orders of their `deps`: every such order must give, bit for bit, what the memgraph's own node order
+    gives (which in turn is the reference interpreter's result) -- a missing dependency shows up as a
+    different result, not as a rare race."""
+    import random
+    import numpy as np
+    mg = load(name)
+    arr = np.load(os.path.join(GRAPHS, "graphs_evict.npz" if "evict" in name else "graphs.npz"))
+    pre = name + "/in/"
+    inputs = {k[len(pre):]: arr[k] for k in arr.files if k.startswith(pre)}
+    pre = name + "/out/"
+    want = {k[len(pre):]: arr[k] for k in arr.files if k.startswith(pre)}
+    units = M.schedule_units(mg, set(range(mg["num_locs"])), False)
+    rng = random.Random(7)
+    base = _run_units_on_cpu(mg, units, list(range(len(units))), inputs)
+    for k, ref in want.items():
+        scale = np.abs(ref.astype(np.float64)).max()
+        err = np.abs(base[k].astype(np.float64) - ref.astype(np.float64)).max()
+        assert err <= (2e-3 if ref.dtype == np.float16 else 1e-6) * scale, (name, k, err, scale)
+    for trial in range(3):
+        indeg = [len(u["deps"]) for u in units]
+        children = [[] for _ in units]
+        for i, u in enumerate(units):
+            for d in u["deps"]:
+                children[d].append(i)
+        ready = [i for i, d in enumerate(indeg) if d == 0]
+        order = []
+        while ready:
+            i = ready.pop(rng.randrange(len(ready)) if trial else 0)
+            order.append(i)
+            for c in children[i]:
+                indeg[c] -= 1
+                if indeg[c] == 0:
+                    ready.append(c)
+        assert len(order) == len(units)
+        got = _run_units_on_cpu(mg, units, order, inputs)
+        for k in want:
+            assert got[k].tobytes() == base[k].tobytes(), (name, trial, k)
