@@ -529,6 +529,10 @@ int es_b200_describe(const es_einsummable_desc_t* desc, int what, char* buf, int
             copy_out(log, buf, buf_len);
         } else if (what == 4) {
             copy_out(tc ? cp.info : std::string(), buf, buf_len);
+        } else if (what == 5) {
+            // compile as build() does: through the on-disk kernel cache
+            copy_out(tc ? std::string() : "cubin bytes=" + std::to_string(nvrtc_compile(plan_pointwise(e, false).source).size()),
+                     buf, buf_len);
         } else {
             fail(ES_BAD_ARGUMENT, "describe: unknown selector");
         }

@@ -3,11 +3,91 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <nvrtc.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <cstdio>
+#include <cstdlib>
 
 namespace es {
 
+namespace {
+
+// Compiled kernels are kept across processes: <dir>/<hash of source + compiler version>.cubin.
+// The directory is $ES_B200_CACHE_DIR, else $XDG_CACHE_HOME/es_b200, else ~/.cache/es_b200;
+// ES_B200_CACHE_DIR=0 turns the cache off.  A build() of an einsummable seen before then costs a file
+// read instead of an NVRTC compilation (20-60 ms each; a LLaMA layer has ~25 distinct kernels).
+std::string cache_dir()
+{
+    char const* d = std::getenv("ES_B200_CACHE_DIR");
+    if (d && std::string(d) == "0") return "";
+    std::string dir;
+    if (d && *d) {
+        dir = d;
+    } else if (char const* x = std::getenv("XDG_CACHE_HOME"); x && *x) {
+        dir = std::string(x) + "/es_b200";
+    } else if (char const* h = std::getenv("HOME"); h && *h) {
+        dir = std::string(h) + "/.cache/es_b200";
+    } else {
+        return "";
+    }
+    // two levels at most (~/.cache may not exist yet); failures just mean no cache
+    std::string parent = dir.substr(0, dir.find_last_of('/'));
+    ::mkdir(parent.c_str(), 0755);
+    ::mkdir(dir.c_str(), 0755);
+    return dir;
+}
+
+std::string cache_path(std::string const& source)
+{
+    static std::string const dir = cache_dir();
+    if (dir.empty()) return "";
+    int major = 0, minor = 0;
+    nvrtcVersion(&major, &minor);
+    // FNV-1a, 64 bits, over the compiler version, the target and the source
+    uint64_t    h = 1469598103934665603ull;
+    std::string salt = "nvrtc" + std::to_string(major) + "." + std::to_string(minor) + "|sm_100a|";
+    for (unsigned char c : salt) h = (h ^ c) * 1099511628211ull;
+    for (unsigned char c : source) h = (h ^ c) * 1099511628211ull;
+    char name[40];
+    std::snprintf(name, sizeof name, "%016llx_%zu.cubin", (unsigned long long)h, source.size());
+    return dir + "/" + name;
+}
+
+bool read_file(std::string const& path, std::vector<char>& out)
+{
+    std::FILE* f = std::fopen(path.c_str(), "rb");
+    if (!f) return false;
+    std::fseek(f, 0, SEEK_END);
+    long n = std::ftell(f);
+    std::fseek(f, 0, SEEK_SET);
+    out.resize(n > 0 ? (size_t)n : 0);
+    bool ok = n > 0 && std::fread(out.data(), 1, (size_t)n, f) == (size_t)n;
+    std::fclose(f);
+    return ok;
+}
+
+void write_file(std::string const& path, std::vector<char> const& data)
+{
+    // write beside and rename: another process may be reading or writing the same kernel
+    std::string tmp = path + "." + std::to_string((long)::getpid()) + ".tmp";
+    std::FILE*  f = std::fopen(tmp.c_str(), "wb");
+    if (!f) return;
+    bool ok = std::fwrite(data.data(), 1, data.size(), f) == data.size();
+    std::fclose(f);
+    if (ok) std::rename(tmp.c_str(), path.c_str());
+    else std::remove(tmp.c_str());
+}
+
+} // namespace
+
 std::vector<char> nvrtc_compile(std::string const& source, std::string* log_out)
 {
+    std::string const cached = log_out ? std::string() : cache_path(source);
+    if (!cached.empty()) {
+        std::vector<char> cubin;
+        if (read_file(cached, cubin)) return cubin;
+    }
     nvrtcProgram prog;
     if (nvrtcCreateProgram(&prog, source.c_str(), "es_kernel.cu", 0, nullptr, nullptr) !=
         NVRTC_SUCCESS) {
@@ -35,6 +115,7 @@ std::vector<char> nvrtc_compile(std::string const& source, std::string* log_out)
     std::vector<char> cubin(size);
     nvrtcGetCUBIN(prog, cubin.data());
     nvrtcDestroyProgram(&prog);
+    if (!cached.empty()) write_file(cached, cubin);
     return cubin;
 }
 

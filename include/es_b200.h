@@ -237,7 +237,10 @@ int es_b200_kernel_info(es_b200_t* h, uint64_t kernel_id, char* buf, int buf_len
  * 0 = merged form "str|join_shape|out_rank|inns", 1 = kernel kind,
  * 2 = generated CUDA source (empty for precompiled kinds),
  * 3 = compile the generated source for sm_100a and return the log,
- * 4 = the tensor-core contraction's plan (tile shape, stages, schedule; empty for other kinds). */
+ * 4 = the tensor-core contraction's plan (tile shape, stages, schedule; empty for other kinds),
+ * 5 = compile the generated source the way build() does -- through the kernel cache on disk
+ *     ($ES_B200_CACHE_DIR, default ~/.cache/es_b200, "0" = off: one file per kernel source and compiler
+ *     version, so that a later process pays a file read instead of an NVRTC run) -- and return its size. */
 int es_b200_describe(const es_einsummable_desc_t* desc, int what, char* buf, int buf_len);
 
 /* Simplify a touch (src/einsummable/touch.cc:3-28); returns the new rank in

@@ -207,3 +207,36 @@ def test_multiply_high_division_is_exact_below_2_31():
         for n in edge + [rng.randrange(0, 1 << 31) for _ in range(200)]:
             if 0 <= n < (1 << 31):
                 assert div(n, d, f) == n // d, (n, d)
+
+
+def test_generated_kernels_are_cached_on_disk(tmp_path):
+    """build() compiles through a cache directory: the second process (here: the second call with a
+    fresh library state is not needed -- the file is what matters) finds the cubin instead of running NVRTC."""
+    import subprocess
+    import sys
+    import time
+    code = (
+        "import sys, time, ctypes; sys.path.insert(0, %r)\n"
+        "from einsummable_b200 import _lib\n"
+        "from einsummable_b200.einsummable import einsummable_t\n"
+        "from einsummable_b200.scalarop import scalarop_t as S\n"
+        "lib = _lib.load()\n"
+        "e = einsummable_t([1234, 512], [[0, 1], [0, 1]], 2, S.combine(S.make_mul('f16'), [S.make_silu('f16'), S.make_identity('f16')]))\n"
+        "buf = ctypes.create_string_buffer(256)\n"
+        "t0 = time.time(); _lib.check(lib.es_b200_describe(ctypes.byref(e.to_desc()), 5, buf, 256)); print(buf.value.decode(), time.time() - t0)\n"
+    ) % (ROOT,)
+    env = dict(os.environ, ES_B200_CACHE_DIR=str(tmp_path / "kernels"))
+    first = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=120)
+    assert first.returncode == 0, first.stderr[-1000:]
+    files = os.listdir(tmp_path / "kernels")
+    assert len(files) == 1 and files[0].endswith(".cubin")
+    size = os.path.getsize(tmp_path / "kernels" / files[0])
+    assert first.stdout.split()[1] == "bytes=%d" % size
+    stamp = os.path.getmtime(tmp_path / "kernels" / files[0])
+    second = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=120)
+    assert second.returncode == 0 and second.stdout.split()[1] == "bytes=%d" % size
+    assert os.path.getmtime(tmp_path / "kernels" / files[0]) == stamp          # read, not rewritten
+    assert float(second.stdout.split()[2]) < float(first.stdout.split()[2])    # a file read beats a compilation
+    off = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True,
+                         env=dict(env, ES_B200_CACHE_DIR="0"), timeout=120)
+    assert off.returncode == 0 and len(os.listdir(tmp_path / "kernels")) == 1
