@@ -40,11 +40,14 @@ BYTES_ROWSUM = N * 2 + ROWS * 2
 BYTES_STEP = BYTES_SILU_MUL + BYTES_ROWMAX + BYTES_EXP_SUB + BYTES_ROWSUM
 WORKLOAD = "C2 f16 [8192,11008]: silu(x)*y; rowmax; exp(x-rowmax); rowsum"
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the silu*y kernel: ncu capture of
-# the [4096,11008] case (180.37 MB read + 47.75 MB written, profiles/c2_kernels_f16_4096x11008.md)
-# scaled x2 to the full launch.  Below the algorithmic 541 MB because part of the output is still
-# dirty in the 126 MB L2 when the kernel ends.
-SILU_MUL_DRAM_TRAFFIC = 2 * (180374528 + 47752960)
+def profiled_traffic(key):
+    """dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the committed table of ncu
+    captures (profiles/traffic.json); None when that kernel was not captured."""
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    if not os.path.exists(path):
+        return None
+    with open(path) as f:
+        return json.load(f).get(key)
 
 
 def set_rows(rows):
@@ -670,7 +673,7 @@ def c2_step_leg(km, dev, stream, peaks, steps=20):
     return {"workload": WORKLOAD, "ms_per_step": round(ms, 4), "GB/s": round(BYTES_STEP / (ms * 1e-3) / 1e9, 1),
             "frac_of_hbm_peak": round(BYTES_STEP / (ms * 1e-3) / 1e9 / peak, 3),
             "per_kernel_frac": {n: round(b / (t * 1e-3) / 1e9 / peak, 3) for n, t, b in zip(names, per, nbytes)},
-            "silu_mul_dram_traffic_per_launch": SILU_MUL_DRAM_TRAFFIC if ROWS == 8192 else None,
+            "silu_mul_dram_traffic_per_launch": profiled_traffic("silu_mul f16 [8192,11008]") if ROWS == 8192 else None,
             "kernels": dict(zip(names, [km.kernel_info(e).split("|")[0] for e in ops]))}
 
 

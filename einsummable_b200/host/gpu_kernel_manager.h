@@ -8,7 +8,8 @@
 // (src/server/gpu/server.cc:39-43) compile against it unchanged.  All work is
 // forwarded to the C ABI of libes_b200.so; no cuBLAS / cuTENSOR is involved.
 //
-// Place this file and gpu_kernel_manager.cc in src/engine/gpu/ (see INTEGRATION.md).
+// Place this file and gpu_kernel_manager.cc in src/engine/gpu/, in place of the reference's two files of
+// the same names, and link libes_b200.so instead of cuTENSOR / cuBLAS.
 #pragma once
 #include "../../base/setup.h"
 

@@ -28,17 +28,28 @@ def regular_rowsum(km, x, rows, cols):
     return out.cpu().numpy(), km.kernel_info(e)
 
 
-@pytest.mark.parametrize("rows,cols", [(3, 1 << 20), (64, 40000), (5, 100003)])
-def test_noalloc_rowsum_matches_regular_entry_point_twice(rows, cols):
+# beyond the three basic shapes: more rows than one block of the second pass handles (1000), the
+# largest row count the scratch allows (65536: one partial per row), and -- `offset` -- an input that
+# starts one float past a 16-byte boundary although cols % 4 == 0, which takes the scalar loads
+@pytest.mark.parametrize("rows,cols,offset", [(3, 1 << 20, 0), (64, 40000, 0), (5, 100003, 0), (1000, 4096, 0),
+                                              (65536, 8, 0), (5, 4096, 1)])
+def test_noalloc_rowsum_matches_regular_entry_point_twice(rows, cols, offset):
     km = es.kernel_manager_t(0)
     rng = np.random.default_rng(11)
+    warm = torch.zeros(8, dtype=torch.float32, device="cuda:0")
+    km.rowsum_f32_noalloc(None, warm[:2], warm, 2, 4)      # the first call on the device looks up the array
+    torch.cuda.synchronize()
     for call in range(2):
         host = rng.standard_normal(rows * cols).astype(np.float32) * (call + 1)
-        x = torch.from_numpy(host).cuda()
-        want, info = regular_rowsum(km, x, rows, cols)
+        x = torch.from_numpy(np.concatenate([np.zeros(offset, np.float32), host])).cuda()[offset:]
+        want, info = regular_rowsum(km, x.clone(), rows, cols)
         got = torch.full((rows,), float("nan"), dtype=torch.float32, device="cuda:0")
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info(0)[0]
         km.rowsum_f32_noalloc(None, got, x, rows, cols)
         torch.cuda.synchronize()
+        # the point of the entry point: the device's free memory is what it was (nothing was allocated)
+        assert torch.cuda.mem_get_info(0)[0] == free_before
         got = got.cpu().numpy()
         # f32 sums of N(0, s) terms: 1e-5 of the scale of the partial sums
         tol = 1e-5 * np.sqrt(cols) * (call + 1) * 4
