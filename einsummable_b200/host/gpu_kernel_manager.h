@@ -70,6 +70,17 @@ struct kernel_manager_t {
     // copy `size` bytes from (src_device, src) into dst on this manager's device.
     void move(int src_device, void const* src, void* dst, uint64_t size, cudaStream_t stream) const;
 
+    // For callers that hand built kernels to the library's program executor (gpu_program.h): the
+    // library handle of this device and the id build() gave the (merged) einsummable.
+    es_b200_t* c_handle() const
+    {
+        return handle;
+    }
+    uint64_t kernel_id(einsummable_t const& e) const
+    {
+        return get_built_kernel_info(e).kernel_id;
+    }
+
 private:
     struct built_t {
         uint64_t kernel_id;

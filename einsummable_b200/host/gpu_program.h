@@ -1,0 +1,48 @@
+// gpu_program_t: the nodes of a memgraph that run on one GPU, compiled once into a program of the
+// es_b200 library's executor and replayed without the host in the loop.
+//
+// An alternative to exec_graph_t::make_gpu_exec_graph + exec_state_t::event_loop
+// (src/engine/gpu/exec_graph.cc:37-256, src/engine/exec_state.cc:110-219) for the part of
+// gpu_mg_server_t::execute_memgraph (src/server/gpu/server.cc:96-136) that runs on one device: the same
+// memgraph_t, the same kernel_manager_t, the same global buffer -- but every op is ordered behind
+// exactly the ops it depends on by CUDA events (or CUDA-graph edges) instead of being launched from a
+// stream callback of its predecessors.
+//
+// Place beside gpu_kernel_manager.{h,cc} in src/engine/gpu/.  One location per program; moves to or from
+// other locations are not handled here (a box driven by one process needs one program per device and
+// events between them; processes that each drive one GPU use the exchange ops of es_b200.h).
+#pragma once
+#include "../../base/setup.h"
+
+#include "../../einsummable/memgraph.h"
+#include "gpu_kernel_manager.h"
+
+struct gpu_program_t {
+    // mem: the global buffer of location `loc` (server.cc:38-43).  The kernel manager must outlive the program.
+    gpu_program_t(memgraph_t const&            memgraph,
+                  int                          loc,
+                  kernel_manager_t&            km,
+                  void*                        mem,
+                  map<string, scalar_t> const& scalar_vars = {},
+                  int                          max_lanes = 16);
+    ~gpu_program_t();
+
+    gpu_program_t(gpu_program_t const&) = delete;
+    gpu_program_t& operator=(gpu_program_t const&) = delete;
+
+    // One run, asynchronous on `stream` (which continues when every op has finished).
+    void launch(cudaStream_t stream);
+    // The run as one CUDA graph: instantiate() once (after one launch()), then replay().
+    void instantiate();
+    void replay(cudaStream_t stream);
+
+    int num_ops() const
+    {
+        return n_ops;
+    }
+
+private:
+    es_b200_program_t* prog;
+    void*              workspace;
+    int                n_ops;
+};

@@ -12,14 +12,18 @@
 //   One location (one GPU).  Writes <dir>/memgraph.json (ref_graph_write_json), reads
 //   <dir>/in.bin (the location buffer with the inputs in place; absent: the buffer is filled with
 //   the byte 0x2e, finite small values in every dtype, for timing runs), runs the event loop
-//   <iters> times, writes <dir>/out.bin (the location buffer afterwards) and prints one JSON line
-//   with the time of build and of each event loop.
+//   <iters> times, writes <dir>/out.bin (the location buffer afterwards); then puts the inputs back
+//   and runs the same memgraph through gpu_program_t (einsummable_b200/host/gpu_program.*: the
+//   library's dependency-ordered program instead of the event loop, built from the same memgraph_t by
+//   C++ code alone), eagerly and as a CUDA-graph replay, and writes <dir>/out_program.bin.  Prints one
+//   JSON line with the times.
 #include "src/engine/exec_graph.h"
 #include "src/engine/exec_state.h"
 #include "src/engine/managers.h"
 #include "src/engine/gpu/workspace.h"
 #include "src/engine/gpu/stream_pool.h"
 #include "src/engine/gpu/gpu_kernel_manager.h"
+#include "src/engine/gpu/gpu_program.h"
 
 #include <cuda_runtime.h>
 
@@ -111,10 +115,58 @@ int main(int argc, char** argv)
             std::ofstream out(dir + "/out.bin", std::ios::binary);
             out.write(host.data(), mem_size);
         }
+        // the same memgraph through the program executor
+        vector<double> eager, replay;
+        int            program_ops = 0;
+        double         t_program_build = 0;
+        if (iters > 0) {
+            std::ifstream in(dir + "/in.bin", std::ios::binary);
+            if (in) {
+                vector<char> host(mem_size);
+                in.read(host.data(), mem_size);
+                handle_cuda_error(cudaMemcpy(mem, host.data(), mem_size, cudaMemcpyHostToDevice));
+            } else {
+                handle_cuda_error(cudaMemset(mem, 0x2e, mem_size));
+            }
+            double        t2 = now_ms();
+            gpu_program_t program(memgraph, 0, kernel_managers[0], mem);
+            t_program_build = now_ms() - t2;
+            program_ops = program.num_ops();
+            cudaStream_t stream;
+            handle_cuda_error(cudaStreamCreate(&stream));
+            for (int it = 0; it != iters; ++it) {
+                double t1 = now_ms();
+                program.launch(stream);
+                handle_cuda_error(cudaStreamSynchronize(stream));
+                eager.push_back(now_ms() - t1);
+            }
+            {
+                vector<char> host(mem_size);
+                handle_cuda_error(cudaMemcpy(host.data(), mem, mem_size, cudaMemcpyDeviceToHost));
+                std::ofstream out(dir + "/out_program.bin", std::ios::binary);
+                out.write(host.data(), mem_size);
+            }
+            program.instantiate();
+            for (int it = 0; it != iters; ++it) {
+                double t1 = now_ms();
+                program.replay(stream);
+                handle_cuda_error(cudaStreamSynchronize(stream));
+                replay.push_back(now_ms() - t1);
+            }
+            handle_cuda_error(cudaStreamDestroy(stream));
+        }
+        auto list = [](vector<double> const& v) {
+            std::stringstream ss;
+            ss << "[";
+            for (size_t i = 0; i != v.size(); ++i) ss << (i ? ", " : "") << v[i];
+            ss << "]";
+            return ss.str();
+        };
         std::cout << "{\"mem_size\": " << mem_size << ", \"exec_nodes\": " << graph.nodes.size()
-                  << ", \"build_ms\": " << t_build << ", \"event_loop_ms\": [";
-        for (size_t i = 0; i != loops.size(); ++i) std::cout << (i ? ", " : "") << loops[i];
-        std::cout << "]}" << std::endl;
+                  << ", \"build_ms\": " << t_build << ", \"event_loop_ms\": " << list(loops)
+                  << ", \"program_ops\": " << program_ops << ", \"program_build_ms\": " << t_program_build
+                  << ", \"program_eager_ms\": " << list(eager) << ", \"program_replay_ms\": " << list(replay) << "}"
+                  << std::endl;
         return 0;
     } catch (std::exception const& e) {
         std::cerr << "engine_parity: " << e.what() << std::endl;

@@ -255,6 +255,41 @@ int ref_graph_build_llama(uint64_t dim,
     G_END
 }
 
+// config 4 with the autoplacer's knobs exposed (autoplace_config_t, src/autoplace/autoplace.h:6-66):
+// flops_per_byte_moved (default 1000), search space 0 contraction / 1 all / 2 all_range (default),
+// max_branching (default 2), discount_input_factor (default 1)
+int ref_graph_build_llama_cfg(uint64_t dim, uint64_t n_heads, uint64_t multiple_of, uint64_t vocab_size, int n_layers,
+                              uint64_t batch, uint64_t seqlen, int nlocs, int dtype_code, uint64_t fpbm, int space,
+                              int branching, uint64_t discount)
+{
+    G_BEGIN
+    set_default_dtype(dtype_code == 0 ? dtype_t::f16 : dtype_t::f32);
+    model_args_t args = model_args_t::llama_7B(batch);
+    args.dim = dim;
+    args.n_heads = n_heads;
+    args.multiple_of = multiple_of;
+    args.vocab_size = vocab_size;
+    args.n_layers = n_layers;
+    args.max_seq_len = seqlen;
+    builder_t builder = builder_t::make_first_token(args, seqlen);
+    auto*     b = new built_graph_t();
+    b->graph = builder.graph;
+    parts_space_t sp = space == 0 ? parts_space_t::contraction : (space == 1 ? parts_space_t::all : parts_space_t::all_range);
+    vector<partition_t> parts = apart01(b->graph, nlocs, branching, discount, sp);
+    b->placements = alocate01(b->graph, parts, nlocs, fpbm);
+    for (auto const& [name, gid] : builder.weights) {
+        b->names[gid] = name;
+    }
+    b->names[builder.freqs_cis] = "freqs_cis";
+    b->names[builder.embeddings] = "embeddings";
+    if (builder.mask) {
+        b->names[builder.mask.value()] = "mask";
+    }
+    b->names[builder.scores] = "scores";
+    return finish(b);
+    G_END
+}
+
 // config 5: forward + backward + vanilla weight update of n_layers LLaMA layers
 int ref_graph_build_llama_train(uint64_t dim,
                                 uint64_t n_heads,

@@ -6,7 +6,9 @@ workspace / group / buffer managers and event loop -- src/engine/exec_graph.cc, 
 gpu/exec_graph.cc, ... compiled unchanged -- linked with the drop-in kernel_manager_t instead of
 the reference's cuTENSOR one.  It builds the memgraph in-process with the reference's compilers,
 runs exec_state_t::event_loop on it and hands back the location buffer; the saved tensors are
-compared with what the reference's interpreter computed for the same inputs (tests/golden/graphs)."""
+compared with what the reference's interpreter computed for the same inputs (tests/golden/graphs).
+The same binary then runs the same memgraph_t through gpu_program_t (einsummable_b200/host/gpu_program.*,
+C++ host code over the C ABI's program executor) and hands back that buffer too."""
 import json
 import os
 import subprocess
@@ -44,6 +46,8 @@ def run_engine(spec, tmp_path, inputs=None, iters=2):
         mg = json.load(f)
     info = json.loads([l for l in res.stdout.splitlines() if l.startswith("{")][-1])   # the engine prints, too
     out = np.fromfile(tmp_path / "out.bin", dtype=np.uint8)
+    if os.path.exists(tmp_path / "out_program.bin"):
+        info["out_program"] = np.fromfile(tmp_path / "out_program.bin", dtype=np.uint8)
     return mg, info, out
 
 
@@ -66,6 +70,16 @@ def test_reference_engine_runs_memgraphs_on_the_drop_in(name, spec, tmp_path):
         assert err <= (2e-2 if ref.dtype == np.float16 else 1e-5) * scale, (name, k, err, scale)
         checked += 1
     assert checked >= 1
+    # the same memgraph_t through gpu_program_t (C++ host code only: the library's dependency-ordered
+    # program instead of the event loop) gives the same saved tensors
+    got2 = O.memgraph_collect_outputs(mg, [np.concatenate([info.pop("out_program"), np.zeros(256, np.uint8)])])
+    assert info["program_ops"] > 0
+    for k in ARR.files:
+        if k.startswith(pre):
+            ref = ARR[k]
+            scale = np.abs(ref.astype(np.float64)).max()
+            err = np.abs(got2[k[len(pre):]].astype(np.float64) - ref.astype(np.float64)).max()
+            assert err <= (2e-2 if ref.dtype == np.float16 else 1e-5) * scale, ("program", name, k, err, scale)
     print(name, info)
 
 
@@ -76,5 +90,10 @@ def test_reference_engine_llama7b_layer_times(tmp_path):
     mg, info, out = run_engine("llama:4096:32:256:32000:1:4:512:0", tmp_path, None, iters=5)
     assert info["exec_nodes"] == len(mg["nodes"])
     loops = info["event_loop_ms"]
+    info.pop("out_program", None)
     print("reference engine on the drop-in, LLaMA-7B layer: build %.0f ms, event loops %s ms" % (info["build_ms"], loops))
+    print("the same memgraph_t through gpu_program_t (C++ host): %d ops, eager %s ms, CUDA-graph replay %s ms"
+          % (info["program_ops"], info["program_eager_ms"], info["program_replay_ms"]))
     assert min(loops) < 50.0
+    # host wall clock incl. the synchronise: the program must beat the callback-driven loop clearly
+    assert min(info["program_replay_ms"]) < 0.5 * min(loops)
