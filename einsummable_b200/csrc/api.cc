@@ -17,6 +17,7 @@
 #include "handle.h"
 #include "kernels.h"
 #include "exchange.h"
+#include "pdl.h"
 
 namespace es {
 
@@ -25,6 +26,12 @@ static thread_local std::string g_last_error;
 void set_last_error(std::string const& msg)
 {
     g_last_error = msg;
+}
+
+bool& pdl_launch_flag()
+{
+    static thread_local bool flag = false;
+    return flag;
 }
 
 } // namespace es

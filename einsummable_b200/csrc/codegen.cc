@@ -272,6 +272,10 @@ struct ctx_t {
         args += ", void* ws_";
         s.add("extern \"C\" __global__ void __launch_bounds__(%d) %s(%s) {", block, name,
               args.c_str());
+        // programmatic dependent launch (see pdl.h): release the next kernel of the lane, then wait
+        // for the one before; both are no-ops for ordinary launches
+        s.add("  asm volatile(\"griddepcontrol.launch_dependents;\");");
+        s.add("  asm volatile(\"griddepcontrol.wait;\" ::: \"memory\");");
         s.add("  %s* out = (%s*)out_;", storage_type(e.out_dtype()), storage_type(e.out_dtype()));
         for (int k = 0; k != n; ++k) {
             char const* t = storage_type(e.inn_dtype(k));

@@ -25,6 +25,7 @@
 // Every wait on an mbarrier is bounded by a clock limit; on expiry the kernel
 // records an error word, lets in-flight copies land, frees its TMEM and returns.
 #include "contraction.h"
+#include "pdl.h"
 
 #include <cuda.h>
 
@@ -467,6 +468,8 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    // everything above touched shared memory and TMEM only; global memory from here on
+    ES_PDL_WAIT();
     uint32_t const tmem_base = ctrl->tmem_base;
 
     uint32_t const k_iters = p.k_blocks * p.kouter_total;
@@ -808,6 +811,7 @@ tc_contraction_kernel(const __grid_constant__ tc_params_t p, void* __restrict__ 
 __global__ void __launch_bounds__(256) split_tf32_kernel(float const* x, float* hi, float* __restrict__ lo,
                                                          uint64_t n4) // hi may alias x (in-place split)
 {
+    ES_PDL_PROLOGUE();
     uint64_t nth = (uint64_t)gridDim.x * blockDim.x;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += nth) {
         float4 v = reinterpret_cast<float4 const*>(x)[i];
@@ -1267,7 +1271,7 @@ void launch_contraction(contraction_plan_t const& plan,
             if (p.n_terms == 2) {
                 float* hi = region;
                 float* lo = region + elems;
-                split_tf32_kernel<<<blocks(elems / 4), 256, 0, stream>>>(cur, hi, lo, elems / 4);
+                launch_k(split_tf32_kernel, dim3(blocks(elems / 4)), dim3(256), 0, stream, cur, hi, lo, elems / 4);
                 encode_map(&tm[0], rc, hi, true);
                 encode_map(&tm[1], rc, lo, true);
             } else {
@@ -1291,7 +1295,7 @@ void launch_contraction(contraction_plan_t const& plan,
             ES_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
             attr_set[slot][dev & 63] = true;
         }
-        kernel<<<tp.grid, NUM_THREADS, tp.smem_bytes, stream>>>(p, out);
+        launch_k(kernel, dim3(tp.grid), dim3(NUM_THREADS), tp.smem_bytes, stream, p, out);
     };
     if (tp.kind == 0 && p.mh == 2) launch(tc_contraction_kernel<0, false, true>, 3);
     else if (tp.kind == 0) launch(tc_contraction_kernel<0, false, false>, 0);

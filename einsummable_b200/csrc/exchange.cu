@@ -19,6 +19,7 @@
 
 #include "common.h"
 #include "exchange.h"
+#include "pdl.h"
 
 namespace es {
 
@@ -51,6 +52,7 @@ __device__ __forceinline__ bool spin_until(uint32_t const* flag, uint32_t epoch,
 
 __global__ void stamp_kernel(unsigned long long* slot)
 {
+    ES_PDL_PROLOGUE();
     if (blockIdx.x == 0 && threadIdx.x == 0) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -60,11 +62,13 @@ __global__ void stamp_kernel(unsigned long long* slot)
 
 __global__ void epoch_bump_kernel(uint32_t* epoch)
 {
+    ES_PDL_PROLOGUE();
     if (blockIdx.x == 0 && threadIdx.x == 0) *epoch = *epoch + 1;
 }
 
 __global__ void signal_many_kernel(uint32_t* const* __restrict__ flags, int n, uint32_t const* __restrict__ epoch)
 {
+    ES_PDL_PROLOGUE();
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     uint32_t e = *epoch;
@@ -77,6 +81,7 @@ __global__ void wait_many_kernel(uint32_t* const* __restrict__ flags,
                                  uint32_t const* __restrict__  epoch,
                                  unsigned long long            limit_cycles)
 {
+    ES_PDL_PROLOGUE();
     uint32_t e = *epoch;
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         if (!spin_until(flags[i], e, limit_cycles)) atomicCAS(&g_exchange_error, 0u, 4u);
@@ -88,6 +93,7 @@ __global__ void __launch_bounds__(256) pull_batch_kernel(pull_item_t const* __re
                                                          uint32_t const* __restrict__    epoch,
                                                          unsigned long long              limit_cycles)
 {
+    ES_PDL_PROLOGUE();
     pull_item_t const it = items[blockIdx.y];
     if (blockIdx.x >= it.n_ctas) return;
     __shared__ int ok;
@@ -148,27 +154,27 @@ uint32_t pull_ctas_for(uint64_t bytes)
 
 void launch_stamp(unsigned long long* slot_dev, cudaStream_t s)
 {
-    stamp_kernel<<<1, 32, 0, s>>>(slot_dev);
+    launch_k(stamp_kernel, dim3(1), dim3(32), 0, s, slot_dev);
     ES_CUDA_CHECK(cudaGetLastError());
 }
 
 void launch_epoch_bump(uint32_t* epoch_dev, cudaStream_t s)
 {
-    epoch_bump_kernel<<<1, 32, 0, s>>>(epoch_dev);
+    launch_k(epoch_bump_kernel, dim3(1), dim3(32), 0, s, epoch_dev);
     ES_CUDA_CHECK(cudaGetLastError());
 }
 
 void launch_signal_many(uint32_t* const* flags_dev, int n, uint32_t const* epoch_dev, cudaStream_t s)
 {
     if (n <= 0) return;
-    signal_many_kernel<<<(n + 127) / 128, 128, 0, s>>>(flags_dev, n, epoch_dev);
+    launch_k(signal_many_kernel, dim3((n + 127) / 128), dim3(128), 0, s, flags_dev, n, epoch_dev);
     ES_CUDA_CHECK(cudaGetLastError());
 }
 
 void launch_wait_many(uint32_t* const* flags_dev, int n, uint32_t const* epoch_dev, uint32_t limit_ms, cudaStream_t s)
 {
     if (n <= 0) return;
-    wait_many_kernel<<<1, std::min(n, 256), 0, s>>>(flags_dev, n, epoch_dev, limit_cycles_of(limit_ms));
+    launch_k(wait_many_kernel, dim3(1), dim3(std::min(n, 256)), 0, s, flags_dev, n, epoch_dev, limit_cycles_of(limit_ms));
     ES_CUDA_CHECK(cudaGetLastError());
 }
 
@@ -182,7 +188,7 @@ void launch_pull_batch(pull_item_t const* items_dev,
 {
     if (n <= 0) return;
     dim3 grid(max_ctas, (unsigned)n);
-    pull_batch_kernel<<<grid, 256, 0, s>>>(items_dev, counters_dev, epoch_dev, limit_cycles_of(limit_ms));
+    launch_k(pull_batch_kernel, grid, dim3(256), 0, s, items_dev, counters_dev, epoch_dev, limit_cycles_of(limit_ms));
     ES_CUDA_CHECK(cudaGetLastError());
 }
 

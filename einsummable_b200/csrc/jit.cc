@@ -1,4 +1,5 @@
 #include "jit.h"
+#include "pdl.h"
 
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -138,6 +139,7 @@ struct driver_t {
     decltype(&cuLaunchKernel)      launch_kernel;
     decltype(&cuGetErrorString)    get_error_string;
     decltype(&cuFuncSetAttribute)  func_set_attribute;
+    decltype(&cuLaunchKernelEx)    launch_kernel_ex;
 };
 
 driver_t const& driver()
@@ -151,6 +153,7 @@ driver_t const& driver()
         x.launch_kernel = (decltype(x.launch_kernel))driver_entry("cuLaunchKernel");
         x.get_error_string = (decltype(x.get_error_string))driver_entry("cuGetErrorString");
         x.func_set_attribute = (decltype(x.func_set_attribute))driver_entry("cuFuncSetAttribute");
+        x.launch_kernel_ex = (decltype(x.launch_kernel_ex))driver_entry("cuLaunchKernelEx");
         return x;
     }();
     return d;
@@ -201,6 +204,22 @@ void launch_function(
                                              CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES,
                                              (int)smem),
                  "cuFuncSetAttribute");
+    }
+    if (pdl_launch_flag()) {
+        CUlaunchConfig cfg = {};
+        cfg.gridDimX = grid;
+        cfg.gridDimY = cfg.gridDimZ = 1;
+        cfg.blockDimX = block;
+        cfg.blockDimY = cfg.blockDimZ = 1;
+        cfg.sharedMemBytes = smem;
+        cfg.hStream = (CUstream)stream;
+        CUlaunchAttribute attr[1];
+        attr[0].id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+        attr[0].value.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cu_check(driver().launch_kernel_ex(&cfg, (CUfunction)fn, args, nullptr), "cuLaunchKernelEx");
+        return;
     }
     cu_check(driver().launch_kernel(
                  (CUfunction)fn, grid, 1, 1, block, 1, 1, smem, (CUstream)stream, args, nullptr),

@@ -10,6 +10,7 @@
 // src/engine/gpu/cuda_kernels.cu:99-246 (per-element dtype switch, threadIdx.x
 // on the slowest dim for rank 3/4).
 #include "kernels.h"
+#include "pdl.h"
 
 #include <algorithm>
 #include <cstring>
@@ -214,6 +215,7 @@ __device__ __forceinline__ void touch_dispatch(touch_args_t const& a, uint32_t s
 template <int W, int DT>
 __global__ void __launch_bounds__(TOUCH_BLOCK) touch_kernel(const __grid_constant__ touch_args_t a)
 {
+    ES_PDL_PROLOGUE();
     uint32_t slot0 = blockIdx.x * (TOUCH_BLOCK * TOUCH_UNROLL) + threadIdx.x;
     touch_dispatch<W, DT>(a, slot0, TOUCH_BLOCK);
     if (a.done != nullptr) {
@@ -235,6 +237,7 @@ __global__ void __launch_bounds__(TOUCH_BLOCK) touch_kernel(const __grid_constan
 template <int W, int DT>
 __global__ void __launch_bounds__(TOUCH_BLOCK) touch_batch_kernel(touch_args_t const* items)
 {
+    ES_PDL_PROLOGUE();
     __shared__ touch_args_t a;
     {
         uint32_t const* src = reinterpret_cast<uint32_t const*>(items + blockIdx.y);
@@ -249,6 +252,7 @@ __global__ void __launch_bounds__(TOUCH_BLOCK) touch_batch_kernel(touch_args_t c
 
 template <typename T> __global__ void fill_constant_kernel(T* out, T v, uint64_t n)
 {
+    ES_PDL_PROLOGUE();
     // 16-byte stores over the aligned body, scalar head/tail
     constexpr int PER = 16 / sizeof(T);
     uint64_t      head = ((16 - (reinterpret_cast<uintptr_t>(out) & 15)) & 15) / sizeof(T);
@@ -272,6 +276,7 @@ template <typename T> __global__ void fill_constant_kernel(T* out, T v, uint64_t
 template <typename T>
 __global__ void fill_lowertri_kernel(T* out, T lower, T upper, int64_t nrow, int64_t ncol, int64_t start)
 {
+    ES_PDL_PROLOGUE();
     int64_t n = nrow * ncol;
     int64_t nth = (int64_t)gridDim.x * blockDim.x;
     for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += nth) {
@@ -288,6 +293,7 @@ __global__ void __launch_bounds__(256) pull_copy_kernel(uint4 const* __restrict_
                                                         unsigned char* __restrict__ dst_tail,
                                                         uint32_t ntail)
 {
+    ES_PDL_PROLOGUE();
     uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     uint64_t nth = (uint64_t)gridDim.x * blockDim.x;
     uint64_t i = tid;
@@ -321,6 +327,7 @@ __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v)
 __global__ void flag_kernel(uint32_t* flag, uint32_t expected, uint32_t next, unsigned long long limit_cycles,
                             unsigned int code)
 {
+    ES_PDL_PROLOGUE();
     if (threadIdx.x != 0 || blockIdx.x != 0) return;
     long long t0 = clock64();
     while (ld_acquire_sys(flag) != expected) {
@@ -462,7 +469,7 @@ template <int W, int DT> static void launch_touch_wd(touch_args_t const& a, cuda
     uint64_t per = (uint64_t)TOUCH_BLOCK * TOUCH_UNROLL;
     uint64_t grid = (a.total_slots + per - 1) / per;
     if (grid > 0x7fffffffull) fail(ES_NOT_SUPPORTED, "touch grid too large");
-    touch_kernel<W, DT><<<(unsigned)grid, TOUCH_BLOCK, 0, s>>>(a);
+    launch_k(touch_kernel<W, DT>, dim3((unsigned)grid), dim3(TOUCH_BLOCK), 0, s, a);
 }
 
 template <int W, int DT>
@@ -472,7 +479,7 @@ static void launch_batch_wd(touch_args_t const* items, int n, uint64_t max_slots
     uint64_t gx = (max_slots + per - 1) / per;
     if (gx > 0x7fffffffull || n > 65535) fail(ES_NOT_SUPPORTED, "touch batch grid too large");
     dim3 grid((unsigned)gx, (unsigned)n, 1);
-    touch_batch_kernel<W, DT><<<grid, TOUCH_BLOCK, 0, s>>>(items);
+    launch_k(touch_batch_kernel<W, DT>, grid, dim3(TOUCH_BLOCK), 0, s, items);
 }
 
 #define ES_TOUCH_SWITCH(FN, ...)                                                                   \
@@ -525,7 +532,7 @@ template <typename T> static void fill_const_t(void* out, void const* v8, uint64
     std::memcpy(&v, v8, sizeof(T));
     uint64_t per = 16 / sizeof(T);
     uint64_t blocks = std::min<uint64_t>((n / per + 255) / 256 + 1, 148ull * 8);
-    fill_constant_kernel<T><<<(unsigned)blocks, 256, 0, s>>>(static_cast<T*>(out), v, n);
+    launch_k(fill_constant_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, s, static_cast<T*>(out), v, n);
 }
 
 void launch_fill_constant(int dtype, void const* value8, uint64_t nelem, cudaStream_t s, void* out)
@@ -551,7 +558,7 @@ static void fill_tri_t(void* out, void const* lo8, void const* up8, uint64_t nro
     std::memcpy(&up, up8, sizeof(T));
     uint64_t n = nrow * ncol;
     uint64_t blocks = std::min<uint64_t>((n + 255) / 256, 148ull * 8);
-    fill_lowertri_kernel<T><<<(unsigned)blocks, 256, 0, s>>>(static_cast<T*>(out), lo, up,
+    launch_k(fill_lowertri_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, s, static_cast<T*>(out), lo, up,
                                                             (int64_t)nrow, (int64_t)ncol, start);
 }
 
@@ -586,14 +593,14 @@ static unsigned long long limit_cycles(uint32_t limit_ms)
 void launch_flag_signal(uint32_t* flag, uint32_t limit_ms, cudaStream_t s)
 {
     if (!flag || (reinterpret_cast<uintptr_t>(flag) & 3)) fail(ES_BAD_ARGUMENT, "flag: null or unaligned pointer");
-    flag_kernel<<<1, 32, 0, s>>>(flag, 0u, 1u, limit_cycles(limit_ms), 1u);
+    launch_k(flag_kernel, dim3(1), dim3(32), 0, s, flag, 0u, 1u, limit_cycles(limit_ms), 1u);
     ES_CUDA_CHECK(cudaGetLastError());
 }
 
 void launch_flag_wait(uint32_t* flag, uint32_t limit_ms, cudaStream_t s)
 {
     if (!flag || (reinterpret_cast<uintptr_t>(flag) & 3)) fail(ES_BAD_ARGUMENT, "flag: null or unaligned pointer");
-    flag_kernel<<<1, 32, 0, s>>>(flag, 1u, 0u, limit_cycles(limit_ms), 2u);
+    launch_k(flag_kernel, dim3(1), dim3(32), 0, s, flag, 1u, 0u, limit_cycles(limit_ms), 2u);
     ES_CUDA_CHECK(cudaGetLastError());
 }
 
@@ -615,7 +622,7 @@ void launch_pull_copy(void const* src, void* dst, uint64_t bytes, cudaStream_t s
     uint64_t blocks = std::max<uint64_t>(std::min<uint64_t>((n16 + 1023) / 1024, 148ull * 4),
                                          (tail + 255) / 256);
     blocks = std::max<uint64_t>(blocks, 1);
-    pull_copy_kernel<<<(unsigned)blocks, 256, 0, s>>>(
+    launch_k(pull_copy_kernel, dim3((unsigned)blocks), dim3(256), 0, s,
         static_cast<uint4 const*>(src), static_cast<uint4*>(dst), n16,
         static_cast<unsigned char const*>(src) + n16 * 16,
         static_cast<unsigned char*>(dst) + n16 * 16, (uint32_t)tail);

@@ -25,6 +25,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <memory>
 #include <sstream>
@@ -35,6 +36,7 @@
 #include "exchange.h"
 #include "handle.h"
 #include "kernels.h"
+#include "pdl.h"
 
 namespace {
 
@@ -97,6 +99,7 @@ struct es_b200_program {
     bool                     has_spin = false;
     int                      exchange_lanes = 1; // lanes shared by the ops that wait for a peer
     int                      n_exchange = 0;     // how many of them the schedule uses
+    bool                     pdl = true;         // programmatic dependent launch between the ops of a lane
     uint32_t                 limit_ms = 0;
     std::vector<cudaStream_t> lanes;
     std::vector<cudaEvent_t>  events; // one per op that some other lane waits for
@@ -390,9 +393,13 @@ void launch_all(es_b200_program* p, cudaStream_t stream, int mode)
         cudaStream_t s = p->lanes[op.lane];
         for (int d : op.wait_on) ES_CUDA_CHECK(cudaStreamWaitEvent(s, p->events[p->event_of[d]], 0));
         if (timed) ES_CUDA_CHECK(cudaEventRecord(p->t0[i], s));
-        if (stamps) launch_stamp(p->stamps_dev + 2 * i, s);
-        launch_op(p, op, s);
-        if (stamps) launch_stamp(p->stamps_dev + 2 * i + 1, s);
+        {
+            // an op may be scheduled while the op before it on its lane finishes (pdl.h)
+            pdl_scope_t scope(p->pdl);
+            if (stamps) launch_stamp(p->stamps_dev + 2 * i, s);
+            launch_op(p, op, s);
+            if (stamps) launch_stamp(p->stamps_dev + 2 * i + 1, s);
+        }
         if (timed) ES_CUDA_CHECK(cudaEventRecord(p->t1[i], s));
         if (op.record) ES_CUDA_CHECK(cudaEventRecord(p->events[p->event_of[i]], s));
     }
@@ -450,6 +457,8 @@ int es_b200_program_create(es_b200_t* h, es_b200_program_t** out)
         if (!out) fail(ES_BAD_ARGUMENT, "null out pointer");
         auto* p = new es_b200_program;
         p->h = h;
+        char const* pdl = std::getenv("ES_B200_PDL");
+        p->pdl = !(pdl && std::string(pdl) == "0");
         *out = p;
     });
 }
