@@ -393,8 +393,17 @@ def make_runner(rk, mg, fuse, **kw):
     from einsummable_b200.memgraph import memgraph_runner_t
     if rk.world > 1:
         transport = os.environ.get("ES_B200_MOVE_TRANSPORT", "p2p")
-        return memgraph_runner_t(mg, rank=rk.rank, world=rk.world, transport=transport, fuse=fuse,
-                                 wait_limit_ms=int(os.environ.get("ES_B200_WAIT_LIMIT_MS", "2000")), **kw)
+        try:
+            return memgraph_runner_t(mg, rank=rk.rank, world=rk.world, transport=transport, fuse=fuse,
+                                     wait_limit_ms=int(os.environ.get("ES_B200_WAIT_LIMIT_MS", "2000")), **kw)
+        except Exception as exc:
+            if transport == "nccl":
+                raise
+            # peer-mapped (symmetric) memory could not be set up on this box -- every rank fails the same
+            # way, at the same collective call -- : moves over NCCL send / recv, one stream in node order
+            sys.stderr.write("peer-memory transport unavailable (%r); using NCCL send/recv\n" % (exc,))
+            kw.pop("schedule", None)
+            return memgraph_runner_t(mg, rank=rk.rank, world=rk.world, transport="nccl", fuse=fuse, **kw)
     return memgraph_runner_t(mg, devices=[rk.local], fuse=fuse, **kw)
 
 
@@ -445,9 +454,14 @@ def run_gpu(args):
     parity = parity_of(rk, r, want)
 
     # the dominant kernel inside the step: the GPU's own timer read before and after every op of one replay
-    tl, run_us = r.timeline(stream)
+    try:
+        tl, run_us = r.timeline(stream)
+        units = r.units
+    except Exception as exc:        # the NCCL fallback has no per-op timer
+        sys.stderr.write("no per-op timeline: %r\n" % (exc,))
+        tl, units = [], []
     dom = None
-    for (cls, label, a, b), u in zip(tl, r.units):
+    for (cls, label, a, b), u in zip(tl, units):
         if cls == "contraction":
             node = mg["nodes"][u["node"]]
             flops = 2.0 * float(np.prod(node["einsummable"]["join_shape"]))

@@ -968,6 +968,10 @@ class memgraph_runner_t:
             self.prog.instantiate()
             self.graph = self.prog
             return self.prog
+        if self.transport == "nccl":
+            # captured NCCL send / recv nodes did not shut down cleanly on this stack: replay() runs the list
+            self.graph = None
+            return None
         if len(set(self.devices.values())) > 1:
             raise RuntimeError("capture: one process driving several GPUs runs as a list and is not captured")
         g = torch.cuda.CUDAGraph()
@@ -979,6 +983,8 @@ class memgraph_runner_t:
     def replay(self, stream=None):
         if self.prog is not None:
             self.prog.replay(stream if stream is not None else torch.cuda.current_stream())
+        elif self.graph is None:
+            self.run(stream)
         else:
             self.graph.replay()
 
