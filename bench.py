@@ -845,8 +845,59 @@ def other_classes(km, dev, stream):
     return out
 
 
+def run_exchange_only(args):
+    """Cross-GPU copy rates of the exchange ops, two ranks (torchrun --nproc-per-node 2): rank 1 reads
+    from rank 0's peer-mapped buffer with the pull op and with a touch whose input is the peer's memory
+    (one-op programs, `steps` launches, CUDA events; the ~13 us floor is the program launch itself)."""
+    rk = Ranks()
+    torch = rk.torch
+    import torch.distributed._symmetric_memory as symm_mem
+    import einsummable_b200 as es
+    from einsummable_b200.einsummable import touch_t
+    from einsummable_b200.program import program_t
+    total = (512 << 20) + 4096
+    buf = symm_mem.empty(total, dtype=torch.uint8, device=rk.dev)
+    buf.copy_(torch.randint(0, 255, (total,), dtype=torch.uint8, device=rk.dev))
+    torch.cuda.synchronize()
+    hdl = symm_mem.rendezvous(buf, rk.dist.group.WORLD)
+    peers = [int(p) for p in hdl.buffer_ptrs]
+    rk.barrier()
+    km = es.kernel_manager_t(rk.local)
+    res = {}
+    if rk.rank == 1:
+        dst = torch.zeros(512 << 20, dtype=torch.uint8, device=rk.dev)
+        stream = torch.cuda.current_stream()
+        flag = peers[0] + (512 << 20)
+        for nbytes in (64 << 10, 1 << 20, 2 << 20, 8 << 20, 32 << 20, 128 << 20, 512 << 20):
+            for kind in ("pull", "remote touch"):
+                p = program_t(km)
+                if kind == "pull":
+                    p.add_pull([(peers[0], dst.data_ptr(), nbytes, None, flag)])
+                else:
+                    n = nbytes // 2
+                    p.add_touch(touch_t([(n, n, 0, 0, n)], None, "f16"), None, dst.data_ptr(), peers[0], done_flag=flag)
+                p.finalize(1)
+                p.set_workspace(dst, 0)
+                iters = args.steps if nbytes <= (32 << 20) else max(args.steps // 4, 2)
+                ms = time_launches(lambda: p.launch(stream), stream, iters=iters, warm=args.warmup)
+                res["%s %d KiB" % (kind, nbytes >> 10)] = {"us": round(ms * 1e3, 1), "GB/s": round(nbytes / (ms * 1e-3) / 1e9, 1)}
+                p.close()
+    rk.barrier()
+    # the last op copied the first 512 MiB of rank 0's buffer: send a checksum over NCCL and compare
+    chk = buf[:512 << 20].view(torch.int64).sum().reshape(1) if rk.rank == 0 else torch.zeros(1, dtype=torch.int64, device=rk.dev)
+    rk.dist.broadcast(chk, src=0)
+    if rk.rank == 1:
+        res["checksum_matches"] = bool(int(dst.view(torch.int64).sum().item()) == int(chk.item()))
+    if rk.rank == 1:
+        print(json.dumps({"only": "exchange", "reference_peer_copy_GB/s": 770, "device_status": km.device_status(),
+                          "sizes": res}))
+    rk.close()
+
+
 def run_only(args):
     """One kernel class alone, `steps` launches after `warmup`, CUDA events."""
+    if args.only == "exchange":
+        return run_exchange_only(args)
     import torch
     import einsummable_b200 as es
     from einsummable_b200 import einsummable_t, scalarop_t as S, touch_t
@@ -954,7 +1005,7 @@ def main():
                     help="rows of the [rows, 11008] tensors (default: the full C2 workload); "
                          "smaller values are for profiler captures only")
     ap.add_argument("--only", default=None,
-                    choices=["llama_layer", "llama_layer_fused", "llama_train", "llama_train_fused", "gemm_qkv", "gemm_ffn", "gemm_f32", "gemm_nn", "gemm_tn", "attn_scores", "attn_pv", "touch", "permute", "move"],
+                    choices=["llama_layer", "llama_layer_fused", "llama_train", "llama_train_fused", "gemm_qkv", "gemm_ffn", "gemm_f32", "gemm_nn", "gemm_tn", "attn_scores", "attn_pv", "touch", "permute", "move", "exchange"],
                     help="time one other kernel class alone (profiler captures); prints its own small JSON line")
     ap.add_argument("--kernels-only", action="store_true",
                     help="skip the end-to-end, other-class and CPU-baseline legs (profiler captures)")

@@ -111,15 +111,17 @@ __global__ void __launch_bounds__(256) pull_batch_kernel(pull_item_t const* __re
         uint4*         dst = reinterpret_cast<uint4*>(it.dst);
         uint64_t const nth = (uint64_t)it.n_ctas * blockDim.x;
         uint64_t       i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
-        // 8 loads in flight per thread: the round trip over NVLink is a few microseconds
-        for (; i + 7 * nth < n16; i += 8 * nth) {
+        // 8 loads in flight per thread, also in the last, partial round: the round trip over NVLink is
+        // a few microseconds and most moves are a single round
+        for (; i < n16; i += 8 * nth) {
             uint4 v[8];
 #pragma unroll
-            for (int u = 0; u != 8; ++u) v[u] = src[i + u * nth];
+            for (int u = 0; u != 8; ++u)
+                if (i + u * nth < n16) v[u] = src[i + u * nth];
 #pragma unroll
-            for (int u = 0; u != 8; ++u) dst[i + u * nth] = v[u];
+            for (int u = 0; u != 8; ++u)
+                if (i + u * nth < n16) dst[i + u * nth] = v[u];
         }
-        for (; i < n16; i += nth) dst[i] = src[i];
         if (blockIdx.x == 0) {
             uint32_t tail = (uint32_t)(it.bytes & 15);
             if (threadIdx.x < tail) it.dst[(n16 << 4) + threadIdx.x] = it.src[(n16 << 4) + threadIdx.x];
@@ -146,10 +148,11 @@ unsigned long long limit_cycles_of(uint32_t limit_ms)
 
 uint32_t pull_ctas_for(uint64_t bytes)
 {
-    // one CTA per 32 KiB, at most 48 per move: enough loads in flight to fill one NVLink
-    // direction while leaving the SMs to the compute kernels that run beside the pull
+    // one CTA per 32 KiB (one round of 8 x 16-byte loads per thread), at most one per SM: 48 CTAs
+    // left a direction of NVLink 15 % short (652 of 770 GB/s) and made a 2 MB move -- the common size
+    // on the dependency chain of a partitioned layer -- a third slower than a touch reading the same bytes
     uint64_t c = (bytes + 32767) / 32768;
-    return (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>(c, 48));
+    return (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>(c, 148));
 }
 
 void launch_stamp(unsigned long long* slot_dev, cudaStream_t s)
