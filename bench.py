@@ -470,6 +470,18 @@ def run_gpu(args):
     by_class = {}
     for cls, _, a, b in tl:
         by_class[cls] = by_class.get(cls, 0.0) + (b - a)
+    # the fused attention chains of this rank inside the step: Q, K, V read and O written once
+    att = None
+    att_ops = [(b - a, mg["nodes"][u["node"]]["attention"]) for (cls, _, a, b), u in zip(tl, units) if cls == "attention"]
+    if att_ops:
+        from einsummable_b200.attention import attention_t
+        us = sum(t for t, _ in att_ops)
+        nbytes = sum(attention_t.from_json(a).algorithmic_bytes() for _, a in att_ops)
+        flops = sum(attention_t.from_json(a).flops() for _, a in att_ops)
+        att = {"launches": len(att_ops), "us": round(us, 1), "algorithmic_MB": round(nbytes / 1e6, 1),
+               "GB/s": round(nbytes / (us * 1e-6) / 1e9, 1), "frac_of_hbm": round(nbytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"], 3),
+               "TFLOP/s_counting_every_key_block": round(flops / (us * 1e-6) / 1e12, 1),
+               "replaces": "scores contraction, max, sum of exponentials, normalisation, contraction with V"}
 
     # ---------------- end to end: the step's input from pinned host memory, its result back to the host ----------------
     e2e = e2e_layer(rk, r, mg, inputs, stream, min(max(args.steps, 4), 50))
@@ -479,7 +491,8 @@ def run_gpu(args):
     r.close()
     del r
     torch.cuda.empty_cache()
-    for name, kw in (("as_compiled", dict(fuse=False)),
+    for name, kw in (("folded_without_the_attention_kernel", dict(fuse="elementwise")),
+                     ("as_compiled", dict(fuse=False)),
                      ("as_compiled_list_schedule", dict(fuse=False, schedule="list"))):
         try:
             if name.endswith("list_schedule") and os.environ.get("ES_B200_BENCH_LIST", "1") == "0":
@@ -533,7 +546,8 @@ def run_gpu(args):
         "config": {"workload": LAYER_WORKLOAD, "tokens_per_step": LAYER_TOKENS,
                    "l2": "weights (405 MB) and activations exceed the 126 MB L2; no flush",
                    "execution": "one CUDA-graph replay per step (dependency-ordered lanes), elementwise chains "
-                                "folded into their readers; eager %.3f ms" % ms_eager,
+                                "folded into their readers, every attention chain one kernel; eager %.3f ms" % ms_eager,
+                   "attention": att,
                    "contraction_gflop_per_step": mg["taskgraph"]["contraction_flops"] / 1e9,
                    "moves_per_step": mg["taskgraph"].get("move"), "move_bytes_per_step": mg["taskgraph"].get("move_bytes"),
                    "variants": variants},
@@ -951,7 +965,7 @@ def run_only(args):
         print(json.dumps({"only": "move", "path": "<=4 MiB: SM pull kernel over NVLink; larger: copy engine",
                           "reference_peer_copy_GB/s": 770, "sizes": res}))
         return
-    if args.only.startswith("gemm") or args.only.startswith("attn"):
+    if args.only.startswith("gemm") or args.only.startswith("attn_"):
         if args.only == "gemm_qkv":
             e = einsummable_t.from_matmul_st(2048, 4096, 4096, "f16")
         elif args.only == "gemm_ffn":
@@ -975,6 +989,19 @@ def run_only(args):
         work, unit = 2.0 * float(np.prod(e.join_shape)), "TFLOP/s"
         nbytes = sum(t.numel() * t.element_size() for t in ins + [out])
         info = km.kernel_info(e)
+    elif args.only in ("attention", "attention_noskip"):
+        # the fused chain at the layer's size: Q, K, V as [batch, row, head, dim], lower-triangular mask
+        from einsummable_b200.attention import attention_t
+        b_, h_, s_, d_ = 4, 32, 512, 128
+        q, k, v = [(torch.randn(b_, s_, h_, d_, device=dev) * 0.5).half() for _ in range(3)]
+        i_, j_ = torch.arange(s_, device=dev).unsqueeze(1), torch.arange(s_, device=dev).unsqueeze(0)
+        mask = torch.where(i_ >= j_, 0.0, float("-inf")).half().contiguous()
+        out = torch.empty(b_, h_, s_, d_, dtype=torch.float16, device=dev)
+        st = [s_ * h_ * d_, d_, h_ * d_]
+        a = attention_t(b_, h_, s_, s_, d_, st, st, st, [h_ * s_ * d_, s_ * d_, d_], s_, 1 if args.only == "attention" else 0, 0)
+        fn = lambda: km.attention(a, stream, out, q, k, v, mask)
+        work, unit, nbytes = float(a.algorithmic_bytes()), "GB/s", a.algorithmic_bytes()
+        info = "attention_tc_f16 %s: %.1f GFLOP counting every key block" % (args.only, a.flops() / 1e9)
     elif args.only == "touch":
         sel = [(16, 32, 0, 16, 16), (256, 512, 0, 256, 256), (16, 32, 0, 16, 16), (64, 128, 0, 64, 64)]
         src = torch.randn(16 * 256 * 16 * 64, dtype=torch.float16, device=dev)
@@ -1005,7 +1032,7 @@ def main():
                     help="rows of the [rows, 11008] tensors (default: the full C2 workload); "
                          "smaller values are for profiler captures only")
     ap.add_argument("--only", default=None,
-                    choices=["llama_layer", "llama_layer_fused", "llama_train", "llama_train_fused", "gemm_qkv", "gemm_ffn", "gemm_f32", "gemm_nn", "gemm_tn", "attn_scores", "attn_pv", "touch", "permute", "move", "exchange"],
+                    choices=["llama_layer", "llama_layer_fused", "llama_train", "llama_train_fused", "gemm_qkv", "gemm_ffn", "gemm_f32", "gemm_nn", "gemm_tn", "attn_scores", "attn_pv", "attention", "attention_noskip", "touch", "permute", "move", "exchange"],
                     help="time one other kernel class alone (profiler captures); prints its own small JSON line")
     ap.add_argument("--kernels-only", action="store_true",
                     help="skip the end-to-end, other-class and CPU-baseline legs (profiler captures)")

@@ -51,6 +51,15 @@ class es_pull_item_t(ctypes.Structure):
                 ("ready_flag", ctypes.c_void_p), ("done_flag", ctypes.c_void_p)]
 
 
+class es_attention_t(ctypes.Structure):
+    _fields_ = [("batch", ctypes.c_uint32), ("heads", ctypes.c_uint32), ("rows", ctypes.c_uint32),
+                ("keys", ctypes.c_uint32), ("head_dim", ctypes.c_uint32), ("skip_known", ctypes.c_int32),
+                ("skip_from", ctypes.c_int32), ("reserved", ctypes.c_int32),
+                ("q_stride", ctypes.c_int64 * 3), ("k_stride", ctypes.c_int64 * 3),
+                ("v_stride", ctypes.c_int64 * 3), ("out_stride", ctypes.c_int64 * 3),
+                ("mask_stride", ctypes.c_int64)]
+
+
 LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libes_b200.so")
 
 # every symbol include/es_b200.h declares: name -> (restype, argtypes)
@@ -77,6 +86,7 @@ SYMBOLS = {
     "es_b200_flag_signal": (_i, [_vp, _vp, ctypes.c_uint32, _vp]),
     "es_b200_flag_wait": (_i, [_vp, _vp, ctypes.c_uint32, _vp]),
     "es_b200_pull": (_i, [_vp, _vp, _vp, _u64, _vp]),
+    "es_b200_launch_attention": (_i, [_vp, ctypes.POINTER(es_attention_t), _vp, _vp, _vp, _vp, _vp, _vp]),
     "es_b200_kernel_info": (_i, [_vp, _u64, _cp, _i]),
     "es_b200_describe": (_i, [_desc_p, _i, _cp, _i]),
     "es_b200_touch_simplify": (_i, [_td_p, _i, _td_p, ctypes.POINTER(_i)]),
@@ -104,6 +114,7 @@ SYMBOLS = {
     "es_b200_evict": (_i, [_vp, _vp, _i, _vp, _u64, _vp]),
     "es_b200_load": (_i, [_vp, _vp, _i, _vp, _u64, _vp]),
     "es_b200_program_add_signal": (_i, [_vp, ctypes.POINTER(_vp), _i, _ip, _i, _ip]),
+    "es_b200_program_add_attention": (_i, [_vp, ctypes.POINTER(es_attention_t), _vp, _vp, _vp, _vp, _vp, _ip, _i, _ip]),
     "es_b200_program_add_pull": (_i, [_vp, ctypes.POINTER(es_pull_item_t), _i, _ip, _i, _ip]),
     "es_b200_program_add_wait": (_i, [_vp, ctypes.POINTER(_vp), _i, _ip, _i, _ip]),
     "es_b200_program_finalize": (_i, [_vp, _i, ctypes.POINTER(_u64)]),

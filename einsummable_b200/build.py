@@ -16,7 +16,7 @@ LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libes_b200.so")
 CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 
-SOURCES = ["api.cc", "scalarop.cc", "einsum.cc", "codegen.cc", "jit.cc", "kernels.cu", "contraction.cu", "noalloc.cu", "exchange.cu", "program.cc", "storage.cc", "wire.cc"]
+SOURCES = ["api.cc", "scalarop.cc", "einsum.cc", "codegen.cc", "jit.cc", "kernels.cu", "contraction.cu", "attention.cu", "noalloc.cu", "exchange.cu", "program.cc", "storage.cc", "wire.cc"]
 
 
 def _stale():

@@ -16,6 +16,7 @@
 #include "jit.h"
 #include "handle.h"
 #include "kernels.h"
+#include "attention.h"
 #include "exchange.h"
 #include "pdl.h"
 
@@ -566,6 +567,8 @@ int es_b200_device_status(es_b200_t* h, unsigned int* error_word)
         set_device(h);
         ES_CUDA_CHECK(cudaDeviceSynchronize());
         unsigned int tc = read_and_clear_tc_error();
+        unsigned int at = read_and_clear_attention_error();
+        if (!tc) tc = at;
         unsigned int fl = read_and_clear_flag_error();
         unsigned int ex = read_and_clear_exchange_error();
         *error_word = tc | ((fl ? fl : ex) << 8);
@@ -614,6 +617,20 @@ int es_b200_pull(es_b200_t* h, const void* src, void* dst, uint64_t bytes, void*
         launch_pull_copy(src, dst, bytes, (cudaStream_t)stream);
         h->counters[3] += 1;
         h->work_bytes[3] += bytes;
+    });
+}
+
+int es_b200_launch_attention(es_b200_t* h, const es_attention_t* a, void* stream, void* out,
+                             const void* q, const void* k, const void* v, const void* mask)
+{
+    return guarded([&] {
+        check_handle(h);
+        if (!a) fail(ES_BAD_ARGUMENT, "attention: null descriptor");
+        set_device(h);
+        launch_attention(*a, (cudaStream_t)stream, out, q, k, v, mask);
+        h->counters[0] += 1;
+        h->work_bytes[0] += attention_bytes(*a);
+        h->work_flops += attention_flops(*a);
     });
 }
 

@@ -32,6 +32,7 @@
 #include <string>
 #include <vector>
 
+#include "attention.h"
 #include "common.h"
 #include "exchange.h"
 #include "handle.h"
@@ -53,12 +54,13 @@ enum op_kind_t {
     OP_WAIT = 7,
     OP_TOUCH_BATCH = 8,
     OP_EVICT = 9,
-    OP_LOAD = 10
+    OP_LOAD = 10,
+    OP_ATTENTION = 11
 };
 
 char const* const OP_NAMES[] = {"einsummable", "touch", "fill_constant", "fill_lowertri", "copy",
                                 "signal",      "pull",  "wait",          "touch_batch",   "evict",
-                                "load"};
+                                "load",        "attention"};
 
 struct op_t {
     int              kind = 0;
@@ -82,6 +84,7 @@ struct op_t {
     std::vector<uint32_t*>   flags;      // signal / wait
     std::vector<pull_item_t> pulls;      // pull
     std::vector<touch_args_t> batch;     // touch batch (one dtype, one width)
+    es_attention_t           attn;
     uint64_t                 batch_slots = 0;
     // device-side descriptor arrays (finalize)
     uint64_t                 dev_off = 0, dev_off2 = 0;
@@ -334,6 +337,12 @@ void launch_op(es_b200_program* p, op_t const& op, cudaStream_t s)
             launch_fill_lowertri(op.dtype, op.v0, op.v1, op.nrow, op.ncol, op.start, s, op.out);
             h->counters[2] += 1;
             h->work_bytes[2] += op.work_bytes;
+            break;
+        case OP_ATTENTION:
+            launch_attention(op.attn, s, op.out, op.inns[0], op.inns[1], op.inns[2], op.inns[3]);
+            h->counters[0] += 1;
+            h->work_bytes[0] += op.work_bytes;
+            h->work_flops += attention_flops(op.attn);
             break;
         case OP_COPY:
             launch_pull_copy(op.src, op.out, op.bytes, s);
@@ -625,6 +634,24 @@ int es_b200_program_add_copy(es_b200_program_t* p,
         op.src = src;
         op.out = dst;
         op.bytes = bytes;
+        add_op(p, std::move(op), deps, n_deps, op_index);
+    });
+}
+
+int es_b200_program_add_attention(es_b200_program_t* p, const es_attention_t* a, void* out,
+                                  const void* q, const void* k, const void* v, const void* mask,
+                                  const int* deps, int n_deps, int* op_index)
+{
+    return guarded([&] {
+        check_program(p, false);
+        if (!a) fail(ES_BAD_ARGUMENT, "program attention: null descriptor");
+        check_attention(*a, out, q, k, v, mask);
+        op_t op;
+        op.kind = OP_ATTENTION;
+        op.attn = *a;
+        op.out = out;
+        op.inns = {q, k, v, mask};
+        op.work_bytes = attention_bytes(*a);
         add_op(p, std::move(op), deps, n_deps, op_index);
     });
 }

@@ -115,6 +115,196 @@ def compose(a, b, slot):
             "join": "".join(parts), "castable": b["castable"]}
 
 
+_X = r"to_f32\[\+\[hole\|f16@0,hole\|f16@1\]\]"
+_E = r"exp\[\+\[" + _X + r",\*\[constant\{f32\|-1\},hole\|f32@2\]\]\]"
+_RE_MAX = re.compile(_X)
+_RE_SUM = re.compile(_E)
+_RE_NORM = re.compile(r"to_f16\[\*\[" + _E + r",power\{-1\}\[hole\|f32@3\]\]\]")
+_RE_MUL16 = re.compile(r"\*\[hole\|f16@0,hole\|f16@1\]")
+
+
+def _row_major_strides(shape):
+    st = [1] * len(shape)
+    for i in range(len(shape) - 2, -1, -1):
+        st[i] = st[i + 1] * int(shape[i + 1])
+    return st
+
+
+def _match_attention(nodes, alive, i_s, saved):
+    """The five nodes of softmax(Q K^T + mask) V that start with the scores contraction nodes[i_s]
+    (after the elementwise fold): returns (indices, descriptor dict, mems [out, q, k, v, mask]) or None."""
+    s = nodes[i_s]
+    es = s["einsummable"]
+    loc = s["loc"]
+    if len(es["join_shape"]) != 5 or es["out_rank"] != 4 or not _is_plain_contraction(es) or not _RE_MUL16.fullmatch(es["join"]):
+        return None
+    b, h, rows, keys, d = [int(x) for x in es["join_shape"]]
+    qk = {}
+    for slot, modes in enumerate(es["inns"]):
+        if sorted(modes) == [0, 1, 2, 4] and modes[-1] == 4:
+            qk["q"] = (slot, modes)
+        elif sorted(modes) == [0, 1, 3, 4] and modes[-1] == 4:
+            qk["k"] = (slot, modes)
+    if len(qk) != 2:
+        return None
+
+    def strides(modes, row_mode):
+        st = _row_major_strides([es["join_shape"][m] for m in modes])
+        at = {m: st[i] for i, m in enumerate(modes)}
+        return [at[0], at[1], at[row_mode]]
+
+    def sole_readers(ix, want):
+        """Indices of the apply nodes that read node ix's result, if they are exactly `want` many, read
+        it as written, and nothing ships or saves it."""
+        n = nodes[ix]
+        out = tuple(n["mems"][0])
+        if any(sv[0] == loc and _overlap(out, sv[1:]) for sv in saved):
+            return None
+        got = []
+        for ib in range(ix + 1, len(nodes)):
+            m = nodes[ib]
+            if not alive[ib] or n["id"] not in m["inns"]:
+                continue
+            if m["kind"] in ("move", "copy", "evict"):
+                return None
+            if m["kind"] == "apply":
+                if m["loc"] != loc or "einsummable" not in m or not any(tuple(x) == out for x in m["mems"][1:]):
+                    return None
+                got.append(ib)
+        return got if len(got) == want else None
+
+    r_s = sole_readers(i_s, 3)
+    if r_s is None:
+        return None
+    i_m, i_l, i_p = r_s
+    m, l, pn = nodes[i_m], nodes[i_l], nodes[i_p]
+    em, el, ep = m["einsummable"], l["einsummable"], pn["einsummable"]
+    s_out = tuple(s["mems"][0])
+    full = [0, 1, 2, 3]
+    shape4 = [b, h, rows, keys]
+    if not (em["castable"] == "max" and em["out_rank"] == 3 and [int(x) for x in em["join_shape"]] == shape4
+            and em["inns"] == [full, [2, 3]] and _RE_MAX.fullmatch(em["join"]) and tuple(m["mems"][1]) == s_out):
+        return None
+    mask = tuple(m["mems"][2])
+    m_out = tuple(m["mems"][0])
+    if not (el["castable"] == "add" and el["out_rank"] == 3 and [int(x) for x in el["join_shape"]] == shape4
+            and el["inns"] == [full, [2, 3], [0, 1, 2]] and _RE_SUM.fullmatch(el["join"])
+            and [tuple(x) for x in l["mems"][1:]] == [s_out, mask, m_out]):
+        return None
+    l_out = tuple(l["mems"][0])
+    if not (ep["out_rank"] == 4 and [int(x) for x in ep["join_shape"]] == shape4
+            and ep["inns"] == [full, [2, 3], [0, 1, 2], [0, 1, 2]] and _RE_NORM.fullmatch(ep["join"])
+            and [tuple(x) for x in pn["mems"][1:]] == [s_out, mask, m_out, l_out]):
+        return None
+    if sole_readers(i_m, 2) != [i_l, i_p] or sole_readers(i_l, 1) != [i_p]:
+        return None
+    r_p = sole_readers(i_p, 1)
+    if r_p is None:
+        return None
+    i_o = r_p[0]
+    o = nodes[i_o]
+    eo = o["einsummable"]
+    if not (_is_plain_contraction(eo) and _RE_MUL16.fullmatch(eo["join"]) and eo["out_rank"] == 4
+            and [int(x) for x in eo["join_shape"]] == [b, h, rows, d, keys]):
+        return None
+    p_out = tuple(pn["mems"][0])
+    v_slot = None
+    for slot, modes in enumerate(eo["inns"]):
+        if modes == [0, 1, 2, 4]:
+            if tuple(o["mems"][1 + slot]) != p_out:
+                return None
+        elif sorted(modes) == [0, 1, 3, 4] and modes[-1] == 3:
+            v_slot = slot
+    if v_slot is None or len(eo["inns"]) != 2 or [0, 1, 2, 4] not in eo["inns"]:
+        return None
+    vm = eo["inns"][v_slot]
+    vst = _row_major_strides([eo["join_shape"][x] for x in vm])
+    vat = {x: vst[i] for i, x in enumerate(vm)}
+    desc = {"batch": b, "heads": h, "rows": rows, "keys": keys, "head_dim": d,
+            "q_stride": strides(qk["q"][1], 2), "k_stride": strides(qk["k"][1], 3),
+            "v_stride": [vat[0], vat[1], vat[4]], "out_stride": _row_major_strides([b, h, rows, d])[:3],
+            "mask_stride": keys, "skip_known": 0, "skip_from": 0}
+    mems = [list(o["mems"][0]), list(s["mems"][1 + qk["q"][0]]), list(s["mems"][1 + qk["k"][0]]),
+            list(o["mems"][1 + v_slot]), list(mask)]
+    return [i_s, i_m, i_l, i_p, i_o], desc, mems
+
+
+def fuse_attention(mg):
+    """Replaces every softmax(Q K^T + mask) V chain -- scores contraction, max, sum of exponentials,
+    normalisation, contraction with V, as they stand after fuse_elementwise_chains -- by one apply node
+    with an "attention" descriptor (einsummable_b200/attention.py), placed where the last of the five
+    stood.  Returns (new memgraph, number of chains replaced).  The same conditions as for folding
+    apply: the four intermediate results have no other reader and are not saved or shipped, and
+    nothing between the first and the last node writes memory the chain reads; later writers into
+    that memory are made to wait for the new node."""
+    from .attention import attention_t
+    mg = copy.deepcopy(mg)
+    nodes = mg["nodes"]
+    saved = [(blk["loc"], blk["offset"], blk["size"]) for t in mg["outputs"] for blk in t["blocks"] if "offset" in blk]
+    alive = [not n.get("folded", False) for n in nodes]
+    fused = 0
+    for i_s, s in enumerate(nodes):
+        if not alive[i_s] or s["kind"] != "apply" or "einsummable" not in s:
+            continue
+        got = _match_attention(nodes, alive, i_s, saved)
+        if got is None:
+            continue
+        idx, desc, mems = got
+        if not attention_t.from_json(desc).eligible() or any(m[0] % 16 for m in mems):
+            continue
+        i_o = idx[-1]
+        loc = s["loc"]
+        reads = [tuple(m) for m in mems[1:]]
+        if any(_overlap(tuple(mems[0]), r) for r in reads):
+            continue
+        # Q and K are now read where the last node stands instead of the first, the mask instead of
+        # where the max node stood (V is read where it always was)
+        hazard = False
+        mask = tuple(mems[4])
+        for ic in range(i_s + 1, i_o):
+            if not alive[ic] or ic in idx:
+                continue
+            w = _written_region(nodes[ic], loc)
+            if w is None:
+                continue
+            if any(_overlap(w, r) for r in reads[:2]) or (ic > idx[1] and _overlap(w, mask)):
+                hazard = True
+                break
+        if hazard:
+            continue
+        # a mask that a lower-triangular fill with -inf above wrote: key blocks above the diagonal are skipped
+        for ic in range(idx[1] - 1, -1, -1):
+            w = _written_region(nodes[ic], loc) if alive[ic] else None
+            if w is None or not _overlap(w, mask):
+                continue
+            f = nodes[ic].get("fill") if nodes[ic]["kind"] == "constant" else None
+            if (f and f["type"] == "lowertri" and w == mask and f["lower"]["dtype"] == "f16"
+                    and int(f["nrow"]) == desc["rows"] and int(f["ncol"]) == desc["keys"]
+                    and list(f["upper"]["raw"][:2]) == [0, 252] and list(f["lower"]["raw"][:2]) == [0, 0]
+                    and abs(int(f["start"])) < (1 << 30)):
+                desc["skip_known"], desc["skip_from"] = 1, int(f["start"])
+            break
+        removed = set(nodes[i]["id"] for i in idx[:-1])
+        deps = set()
+        for i in idx:
+            deps |= set(nodes[i]["inns"])
+        o = nodes[i_o]
+        nodes[i_o] = {"id": o["id"], "inns": sorted(deps - removed - {o["id"]}), "kind": "apply", "loc": loc,
+                      "group": -1, "attention": desc, "mems": mems}
+        for ic in range(i_o + 1, len(nodes)):
+            if not alive[ic]:
+                continue
+            w = _written_region(nodes[ic], loc)
+            if w is not None and any(_overlap(w, r) for r in reads):
+                nodes[ic]["inns"] = sorted(set(nodes[ic]["inns"]) | {o["id"]})
+        for i in idx[:-1]:
+            n = nodes[i]
+            alive[i] = False
+            nodes[i] = {"id": n["id"], "inns": n["inns"], "kind": "alloc", "loc": n["loc"], "folded": True}
+        fused += 1
+    return mg, fused
+
+
 def fuse_elementwise_chains(mg):
     """Returns (new memgraph, number of nodes folded away).  With several locations the same rules
     apply inside each location (every rank must fold the same way, which it does: the pass only

@@ -191,6 +191,14 @@ class kernel_manager_t:
         """SM copy from a peer-mapped source into local memory."""
         _lib.check(self._lib.es_b200_pull(self._h, _ptr(src), _ptr(dst), int(nbytes), _stream(stream)))
 
+    def attention(self, desc, stream, out, q, k, v, mask):
+        """The fused attention chain (scores, mask, softmax, values) as one launch; `desc` is an
+        attention_t (einsummable_b200.attention)."""
+        c = desc.c_struct()
+        _lib.check(self._lib.es_b200_launch_attention(
+            self._h, ctypes.byref(c), _stream(stream), _ptr(out), _ptr(q), _ptr(k), _ptr(v),
+            _ptr(mask) if mask is not None else None))
+
     def rowsum_f32_noalloc(self, stream, out, inn, rows, cols):
         """out[a] = sum_b inn[a,b] for f32 without any device allocation: the
         scratch of the two-pass reduction is a fixed array inside the library

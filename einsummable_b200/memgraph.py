@@ -30,6 +30,7 @@ import json
 import numpy as np
 import torch
 
+from .attention import attention_t
 from .einsummable import einsummable_t, fill_t, touch_t
 from .kernel_manager import kernel_manager_t
 from .program import program_t
@@ -269,6 +270,8 @@ def schedule_units(mg, owned, exchange):
                 idx = emit({"kind": "touch", "node": nid, "deps": deps, "first": first, "loc": loc})
             if n["group"] >= 0:
                 group_last[(loc, n["group"])] = idx
+        elif kind == "apply" and "attention" in n:
+            idx = emit({"kind": "attention", "node": nid, "deps": deps, "loc": loc})
         elif kind == "apply":
             idx = emit({"kind": "einsummable", "node": nid, "deps": deps, "loc": loc})
         elif kind == "constant":
@@ -308,6 +311,10 @@ def unit_cost_us(mg, u):
                 flops *= d
             return 5.0, max(flops / 1.25e9, nbytes / 5.0e6), "gpu"
         return 2.5, nbytes / 5.5e6, "gpu"
+    if k == "attention":
+        a = nodes[u["node"]]["attention"]
+        flops = 4.0 * a["batch"] * a["heads"] * a["rows"] * a["keys"] * a["head_dim"] * (0.6 if a["skip_known"] else 1.0)
+        return 5.0, flops / 0.6e9, "gpu"
     if k == "touch":
         n = nodes[u["node"]]
         return 2.5, n["mems"][1][1] * (2 if u["first"] else 3) / 4.5e6, "gpu"
@@ -419,10 +426,14 @@ class memgraph_runner_t:
         schedule: "dag" = the library's program executor (dependency-ordered lanes, see the
         module text); "list" = one stream in node order.  The NCCL transport always runs as a list."""
         self.folded = 0
+        self.attention_chains = 0
         if fuse:
-            # elementwise producers folded into their readers (one location only, see fuse.py)
-            from .fuse import fuse_elementwise_chains
+            # elementwise producers folded into their readers, then whole attention chains into one
+            # node (fuse.py); fuse="elementwise" stops after the first pass
+            from .fuse import fuse_attention, fuse_elementwise_chains
             mg, self.folded = fuse_elementwise_chains(mg)
+            if fuse != "elementwise":
+                mg, self.attention_chains = fuse_attention(mg)
         self.mg = mg
         self.num_locs = mg["num_locs"]
         self.distributed = rank is not None
@@ -551,6 +562,15 @@ class memgraph_runner_t:
                 kk = km.kernel_info(e).split("|")[0]
                 self.unit_labels.append(("contraction" if kk.startswith("contraction") else
                                          ("reduction" if e.has_aggregation() else "elementwise"), repr(e)))
+            elif kind == "attention":
+                node = nodes[u["node"]]
+                a = attention_t.from_json(node["attention"])
+                loc = node["loc"]
+                out, q, k, v, mask = [self.ptr(loc, m[0]) for m in node["mems"]]
+                prog.add_attention(a, out, q, k, v, mask, deps)
+                self.stats["einsummable"] += 1
+                self.unit_labels.append(("attention", "b%d h%d rows%d keys%d d%d%s" % (
+                    a.batch, a.heads, a.rows, a.keys, a.head_dim, " skip" if a.skip_known else "")))
             elif kind in ("touch", "rtouch"):
                 node = nodes[u["node"]]
                 d = node["touch"]
@@ -746,7 +766,11 @@ class memgraph_runner_t:
                 loc = node["loc"]
                 if not self.owns(loc):
                     continue
-                if "einsummable" in node:
+                if "attention" in node:
+                    self.program.append(("attention", loc, attention_t.from_json(node["attention"]),
+                                         [m[0] for m in node["mems"]]))
+                    self.stats["einsummable"] += 1
+                elif "einsummable" in node:
                     d = node["einsummable"]
                     e = einsummable_t(d["join_shape"], d["inns"], d["out_rank"], d["join"], d["castable"])
                     ws = self.km(loc).build(e)
@@ -897,6 +921,9 @@ class memgraph_runner_t:
                 w = self.workspace[loc]
                 self.km(loc)(e, self._stream(loc, stream), self.ptr(loc, offs[0]),
                              [self.ptr(loc, o) for o in offs[1:]], (w[0], w[1]) if ws else None)
+            elif kind == "attention":
+                _, loc, a, offs = op
+                self.km(loc).attention(a, self._stream(loc, stream), *[self.ptr(loc, o) for o in offs])
             elif kind == "touch":
                 _, loc, t, t_copy, group, offs = op
                 first = group < 0 or (loc, group) not in groups_touched
@@ -999,11 +1026,15 @@ class memgraph_runner_t:
                     e = einsummable_t(d["join_shape"], d["inns"], d["out_rank"], d["join"], d["castable"])
                     k = self.km(node["loc"]).kernel_info(e).split("|")[0]
                     kinds[k] = kinds.get(k, 0) + 1
+                elif u["kind"] == "attention":
+                    kinds["attention_tc_f16"] = kinds.get("attention_tc_f16", 0) + 1
         else:
             for op in self.program:
                 if op[0] == "einsummable":
                     k = self.km(op[1]).kernel_info(op[2]).split("|")[0]
                     kinds[k] = kinds.get(k, 0) + 1
+                elif op[0] == "attention":
+                    kinds["attention_tc_f16"] = kinds.get("attention_tc_f16", 0) + 1
         return kinds
 
     def device_status(self):

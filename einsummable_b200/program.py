@@ -109,6 +109,16 @@ class program_t:
             l.nrow, l.ncol, l.start, _ptr(out), d, nd, ctypes.byref(idx)))
         return self._added(idx)
 
+    def add_attention(self, desc, out, q, k, v, mask, deps=()):
+        """The fused attention chain as one op (desc: attention_t)."""
+        d, nd = _deps(deps)
+        idx = ctypes.c_int(-1)
+        c = desc.c_struct()
+        _lib.check(self._lib.es_b200_program_add_attention(
+            self._p, ctypes.byref(c), _ptr(out), _ptr(q), _ptr(k), _ptr(v),
+            _ptr(mask) if mask is not None else None, d, nd, ctypes.byref(idx)))
+        return self._added(idx)
+
     def add_copy(self, src, dst, nbytes, deps=()):
         d, nd = _deps(deps)
         idx = ctypes.c_int(-1)

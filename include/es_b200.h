@@ -230,6 +230,33 @@ int es_b200_flag_signal(es_b200_t* h, void* flag, uint32_t limit_ms, void* strea
 int es_b200_flag_wait(es_b200_t* h, void* flag, uint32_t limit_ms, void* stream);
 int es_b200_pull(es_b200_t* h, const void* src, void* dst, uint64_t bytes, void* stream);
 
+/* The attention chain of a transformer layer as one launch.  It stands for FIVE consecutive apply
+ * nodes of the reference -- the scores contraction, the max and sum reductions and the elementwise
+ * node of the softmax (src/einsummable/gwriter.cc:830-855), and the contraction with the values
+ * (attention_t::forward, llama/modules.cc:285-383) -- each of which the reference launches through
+ * kernel_manager_t::operator() (src/engine/gpu/gpu_kernel_manager.cc:852-978):
+ *   S[b,h,i,j] = sum_d Q[b,h,i,d] K[b,h,j,d]    f16 inputs, f32 accumulate, rounded to f16
+ *   X          = S + mask[i,j]                  f16 add (mask may be NULL), taken to f32
+ *   P          = exp(X - max_j X) / sum_j exp(X - max_j X), rounded to f16
+ *   O[b,h,i,d] = sum_j P[b,h,i,j] V[b,h,j,d]    f32 accumulate, rounded to f16
+ * Q, K, V, O are f16 views with arbitrary element strides for (batch, head, row) -- multiples of 8
+ * -- and the head dim (a multiple of 8, at most 128) contiguous; all 16-byte aligned.  The
+ * [b,h,i,j] tensors never exist in memory. */
+typedef struct {
+    uint32_t batch, heads, rows, keys, head_dim;
+    int32_t  skip_known;    /* nonzero: mask[i][j] = -inf for every j > i - skip_from (the mask is a
+                               lower-triangular fill); blocks of such keys are not visited */
+    int32_t  skip_from;
+    int32_t  reserved;
+    int64_t  q_stride[3];   /* elements: batch, head, row */
+    int64_t  k_stride[3];   /* batch, head, key */
+    int64_t  v_stride[3];   /* batch, head, key */
+    int64_t  out_stride[3]; /* batch, head, row */
+    int64_t  mask_stride;   /* row stride of the f16 mask [rows, keys]; keys contiguous */
+} es_attention_t;
+int es_b200_launch_attention(es_b200_t* h, const es_attention_t* a, void* stream, void* out,
+                             const void* q, const void* k, const void* v, const void* mask);
+
 /* Introspection: "kind|merged str|vector width|..." of a built kernel. */
 int es_b200_kernel_info(es_b200_t* h, uint64_t kernel_id, char* buf, int buf_len);
 
@@ -377,6 +404,10 @@ int es_b200_program_add_evict(es_b200_program_t* p, const void* dev_src, void* h
                               const int* deps, int n_deps, int* op_index);
 int es_b200_program_add_load(es_b200_program_t* p, const void* host_src, void* dev_dst, uint64_t bytes,
                              const int* deps, int n_deps, int* op_index);
+/* The fused attention chain (es_b200_launch_attention) as one op of the program. */
+int es_b200_program_add_attention(es_b200_program_t* p, const es_attention_t* a, void* out,
+                                  const void* q, const void* k, const void* v, const void* mask,
+                                  const int* deps, int n_deps, int* op_index);
 int es_b200_program_add_signal(es_b200_program_t* p, void* const* flags, int n,
                                const int* deps, int n_deps, int* op_index);
 int es_b200_program_add_pull(es_b200_program_t* p, const es_pull_item_t* items, int n,

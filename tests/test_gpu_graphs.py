@@ -114,15 +114,19 @@ def test_c1_full_size(nlocs):
 FULL = np.load(os.path.join(GOLDEN_DIR, "c4_full.npz"))
 
 
-@pytest.mark.parametrize("nlocs,fuse", [(1, False), (1, True), (8, False), (8, True)])
+@pytest.mark.parametrize("nlocs,fuse", [(1, False), (1, "elementwise"), (1, True), (8, False), (8, True)])
 def test_llama7b_layer_full_size_against_the_cpu_oracle(nlocs, fuse):
     """Config 4 at full size (2048 tokens, dim 4096, FFN 11008, vocabulary 32000): the reference's
-    memgraph for 1 and for 8 locations (all on this GPU), as compiled and with elementwise chains
-    folded, against the scores of the CPU oracle with f64-accumulated contractions
+    memgraph for 1 and for 8 locations (all on this GPU), as compiled, with elementwise chains
+    folded, and with the attention chains as one kernel on top of that (fuse=True), against the
+    scores of the CPU oracle with f64-accumulated contractions
     (tests/golden/make_c4_full.py).  f16 tolerance 1e-2 of the largest score."""
     from einsummable_b200.memgraph import synthetic_llama_inputs
     mg = load_memgraph(os.path.join(GRAPHS, "llama7b_layer_locs%d.json.gz" % nlocs))
     r = memgraph_runner_t(mg, fuse=fuse)
+    # one attention chain per block of heads and rows: all of them are found
+    assert r.attention_chains == (nlocs if fuse is True else 0)
+    assert r.kernel_kinds().get("attention_tc_f16", 0) == r.attention_chains
     for k, v in synthetic_llama_inputs(mg, seed=7).items():
         r.set_input(k, v)
     r.run()
@@ -173,6 +177,9 @@ def test_fused_memgraphs_match_reference(name):
     mg = load_memgraph(graph_path(name))
     r = memgraph_runner_t(mg, fuse=True)
     assert r.folded > 0
+    # the forward graph's attention runs as the fused kernel (head dim 32 inside a 64-wide tile); the
+    # training graphs keep the softmax result for the backward pass
+    assert r.attention_chains == (1 if name == "llama_tiny_locs1" else 0)
     for k, v in inputs_of(name).items():
         r.set_input(k, v)
     r.run()

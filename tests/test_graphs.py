@@ -162,6 +162,38 @@ def test_fused_memgraph_still_matches_reference(name):
             assert err <= tol * scale, (name, mode, k, err, scale)
 
 
+def test_attention_chain_becomes_one_node_and_still_matches_reference():
+    """fuse_attention replaces scores / max / sum / normalise / values by one node; the oracle computes
+    that node as the reference's five einsummables, so the result is, bit for bit, the folded graph's."""
+    from einsummable_b200.fuse import fuse_attention, fuse_elementwise_chains
+    name = "llama_tiny_locs1"
+    mg = load(name)
+    assert fuse_attention(mg)[1] == 0            # the pattern is the folded one
+    folded, _ = fuse_elementwise_chains(mg)
+    fused, n = fuse_attention(folded)
+    assert n == 1 and len(fused["nodes"]) == len(mg["nodes"])
+    (node,) = [x for x in fused["nodes"] if "attention" in x]
+    a = node["attention"]
+    assert (a["batch"], a["heads"], a["rows"], a["keys"], a["head_dim"]) == (2, 2, 16, 16, 32)
+    assert (a["skip_known"], a["skip_from"]) == (1, 0)       # the mask is the lower-triangular fill
+    # Q and K are [batch, row, head, dim] tensors, the result [batch, head, row, dim]
+    assert a["q_stride"] == [16 * 64, 32, 64] and a["k_stride"] == a["q_stride"] and a["out_stride"] == [1024, 512, 32]
+    gone = sum(1 for x, y in zip(folded["nodes"], fused["nodes"]) if x["kind"] == "apply" and y.get("folded"))
+    assert gone == 4
+    results = []
+    for g in (folded, fused):
+        bufs = O.memgraph_place_inputs(g, inputs_of(name))
+        O.run_memgraph(g, bufs, "interp")
+        results.append(O.memgraph_collect_outputs(g, bufs))
+    for k, want in outputs_of(name).items():
+        assert np.array_equal(results[0][k], results[1][k]), k
+        scale = np.abs(want.astype(np.float64)).max()
+        assert np.abs(results[1][k].astype(np.float64) - want.astype(np.float64)).max() <= 2e-2 * scale
+    # the training graphs keep the softmax result for the backward pass: nothing to replace
+    t, _ = fuse_elementwise_chains(load("llama_train_tiny_locs1"))
+    assert fuse_attention(t)[1] == 0
+
+
 def test_fusion_never_folds_a_tensor_that_a_move_ships():
     from einsummable_b200.fuse import fuse_elementwise_chains
     mg = load("llama_tiny_locs2")

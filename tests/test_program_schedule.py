@@ -58,6 +58,10 @@ def plan(mg, owned, exchange, max_lanes=8, order="memgraph", exchange_lanes=1):
             n = nodes[u["node"]]
             offs = [m[0] for m in n["mems"]]
             prog.add_einsummable(0, ptr(n["loc"], offs[0]), [ptr(n["loc"], o) for o in offs[1:]], deps)
+        elif k == "attention":
+            from einsummable_b200.attention import attention_t
+            n = nodes[u["node"]]
+            prog.add_attention(attention_t.from_json(n["attention"]), *[ptr(n["loc"], m[0]) for m in n["mems"]], deps)
         elif k in ("touch", "rtouch"):
             n = nodes[u["node"]]
             d = n["touch"]
@@ -122,7 +126,7 @@ def regions(mg, u):
     do not count as a conflict."""
     nodes = mg["nodes"]
     k = u["kind"]
-    if k == "einsummable":
+    if k in ("einsummable", "attention"):
         n = nodes[u["node"]]
         mems = n["mems"]
         return ([(n["loc"], m[0], m[0] + m[1], None) for m in mems[1:]],
@@ -209,10 +213,15 @@ def test_single_process_schedule_has_no_unordered_hazard(name, world, lanes):
 def test_folded_graphs_stay_hazard_free_under_dependency_order(name, world):
     """The fold pass moves reads (a reader now reads its folded producer's inputs): later writers
     into that memory must have been made to wait for the reader."""
-    from einsummable_b200.fuse import fuse_elementwise_chains
+    from einsummable_b200.fuse import fuse_attention, fuse_elementwise_chains
     mg, folded = fuse_elementwise_chains(load(name))
     if not name.startswith("c1"):
         assert folded > 0
+    mg, chains = fuse_attention(mg)
+    if name.startswith("llama7b_layer"):
+        # the five nodes of every attention block of the layer graphs become one
+        assert chains == {1: 1, 2: 2, 4: 4, 8: 8}[world]
+        assert sum(1 for n in mg["nodes"] if "attention" in n) == chains
     units, d = plan(mg, set(range(world)), False, 8)
     check_plan(mg, units, d)
     for rank in range(world if world > 1 else 0):
