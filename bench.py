@@ -463,7 +463,7 @@ def run_gpu(args):
     dom = None
     for (cls, label, a, b), u in zip(tl, units):
         if cls == "contraction":
-            node = mg["nodes"][u["node"]]
+            node = r.mg["nodes"][u["node"]]
             flops = 2.0 * float(np.prod(node["einsummable"]["join_shape"]))
             if dom is None or flops > dom["flops"]:
                 dom = {"flops": flops, "us": b - a, "label": label}
@@ -472,7 +472,7 @@ def run_gpu(args):
         by_class[cls] = by_class.get(cls, 0.0) + (b - a)
     # the fused attention chains of this rank inside the step: Q, K, V read and O written once
     att = None
-    att_ops = [(b - a, mg["nodes"][u["node"]]["attention"]) for (cls, _, a, b), u in zip(tl, units) if cls == "attention"]
+    att_ops = [(b - a, r.mg["nodes"][u["node"]]["attention"]) for (cls, _, a, b), u in zip(tl, units) if cls == "attention"]
     if att_ops:
         from einsummable_b200.attention import attention_t
         us = sum(t for t, _ in att_ops)

@@ -583,6 +583,8 @@ int es_b200_debug_trace(es_b200_t* h, unsigned long long* out, int n, int* n_out
         set_device(h);
         int got = read_trace(out, n);
         if (got < 0) fail(ES_NOT_SUPPORTED, "this library was built without ES_B200_TRACE");
+        // entries 8000.. : the attention kernel's samples
+        if (n > 8000 && got == 8000) got += read_attention_trace(out + 8000, n - 8000);
         *n_out = got;
     });
 }

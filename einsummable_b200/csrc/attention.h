@@ -29,4 +29,8 @@ inline uint64_t attention_flops(es_attention_t const& a)
 // P tile, V copy, P V MMA)
 unsigned int read_and_clear_attention_error();
 
+// Trace builds (-DES_B200_TRACE): copies the first `n` of the 512 clock samples of the traced CTA (see
+// attention.cu); returns the number copied, -1 when the library was built without the trace.
+int read_attention_trace(unsigned long long* out, int n);
+
 } // namespace es

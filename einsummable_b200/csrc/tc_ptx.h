@@ -126,6 +126,12 @@ __device__ __forceinline__ void tma_load4(uint32_t dst, uint64_t desc, uint32_t 
         ::"r"(dst), "l"(desc), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
 
+__device__ __forceinline__ void tma_store4(uint64_t desc, uint32_t src, int c0, int c1, int c2, int c3)
+{
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                 ::"l"(desc), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+
 // 32 consecutive TMEM columns of this thread's lane <- 32 registers
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, uint32_t const* r)
 {

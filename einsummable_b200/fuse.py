@@ -229,6 +229,59 @@ def _match_attention(nodes, alive, i_s, saved):
     return [i_s, i_m, i_l, i_p, i_o], desc, mems
 
 
+def _lowertri_start(nodes, alive, loc, region, before, rows, cols, depth=0):
+    """If the f16 [rows, cols] tensor in `region` of location `loc`, as the node at index `before`
+    reads it, is a lower-triangular fill -- 0 where column <= row - start, -inf elsewhere -- returns
+    start, else None.  Looks through what the compilers put between the fill and its readers: copies of
+    row blocks (touches without a castable) and moves of whole tensors."""
+    if depth > 4 or region[1] != rows * cols * 2:
+        return None
+    covered, start = [], None
+    for ic in range(before - 1, -1, -1):
+        n = nodes[ic]
+        if not alive[ic]:
+            continue
+        w = _written_region(n, loc)
+        if w is None or not _overlap(w, region):
+            continue
+        if n["kind"] == "constant":
+            f = n["fill"]
+            if (covered or w != region or f["type"] != "lowertri" or f["lower"]["dtype"] != "f16"
+                    or int(f["nrow"]) != rows or int(f["ncol"]) != cols
+                    or list(f["upper"]["raw"][:2]) != [0, 252] or list(f["lower"]["raw"][:2]) != [0, 0]
+                    or abs(int(f["start"])) >= (1 << 30)):
+                return None
+            return int(f["start"])
+        if n["kind"] == "move":
+            if covered or w != region:
+                return None
+            src = (n["src_offset"], n["size"])
+            return _lowertri_start(nodes, alive, n["src_loc"], src, ic, rows, cols, depth + 1)
+        if n["kind"] == "apply" and "touch" in n:
+            t = n["touch"]
+            sel = t["selection"]
+            if w != region or t["dtype"] != "f16" or t["castable"] is not None or len(sel) != 2:
+                return None
+            (ri, ro, oi, oo, sz), (ci, co, coi, coo, csz) = [[int(x) for x in d] for d in sel]
+            if ro != rows or (ci, co, coi, coo, csz) != (cols, cols, 0, 0, cols):
+                return None
+            if any(oo < hi and lo < oo + sz for lo, hi in covered):
+                return None                  # an older lifetime of the memory shows through
+            sub = _lowertri_start(nodes, alive, loc, tuple(n["mems"][1]), ic, ri, cols, depth + 1)
+            if sub is None:
+                return None
+            s_here = sub + oo - oi           # row r of the block is row r - oo + oi of the source
+            if start is not None and s_here != start:
+                return None
+            start = s_here
+            covered.append((oo, oo + sz))
+            if sum(hi - lo for lo, hi in covered) == rows:
+                return start
+            continue
+        return None
+    return None
+
+
 def fuse_attention(mg):
     """Replaces every softmax(Q K^T + mask) V chain -- scores contraction, max, sum of exponentials,
     normalisation, contraction with V, as they stand after fuse_elementwise_chains -- by one apply node
@@ -272,18 +325,11 @@ def fuse_attention(mg):
                 break
         if hazard:
             continue
-        # a mask that a lower-triangular fill with -inf above wrote: key blocks above the diagonal are skipped
-        for ic in range(idx[1] - 1, -1, -1):
-            w = _written_region(nodes[ic], loc) if alive[ic] else None
-            if w is None or not _overlap(w, mask):
-                continue
-            f = nodes[ic].get("fill") if nodes[ic]["kind"] == "constant" else None
-            if (f and f["type"] == "lowertri" and w == mask and f["lower"]["dtype"] == "f16"
-                    and int(f["nrow"]) == desc["rows"] and int(f["ncol"]) == desc["keys"]
-                    and list(f["upper"]["raw"][:2]) == [0, 252] and list(f["lower"]["raw"][:2]) == [0, 0]
-                    and abs(int(f["start"])) < (1 << 30)):
-                desc["skip_known"], desc["skip_from"] = 1, int(f["start"])
-            break
+        # a mask that is a lower-triangular fill (0 / -inf): the kernel computes it and skips the key
+        # blocks above the diagonal
+        tri = _lowertri_start(nodes, alive, loc, mask, idx[1], desc["rows"], desc["keys"])
+        if tri is not None:
+            desc["skip_known"], desc["skip_from"] = 1, tri
         removed = set(nodes[i]["id"] for i in idx[:-1])
         deps = set()
         for i in idx:

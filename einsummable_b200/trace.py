@@ -3,6 +3,7 @@
     python -m einsummable_b200.build --trace
     python -m einsummable_b200.trace gemm 2048 4096 4096 [f16|f32]      # ij,kj->ik, M N K
     python -m einsummable_b200.trace scores | pv | nn | tn
+    python -m einsummable_b200.trace attention [noskip]                 # the fused attention chain, layer size
 
 Loads lib/libes_b200_trace.so (the library compiled with -DES_B200_TRACE: CTA 0 records
 clock64() at the role boundaries, see csrc/contraction.cu), launches one contraction a few
@@ -17,6 +18,64 @@ import sys
 import numpy as np
 
 
+def attention_trace(torch, kernel_manager_t, skip):
+    """Cycles per key block of the traced CTA (last query tile of head 0, batch 0): where the
+    softmax warp and the issuing lane spend them."""
+    from .attention import attention_t
+    b, h, s, d = 4, 32, 512, 128
+    q, k, v = [(torch.randn(b, s, h, d, device="cuda") * 0.5).half() for _ in range(3)]
+    i, j = torch.arange(s, device="cuda").unsqueeze(1), torch.arange(s, device="cuda").unsqueeze(0)
+    mask = torch.where(i >= j, 0.0, float("-inf")).half().contiguous()
+    out = torch.empty(b, h, s, d, dtype=torch.float16, device="cuda")
+    st = [s * h * d, d, h * d]
+    a = attention_t(b, h, s, s, d, st, st, st, [h * s * d, s * d, d], s, 1 if skip else 0, 0)
+    km = kernel_manager_t(0)
+    for _ in range(5):
+        km.attention(a, None, out, q, k, v, mask)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(20):
+        km.attention(a, None, out, q, k, v, mask)
+    e1.record()
+    torch.cuda.synchronize()
+    print("%.1f us per launch (with the trace compiled in), device status %d" % (e0.elapsed_time(e1) / 20 * 1e3, km.device_status()))
+    raw = np.array(km.debug_trace(8512 + 4096)[8000:], dtype=np.int64)
+    cta = raw[512:].reshape(1024, 4)[:b * h * ((s + 127) // 128)]
+    t0 = cta[:, 1].min()
+    print("CTAs: %d, first start to last end %.1f us; duration by key blocks:" % (len(cta), (cta[:, 2].max() - t0) / 1e3),
+          {int(nb): "%.1f us (n=%d)" % ((cta[cta[:, 3] == nb, 2] - cta[cta[:, 3] == nb, 1]).mean() / 1e3, (cta[:, 3] == nb).sum())
+           for nb in sorted(set(cta[:, 3]))})
+    starts = np.sort(cta[:, 1] - t0) / 1e3
+    print("start times (us), every 32nd CTA in start order:", np.round(starts[::32], 1))
+    for sm in (0, 1, 73, 147):
+        mine = cta[cta[:, 0] == sm]
+        order = np.argsort(mine[:, 1])
+        print("  SM %3d:" % sm, ["%.1f-%.1f (%d blocks)" % ((r[1] - t0) / 1e3, (r[2] - t0) / 1e3, r[3]) for r in mine[order]])
+    tr = raw[:512].reshape(16, 32)
+    n = 0
+    while n < 32 and tr[6, n] != 0:
+        n += 1
+    np.set_printoptions(linewidth=220)
+    print("key blocks of the traced CTA:", n)
+    names = ["wait for the scores", "read + pack the scores", "mask + maximum", "wait for P V of the block before (+ rescale)",
+             "exponentials + store P", "fence + arrive"]
+    print("softmax warp 0, cycles per block:", np.diff(tr[0, :n]))
+    for x, name in enumerate(names):
+        print("  %-46s" % name, tr[x + 1, :n] - tr[x, :n])
+    names = ["wait for K, issue the next block's scores", "wait for this block's scores, copy K", "wait for P",
+             "wait for V, issue P V", "wait for P V", "copy V"]
+    print("issuing lane, cycles per block  :", np.diff(tr[8, :n]))
+    for x, name in enumerate(names):
+        print("  %-46s" % name, tr[9 + x, :n] - tr[8 + x, :n])
+    print("softmax start - issuer start      :", tr[0, :n] - tr[8, :n])
+    print("setup: entry -> TMEM allocated %d -> after the CTA barrier %d -> first block starts %d" % (
+        tr[7, 1] - tr[7, 0], tr[7, 2] - tr[7, 0], tr[0, 0] - tr[7, 0]))
+    print("end: last arrive -> last P V seen %d -> result stored %d -> after the CTA barrier %d -> TMEM freed %d" % (
+        tr[15, 0] - tr[6, n - 1], tr[15, 1] - tr[6, n - 1], tr[15, 2] - tr[6, n - 1], tr[15, 3] - tr[6, n - 1]))
+    km.close()
+
+
 def main(argv):
     import torch
     from . import _lib
@@ -26,6 +85,8 @@ def main(argv):
     _lib.LIB_PATH = TRACE_LIB
     from . import einsummable_t, kernel_manager_t, scalarop_t as S
     which = argv[0] if argv else "gemm"
+    if which == "attention":
+        return attention_trace(torch, kernel_manager_t, "noskip" not in argv)
     dt = "f16"
     if which == "gemm":
         m, n, k = [int(v) for v in argv[1:4]] if len(argv) >= 4 else (2048, 4096, 4096)

@@ -244,8 +244,9 @@ int es_b200_pull(es_b200_t* h, const void* src, void* dst, uint64_t bytes, void*
  * [b,h,i,j] tensors never exist in memory. */
 typedef struct {
     uint32_t batch, heads, rows, keys, head_dim;
-    int32_t  skip_known;    /* nonzero: mask[i][j] = -inf for every j > i - skip_from (the mask is a
-                               lower-triangular fill); blocks of such keys are not visited */
+    int32_t  skip_known;    /* nonzero: the mask is exactly a lower-triangular fill, mask[i][j] = 0 for
+                               j <= i - skip_from and -inf above: it is then computed, not read, and
+                               blocks of keys no row of a tile may see are not visited */
     int32_t  skip_from;
     int32_t  reserved;
     int64_t  q_stride[3];   /* elements: batch, head, row */
@@ -302,12 +303,14 @@ int es_b200_rowsum_f32_noalloc(es_b200_t*   h,
 /* Synchronises the device and returns (and clears) the error word of the
  * tensor-core kernels: 0 = fine; nonzero = a bounded wait inside a kernel gave
  * up (1 producer, 2/3 MMA issuer, 4 epilogue) and that launch's output is not
- * valid.  The reference has no counterpart: its library kernels cannot report. */
+ * valid; 0x11..0x16 = the same inside the attention kernel (Q copy, K copy, scores, P tile,
+ * V copy, P V).  The reference has no counterpart: its library kernels cannot report. */
 int es_b200_device_status(es_b200_t* h, unsigned int* error_word);
 
 /* Clock trace of the tensor-core contraction kernel (trace builds only: the library compiled
  * with -DES_B200_TRACE records clock64() at the role boundaries of CTA 0, 8 slots of 1000
- * entries, see csrc/contraction.cu).  Copies up to `n` samples of the last launch; a normal
+ * entries, see csrc/contraction.cu; entries 8000..8511: 16 slots of 32 entries of the attention
+ * kernel, see csrc/attention.cu).  Copies up to `n` samples of the last launch; a normal
  * build returns ES_NOT_SUPPORTED.  The reference has no counterpart (its timetracker hooks in
  * src/engine/cpu/kernel_executor.cc:459-591 are host-side and commented out). */
 int es_b200_debug_trace(es_b200_t* h, unsigned long long* out, int n, int* n_out);
