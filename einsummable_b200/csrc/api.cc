@@ -17,6 +17,7 @@
 #include "handle.h"
 #include "kernels.h"
 #include "attention.h"
+#include "nvtx_ranges.h"
 #include "exchange.h"
 #include "pdl.h"
 
@@ -136,6 +137,7 @@ void launch_built(es_b200*           h,
             fail(ES_BAD_ARGUMENT, "einsummable launch: workspace must be 16-byte aligned");
     }
     set_device(h);
+    nvtx_range_t range(nvtx_on() ? k->kind + " " + k->e.describe() : std::string());
     if (k->contraction && contraction_pointers_ok(inns[0], inns[1])) {
         launch_contraction(*k->contraction, stream, out, inns[0], inns[1], workspace);
         h->counters[0] += k->contraction->n_launches;
@@ -629,6 +631,7 @@ int es_b200_launch_attention(es_b200_t* h, const es_attention_t* a, void* stream
         check_handle(h);
         if (!a) fail(ES_BAD_ARGUMENT, "attention: null descriptor");
         set_device(h);
+        nvtx_range_t range("attention_tc_f16");
         launch_attention(*a, (cudaStream_t)stream, out, q, k, v, mask);
         h->counters[0] += 1;
         h->work_bytes[0] += attention_bytes(*a);

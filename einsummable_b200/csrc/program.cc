@@ -37,6 +37,7 @@
 #include "exchange.h"
 #include "handle.h"
 #include "kernels.h"
+#include "nvtx_ranges.h"
 #include "pdl.h"
 
 namespace {
@@ -404,7 +405,10 @@ void launch_all(es_b200_program* p, cudaStream_t stream, int mode)
         if (timed) ES_CUDA_CHECK(cudaEventRecord(p->t0[i], s));
         {
             // an op may be scheduled while the op before it on its lane finishes (pdl.h)
-            pdl_scope_t scope(p->pdl);
+            pdl_scope_t  scope(p->pdl);
+            nvtx_range_t range(nvtx_on() ? std::string("op ") + std::to_string(i) + " lane " + std::to_string(op.lane) + " " +
+                                               OP_NAMES[op.kind]
+                                         : std::string());
             if (stamps) launch_stamp(p->stamps_dev + 2 * i, s);
             launch_op(p, op, s);
             if (stamps) launch_stamp(p->stamps_dev + 2 * i + 1, s);
