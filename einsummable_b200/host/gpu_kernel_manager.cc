@@ -133,6 +133,20 @@ void kernel_manager_t::operator()(einsummable_t const&             e,
     }
 }
 
+void kernel_manager_t::attention(es_attention_t const& a,
+                                 cudaStream_t          stream,
+                                 void*                 out,
+                                 void const*           q,
+                                 void const*           k,
+                                 void const*           v,
+                                 void const*           mask) const
+{
+    int status = es_b200_launch_attention(handle, &a, stream, out, q, k, v, mask);
+    if (status != ES_OK) {
+        throw_status("kernel_manager_t::attention", status);
+    }
+}
+
 void kernel_manager_t::operator()(touch_t const& touch,
                                   cudaStream_t   stream,
                                   void*          out,

@@ -70,6 +70,18 @@ struct kernel_manager_t {
     // copy `size` bytes from (src_device, src) into dst on this manager's device.
     void move(int src_device, void const* src, void* dst, uint64_t size, cudaStream_t stream) const;
 
+    // An extension without a counterpart in the reference's manager: softmax(Q K^T + mask) V, the five
+    // apply nodes the graph writer emits for attention (src/einsummable/gwriter.cc:830-855,
+    // llama/modules.cc:285-383), as one launch.  A caller that finds the chain in its memgraph passes the
+    // shapes and strides here; see es_attention_t in es_b200.h.
+    void attention(es_attention_t const& a,
+                   cudaStream_t          stream,
+                   void*                 out,
+                   void const*           q,
+                   void const*           k,
+                   void const*           v,
+                   void const*           mask) const;
+
     // For callers that hand built kernels to the library's program executor (gpu_program.h): the
     // library handle of this device and the id build() gave the (merged) einsummable.
     es_b200_t* c_handle() const

@@ -343,7 +343,7 @@ def simulate_schedule(mg, units_by_rank):
     destination ranks' pulls or remote touches -- have finished; ready units are served first come first served; each
     rank's GPU and each rank's incoming link do one unit's work at a time, launch latencies overlap.
     Deterministic (ties by rank and index), so every rank that runs it gets the same answer.
-    Returns {(rank, index): (start, finish)}."""
+    Returns {(rank, index): (start, finish, place in the order of service)}."""
     import heapq
     sig_of, pull_of = {}, {}
     for r, units in enumerate(units_by_rank):
@@ -366,29 +366,44 @@ def simulate_schedule(mg, units_by_rank):
             cost[(r, i)] = unit_cost_us(mg, u)
             for q in p:
                 succs.setdefault(q, []).append((r, i))
+    # among units that become ready at the same moment the one with the longest chain of work behind
+    # it goes first (its "bottom level": three projections that are ready together are launched in
+    # the order of what still hangs on each, not in node order)
+    order, left = [], {k: len(p) for k, p in preds.items()}
+    stack = [k for k, n in left.items() if n == 0]
+    while stack:
+        k = stack.pop()
+        order.append(k)
+        for c in succs.get(k, ()):
+            left[c] -= 1
+            if left[c] == 0:
+                stack.append(c)
+    if len(order) != len(preds):
+        raise RuntimeError("simulate_schedule: the units of the ranks wait for one another in a cycle")
+    bottom = {}
+    for k in reversed(order):
+        bottom[k] = cost[k][0] + cost[k][1] + max((bottom[c] for c in succs.get(k, ())), default=0.0)
     left = {k: len(p) for k, p in preds.items()}
     ready_at = {k: 0.0 for k in preds}
-    heap = [(0.0, k) for k, n in left.items() if n == 0]
+    heap = [(0.0, -bottom[k], k) for k, n in left.items() if n == 0]
     heapq.heapify(heap)
     free = {}
     times = {}
     while heap:
-        t, k = heapq.heappop(heap)
+        t, _, k = heapq.heappop(heap)
         lat, work, server = cost[k]
         begin = t + lat
         if server is not None and work > 0:
             begin = max(begin, free.get((k[0], server), 0.0))
             free[(k[0], server)] = begin + work
         fin = begin + work
-        times[k] = (t, fin)
+        times[k] = (t, fin, len(times))     # ready time, finish, place in the global order of service
         for c in succs.get(k, ()):
             # a flag takes about 2 us to cross NVLink
             ready_at[c] = max(ready_at[c], fin + (2.0 if c[0] != k[0] else 0.0))
             left[c] -= 1
             if left[c] == 0:
-                heapq.heappush(heap, (ready_at[c], c))
-    if len(times) != len(preds):
-        raise RuntimeError("simulate_schedule: the units of the ranks wait for one another in a cycle")
+                heapq.heappush(heap, (ready_at[c], -bottom[c], c))
     return times
 
 
@@ -404,14 +419,14 @@ def order_units_by_simulation(mg, world, rank):
     units = all_units[rank]
     # the closing wait (acknowledgements nobody on this rank needs during the run) stays last
     closing = len(units) - 1 if units and units[-1]["kind"] == "wait" else -1
-    order = sorted(range(len(units)), key=lambda i: (i == closing, times[(rank, i)][0], i))
+    order = sorted(range(len(units)), key=lambda i: (i == closing, times[(rank, i)][2]))
     new_index = {old: new for new, old in enumerate(order)}
     out = []
     for old in order:
         u = dict(units[old])
         u["deps"] = sorted(new_index[d] for d in u["deps"])
         assert all(d < len(out) for d in u["deps"])
-        u["sim_start_us"], u["sim_finish_us"] = times[(rank, old)]
+        u["sim_start_us"], u["sim_finish_us"] = times[(rank, old)][:2]
         out.append(u)
     return out
 
@@ -540,6 +555,8 @@ class memgraph_runner_t:
         nodes = self.mg["nodes"]
         if self.transport == "p2p" and self.order == "simulated":
             self.units = order_units_by_simulation(self.mg, self.num_locs, self.rank)
+        elif self.num_locs == 1 and self.order == "simulated":
+            self.units = order_units_by_simulation(self.mg, 1, 0)
         else:
             self.units = schedule_units(self.mg, set(self.devices), self.transport == "p2p")
         dev = next(iter(self.devices.values()))

@@ -299,3 +299,26 @@ def test_storage_evict_load_through_the_c_abi():
     torch.cuda.synchronize()
     _lib.check(lib.es_b200_storage_destroy(sto))
     km.close()
+
+
+def test_nvtx_ranges_are_opt_in_and_harmless():
+    """ES_B200_NVTX=1: every launch and program op pushes / pops a named NVTX range (nothing listens here:
+    the run must simply behave as before)."""
+    import subprocess
+    import sys
+    code = (
+        "import numpy as np, torch\n"
+        "from einsummable_b200.memgraph import load_memgraph, memgraph_runner_t\n"
+        "mg = load_memgraph(%r)\n"
+        "r = memgraph_runner_t(mg)\n"
+        "rng = np.random.default_rng(0)\n"
+        "for t in mg['inputs']:\n"
+        "    r.set_input(t['name'], rng.uniform(-1, 1, t['shape']).astype(np.float32))\n"
+        "r.run(); torch.cuda.synchronize()\n"
+        "assert r.device_status() == 0\n"
+        "print('ok', float(np.abs(r.get_output(mg['outputs'][0]['name'])).max()))\n"
+    ) % graph_path("c1_n64_locs1")
+    env = dict(os.environ, ES_B200_NVTX="1")
+    root = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..")
+    res = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, cwd=root, timeout=300)
+    assert res.returncode == 0 and res.stdout.startswith("ok"), res.stdout[-500:] + res.stderr[-2000:]
