@@ -491,14 +491,23 @@ def run_gpu(args):
     r.close()
     del r
     torch.cuda.empty_cache()
-    for name, kw in (("folded_without_the_attention_kernel", dict(fuse="elementwise")),
+    # (the first one: the same layer under a hand-written tensor-parallel placement instead of autoplace01 --
+    # residual stream split over the sequence, projections over heads / the hidden dim / the vocabulary --
+    # compiled by the reference's taskgraph and memgraph compilers, tests/golden/make_tp_graphs.py)
+    for name, kw in (("tensor_parallel_placement", dict(fuse=True)),
+                     ("folded_without_the_attention_kernel", dict(fuse="elementwise")),
                      ("as_compiled", dict(fuse=False)),
                      ("as_compiled_list_schedule", dict(fuse=False, schedule="list"))):
         try:
             if name.endswith("list_schedule") and os.environ.get("ES_B200_BENCH_LIST", "1") == "0":
                 continue
-            rv = make_runner(rk, mg, **kw)
-            for k, v in inputs.items():
+            mgv = mg
+            if name == "tensor_parallel_placement":
+                if world == 1:
+                    continue
+                mgv = load_layer_graph(world, LAYER_FIXTURE + "_tp")
+            rv = make_runner(rk, mgv, **kw)
+            for k, v in layer_inputs(mgv).items() if mgv is not mg else inputs.items():
                 rv.set_input(k, v)
             rv.capture()
             for _ in range(3):

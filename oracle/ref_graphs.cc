@@ -290,6 +290,177 @@ int ref_graph_build_llama_cfg(uint64_t dim, uint64_t n_heads, uint64_t multiple_
     G_END
 }
 
+// Config 4's graph under a hand-written tensor-parallel placement instead of autoplace01 -- the kind of
+// placement llama/first_token.cc:240-343 offers beside "auto" (its "data" / "dim" / "seq" partitioners feed
+// apart03; this one needs a different split in different parts of the layer, which apart03's forward
+// propagation cannot express, so every node's partition is set here):
+//   * the residual stream ([batch, seq, heads, head_dim] and its row statistics) is split over the sequence;
+//   * wq / wk / wv are split over their output heads, everything between them and wo (RoPE, scores,
+//     softmax, P V) over heads, wo over its input heads with the partial sums added into the
+//     sequence-split residual stream;
+//   * w1 / w3 over the hidden dim, the SwiGLU product over the hidden dim, w2 over its hidden (contracted)
+//     dim with the partial sums added into the residual stream;
+//   * the vocabulary projection over the vocabulary; what is left (the last token's rows) on location 0.
+// Block k of the one split dim lives on location k, so every weight block is used where it lives.
+// The reference's taskgraph compiler does the rest (refinement touches, moves, partial-sum groups).
+int ref_graph_build_llama_tp(uint64_t dim, uint64_t n_heads, uint64_t multiple_of, uint64_t vocab_size, int n_layers,
+                             uint64_t batch, uint64_t seqlen, int nlocs, int dtype_code)
+{
+    G_BEGIN
+    set_default_dtype(dtype_code == 0 ? dtype_t::f16 : dtype_t::f32);
+    model_args_t args = model_args_t::llama_7B(batch);
+    args.dim = dim;
+    args.n_heads = n_heads;
+    args.multiple_of = multiple_of;
+    args.vocab_size = vocab_size;
+    args.n_layers = n_layers;
+    args.max_seq_len = seqlen;
+    builder_t builder = builder_t::make_first_token(args, seqlen);
+    auto*     b = new built_graph_t();
+    b->graph = builder.graph;
+    graph_t const& graph = b->graph;
+    enum region_t { NONE = 0, ROW, HEAD, HID, VOC, TAIL };
+    enum role_t { R_NONE = 0, R_QKV, R_WO, R_W13, R_W2, R_VOCAB };
+    map<int, role_t> weight_role;
+    for (auto const& [name, gid] : builder.weights) {
+        auto ends = [&](char const* suffix) {
+            string sfx(suffix);
+            return name.size() >= sfx.size() && name.compare(name.size() - sfx.size(), sfx.size(), sfx) == 0;
+        };
+        if (ends("wq.weight") || ends("wk.weight") || ends("wv.weight")) weight_role[gid] = R_QKV;
+        else if (ends("wo.weight")) weight_role[gid] = R_WO;
+        else if (ends("w1.weight") || ends("w3.weight")) weight_role[gid] = R_W13;
+        else if (ends("w2.weight")) weight_role[gid] = R_W2;
+        else if (ends("output.weight")) weight_role[gid] = R_VOCAB;
+    }
+    uint64_t const hidden = [&] {
+        for (auto const& [name, gid] : builder.weights)
+            if (weight_role.count(gid) && weight_role[gid] == R_W2) return graph.nodes[gid].op.out_shape().back();
+        return uint64_t(0);
+    }();
+    int const n = nlocs;
+    vector<region_t>          region(graph.nodes.size(), NONE);
+    vector<role_t>            role(graph.nodes.size(), R_NONE);
+    vector<vector<partdim_t>> pds(graph.nodes.size());
+    auto singletons = [](vector<uint64_t> const& shape) {
+        vector<partdim_t> ret;
+        for (uint64_t d : shape) ret.push_back(partdim_t::singleton(d));
+        return ret;
+    };
+    // the partition of a shape in a region: one dim split n ways, chosen by what the dim is
+    auto split_by_region = [&](vector<uint64_t> const& shape, region_t r) {
+        vector<partdim_t> ret = singletons(shape);
+        int               which = -1;
+        if (r == ROW) {
+            if (shape.size() >= 2 && shape[0] == batch && shape[1] == seqlen) which = 1;
+        } else if (r == HEAD) {
+            for (int i = 0; i != int(shape.size()); ++i)
+                if (shape[i] == n_heads) { which = i; break; }
+        } else if (r == HID) {
+            for (int i = 0; i != int(shape.size()); ++i)
+                if (shape[i] == hidden) { which = i; break; }
+        } else if (r == VOC) {
+            for (int i = 0; i != int(shape.size()); ++i)
+                if (shape[i] == vocab_size) { which = i; break; }
+        }
+        if (which >= 0 && shape[which] % uint64_t(n) == 0) ret[which] = partdim_t::split(shape[which], n);
+        return ret;
+    };
+    for (int gid : graph.get_order()) {
+        auto const&      node = graph.nodes[gid];
+        vector<uint64_t> out_shape = node.op.out_shape();
+        if (node.op.is_input()) {
+            auto it = weight_role.find(gid);
+            pds[gid] = singletons(out_shape);
+            if (it != weight_role.end()) {
+                int which = (it->second == R_QKV || it->second == R_W13 || it->second == R_VOCAB) ? 0 : 2;
+                pds[gid][which] = partdim_t::split(out_shape[which], n);
+            } else if (gid == builder.embeddings) {
+                region[gid] = ROW;
+                pds[gid] = split_by_region(out_shape, ROW);
+            }
+            continue;
+        }
+        if (node.op.is_fill()) {
+            pds[gid] = singletons(out_shape);
+            continue;
+        }
+        // what the inputs say
+        region_t r = NONE;
+        for (int inn : node.inns)
+            if (region[inn] != NONE) r = region[inn];
+        if (node.op.is_einsummable()) {
+            einsummable_t const& e = node.op.get_einsummable();
+            role_t               w = R_NONE;
+            int                  w_slot = -1;
+            for (int k = 0; k != int(node.inns.size()); ++k) {
+                int  src = node.inns[k];
+                auto it = weight_role.find(src);
+                if (it != weight_role.end() && e.has_aggregation()) { w = it->second; w_slot = k; }
+            }
+            vector<partdim_t> join = singletons(e.join_shape);
+            if (w != R_NONE) {
+                // a projection: split the join mode that the weight's split dim maps to
+                int wdim = (w == R_QKV || w == R_W13 || w == R_VOCAB) ? 0 : 2;
+                int mode = e.inns[w_slot][wdim];
+                join[mode] = partdim_t::split(e.join_shape[mode], n);
+                role[gid] = w;
+                region[gid] = w == R_QKV ? HEAD : (w == R_W13 ? HID : (w == R_VOCAB ? VOC : ROW));
+            } else {
+                region[gid] = r;
+                // follow the first input that is split; modes it lacks stay whole
+                for (int k = 0; k != int(node.inns.size()); ++k) {
+                    auto const& ipd = pds[node.inns[k]];
+                    bool        any = false;
+                    for (int i = 0; i != int(ipd.size()); ++i)
+                        if (ipd[i].num_parts() > 1) any = true;
+                    if (!any || region[node.inns[k]] != r) continue;
+                    for (int i = 0; i != int(ipd.size()); ++i) join[e.inns[k][i]] = ipd[i];
+                    break;
+                }
+            }
+            pds[gid] = join;
+            continue;
+        }
+        if (node.op.is_formation()) {
+            int inn = node.inns[0];
+            if (role[inn] == R_WO || role[inn] == R_W2) {
+                region[gid] = ROW; // the partial sums land in the sequence-split residual stream
+                pds[gid] = split_by_region(out_shape, ROW);
+            } else {
+                region[gid] = region[inn];
+                pds[gid] = vector<partdim_t>(pds[inn].begin(), pds[inn].begin() + out_shape.size());
+            }
+            continue;
+        }
+        // complexer / squeezer / select: by region and shape
+        region[gid] = r;
+        pds[gid] = split_by_region(out_shape, r);
+        if (r == ROW && !(out_shape.size() >= 2 && out_shape[0] == batch && out_shape[1] == seqlen)) region[gid] = TAIL;
+    }
+    for (int gid = 0; gid != int(graph.nodes.size()); ++gid) {
+        partition_t    part(pds[gid]);
+        vtensor_t<int> locs(part.block_shape());
+        if (part.num_parts() == n)
+            for (int i = 0; i != n; ++i) locs.get()[i] = i;
+        else if (part.num_parts() != 1)
+            throw std::runtime_error("tensor-parallel placement: node " + std::to_string(gid) + " has " +
+                                     std::to_string(part.num_parts()) + " blocks");
+        b->placements.emplace_back(part, locs);
+    }
+    for (auto const& [name, gid] : builder.weights) {
+        b->names[gid] = name;
+    }
+    b->names[builder.freqs_cis] = "freqs_cis";
+    b->names[builder.embeddings] = "embeddings";
+    if (builder.mask) {
+        b->names[builder.mask.value()] = "mask";
+    }
+    b->names[builder.scores] = "scores";
+    return finish(b);
+    G_END
+}
+
 // config 5: forward + backward + vanilla weight update of n_layers LLaMA layers
 int ref_graph_build_llama_train(uint64_t dim,
                                 uint64_t n_heads,

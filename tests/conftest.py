@@ -15,6 +15,22 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200)")
 
 
+class GraphArrays:
+    """graphs.npz and graphs_tp.npz (inputs and reference results of the small memgraph fixtures) as one
+    read-only mapping with the `.files` of an npz."""
+
+    def __init__(self):
+        self._d = {}
+        for name in ("graphs.npz", "graphs_tp.npz"):
+            a = np.load(os.path.join(GOLDEN_DIR, "graphs", name))
+            for k in a.files:
+                self._d[k] = a[k]
+        self.files = list(self._d)
+
+    def __getitem__(self, k):
+        return self._d[k]
+
+
 class Golden:
     def __init__(self):
         with open(os.path.join(GOLDEN_DIR, "golden.json")) as f:

@@ -26,7 +26,7 @@ def main():
     graphs = os.path.join(ROOT, "tests", "golden", "graphs")
     path = os.path.join(graphs, name + ".json")
     mg = load_memgraph(path if os.path.exists(path) else path + ".gz")
-    arr = np.load(os.path.join(graphs, "graphs.npz"))
+    arr = np.load(os.path.join(graphs, "graphs_tp.npz" if "_tp_" in name else "graphs.npz"))
     log("process group up; building runner", transport)
     r = memgraph_runner_t(mg, rank=rank, world=world, transport=transport, wait_limit_ms=2000,
                           fuse="fuse" in sys.argv[3:])

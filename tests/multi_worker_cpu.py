@@ -28,7 +28,7 @@ def main():
     if fuse:
         from einsummable_b200.fuse import fuse_elementwise_chains
         mg, _ = fuse_elementwise_chains(mg)
-    arr = np.load(os.path.join(graphs, "graphs.npz"))
+    arr = np.load(os.path.join(graphs, "graphs_tp.npz" if "_tp_" in name else "graphs.npz"))
     pre = name + "/in/"
     ins = {k[len(pre):]: arr[k] for k in arr.files if k.startswith(pre)}
     bufs = O.memgraph_place_inputs(mg, ins)          # every location's inputs; only this rank's buffer is used

@@ -17,11 +17,11 @@ import numpy as np
 import pytest
 
 import es_oracle as O
-from conftest import GOLDEN_DIR, ROOT
+from conftest import GOLDEN_DIR, GraphArrays, ROOT
 
 pytestmark = pytest.mark.gpu
 BIN = os.path.join(ROOT, "oracle", "_ref", "engine_parity")
-ARR = np.load(os.path.join(GOLDEN_DIR, "graphs", "graphs.npz"))
+ARR = GraphArrays()
 
 CASES = [
     ("c1_n64_locs1", "c1:64:2:1"),

@@ -13,13 +13,13 @@ import pytest
 import torch
 
 import es_oracle as O
-from conftest import GOLDEN_DIR
+from conftest import GOLDEN_DIR, GraphArrays
 from einsummable_b200.memgraph import load_memgraph, memgraph_runner_t
 
 pytestmark = pytest.mark.gpu
 GRAPHS = os.path.join(GOLDEN_DIR, "graphs")
-ARR = np.load(os.path.join(GRAPHS, "graphs.npz"))
-SMALL = ["c1_n64_locs1", "c1_n64_locs2", "llama_tiny_locs1", "llama_tiny_locs2", "llama_tiny_locs4",
+ARR = GraphArrays()
+SMALL = ["c1_n64_locs1", "c1_n64_locs2", "llama_tiny_locs1", "llama_tiny_locs2", "llama_tiny_locs4", "llama_tiny_tp_locs2",
          "llama_train_tiny_locs1", "llama_train_tiny_locs2", "llama_train_adamw_tiny_locs1",
          "llama_train_adamw_tiny_locs2", "llama_train_lora_tiny_locs1", "llama_train_lora_tiny_locs2"]
 
@@ -114,7 +114,7 @@ def test_c1_full_size(nlocs):
 FULL = np.load(os.path.join(GOLDEN_DIR, "c4_full.npz"))
 
 
-@pytest.mark.parametrize("nlocs,fuse", [(1, False), (1, "elementwise"), (1, True), (8, False), (8, True)])
+@pytest.mark.parametrize("nlocs,fuse", [(1, False), (1, "elementwise"), (1, True), (8, False), (8, True), ("tp_locs8", True)])
 def test_llama7b_layer_full_size_against_the_cpu_oracle(nlocs, fuse):
     """Config 4 at full size (2048 tokens, dim 4096, FFN 11008, vocabulary 32000): the reference's
     memgraph for 1 and for 8 locations (all on this GPU), as compiled, with elementwise chains
@@ -122,7 +122,10 @@ def test_llama7b_layer_full_size_against_the_cpu_oracle(nlocs, fuse):
     scores of the CPU oracle with f64-accumulated contractions
     (tests/golden/make_c4_full.py).  f16 tolerance 1e-2 of the largest score."""
     from einsummable_b200.memgraph import synthetic_llama_inputs
-    mg = load_memgraph(os.path.join(GRAPHS, "llama7b_layer_locs%d.json.gz" % nlocs))
+    if nlocs == "tp_locs8":     # the hand-written tensor-parallel placement (tests/golden/make_tp_graphs.py)
+        mg, nlocs = load_memgraph(os.path.join(GRAPHS, "llama7b_layer_tp_locs8.json.gz")), 8
+    else:
+        mg = load_memgraph(os.path.join(GRAPHS, "llama7b_layer_locs%d.json.gz" % nlocs))
     r = memgraph_runner_t(mg, fuse=fuse)
     # one attention chain per block of heads and rows: all of them are found
     assert r.attention_chains == (nlocs if fuse is True else 0)

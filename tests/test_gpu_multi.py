@@ -42,7 +42,7 @@ def test_two_ranks_llama_tiny(transport):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("name", ["llama_tiny_locs2", "llama_train_tiny_locs2"])
+@pytest.mark.parametrize("name", ["llama_tiny_locs2", "llama_train_tiny_locs2", "llama_tiny_tp_locs2"])
 def test_two_ranks_fused(name):
     """Elementwise nodes folded into their readers inside each location (every rank folds the same
     way); the moves and their hand-shakes are those of the unfused graph."""

@@ -7,11 +7,11 @@ import numpy as np
 import pytest
 
 import es_oracle as O
-from conftest import GOLDEN_DIR
+from conftest import GOLDEN_DIR, GraphArrays
 
 GRAPHS = os.path.join(GOLDEN_DIR, "graphs")
-ARR = np.load(os.path.join(GRAPHS, "graphs.npz"))
-SMALL = ["c1_n64_locs1", "c1_n64_locs2", "llama_tiny_locs1", "llama_tiny_locs2", "llama_tiny_locs4",
+ARR = GraphArrays()
+SMALL = ["c1_n64_locs1", "c1_n64_locs2", "llama_tiny_locs1", "llama_tiny_locs2", "llama_tiny_locs4", "llama_tiny_tp_locs2",
          "llama_train_tiny_locs1", "llama_train_tiny_locs2", "llama_train_adamw_tiny_locs1",
          "llama_train_adamw_tiny_locs2", "llama_train_lora_tiny_locs1", "llama_train_lora_tiny_locs2"]
 
@@ -87,7 +87,7 @@ def test_llama7b_layer_statistics():
         assert abs(mg["taskgraph"]["contraction_flops"] - 847.157e9) < 1e7
 
 
-@pytest.mark.parametrize("name", ["llama_tiny_locs2", "llama_tiny_locs4", "c1_n64_locs2"])
+@pytest.mark.parametrize("name", ["llama_tiny_locs2", "llama_tiny_locs4", "c1_n64_locs2", "llama_tiny_tp_locs2"])
 def test_move_runs_cut_groups_the_same_way_on_every_rank(name):
     """The NCCL transport posts a rank's members of one run as one group.  Runs must come from
     the global order alone: no non-move node inside a run, no dependency between two members."""
@@ -139,7 +139,7 @@ def test_compose_substitutes_and_renumbers():
     assert c["castable"] == "add" and c["out_rank"] == 1 and c["join_shape"] == [8, 4]
 
 
-@pytest.mark.parametrize("name", ["llama_tiny_locs1", "llama_train_tiny_locs1", "c1_n64_locs1", "llama_tiny_locs2",
+@pytest.mark.parametrize("name", ["llama_tiny_locs1", "llama_train_tiny_locs1", "c1_n64_locs1", "llama_tiny_locs2", "llama_tiny_tp_locs2",
                                   "llama_tiny_locs4", "llama_train_tiny_locs2", "llama_train_adamw_tiny_locs1",
                                   "llama_train_adamw_tiny_locs2", "llama_train_lora_tiny_locs1",
                                   "llama_train_lora_tiny_locs2"])

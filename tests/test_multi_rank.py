@@ -89,6 +89,11 @@ def test_partitioned_memgraph_over_two_gloo_ranks():
     _run_cpu_workers(2, "llama_tiny_locs2")
 
 
+def test_tensor_parallel_memgraph_over_two_gloo_ranks():
+    """The same model under the hand-written tensor-parallel placement (tests/golden/make_tp_graphs.py)."""
+    _run_cpu_workers(2, "llama_tiny_tp_locs2")
+
+
 def test_partitioned_memgraph_over_four_gloo_ranks():
     """The four-location graph is the one whose groups, cut per rank instead of from the global
     order, made the ranks wait on each other for ever."""

@@ -196,8 +196,10 @@ def check_plan(mg, units, d):
 
 
 SMALL = [("c1_n64_evict_locs1", 1), ("c1_n64_evict_locs2", 2), ("c1_n64_locs2", 2), ("llama_tiny_locs2", 2), ("llama_tiny_locs4", 4), ("llama_train_tiny_locs2", 2),
-         ("llama_train_adamw_tiny_locs2", 2)]
-LARGE = [("llama7b_layer_locs1", 1), ("llama7b_layer_locs2", 2), ("llama7b_layer_locs4", 4), ("llama7b_layer_locs8", 8)]
+         ("llama_train_adamw_tiny_locs2", 2), ("llama_tiny_tp_locs2", 2)]
+# the layer under the reference's autoplace01 and under the hand-written tensor-parallel placement
+LARGE = [("llama7b_layer_locs1", 1), ("llama7b_layer_locs2", 2), ("llama7b_layer_locs4", 4), ("llama7b_layer_locs8", 8),
+         ("llama7b_layer_tp_locs2", 2), ("llama7b_layer_tp_locs4", 4), ("llama7b_layer_tp_locs8", 8)]
 
 
 @pytest.mark.parametrize("name,world", SMALL + LARGE)
@@ -407,7 +409,7 @@ def _run_units_on_cpu(mg, units, order, inputs):
 
 
 @pytest.mark.parametrize("name", ["c1_n64_evict_locs1", "c1_n64_evict_locs2", "c1_n64_locs2", "llama_tiny_locs2",
-                                  "llama_train_tiny_locs2"])
+                                  "llama_train_tiny_locs2", "llama_tiny_tp_locs2"])
 def test_any_order_that_respects_the_dependencies_gives_the_reference_result(name):
     """The units of a memgraph (all locations in one process) run by the oracle in random topological
     orders of their `deps`: every such order must give, bit for bit, what the memgraph's own node order
@@ -416,7 +418,7 @@ def test_any_order_that_respects_the_dependencies_gives_the_reference_result(nam
     import random
     import numpy as np
     mg = load(name)
-    arr = np.load(os.path.join(GRAPHS, "graphs_evict.npz" if "evict" in name else "graphs.npz"))
+    arr = np.load(os.path.join(GRAPHS, "graphs_evict.npz" if "evict" in name else ("graphs_tp.npz" if "_tp_" in name else "graphs.npz")))
     pre = name + "/in/"
     inputs = {k[len(pre):]: arr[k] for k in arr.files if k.startswith(pre)}
     pre = name + "/out/"
