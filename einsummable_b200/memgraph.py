@@ -115,6 +115,42 @@ def move_runs(mg):
 BOOKKEEPING = ("alloc", "del", "inputmem", "inputsto", "partialize")
 
 
+def node_levels(mg):
+    """Earliest finish time (us) of every launching node if nothing ever waited for a free GPU or link:
+    the longest chain of estimated costs (unit_cost_us) that leads to it, through all locations.  The same
+    on every rank; used to tell moves that become ready early from moves that become ready late."""
+    nodes = mg["nodes"]
+    level = {}
+    for n in nodes:
+        kind = n["kind"]
+        start = max((level[i] for i in n["inns"]), default=0.0)
+        if kind in BOOKKEEPING:
+            level[n["id"]] = start
+            continue
+        if kind == "apply" and "attention" in n:
+            u = {"kind": "attention", "node": n["id"]}
+        elif kind == "apply" and "touch" in n:
+            u = {"kind": "touch", "node": n["id"], "first": True}
+        elif kind == "apply":
+            u = {"kind": "einsummable", "node": n["id"]}
+        elif kind == "constant":
+            u = {"kind": "constant", "node": n["id"]}
+        elif kind == "move" and n["src_loc"] != n["dst_loc"]:
+            u = {"kind": "pull", "moves": [n["id"]]}
+        elif kind in ("move", "copy"):
+            u = {"kind": "copy", "node": n["id"]}
+        else:
+            u = {"kind": kind, "node": n["id"]}
+        lat, work, _ = unit_cost_us(mg, u)
+        level[n["id"]] = start + lat + work + (5.0 if u["kind"] == "pull" else 0.0)   # + signal and flag
+    return level
+
+
+# incoming moves of one run share an await (and a pull) only when their sources are expected to be ready
+# within this many microseconds of each other: a shared await is as late as its latest signal
+AWAIT_SPREAD_US = 12.0
+
+
 def _sides(node):
     if node["kind"] == "move":
         return (node["src_loc"], node["dst_loc"])
@@ -151,6 +187,11 @@ def schedule_units(mg, owned, exchange):
 
     def is_cross(n):
         return exchange and n["kind"] == "move" and n["src_loc"] != n["dst_loc"]
+
+    levels = node_levels(mg) if exchange else {}
+
+    def ready_level(m):   # when the source of move m is expected to be ready
+        return max((levels[i] for i in nodes[m]["inns"]), default=0.0)
 
     # real nodes a bookkeeping node stands for (nodes are in topological order)
     closure = {}
@@ -228,20 +269,30 @@ def schedule_units(mg, owned, exchange):
         if kind == "move" and is_cross(n):
             run = run_members[runs[nid]]
             if n["dst_loc"] in owned and nid not in unit_of:
-                members = [m for m in run if nodes[m]["dst_loc"] in owned and nodes[m]["dst_loc"] == n["dst_loc"]
-                           and is_cross(nodes[m])]
-                aw = emit({"kind": "await", "moves": members, "deps": [], "loc": n["dst_loc"]})
-                copied = [m for m in members if m not in remote_touch]
-                for m in members:
-                    unit_of[m] = aw
-                if copied:
-                    raw = set()
-                    for m in copied:
-                        raw |= raw_deps(nodes[m], nodes[m]["dst_loc"])
-                    deps = resolve(raw)      # may put a wait unit in front
-                    idx = emit({"kind": "pull", "moves": copied, "deps": sorted(set(deps) | {aw}), "loc": n["dst_loc"]})
-                    for m in copied:
-                        unit_of[m] = idx
+                all_members = [m for m in run if nodes[m]["dst_loc"] in owned and nodes[m]["dst_loc"] == n["dst_loc"]
+                               and is_cross(nodes[m])]
+                # members in the order in which their sources are expected to be ready, cut where that
+                # jumps: an early tensor must not wait behind the flag of a late one
+                by_level = sorted(all_members, key=lambda m: (ready_level(m), m))
+                clusters = [[by_level[0]]]
+                for m in by_level[1:]:
+                    if ready_level(m) - ready_level(clusters[-1][0]) > AWAIT_SPREAD_US:
+                        clusters.append([])
+                    clusters[-1].append(m)
+                for members in clusters:
+                    members = sorted(members)
+                    aw = emit({"kind": "await", "moves": members, "deps": [], "loc": n["dst_loc"]})
+                    copied = [m for m in members if m not in remote_touch]
+                    for m in members:
+                        unit_of[m] = aw
+                    if copied:
+                        raw = set()
+                        for m in copied:
+                            raw |= raw_deps(nodes[m], nodes[m]["dst_loc"])
+                        deps = resolve(raw)      # may put a wait unit in front
+                        idx = emit({"kind": "pull", "moves": copied, "deps": sorted(set(deps) | {aw}), "loc": n["dst_loc"]})
+                        for m in copied:
+                            unit_of[m] = idx
             if n["src_loc"] in owned and ("signal", nid) not in unit_of:
                 members = [m for m in run if nodes[m]["src_loc"] == n["src_loc"] and is_cross(nodes[m])]
                 by_deps = {}

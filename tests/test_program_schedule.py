@@ -323,10 +323,18 @@ def test_exchange_ops_come_in_the_same_global_order_on_every_rank():
     mg = load("llama7b_layer_locs8")
     for rank in range(8):
         units = M.schedule_units(mg, {rank}, True)
-        keys = [min(u["moves"]) for u in units if u["kind"] == "await"]
-        assert keys == sorted(keys)
-        # the incoming moves of one run share a unit; units never mix runs
+        # runs in memgraph order; inside a run (its moves do not depend on one another) the awaits in the
+        # order in which their sources are expected to be ready -- a function of the graph alone
         runs = M.move_runs(mg)
+        levels = M.node_levels(mg)
+        ready = lambda m: max((levels[i] for i in mg["nodes"][m]["inns"]), default=0.0)  # noqa: E731
+        keys = [(runs[u["moves"][0]], min(ready(m) for m in u["moves"])) for u in units if u["kind"] == "await"]
+        assert keys == sorted(keys)
+        # an await never spans sources expected more than the spread apart
+        for u in units:
+            if u["kind"] == "await":
+                assert max(ready(m) for m in u["moves"]) - min(ready(m) for m in u["moves"]) <= M.AWAIT_SPREAD_US
+        # the incoming moves of one run share a unit where their sources come together; units never mix runs
         for u in units:
             if u["kind"] in ("await", "pull"):
                 assert len({runs[m] for m in u["moves"]}) == 1
