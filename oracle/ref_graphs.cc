@@ -300,7 +300,8 @@ int ref_graph_build_llama_cfg(uint64_t dim, uint64_t n_heads, uint64_t multiple_
 //     sequence-split residual stream;
 //   * w1 / w3 over the hidden dim, the SwiGLU product over the hidden dim, w2 over its hidden (contracted)
 //     dim with the partial sums added into the residual stream;
-//   * the vocabulary projection over the vocabulary; what is left (the last token's rows) on location 0.
+//   * the vocabulary projection over the vocabulary; what is left (the last token's rows: the final norm
+//     of one row per batch entry) on the last location, where those rows already are.
 // Block k of the one split dim lives on location k, so every weight block is used where it lives.
 // The reference's taskgraph compiler does the rest (refinement touches, moves, partial-sum groups).
 int ref_graph_build_llama_tp(uint64_t dim, uint64_t n_heads, uint64_t multiple_of, uint64_t vocab_size, int n_layers,
@@ -443,7 +444,9 @@ int ref_graph_build_llama_tp(uint64_t dim, uint64_t n_heads, uint64_t multiple_o
         vtensor_t<int> locs(part.block_shape());
         if (part.num_parts() == n)
             for (int i = 0; i != n; ++i) locs.get()[i] = i;
-        else if (part.num_parts() != 1)
+        else if (part.num_parts() == 1)
+            locs.get()[0] = region[gid] == TAIL ? n - 1 : 0;
+        else
             throw std::runtime_error("tensor-parallel placement: node " + std::to_string(gid) + " has " +
                                      std::to_string(part.num_parts()) + " blocks");
         b->placements.emplace_back(part, locs);
