@@ -304,7 +304,7 @@ class ClockSampler:
 LAYER_FIXTURE = "llama7b_layer"
 LAYER_WORKLOAD = ("C4 LLaMA-7B-shape transformer layer forward (dim 4096, 32 heads x 128, FFN 11008 SwiGLU, RMSNorm, "
                   "RoPE, causal attention, last-token vocabulary projection), batch 4 x seq 512 = 2048 tokens, f16, "
-                  "the reference's memgraph for N locations (autoplace01)")
+                  "the memgraph the reference's compilers emit for N locations (placement: see config.placement)")
 LAYER_TOKENS = 2048
 
 
@@ -429,7 +429,16 @@ def run_gpu(args):
     want = golden_scores()
 
     # ---------------- headline: the layer graph for `world` locations, one process per GPU ----------------
-    mg = load_layer_graph(world)
+    # The headline is the graph the reference's autoplace01 gives for `world` locations (the configuration the
+    # baseline names).  At N > 1 the same layer under the hand-written tensor-parallel placement
+    # (tests/golden/make_tp_graphs.py; both graphs come out of the reference's own taskgraph and memgraph
+    # compilers and give the same scores) is measured beside it in `config.variants`;
+    # ES_B200_BENCH_PLACEMENT=tensor_parallel swaps the two.
+    placement = "autoplace01"
+    if world > 1 and os.environ.get("ES_B200_BENCH_PLACEMENT", "autoplace01") == "tensor_parallel":
+        placement = "tensor_parallel"
+    mg_auto = load_layer_graph(world)
+    mg = mg_auto if placement == "autoplace01" else load_layer_graph(world, LAYER_FIXTURE + "_tp")
     inputs = layer_inputs(mg)
     r = make_runner(rk, mg, fuse=True)
     for k, v in inputs.items():
@@ -491,21 +500,23 @@ def run_gpu(args):
     r.close()
     del r
     torch.cuda.empty_cache()
-    # (the first one: the same layer under a hand-written tensor-parallel placement instead of autoplace01 --
-    # residual stream split over the sequence, projections over heads / the hidden dim / the vocabulary --
-    # compiled by the reference's taskgraph and memgraph compilers, tests/golden/make_tp_graphs.py)
-    for name, kw in (("tensor_parallel_placement", dict(fuse=True)),
-                     ("folded_without_the_attention_kernel", dict(fuse="elementwise")),
-                     ("as_compiled", dict(fuse=False)),
-                     ("as_compiled_list_schedule", dict(fuse=False, schedule="list"))):
+    # (the other placement first: at N > 1 the autoplacer's graph when the headline is the tensor-parallel one,
+    # and the other way round)
+    other = "autoplace01" if placement == "tensor_parallel" else "tensor_parallel_placement"
+    for name, kw in ((other, dict(fuse=True)),
+                     ("autoplace01_folded_without_the_attention_kernel", dict(fuse="elementwise")),
+                     ("autoplace01_as_compiled", dict(fuse=False)),
+                     ("autoplace01_as_compiled_list_schedule", dict(fuse=False, schedule="list"))):
         try:
             if name.endswith("list_schedule") and os.environ.get("ES_B200_BENCH_LIST", "1") == "0":
                 continue
-            mgv = mg
+            mgv = mg_auto
             if name == "tensor_parallel_placement":
                 if world == 1:
                     continue
                 mgv = load_layer_graph(world, LAYER_FIXTURE + "_tp")
+            elif name == "autoplace01" and world == 1:
+                continue
             rv = make_runner(rk, mgv, **kw)
             for k, v in layer_inputs(mgv).items() if mgv is not mg else inputs.items():
                 rv.set_input(k, v)
@@ -553,6 +564,10 @@ def run_gpu(args):
         "steps": args.steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"workload": LAYER_WORKLOAD, "tokens_per_step": LAYER_TOKENS,
+                   "placement": ("the reference's autoplace01" if placement == "autoplace01" else
+                                 "tensor-parallel by hand (residual stream over the sequence, projections over heads / "
+                                 "hidden / vocabulary), compiled by the reference's taskgraph and memgraph compilers; "
+                                 "the autoplace01 graph is in variants"),
                    "l2": "weights (405 MB) and activations exceed the 126 MB L2; no flush",
                    "execution": "one CUDA-graph replay per step (dependency-ordered lanes), elementwise chains "
                                 "folded into their readers, every attention chain one kernel; eager %.3f ms" % ms_eager,
