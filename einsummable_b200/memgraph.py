@@ -26,6 +26,7 @@ Two schedules:
 """
 import gzip
 import json
+import os
 
 import numpy as np
 import torch
@@ -157,7 +158,7 @@ def _sides(node):
     return (node["loc"],)
 
 
-def schedule_units(mg, owned, exchange):
+def schedule_units(mg, owned, exchange, group_sum=False):
     """The launchable units of the locations in `owned`, in the memgraph's node order, each with
     the units it depends on.
 
@@ -223,6 +224,31 @@ def schedule_units(mg, owned, exchange):
                         and sum(1 for i in t["inns"] if is_cross(nodes[i])) == 1):
                     remote_touch[m] = t["id"]
     touch_move = {t: m for m, t in remote_touch.items()}
+
+    # group_sum: the remote adds of a partial-sum group -- whole dense blocks that arrive from
+    # several peers and are added into the same tensor one after the other -- as ONE elementwise kernel
+    # out = out + r1 + ... + rk over the peers' memory (plus one launch that acknowledges the k moves),
+    # instead of k dependent touches of 8-12 us each.  fused_tail[touch id] = (group key, members).
+    fused_tail = {}
+    if exchange and group_sum:
+        members_of = {}
+        for n in nodes:
+            if n["kind"] == "apply" and "touch" in n and n["group"] >= 0 and n["loc"] in owned:
+                members_of.setdefault((n["loc"], n["group"]), []).append(n["id"])
+
+        def dense_add(tid):
+            t = nodes[tid]["touch"]
+            return (tid in touch_move and t["castable"] == "add" and t["dtype"] in ("f16", "f32")
+                    and all(int(d[0]) == int(d[1]) == int(d[4]) and int(d[2]) == 0 and int(d[3]) == 0 for d in t["selection"]))
+
+        for key, ms in members_of.items():
+            # never the first member (that one is the copy); the others commute, so the remote ones may
+            # be added together where the last of them stands
+            tail = [tid for tid in ms[1:] if dense_add(tid)]
+            if 2 <= len(tail) <= 7:
+                for tid in tail:
+                    fused_tail[tid] = (key, tail)
+    pending_tail = {}
 
     def raw_deps(n, side=None):
         acc = set()
@@ -314,6 +340,19 @@ def schedule_units(mg, owned, exchange):
                 first = key not in group_last
                 if not first:
                     deps = sorted(set(deps) | {group_last[key]})
+            if nid in fused_tail:
+                key, tail = fused_tail[nid]
+                acc = pending_tail.setdefault(key, set())
+                acc |= set(deps)
+                if nid != tail[-1]:
+                    continue                      # emitted with the last member of the tail
+                idx = emit({"kind": "rsum", "nodes": list(tail), "node": tail[0], "moves": [touch_move[t] for t in tail],
+                            "deps": sorted(acc), "loc": loc})
+                for t in tail:
+                    unit_of[t] = idx
+                emit({"kind": "ack", "moves": [touch_move[t] for t in tail], "deps": [idx], "loc": loc})
+                group_last[key] = idx
+                continue
             if nid in touch_move:
                 idx = emit({"kind": "rtouch", "node": nid, "moves": [touch_move[nid]], "deps": deps, "first": first,
                             "loc": loc})
@@ -371,6 +410,10 @@ def unit_cost_us(mg, u):
         return 2.5, n["mems"][1][1] * (2 if u["first"] else 3) / 4.5e6, "gpu"
     if k == "rtouch":
         return 6.0, nodes[u["node"]]["mems"][1][1] / 0.65e6, "link"
+    if k == "rsum":
+        return 6.0, sum(nodes[t]["mems"][1][1] for t in u["nodes"]) / 0.65e6, "link"
+    if k == "ack":
+        return 3.0, 0.0, None
     if k == "await":
         return 3.0, 0.0, None
     if k == "constant":
@@ -402,7 +445,7 @@ def simulate_schedule(mg, units_by_rank):
             if u["kind"] == "signal":
                 for m in u["moves"]:
                     sig_of[m] = (r, i)
-            elif u["kind"] in ("pull", "rtouch"):
+            elif u["kind"] in ("pull", "rtouch", "ack"):
                 for m in u["moves"]:
                     pull_of[m] = (r, i)
     preds, succs, cost = {}, {}, {}
@@ -458,14 +501,14 @@ def simulate_schedule(mg, units_by_rank):
     return times
 
 
-def order_units_by_simulation(mg, world, rank):
+def order_units_by_simulation(mg, world, rank, group_sum=False):
     """The units of `rank` (schedule_units) reordered by their simulated start time, dependencies
     renumbered.  Every rank simulates all ranks, so the ranks agree on when each exchange is expected:
     the pull / wait ops, which share one in-order lane, are then served in the order in which their
     data is expected to be ready instead of the memgraph's node order.  The order stays a valid one
     on every rank and across ranks: along every dependency, also those that cross ranks, the
     simulated start times strictly increase."""
-    all_units = [schedule_units(mg, {r}, True) for r in range(world)]
+    all_units = [schedule_units(mg, {r}, True, group_sum) for r in range(world)]
     times = simulate_schedule(mg, all_units)
     units = all_units[rank]
     # the closing wait (acknowledgements nobody on this rank needs during the run) stays last
@@ -484,13 +527,15 @@ def order_units_by_simulation(mg, world, rank):
 
 class memgraph_runner_t:
     def __init__(self, mg, devices=None, rank=None, world=None, transport="nccl", wait_limit_ms=0, fuse=False,
-                 schedule="dag", max_lanes=0, order="simulated", exchange_lanes=1):
+                 schedule="dag", max_lanes=0, order="simulated", exchange_lanes=1, group_sum=None):
         """transport (one process per GPU only): "nccl" = send/recv pairs; "p2p" = every
         location buffer lives in symmetric memory, the destination rank pulls the bytes over
         NVLink with an SM copy kernel, and the two ranks hand-shake through bounded flag
         kernels (data ready / copy finished).
         schedule: "dag" = the library's program executor (dependency-ordered lanes, see the
         module text); "list" = one stream in node order.  The NCCL transport always runs as a list."""
+        # the trailing remote adds of a partial-sum group as one kernel (schedule_units); ES_B200_GROUP_SUM=1 turns it on
+        self.group_sum = (os.environ.get("ES_B200_GROUP_SUM", "0") == "1") if group_sum is None else bool(group_sum)
         self.folded = 0
         self.attention_chains = 0
         if fuse:
@@ -605,11 +650,11 @@ class memgraph_runner_t:
         """Translates schedule_units into ops of the library's program executor."""
         nodes = self.mg["nodes"]
         if self.transport == "p2p" and self.order == "simulated":
-            self.units = order_units_by_simulation(self.mg, self.num_locs, self.rank)
+            self.units = order_units_by_simulation(self.mg, self.num_locs, self.rank, self.group_sum)
         elif self.num_locs == 1 and self.order == "simulated":
             self.units = order_units_by_simulation(self.mg, 1, 0)
         else:
-            self.units = schedule_units(self.mg, set(self.devices), self.transport == "p2p")
+            self.units = schedule_units(self.mg, set(self.devices), self.transport == "p2p", self.group_sum)
         dev = next(iter(self.devices.values()))
         km = self.kms[dev]
         prog = program_t(km)
@@ -657,6 +702,28 @@ class memgraph_runner_t:
                                    self.ptr(loc, offs[1]), deps)
                 self.stats["touch"] += 1
                 self.unit_labels.append((kind, "%s %s %d bytes" % (d["castable"], d["dtype"], node["mems"][1][1])))
+            elif kind == "rsum":
+                # out = out + r1 + ... + rk, the r's read in the peers' memory (generated elementwise kernel)
+                first = nodes[u["nodes"][0]]
+                dt = first["touch"]["dtype"]
+                nelem = first["mems"][0][1] // DTYPE_SIZE[dt]
+                k = len(u["nodes"])
+                join = "hole|%s@0" % dt
+                for i in range(1, k + 1):
+                    join = "+[%s,hole|%s@%d]" % (join, dt, i)
+                e = einsummable_t([nelem], [[0]] * (k + 1), 1, join, None)
+                if km.build(e) is None:
+                    raise RuntimeError("build returned nullopt for %r" % (e,))
+                out = self.ptr(first["loc"], first["mems"][0][0])
+                srcs = [self.peer_base[nodes[m]["src_loc"]] + nodes[m]["src_offset"] for m in u["moves"]]
+                prog.add_einsummable(km._built(e)[0], out, [out] + srcs, deps)
+                self.stats["touch"] += k
+                self.stats["move"] += k
+                self.stats["move_bytes"] += sum(nodes[m]["size"] for m in u["moves"])
+                self.unit_labels.append(("rsum", "%d peers x %d bytes %s" % (k, first["mems"][0][1], dt)))
+            elif kind == "ack":
+                prog.add_signal([self._flag_ptr(nodes[m]["src_loc"], 1, self.move_index[m]) for m in u["moves"]], deps)
+                self.unit_labels.append(("signal", "ack %d" % len(u["moves"])))
             elif kind == "constant":
                 node = nodes[u["node"]]
                 f = node["fill"]

@@ -36,15 +36,15 @@ def ptr(loc, off):
     return (loc + 1) * BASE + off
 
 
-def plan(mg, owned, exchange, max_lanes=8, order="memgraph", exchange_lanes=1):
+def plan(mg, owned, exchange, max_lanes=8, order="memgraph", exchange_lanes=1, group_sum=False):
     """(units, described schedule) of the program a runner would build for `owned`; order
     "simulated": the units of one rank sorted by the start times of the all-rank simulation."""
     nodes = mg["nodes"]
     if order == "simulated":
         (rank,) = owned
-        units = M.order_units_by_simulation(mg, mg["num_locs"], rank)
+        units = M.order_units_by_simulation(mg, mg["num_locs"], rank, group_sum)
     else:
-        units = M.schedule_units(mg, owned, exchange)
+        units = M.schedule_units(mg, owned, exchange, group_sum)
     cross = [n["id"] for n in nodes if n["kind"] == "move" and n["src_loc"] != n["dst_loc"]]
     index = {m: k for k, m in enumerate(cross)}
 
@@ -87,6 +87,12 @@ def plan(mg, owned, exchange, max_lanes=8, order="memgraph", exchange_lanes=1):
                 prog.add_evict(ptr(n["loc"], n["offset"]), host, n["size"], deps)
             else:
                 prog.add_load(host, ptr(n["loc"], n["offset"]), n["size"], deps)
+        elif k == "rsum":
+            n = nodes[u["nodes"][0]]
+            out = ptr(n["loc"], n["mems"][0][0])
+            prog.add_einsummable(0, out, [out] + [ptr(nodes[m]["src_loc"], nodes[m]["src_offset"]) for m in u["moves"]], deps)
+        elif k == "ack":
+            prog.add_signal([flag(nodes[m]["src_loc"], 1, m) for m in u["moves"]], deps)
         elif k == "signal":
             prog.add_signal([flag(nodes[m]["dst_loc"], 0, m) for m in u["moves"]], deps)
         elif k == "await":
@@ -141,6 +147,10 @@ def regions(mg, u):
         if not u["first"]:
             reads.append(out)
         return reads, [out]
+    if k == "rsum":     # out += peers' blocks (read in the peers' memory under the signal / acknowledgement pair)
+        n = nodes[u["nodes"][0]]
+        out = (n["loc"], n["mems"][0][0], n["mems"][0][0] + n["mems"][0][1], None)
+        return [out], [out]
     if k == "constant":
         n = nodes[u["node"]]
         f = n["fill"]
@@ -297,7 +307,9 @@ def test_exchange_never_blocks_over_repeated_runs(name, world, order, exchange_l
                             if not all(ready.get(m, 0) >= run for m in u["moves"]):
                                 break
                             assert all(ready[m] == run for m in u["moves"]), "an await saw a flag of another run"
-                        elif u["kind"] in ("pull", "rtouch"):
+                        elif u["kind"] == "rsum":
+                            assert all(ready.get(m, 0) == run for m in u["moves"]), "bytes read before their signal"
+                        elif u["kind"] in ("pull", "rtouch", "ack"):
                             assert all(ready.get(m, 0) == run for m in u["moves"]), "bytes read before their signal"
                             for m in u["moves"]:
                                 done[m] = run
@@ -343,6 +355,74 @@ def test_exchange_ops_come_in_the_same_global_order_on_every_rank():
         assert sorted(read) == sorted(n["id"] for n in mg["nodes"] if n["kind"] == "move"
                                       and n["dst_loc"] == rank and n["src_loc"] != rank)
         assert sum(1 for u in units if u["kind"] == "rtouch") >= 10
+
+
+GROUP_SUM = [("llama7b_layer_locs4", 4), ("llama7b_layer_locs8", 8), ("llama7b_layer_tp_locs4", 4), ("llama7b_layer_tp_locs8", 8)]
+
+
+@pytest.mark.parametrize("name,world", GROUP_SUM)
+def test_group_sums_keep_the_plans_hazard_free_and_the_exchange_live(name, world):
+    """group_sum=True: the remote adds of a partial-sum group become one elementwise op over the peers' memory
+    followed by one op that acknowledges the moves.  Same checks as for the plain plans: every hazard ordered,
+    sources protected, all ranks together never block and read only what was signalled in the same run."""
+    from einsummable_b200.fuse import fuse_attention, fuse_elementwise_chains
+    mg = fuse_attention(fuse_elementwise_chains(load(name))[0])[0]
+    nodes = mg["nodes"]
+    plans = [plan(mg, {r}, True, order="simulated", group_sum=True) for r in range(world)]
+    n_sums = 0
+    for rank, (units, d) in enumerate(plans):
+        check_plan(mg, units, d)
+        sums = [u for u in units if u["kind"] == "rsum"]
+        n_sums += len(sums)
+        for u in sums:
+            assert 2 <= len(u["moves"]) <= 7 and len(set(u["moves"])) == len(u["moves"])
+            for t, m in zip(u["nodes"], u["moves"]):       # each member is the one reader of its move
+                assert m in nodes[t]["inns"] and nodes[t]["touch"]["castable"] == "add"
+                assert nodes[t]["mems"][0] == nodes[u["nodes"][0]]["mems"][0]
+        # every incoming move is still read exactly once
+        read = [m for u in units if u["kind"] in ("pull", "rtouch", "rsum") for m in u["moves"]]
+        assert sorted(read) == sorted(n["id"] for n in nodes if n["kind"] == "move" and n["dst_loc"] == rank
+                                      and n["src_loc"] != rank)
+    assert n_sums >= 2
+    ready, done = {}, {}
+    for run in range(1, 3):
+        finished = [set() for _ in range(world)]
+        queues = []
+        for r in range(world):
+            lanes = {}
+            for i, op in enumerate(plans[r][1]["ops"]):
+                lanes.setdefault(op["lane"], []).append(i)
+            queues.append(lanes)
+        remaining = sum(len(p[0]) for p in plans)
+        while remaining:
+            progressed = False
+            for r in range(world):
+                units, d = plans[r]
+                for lane, queue in queues[r].items():
+                    while queue:
+                        i = queue[0]
+                        if not all(w in finished[r] for w in d["ops"][i]["wait_on"]):
+                            break
+                        u = units[i]
+                        if u["kind"] == "await" and not all(ready.get(m, 0) >= run for m in u["moves"]):
+                            break
+                        if u["kind"] == "wait" and not all(done.get(m, 0) >= run for m in u["moves"]):
+                            break
+                        if u["kind"] in ("pull", "rtouch", "rsum", "ack"):
+                            assert all(ready.get(m, 0) == run for m in u["moves"]), "bytes read before their signal"
+                        if u["kind"] in ("pull", "rtouch", "ack"):
+                            for m in u["moves"]:
+                                done[m] = run
+                        if u["kind"] == "signal":
+                            for m in u["moves"]:
+                                assert ready.get(m, 0) == run - 1
+                                ready[m] = run
+                        finished[r].add(i)
+                        queue.pop(0)
+                        remaining -= 1
+                        progressed = True
+            assert progressed, "every rank is blocked in run %d" % run
+        assert set(ready.values()) == set(done.values()) == {run}
 
 
 def test_simulated_order_is_the_same_on_every_rank_and_increases_along_dependencies():
