@@ -19,7 +19,7 @@ from einsummable_b200.memgraph import load_memgraph, memgraph_runner_t
 pytestmark = pytest.mark.gpu
 GRAPHS = os.path.join(GOLDEN_DIR, "graphs")
 ARR = GraphArrays()
-SMALL = ["c1_n64_locs1", "c1_n64_locs2", "llama_tiny_locs1", "llama_tiny_locs2", "llama_tiny_locs4", "llama_tiny_tp_locs2",
+SMALL = ["c1_n64_locs1", "c1_n64_locs2", "llama_tiny_locs1", "llama_tiny_locs2", "llama_tiny_locs4", "llama_tiny_tp_locs2", "llama_tiny_tp_locs4",
          "llama_train_tiny_locs1", "llama_train_tiny_locs2", "llama_train_adamw_tiny_locs1",
          "llama_train_adamw_tiny_locs2", "llama_train_lora_tiny_locs1", "llama_train_lora_tiny_locs2"]
 

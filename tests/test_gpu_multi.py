@@ -21,8 +21,8 @@ def free_port():
         return s.getsockname()[1]
 
 
-def run_workers(nproc, name, transport, *extra):
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+def run_workers(nproc, name, transport, *extra, **env_extra):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", **env_extra)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(nproc),
            "--master-addr", "127.0.0.1", "--master-port", str(free_port()),
            os.path.join(ROOT, "tests", "multi_worker.py"), name, transport] + list(extra)
@@ -58,6 +58,15 @@ def test_two_ranks_c1(tmp_path):
 @pytest.mark.parametrize("transport", ["nccl", "p2p"])
 def test_four_ranks_llama_tiny(transport):
     run_workers(4, "llama_tiny_locs4", transport)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
+@pytest.mark.parametrize("group_sum", ["0", "1"])
+def test_four_ranks_tensor_parallel_placement(group_sum):
+    """The tiny model under the hand-written tensor-parallel placement on 4 locations (partial-sum groups
+    with three remote members), folded, attention as one kernel, captured; with group_sum the three remote
+    adds of a group run as one elementwise kernel over the peers' memory."""
+    run_workers(4, "llama_tiny_tp_locs4", "p2p", "fuse", "capture", ES_B200_GROUP_SUM=group_sum)
 
 
 def test_flag_kernels_single_gpu():

@@ -206,7 +206,7 @@ def check_plan(mg, units, d):
 
 
 SMALL = [("c1_n64_evict_locs1", 1), ("c1_n64_evict_locs2", 2), ("c1_n64_locs2", 2), ("llama_tiny_locs2", 2), ("llama_tiny_locs4", 4), ("llama_train_tiny_locs2", 2),
-         ("llama_train_adamw_tiny_locs2", 2), ("llama_tiny_tp_locs2", 2)]
+         ("llama_train_adamw_tiny_locs2", 2), ("llama_tiny_tp_locs2", 2), ("llama_tiny_tp_locs4", 4)]
 # the layer under the reference's autoplace01 and under the hand-written tensor-parallel placement
 LARGE = [("llama7b_layer_locs1", 1), ("llama7b_layer_locs2", 2), ("llama7b_layer_locs4", 4), ("llama7b_layer_locs8", 8),
          ("llama7b_layer_tp_locs2", 2), ("llama7b_layer_tp_locs4", 4), ("llama7b_layer_tp_locs8", 8)]
@@ -357,7 +357,7 @@ def test_exchange_ops_come_in_the_same_global_order_on_every_rank():
         assert sum(1 for u in units if u["kind"] == "rtouch") >= 10
 
 
-GROUP_SUM = [("llama7b_layer_locs4", 4), ("llama7b_layer_locs8", 8), ("llama7b_layer_tp_locs4", 4), ("llama7b_layer_tp_locs8", 8)]
+GROUP_SUM = [("llama_tiny_tp_locs4", 4), ("llama7b_layer_locs4", 4), ("llama7b_layer_locs8", 8), ("llama7b_layer_tp_locs4", 4), ("llama7b_layer_tp_locs8", 8)]
 
 
 @pytest.mark.parametrize("name,world", GROUP_SUM)
