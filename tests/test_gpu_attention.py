@@ -93,6 +93,7 @@ CASES = [
     (1, 2, 128, 320, 128, "bshd", "random"),     # five blocks
     (2, 3, 200, 150, 64, "bshd", "random"),      # ragged rows and keys, one 64-wide block of the head dim
     (2, 2, 16, 16, 32, "bshd", "causal"),        # the tiny llama fixture's shape: head dim 32 of a 64-wide tile
+    (2, 1, 16, 16, 16, "bshd", "causal"),        # one of four heads of the tiny tensor-parallel fixture: head dim 16
     (1, 2, 130, 70, 96, "bhsd", "causal"),       # head dim 96 of a 128-wide tile
     (2, 4, 256, 512, 128, "bshd", "causal"),
     (1, 3, 64, 64, 128, "bhsd", None),           # no mask

@@ -173,7 +173,7 @@ def test_llama7b_training_graph_full_size_loss(fuse):
 
 
 @pytest.mark.parametrize("name", ["llama_tiny_locs1", "llama_train_tiny_locs1", "llama_train_adamw_tiny_locs1",
-                                  "llama_train_lora_tiny_locs1"])
+                                  "llama_train_lora_tiny_locs1", "llama_tiny_tp_locs2", "llama_tiny_tp_locs4"])
 def test_fused_memgraphs_match_reference(name):
     """Elementwise producers folded into their readers (einsummable_b200/fuse.py): every fused
     join goes through the same code generator; results against the reference interpreter's."""
@@ -182,7 +182,8 @@ def test_fused_memgraphs_match_reference(name):
     assert r.folded > 0
     # the forward graph's attention runs as the fused kernel (head dim 32 inside a 64-wide tile); the
     # training graphs keep the softmax result for the backward pass
-    assert r.attention_chains == (1 if name == "llama_tiny_locs1" else 0)
+    # (the tensor-parallel fixtures: one chain per location, on its own heads, all locations on this GPU)
+    assert r.attention_chains == {"llama_tiny_locs1": 1, "llama_tiny_tp_locs2": 2, "llama_tiny_tp_locs4": 4}.get(name, 0)
     for k, v in inputs_of(name).items():
         r.set_input(k, v)
     r.run()

@@ -26,7 +26,12 @@ def run_workers(nproc, name, transport, *extra, **env_extra):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(nproc),
            "--master-addr", "127.0.0.1", "--master-port", str(free_port()),
            os.path.join(ROOT, "tests", "multi_worker.py"), name, transport] + list(extra)
-    res = subprocess.run(cmd, capture_output=True, text=True, timeout=180, env=env)
+    for attempt in range(3):
+        res = subprocess.run(cmd, capture_output=True, text=True, timeout=180, env=env)
+        if res.returncode == 0 or "EADDRINUSE" not in res.stderr:
+            break
+        # the port found free a moment ago was taken by the time torchrun bound it: pick another
+        cmd[cmd.index("--master-port") + 1] = str(free_port())
     print(res.stdout[-3000:])
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
     return res.stdout
