@@ -164,7 +164,8 @@ def schedule_units(mg, owned, exchange, group_sum=False):
 
     owned: the locations this process drives.  exchange: True when a move between two locations
     is an exchange between two processes (one process per GPU) -- the source rank gets a
-    `signal` unit; the destination rank an `await` unit (waits for the signal) followed by a
+    `signal` unit; the destination rank an `await` unit (waits for the signal; the incoming moves of a run
+    share one only where their sources are expected to be ready together, node_levels) followed by a
     `pull` unit (copies the bytes over and acknowledges), or, when the moved block is read by
     exactly one touch, by that touch as an `rtouch` unit that reads the peer's memory directly;
     and whatever later reuses the source's memory a `wait` unit for the acknowledgement.
@@ -177,8 +178,9 @@ def schedule_units(mg, owned, exchange, group_sum=False):
     the same producers share a signal unit.  Touches of one group are chained in node order, the
     first being the copy (src/engine/gpu/exec_graph.cc:167-172,368-378).
 
-    Units are dicts: kind in {einsummable, touch, rtouch, constant, copy, signal, await, pull,
-    wait}, `deps` (indices of earlier units), `node` and / or `moves` (memgraph node ids)."""
+    Units are dicts: kind in {einsummable, attention, touch, rtouch, constant, copy, evict, load, signal,
+    await, pull, wait, and with group_sum: rsum, ack}, `deps` (indices of earlier units), `node` and / or
+    `moves` (memgraph node ids)."""
     nodes = mg["nodes"]
     owned = set(owned)
     runs = move_runs(mg)
