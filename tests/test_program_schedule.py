@@ -357,35 +357,13 @@ def test_exchange_ops_come_in_the_same_global_order_on_every_rank():
         assert sum(1 for u in units if u["kind"] == "rtouch") >= 10
 
 
-GROUP_SUM = [("llama_tiny_tp_locs4", 4), ("llama7b_layer_locs4", 4), ("llama7b_layer_locs8", 8), ("llama7b_layer_tp_locs4", 4), ("llama7b_layer_tp_locs8", 8)]
-
-
-@pytest.mark.parametrize("name,world", GROUP_SUM)
-def test_group_sums_keep_the_plans_hazard_free_and_the_exchange_live(name, world):
-    """group_sum=True: the remote adds of a partial-sum group become one elementwise op over the peers' memory
-    followed by one op that acknowledges the moves.  Same checks as for the plain plans: every hazard ordered,
-    sources protected, all ranks together never block and read only what was signalled in the same run."""
-    from einsummable_b200.fuse import fuse_attention, fuse_elementwise_chains
-    mg = fuse_attention(fuse_elementwise_chains(load(name))[0])[0]
-    nodes = mg["nodes"]
-    plans = [plan(mg, {r}, True, order="simulated", group_sum=True) for r in range(world)]
-    n_sums = 0
-    for rank, (units, d) in enumerate(plans):
-        check_plan(mg, units, d)
-        sums = [u for u in units if u["kind"] == "rsum"]
-        n_sums += len(sums)
-        for u in sums:
-            assert 2 <= len(u["moves"]) <= 7 and len(set(u["moves"])) == len(u["moves"])
-            for t, m in zip(u["nodes"], u["moves"]):       # each member is the one reader of its move
-                assert m in nodes[t]["inns"] and nodes[t]["touch"]["castable"] == "add"
-                assert nodes[t]["mems"][0] == nodes[u["nodes"][0]]["mems"][0]
-        # every incoming move is still read exactly once
-        read = [m for u in units if u["kind"] in ("pull", "rtouch", "rsum") for m in u["moves"]]
-        assert sorted(read) == sorted(n["id"] for n in nodes if n["kind"] == "move" and n["dst_loc"] == rank
-                                      and n["src_loc"] != rank)
-    assert n_sums >= 2
+def all_ranks_stay_live(plans, world, runs=2):
+    """Every rank's program executed together with the kernels' semantics for a few runs: an op starts when
+    the op before it on its lane and the ops it waits for have finished; an await passes when its flags have
+    reached the run number, a wait when the acknowledgements have; whoever reads a move sees the flag of the
+    same run."""
     ready, done = {}, {}
-    for run in range(1, 3):
+    for run in range(1, runs + 1):
         finished = [set() for _ in range(world)]
         queues = []
         for r in range(world):
@@ -423,6 +401,48 @@ def test_group_sums_keep_the_plans_hazard_free_and_the_exchange_live(name, world
                         progressed = True
             assert progressed, "every rank is blocked in run %d" % run
         assert set(ready.values()) == set(done.values()) == {run}
+
+
+GROUP_SUM = [("llama_tiny_tp_locs4", 4), ("llama7b_layer_locs4", 4), ("llama7b_layer_locs8", 8), ("llama7b_layer_tp_locs4", 4), ("llama7b_layer_tp_locs8", 8)]
+
+
+@pytest.mark.parametrize("name,world", GROUP_SUM)
+def test_group_sums_keep_the_plans_hazard_free_and_the_exchange_live(name, world):
+    """group_sum=True: the remote adds of a partial-sum group become one elementwise op over the peers' memory
+    followed by one op that acknowledges the moves.  Same checks as for the plain plans: every hazard ordered,
+    sources protected, all ranks together never block and read only what was signalled in the same run."""
+    from einsummable_b200.fuse import fuse_attention, fuse_elementwise_chains
+    mg = fuse_attention(fuse_elementwise_chains(load(name))[0])[0]
+    nodes = mg["nodes"]
+    plans = [plan(mg, {r}, True, order="simulated", group_sum=True) for r in range(world)]
+    n_sums = 0
+    for rank, (units, d) in enumerate(plans):
+        check_plan(mg, units, d)
+        sums = [u for u in units if u["kind"] == "rsum"]
+        n_sums += len(sums)
+        for u in sums:
+            assert 2 <= len(u["moves"]) <= 7 and len(set(u["moves"])) == len(u["moves"])
+            for t, m in zip(u["nodes"], u["moves"]):       # each member is the one reader of its move
+                assert m in nodes[t]["inns"] and nodes[t]["touch"]["castable"] == "add"
+                assert nodes[t]["mems"][0] == nodes[u["nodes"][0]]["mems"][0]
+        # every incoming move is still read exactly once
+        read = [m for u in units if u["kind"] in ("pull", "rtouch", "rsum") for m in u["moves"]]
+        assert sorted(read) == sorted(n["id"] for n in nodes if n["kind"] == "move" and n["dst_loc"] == rank
+                                      and n["src_loc"] != rank)
+    assert n_sums >= 2
+    all_ranks_stay_live(plans, world)
+
+
+@pytest.mark.parametrize("name,world", [("llama7b_train_l4_locs2", 2), ("llama7b_train_l4_locs4", 4)])
+def test_training_graphs_are_hazard_free_and_live(name, world):
+    """Config 5's shape (four layers forward, loss, backward, update; 6625 / 14000 memgraph nodes), folded, one
+    process per location in simulated order: every hazard ordered, the exchange never blocks."""
+    from einsummable_b200.fuse import fuse_attention, fuse_elementwise_chains
+    mg = fuse_attention(fuse_elementwise_chains(load(name))[0])[0]
+    plans = [plan(mg, {r}, True, order="simulated") for r in range(world)]
+    for units, d in plans:
+        check_plan(mg, units, d)
+    all_ranks_stay_live(plans, world)
 
 
 def test_simulated_order_is_the_same_on_every_rank_and_increases_along_dependencies():
