@@ -611,9 +611,12 @@ def ffn_traffic(dom):
 
 
 def e2e_layer(rk, r, mg, inputs, stream, steps):
-    """tokens/s through the public call with host buffers: every step copies the step's input (the
-    token embeddings; the weights are the resident model) from pinned host memory into the location
-    buffers, replays the graph and reads the result (`scores`) back into pinned host memory."""
+    """tokens/s through the public call with host buffers: every step's input (the token embeddings; the
+    weights are the resident model) crosses PCIe from pinned host memory, the graph is replayed, and the step's
+    result (`scores`) is read back into pinned host memory, all inside the timed region.  The input is
+    double-buffered the way a serving loop would do it: the host-to-device copy of step k + 1 runs on a copy
+    stream into a staging buffer while step k is replayed, and a device-to-device copy at the top of the step
+    puts it where the graph reads it.  `serial_ms_per_step` is the same with the copy in line (no overlap)."""
     torch = rk.torch
     name = "embeddings" if any(t["name"] == "embeddings" for t in mg["inputs"]) else mg["inputs"][0]["name"]
     up = r.stage_input(name, inputs[name])
@@ -621,20 +624,43 @@ def e2e_layer(rk, r, mg, inputs, stream, steps):
     h2d = sum(h.numel() * h.element_size() for h, _ in up)
     d2h = sum(h.numel() * h.element_size() for h, _ in down)
 
-    def step():
+    def serial_step():
         for h, d in up:
             d.copy_(h, non_blocking=True)
         r.replay(stream)
         for h, d in down:
             h.copy_(d, non_blocking=True)
     for _ in range(3):
+        serial_step()
+    ms_serial = timed_steps(rk, stream, serial_step, steps)
+
+    copy_stream = torch.cuda.Stream(device=rk.dev)
+    staging = [torch.empty_like(d) for _, d in up]
+    arrived, consumed = torch.cuda.Event(), torch.cuda.Event()
+    consumed.record(stream)
+
+    def step():
+        copy_stream.wait_event(consumed)          # the staging buffer of the step before has been read
+        with torch.cuda.stream(copy_stream):
+            for (h, _), sbuf in zip(up, staging):
+                sbuf.copy_(h, non_blocking=True)
+            arrived.record(copy_stream)
+        stream.wait_event(arrived)
+        for (_, d), sbuf in zip(up, staging):
+            d.copy_(sbuf, non_blocking=True)
+        consumed.record(stream)
+        r.replay(stream)
+        for h, d in down:
+            h.copy_(d, non_blocking=True)
+    for _ in range(3):
         step()
     ms = timed_steps(rk, stream, step, steps)
+    torch.cuda.synchronize(rk.dev)
     tot_h2d, tot_d2h = sum_int(rk, h2d), sum_int(rk, d2h)
     return {"value": LAYER_TOKENS / (ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": tot_h2d,
-            "d2h_bytes_per_step": tot_d2h, "ms_per_step": ms, "steps": steps,
-            "what": "input `%s` from pinned host memory every step, result `scores` back to pinned host memory; "
-                    "weights stay resident" % name}
+            "d2h_bytes_per_step": tot_d2h, "ms_per_step": ms, "serial_ms_per_step": ms_serial, "steps": steps,
+            "what": "input `%s` from pinned host memory every step (its copy overlaps the step before: staging buffer + "
+                    "copy stream), result `scores` back to pinned host memory; weights stay resident" % name}
 
 
 def sum_int(rk, v):
