@@ -445,6 +445,51 @@ def test_training_graphs_are_hazard_free_and_live(name, world):
     all_ranks_stay_live(plans, world)
 
 
+def test_an_early_tensor_does_not_wait_behind_the_flag_of_a_late_one():
+    """Two adjacent, independent moves from location 0 to location 1 -- one whose source exists from the
+    start, one whose source is the end of a long chain -- form one run.  They must not share an await: the
+    reader of the early tensor would otherwise start when the late one is ready."""
+    n_el = 1 << 20                                  # 4 MiB f32 per tensor: each chain node costs microseconds
+    size = 4 * n_el
+
+    def ew(i, inns, loc, out, reads):
+        return {"id": i, "inns": inns, "kind": "apply", "loc": loc, "group": -1,
+                "mems": [[out, size]] + [[r, size] for r in reads],
+                "einsummable": {"join_shape": [n_el], "inns": [[0] for _ in reads], "out_rank": 1,
+                                "join": "exp[hole|f32@0]", "castable": None}}
+
+    nodes = [{"id": 0, "inns": [], "kind": "inputmem", "loc": 0, "offset": 0, "size": size}]
+    chain = 30                                      # x -> exp -> exp -> ... on location 0
+    for k in range(chain):
+        nodes.append(ew(1 + k, [k], 0, (1 + k) * size, [k * size]))
+    early, late = chain + 1, chain + 2
+    nodes.append({"id": early, "inns": [0], "kind": "move", "src_loc": 0, "src_offset": 0,
+                  "dst_loc": 1, "dst_offset": 0, "size": size})
+    nodes.append({"id": late, "inns": [chain], "kind": "move", "src_loc": 0, "src_offset": chain * size,
+                  "dst_loc": 1, "dst_offset": size, "size": size})
+    nodes.append(ew(chain + 3, [early], 1, 2 * size, [0]))          # reads the early tensor
+    nodes.append(ew(chain + 4, [late], 1, 3 * size, [size]))        # reads the late one
+    mg = {"num_locs": 2, "mem_sizes": [(chain + 1) * size, 4 * size], "taskgraph": {}, "inputs": [], "outputs": [],
+          "nodes": nodes}
+    assert M.move_runs(mg)[early] == M.move_runs(mg)[late]            # one run
+    levels = M.node_levels(mg)
+    assert levels[chain] - levels[0] > 10 * M.AWAIT_SPREAD_US
+    units = M.schedule_units(mg, {1}, True)
+    awaits = [u for u in units if u["kind"] == "await"]
+    assert [u["moves"] for u in awaits] == [[early], [late]]
+    both = [M.schedule_units(mg, {r}, True) for r in range(2)]
+    times = M.simulate_schedule(mg, both)
+    reader_of_early = next(i for i, u in enumerate(both[1]) if u.get("node") == chain + 3)
+    signal_of_late = next(i for i, u in enumerate(both[0]) if u["kind"] == "signal" and late in u["moves"])
+    assert times[(1, reader_of_early)][1] < times[(0, signal_of_late)][0]
+    # sources that come together still share one await (and one pull launch)
+    nodes[late]["inns"] = [0]
+    nodes[late]["src_offset"] = 0
+    units = M.schedule_units(mg, {1}, True)
+    assert [u["moves"] for u in units if u["kind"] == "await"] == [[early, late]]
+    assert [u["moves"] for u in units if u["kind"] == "pull"] == [[early, late]]
+
+
 def test_simulated_order_is_the_same_on_every_rank_and_increases_along_dependencies():
     """Every rank simulates all ranks and must get the same times; along every dependency --
     local, signal -> pull, pull -> wait -- the simulated start time strictly increases, which is
