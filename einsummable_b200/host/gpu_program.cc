@@ -171,3 +171,172 @@ void gpu_program_t::replay(cudaStream_t stream)
 {
     check(es_b200_program_replay(prog, stream), "es_b200_program_replay");
 }
+
+
+// ------------------------------------------------------------------ one process per GPU
+gpu_exchange_program_t::gpu_exchange_program_t(memgraph_t const&            memgraph,
+                                               int                          rank,
+                                               kernel_manager_t&            km,
+                                               vector<void*> const&         peer_mem,
+                                               vector<void*> const&         peer_flags,
+                                               map<string, scalar_t> const& scalar_vars,
+                                               int                          max_lanes,
+                                               uint32_t                     wait_limit_ms)
+    : prog(nullptr), workspace(nullptr), n_ops(0)
+{
+    check(es_b200_program_create(km.c_handle(), &prog), "es_b200_program_create");
+    auto at = [&](int loc, uint64_t offset) { return static_cast<void*>(static_cast<char*>(peer_mem.at(loc)) + offset); };
+    // cross-location moves in node order index the flag words
+    map<int, int> move_index;
+    for (int mid = 0; mid != int(memgraph.nodes.size()); ++mid) {
+        auto const& op = memgraph.nodes[mid].op;
+        if (op.is_move() && op.get_move().get_src_loc() != op.get_move().get_dst_loc()) {
+            int k = int(move_index.size());
+            move_index[mid] = k;
+        }
+    }
+    int const n_moves = int(move_index.size());
+    auto flag = [&](int owner, int kind, int mid) {
+        return static_cast<void*>(static_cast<uint32_t*>(peer_flags.at(owner)) + kind * n_moves + move_index.at(mid));
+    };
+    for (es_exchange::unit_t const& u : es_exchange::make_units(memgraph, rank)) {
+        int         index = -1;
+        int const*  deps = u.deps.data();
+        int const   n_deps = int(u.deps.size());
+        if (u.kind == "einsummable") {
+            auto const&   apply = memgraph.nodes[u.node].op.get_apply();
+            einsummable_t e = apply.get_einsummable().replace_scalar_variables(scalar_vars).merge_adjacent_dims();
+            if (!km.build(e)) {
+                throw std::runtime_error("gpu_exchange_program_t: could not build " + write_with_ss(e));
+            }
+            vector<void const*> inns;
+            for (size_t i = 1; i != apply.mems.size(); ++i) {
+                inns.push_back(at(rank, apply.mems[i].offset));
+            }
+            check(es_b200_program_add_einsummable(prog, km.kernel_id(e), at(rank, apply.mems[0].offset), inns.data(),
+                                                  int(inns.size()), deps, n_deps, &index),
+                  "es_b200_program_add_einsummable");
+        } else if (u.kind == "touch" || u.kind == "rtouch") {
+            auto const&    apply = memgraph.nodes[u.node].op.get_apply();
+            touch_t const& touch = apply.get_touch();
+            int castable = (u.first || !touch.castable) ? ES_CASTABLE_NONE : int(touch.castable.value());
+            vector<es_touchdim_t> dims;
+            for (auto const& d : touch.selection) {
+                dims.push_back(es_touchdim_t{d.d_inn, d.d_out, d.offset_inn, d.offset_out, d.size});
+            }
+            if (u.kind == "rtouch") {
+                // the one reader of a moved block reads it where it is, in the source rank's memory
+                auto const& mv = memgraph.nodes[u.moves[0]].op.get_move();
+                check(es_b200_program_add_remote_touch(prog, dims.data(), int(dims.size()), castable, int(touch.dtype),
+                                                       at(rank, apply.mems[0].offset),
+                                                       at(mv.get_src_loc(), std::get<1>(mv.src)),
+                                                       flag(mv.get_src_loc(), 1, u.moves[0]), deps, n_deps, &index),
+                      "es_b200_program_add_remote_touch");
+            } else {
+                check(es_b200_program_add_touch(prog, dims.data(), int(dims.size()), castable, int(touch.dtype),
+                                                at(rank, apply.mems[0].offset), at(rank, apply.mems[1].offset), deps,
+                                                n_deps, &index),
+                      "es_b200_program_add_touch");
+            }
+        } else if (u.kind == "constant") {
+            auto const&   c = memgraph.nodes[u.node].op.get_constant();
+            unsigned char a[8], b[8];
+            if (c.fill.is_constant()) {
+                auto const& f = c.fill.get_constant();
+                scalar_bytes(f.value, a);
+                check(es_b200_program_add_fill_constant(prog, int(f.value.dtype), a, product(f.shape), at(rank, c.offset),
+                                                        deps, n_deps, &index),
+                      "es_b200_program_add_fill_constant");
+            } else {
+                auto const& f = c.fill.get_lowertri();
+                scalar_bytes(f.lower, a);
+                scalar_bytes(f.upper, b);
+                check(es_b200_program_add_fill_lowertri(prog, int(f.lower.dtype), a, b, f.nrow, f.ncol, f.start,
+                                                        at(rank, c.offset), deps, n_deps, &index),
+                      "es_b200_program_add_fill_lowertri");
+            }
+        } else if (u.kind == "copy") {
+            auto const& op = memgraph.nodes[u.node].op;
+            if (op.is_move()) {
+                auto const& m = op.get_move();
+                check(es_b200_program_add_copy(prog, at(rank, std::get<1>(m.src)), at(rank, std::get<1>(m.dst)), m.size, deps,
+                                               n_deps, &index),
+                      "es_b200_program_add_copy");
+            } else {
+                auto const& c = op.get_copy();
+                check(es_b200_program_add_copy(prog, at(rank, c.src_offset), at(rank, c.dst_offset), c.size, deps, n_deps,
+                                               &index),
+                      "es_b200_program_add_copy");
+            }
+        } else if (u.kind == "signal" || u.kind == "await" || u.kind == "wait") {
+            // signal: the ready flags in the destinations' arrays; await: this rank's ready flags;
+            // wait: this rank's done flags
+            vector<void*> flags;
+            for (int m : u.moves) {
+                auto const& mv = memgraph.nodes[m].op.get_move();
+                flags.push_back(u.kind == "wait" ? flag(rank, 1, m) : flag(mv.get_dst_loc(), 0, m));
+            }
+            if (u.kind == "signal") {
+                check(es_b200_program_add_signal(prog, flags.data(), int(flags.size()), deps, n_deps, &index),
+                      "es_b200_program_add_signal");
+            } else {
+                check(es_b200_program_add_wait(prog, flags.data(), int(flags.size()), deps, n_deps, &index),
+                      "es_b200_program_add_wait");
+            }
+        } else if (u.kind == "pull") {
+            vector<es_pull_item_t> items;
+            for (int m : u.moves) {
+                auto const&    mv = memgraph.nodes[m].op.get_move();
+                es_pull_item_t it;
+                it.src = at(mv.get_src_loc(), std::get<1>(mv.src));
+                it.dst = at(rank, std::get<1>(mv.dst));
+                it.bytes = mv.size;
+                it.ready_flag = nullptr; // the await in front of this pull has seen the flag
+                it.done_flag = flag(mv.get_src_loc(), 1, m);
+                items.push_back(it);
+            }
+            check(es_b200_program_add_pull(prog, items.data(), int(items.size()), deps, n_deps, &index),
+                  "es_b200_program_add_pull");
+        } else {
+            throw std::runtime_error("gpu_exchange_program_t: evict / load nodes need a storage "
+                                     "(es_b200_program_add_evict / _add_load)");
+        }
+        n_ops++;
+    }
+    uint64_t ws = 0;
+    check(es_b200_program_finalize(prog, max_lanes, &ws), "es_b200_program_finalize");
+    if (ws > 0) {
+        if (cudaMalloc(&workspace, ws) != cudaSuccess) {
+            throw std::runtime_error("gpu_exchange_program_t: could not allocate the workspace");
+        }
+    }
+    check(es_b200_program_set_workspace(prog, workspace, ws), "es_b200_program_set_workspace");
+    if (wait_limit_ms) {
+        check(es_b200_program_set_wait_limit(prog, wait_limit_ms), "es_b200_program_set_wait_limit");
+    }
+}
+
+gpu_exchange_program_t::~gpu_exchange_program_t()
+{
+    if (prog) {
+        es_b200_program_destroy(prog);
+    }
+    if (workspace) {
+        cudaFree(workspace);
+    }
+}
+
+void gpu_exchange_program_t::launch(cudaStream_t stream)
+{
+    check(es_b200_program_launch(prog, stream), "es_b200_program_launch");
+}
+
+void gpu_exchange_program_t::instantiate()
+{
+    check(es_b200_program_instantiate(prog), "es_b200_program_instantiate");
+}
+
+void gpu_exchange_program_t::replay(cudaStream_t stream)
+{
+    check(es_b200_program_replay(prog, stream), "es_b200_program_replay");
+}

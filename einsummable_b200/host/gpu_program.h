@@ -15,6 +15,7 @@
 #include "../../base/setup.h"
 
 #include "../../einsummable/memgraph.h"
+#include "gpu_exchange_plan.h"
 #include "gpu_kernel_manager.h"
 
 struct gpu_program_t {
@@ -33,6 +34,45 @@ struct gpu_program_t {
     // One run, asynchronous on `stream` (which continues when every op has finished).
     void launch(cudaStream_t stream);
     // The run as one CUDA graph: instantiate() once (after one launch()), then replay().
+    void instantiate();
+    void replay(cudaStream_t stream);
+
+    int num_ops() const
+    {
+        return n_ops;
+    }
+
+private:
+    es_b200_program_t* prog;
+    void*              workspace;
+    int                n_ops;
+};
+
+// One rank's share of a memgraph when every location is driven by its own process (one process per GPU):
+// the units of gpu_exchange_plan.h as a program, moves between locations as the library's exchange ops
+// (es_b200_program_add_signal / _add_wait / _add_pull / _add_remote_touch).
+//
+// peer_mem[r] is location r's global buffer as THIS process can address it (peer-mapped / IPC / symmetric
+// memory; peer_mem[rank] is the local buffer), and flags(r) the same for an array of 2 x n_moves zeroed 32-bit
+// words that every rank places at the same offset: word k is the ready flag of cross-location move k (it lives in
+// the destination's array), word n_moves + k its done flag (in the source's array), k counting the memgraph's
+// cross-location moves in node order.  All ranks build their programs from the same memgraph and launch them
+// the same number of times.
+struct gpu_exchange_program_t {
+    gpu_exchange_program_t(memgraph_t const&            memgraph,
+                           int                          rank,
+                           kernel_manager_t&            km,
+                           vector<void*> const&         peer_mem,
+                           vector<void*> const&         peer_flags,
+                           map<string, scalar_t> const& scalar_vars = {},
+                           int                          max_lanes = 16,
+                           uint32_t                     wait_limit_ms = 0);
+    ~gpu_exchange_program_t();
+
+    gpu_exchange_program_t(gpu_exchange_program_t const&) = delete;
+    gpu_exchange_program_t& operator=(gpu_exchange_program_t const&) = delete;
+
+    void launch(cudaStream_t stream);
     void instantiate();
     void replay(cudaStream_t stream);
 

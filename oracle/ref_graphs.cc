@@ -28,6 +28,8 @@
 
 #include <fstream>
 
+#include "../einsummable_b200/host/gpu_exchange_plan.h"
+
 namespace {
 
 struct built_graph_t {
@@ -461,6 +463,19 @@ int ref_graph_build_llama_tp(uint64_t dim, uint64_t n_heads, uint64_t multiple_o
     }
     b->names[builder.scores] = "scores";
     return finish(b);
+    G_END
+}
+
+// The exchange units of one rank as the C++ planner (einsummable_b200/host/gpu_exchange_plan.h) makes them
+// from the built memgraph, as JSON: compared in the tests with what the Python planner makes of the
+// JSON form of the same memgraph.
+int ref_graph_exchange_units(int h, int rank, char const* path)
+{
+    G_BEGIN
+    built_graph_t* b = g_graphs.at(h);
+    std::ofstream  out(path);
+    out << es_exchange::units_json(es_exchange::make_units(b->memgraph, rank)) << "\n";
+    return 0;
     G_END
 }
 
