@@ -13,9 +13,10 @@
 // src/engine/exec_state.cc:110-219).  Dependencies are the memgraph's own edges looked through the
 // nodes that launch nothing (inputmem, inputsto, partialize, alloc, del: src/einsummable/memgraph.h:189-309);
 // the touches of a partial-sum group are chained in node order, the first being the copy
-// (src/engine/gpu/exec_graph.cc:167-172,368-378).  Units come in memgraph order, which all ranks
-// share: along it every dependency, also across ranks, points forward, so one in-order lane for the
-// ops that wait for a peer cannot dead-lock.
+// (src/engine/gpu/exec_graph.cc:167-172,368-378).  make_units gives the units in memgraph order, which
+// all ranks share: along it every dependency, also across ranks, points forward, so one in-order lane
+// for the ops that wait for a peer cannot dead-lock.  order_units gives them in the order in which a
+// simulation of all ranks served them (what the data is expected to be ready for first comes first).
 //
 // Header-only; include from a file that sees the reference's src/ tree (as gpu_kernel_manager.h does
 // when placed in src/engine/gpu/, or with the tree's root on the include path).
@@ -28,9 +29,12 @@
 
 #include <algorithm>
 #include <map>
+#include <queue>
 #include <set>
 #include <sstream>
+#include <stdexcept>
 #include <string>
+#include <tuple>
 #include <vector>
 
 namespace es_exchange {
@@ -398,6 +402,202 @@ inline std::vector<unit_t> make_units(memgraph_t const& mg, int rank)
         units.push_back(w);
     }
     return units;
+}
+
+// ---- the order of a rank's units: by simulated service --------------------------------------------------
+//
+// make_units gives memgraph order.  That order is valid but serves the exchange ops, which share one
+// in-order lane, by node number instead of by when their data is expected.  order_units simulates all
+// ranks under a simple machine model (each rank's GPU, incoming link and PCIe link do one unit's work at
+// a time; launch latencies overlap; a flag takes about 2 us to cross NVLink) and returns the rank's
+// units in the order in which the simulation served them, dependencies renumbered.  Every rank
+// simulates all ranks and gets the same answer, and along every dependency, also across ranks, the
+// place in the order of service increases, so the reordered lanes cannot dead-lock either.
+
+namespace detail {
+
+enum server_t { SERVER_NONE = 0, SERVER_GPU = 1, SERVER_LINK = 2, SERVER_PCIE = 3 };
+
+struct unit_cost_t {
+    double lat, work;
+    int    server;
+};
+
+inline unit_cost_t unit_cost_us(memgraph_t const& mg, unit_t const& u)
+{
+    std::string const& k = u.kind;
+    if (k == "einsummable") {
+        cost_t c = cost_us(mg, u.node);
+        return {c.lat, c.work, SERVER_GPU};
+    }
+    if (k == "touch") {
+        double bytes = double(mg.nodes[u.node].op.get_apply().mems[1].size * uint64_t(u.first ? 2 : 3));
+        return {2.5, bytes / 4.5e6, SERVER_GPU};
+    }
+    if (k == "rtouch") return {6.0, double(mg.nodes[u.node].op.get_apply().mems[1].size) / 0.65e6, SERVER_LINK};
+    if (k == "await" || k == "signal") return {3.0, 0.0, SERVER_NONE};
+    if (k == "constant") return {2.5, 0.5, SERVER_GPU};
+    if (k == "copy") {
+        auto const& op = mg.nodes[u.node].op;
+        uint64_t    size = op.is_move() ? op.get_move().size : op.get_copy().size;
+        return {2.5, double(2 * size) / 4.5e6, SERVER_GPU};
+    }
+    if (k == "evict") return {4.0, double(mg.nodes[u.node].op.get_evict().src.size) / 0.05e6, SERVER_PCIE};
+    if (k == "load") return {4.0, double(mg.nodes[u.node].op.get_load().dst.size) / 0.05e6, SERVER_PCIE};
+    if (k == "pull") {
+        uint64_t size = 0;
+        for (int m : u.moves) size += mg.nodes[m].op.get_move().size;
+        return {6.0, double(size) / 0.65e6, SERVER_LINK};
+    }
+    if (k == "wait") return {2.0, 0.0, SERVER_NONE};
+    throw std::runtime_error("es_exchange: no cost for a unit of kind " + k);
+}
+
+} // namespace detail
+
+struct service_t {
+    double ready = 0.0, finish = 0.0;
+    int    place = -1; // in the order of service over all ranks
+};
+
+// Ready time, finish time and place in the order of service of every unit of every rank.
+inline std::vector<std::vector<service_t>> simulate(memgraph_t const& mg, std::vector<std::vector<unit_t>> const& units_by_rank)
+{
+    using namespace detail;
+    using key_t = std::pair<int, int>; // rank, index
+    int const                        world = int(units_by_rank.size());
+    std::map<int, key_t>             sig_of, pull_of;
+    for (int r = 0; r != world; ++r) {
+        for (int i = 0; i != int(units_by_rank[r].size()); ++i) {
+            unit_t const& u = units_by_rank[r][i];
+            if (u.kind == "signal") {
+                for (int m : u.moves) sig_of[m] = {r, i};
+            } else if (u.kind == "pull" || u.kind == "rtouch") {
+                for (int m : u.moves) pull_of[m] = {r, i};
+            }
+        }
+    }
+    std::vector<std::vector<std::vector<key_t>>> preds(world), succs(world);
+    std::vector<std::vector<unit_cost_t>>        cost(world);
+    size_t                                       total = 0;
+    for (int r = 0; r != world; ++r) {
+        preds[r].resize(units_by_rank[r].size());
+        succs[r].resize(units_by_rank[r].size());
+        cost[r].resize(units_by_rank[r].size());
+        total += units_by_rank[r].size();
+    }
+    for (int r = 0; r != world; ++r) {
+        for (int i = 0; i != int(units_by_rank[r].size()); ++i) {
+            unit_t const& u = units_by_rank[r][i];
+            auto&         p = preds[r][i];
+            for (int d : u.deps) p.push_back({r, d});
+            if (u.kind == "await") {
+                for (int m : u.moves) p.push_back(sig_of.at(m));
+            } else if (u.kind == "wait") {
+                for (int m : u.moves) p.push_back(pull_of.at(m));
+            }
+            cost[r][i] = unit_cost_us(mg, u);
+        }
+    }
+    for (int r = 0; r != world; ++r)
+        for (int i = 0; i != int(preds[r].size()); ++i)
+            for (key_t q : preds[r][i]) succs[q.first][q.second].push_back({r, i});
+    // the bottom level of a unit: its own time plus the longest chain of work that hangs on it; among
+    // units that become ready at the same moment the one with the largest goes first
+    std::vector<std::vector<int>> left(world);
+    std::vector<key_t>            order, stack;
+    for (int r = 0; r != world; ++r) {
+        left[r].resize(preds[r].size());
+        for (int i = 0; i != int(preds[r].size()); ++i) {
+            left[r][i] = int(preds[r][i].size());
+            if (left[r][i] == 0) stack.push_back({r, i});
+        }
+    }
+    while (!stack.empty()) {
+        key_t k = stack.back();
+        stack.pop_back();
+        order.push_back(k);
+        for (key_t c : succs[k.first][k.second])
+            if (--left[c.first][c.second] == 0) stack.push_back(c);
+    }
+    if (order.size() != total) throw std::runtime_error("es_exchange: the units of the ranks wait for one another in a cycle");
+    std::vector<std::vector<double>> bottom(world);
+    for (int r = 0; r != world; ++r) bottom[r].assign(preds[r].size(), 0.0);
+    for (auto it = order.rbegin(); it != order.rend(); ++it) {
+        double below = 0.0;
+        for (key_t c : succs[it->first][it->second]) below = std::max(below, bottom[c.first][c.second]);
+        unit_cost_t const& c = cost[it->first][it->second];
+        bottom[it->first][it->second] = c.lat + c.work + below;
+    }
+    // first come first served; ties by bottom level, then by rank and index
+    using item_t = std::tuple<double, double, int, int>;
+    std::priority_queue<item_t, std::vector<item_t>, std::greater<item_t>> heap;
+    std::vector<std::vector<service_t>>                                    times(world);
+    std::vector<std::vector<double>>                                       ready_at(world);
+    for (int r = 0; r != world; ++r) {
+        times[r].resize(preds[r].size());
+        ready_at[r].assign(preds[r].size(), 0.0);
+        for (int i = 0; i != int(preds[r].size()); ++i) {
+            left[r][i] = int(preds[r][i].size());
+            if (left[r][i] == 0) heap.push({0.0, -bottom[r][i], r, i});
+        }
+    }
+    std::map<std::pair<int, int>, double> free_at; // (rank, server) -> when its current work ends
+    int                                   served = 0;
+    while (!heap.empty()) {
+        auto [t, nb, r, i] = heap.top();
+        (void)nb;
+        heap.pop();
+        unit_cost_t const& c = cost[r][i];
+        double             begin = t + c.lat;
+        if (c.server != SERVER_NONE && c.work > 0) {
+            auto it = free_at.find({r, c.server});
+            if (it != free_at.end()) begin = std::max(begin, it->second);
+            free_at[{r, c.server}] = begin + c.work;
+        }
+        double fin = begin + c.work;
+        times[r][i].ready = t;
+        times[r][i].finish = fin;
+        times[r][i].place = served++;
+        for (key_t s : succs[r][i]) {
+            double& ra = ready_at[s.first][s.second];
+            ra = std::max(ra, fin + (s.first != r ? 2.0 : 0.0));
+            if (--left[s.first][s.second] == 0) heap.push({ra, -bottom[s.first][s.second], s.first, s.second});
+        }
+    }
+    return times;
+}
+
+// The units of `rank` in the order of simulated service (the closing wait stays last), dependencies
+// renumbered; `service`, when given, receives each returned unit's simulated ready and finish time.
+inline std::vector<unit_t> order_units(memgraph_t const& mg, int world, int rank, std::vector<service_t>* service = nullptr)
+{
+    std::vector<std::vector<unit_t>> all;
+    for (int r = 0; r != world; ++r) all.push_back(make_units(mg, r));
+    auto                       times = simulate(mg, all);
+    std::vector<unit_t> const& units = all[rank];
+    int const                  n = int(units.size());
+    int const                  closing = (n && units[n - 1].kind == "wait") ? n - 1 : -1;
+    std::vector<int>           order(n);
+    for (int i = 0; i != n; ++i) order[i] = i;
+    std::sort(order.begin(), order.end(), [&](int a, int b) {
+        if ((a == closing) != (b == closing)) return b == closing;
+        return times[rank][a].place < times[rank][b].place;
+    });
+    std::vector<int> new_index(n);
+    for (int i = 0; i != n; ++i) new_index[order[i]] = i;
+    std::vector<unit_t> out;
+    if (service) service->clear();
+    for (int old : order) {
+        unit_t u = units[old];
+        for (int& d : u.deps) d = new_index[d];
+        std::sort(u.deps.begin(), u.deps.end());
+        for (int d : u.deps)
+            if (d >= int(out.size())) throw std::runtime_error("es_exchange: the simulated order breaks a dependency");
+        out.push_back(u);
+        if (service) service->push_back(times[rank][old]);
+    }
+    return out;
 }
 
 // The units as JSON, for comparing plans across implementations.

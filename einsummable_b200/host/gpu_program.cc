@@ -199,7 +199,9 @@ gpu_exchange_program_t::gpu_exchange_program_t(memgraph_t const&            memg
     auto flag = [&](int owner, int kind, int mid) {
         return static_cast<void*>(static_cast<uint32_t*>(peer_flags.at(owner)) + kind * n_moves + move_index.at(mid));
     };
-    for (es_exchange::unit_t const& u : es_exchange::make_units(memgraph, rank)) {
+    // the rank's units in the order in which a simulation of all ranks serves them: the exchange ops share
+    // one in-order lane, so what is expected to be ready first has to be asked for first
+    for (es_exchange::unit_t const& u : es_exchange::order_units(memgraph, memgraph.num_compute_locs, rank)) {
         int         index = -1;
         int const*  deps = u.deps.data();
         int const   n_deps = int(u.deps.size());

@@ -49,7 +49,8 @@ private:
 };
 
 // One rank's share of a memgraph when every location is driven by its own process (one process per GPU):
-// the units of gpu_exchange_plan.h as a program, moves between locations as the library's exchange ops
+// the units of gpu_exchange_plan.h, in the order of simulated service, as a program, moves between locations as the
+// library's exchange ops
 // (es_b200_program_add_signal / _add_wait / _add_pull / _add_remote_touch).
 //
 // peer_mem[r] is location r's global buffer as THIS process can address it (peer-mapped / IPC / symmetric

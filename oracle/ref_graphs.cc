@@ -479,6 +479,25 @@ int ref_graph_exchange_units(int h, int rank, char const* path)
     G_END
 }
 
+// The same in the order of simulated service (es_exchange::order_units), each unit with its simulated
+// ready and finish time: compared with the Python runner's order_units_by_simulation.
+int ref_graph_exchange_units_ordered(int h, int rank, char const* path)
+{
+    G_BEGIN
+    built_graph_t*                      b = g_graphs.at(h);
+    std::vector<es_exchange::service_t> service;
+    auto units = es_exchange::order_units(b->memgraph, b->memgraph.num_compute_locs, rank, &service);
+    std::ofstream out(path);
+    out.precision(17);
+    out << "{\"units\":" << es_exchange::units_json(units) << ",\"ready_us\":[";
+    for (size_t i = 0; i != service.size(); ++i) out << (i ? "," : "") << service[i].ready;
+    out << "],\"finish_us\":[";
+    for (size_t i = 0; i != service.size(); ++i) out << (i ? "," : "") << service[i].finish;
+    out << "]}\n";
+    return 0;
+    G_END
+}
+
 // config 5: forward + backward + vanilla weight update of n_layers LLaMA layers
 int ref_graph_build_llama_train(uint64_t dim,
                                 uint64_t n_heads,
