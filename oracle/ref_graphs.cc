@@ -29,6 +29,7 @@
 #include <fstream>
 
 #include "../einsummable_b200/host/gpu_exchange_plan.h"
+#include "../einsummable_b200/host/gpu_fuse.h"
 
 namespace {
 
@@ -495,6 +496,29 @@ int ref_graph_exchange_units_ordered(int h, int rank, char const* path)
     for (size_t i = 0; i != service.size(); ++i) out << (i ? "," : "") << service[i].finish;
     out << "]}\n";
     return 0;
+    G_END
+}
+
+// A new handle whose memgraph is the C++ fold of handle h's (einsummable_b200/host/gpu_fuse.h): the
+// folded graph is again a memgraph_t, so ref_graph_write_json / ref_graph_run / ref_graph_exchange_units
+// take it like any other.  Returns the handle; *n_folded receives the number of nodes folded away.
+int ref_graph_fold_elementwise(int h, int* n_folded)
+{
+    G_BEGIN
+    built_graph_t const&  b = *g_graphs.at(h);
+    std::vector<memloc_t> saved;
+    if (b.has_storage) {
+        for (auto const& [tid, msl] : b.save_msl)
+            if (msl.is_memloc()) saved.push_back(msl.get_memloc());
+    } else {
+        for (auto const& [tid, m] : b.save_mem) saved.push_back(memloc_t{m.offset, m.size, b.taskgraph.out_loc(tid)});
+    }
+    es_fuse::folded_t f = es_fuse::fold_elementwise(b.memgraph, saved);
+    built_graph_t*    nb = new built_graph_t(b);
+    nb->memgraph = f.memgraph;
+    if (n_folded) *n_folded = int(f.folded.size());
+    g_graphs.push_back(nb);
+    return int(g_graphs.size()) - 1;
     G_END
 }
 
