@@ -27,6 +27,8 @@
 #include "src/einsummable/memgraph.h"
 #endif
 
+#include "gpu_fuse.h"
+
 #include <algorithm>
 #include <map>
 #include <queue>
@@ -39,8 +41,12 @@
 
 namespace es_exchange {
 
+// the nodes of a graph that stand for a whole attention chain (es_fuse::fold_attention), by node id;
+// every function below takes it as an optional last argument
+using attention_map_t = std::map<int, es_fuse::attention_node_t>;
+
 struct unit_t {
-    std::string      kind;       // einsummable touch rtouch constant copy evict load signal await pull wait
+    std::string      kind;       // einsummable attention touch rtouch constant copy evict load signal await pull wait
     int              node = -1;  // memgraph node (compute units)
     std::vector<int> moves;      // memgraph move nodes (exchange units; rtouch: the move it consumes)
     std::vector<int> deps;       // indices of earlier units of this rank
@@ -86,9 +92,17 @@ inline std::vector<int> sides(memgraph_t::op_t const& op)
 struct cost_t {
     double lat, work, extra;
 };
-inline cost_t cost_us(memgraph_t const& mg, int id)
+inline cost_t attention_cost_us(es_fuse::attention_t const& a)
+{
+    double flops = 4.0 * double(a.batch) * double(a.heads) * double(a.rows) * double(a.keys) * double(a.head_dim) *
+                   (a.skip_known ? 0.6 : 1.0);
+    return {5.0, flops / 0.6e9, 0.0};
+}
+
+inline cost_t cost_us(memgraph_t const& mg, int id, attention_map_t const* attention = nullptr)
 {
     auto const& op = mg.nodes[id].op;
+    if (attention && attention->count(id)) return attention_cost_us(attention->at(id).desc);
     if (op.is_apply()) {
         auto const& a = op.get_apply();
         if (a.is_einsummable()) {
@@ -155,7 +169,7 @@ inline std::map<int, int> move_runs(memgraph_t const& mg)
 }
 
 // Earliest finish time of every node if nothing ever waited for a free GPU or link.
-inline std::vector<double> node_levels(memgraph_t const& mg)
+inline std::vector<double> node_levels(memgraph_t const& mg, attention_map_t const* attention = nullptr)
 {
     using namespace detail;
     std::vector<double> level(mg.nodes.size(), 0.0);
@@ -165,21 +179,21 @@ inline std::vector<double> node_levels(memgraph_t const& mg)
         if (bookkeeping(mg.nodes[id].op)) {
             level[id] = start;
         } else {
-            cost_t c = cost_us(mg, id);
+            cost_t c = cost_us(mg, id, attention);
             level[id] = start + c.lat + c.work + c.extra;
         }
     }
     return level;
 }
 
-inline std::vector<unit_t> make_units(memgraph_t const& mg, int rank)
+inline std::vector<unit_t> make_units(memgraph_t const& mg, int rank, attention_map_t const* attention = nullptr)
 {
     using namespace detail;
     int const                  n = int(mg.nodes.size());
     std::map<int, int>         runs = move_runs(mg);
     std::map<int, std::vector<int>> run_members;
     for (auto const& [id, r] : runs) run_members[r].push_back(id);
-    std::vector<double> levels = node_levels(mg);
+    std::vector<double> levels = node_levels(mg, attention);
     auto ready_level = [&](int m) {
         double v = 0.0;
         for (int i : mg.nodes[m].inns) v = std::max(v, levels[i]);
@@ -375,7 +389,7 @@ inline std::vector<unit_t> make_units(memgraph_t const& mg, int rank)
             unit_of[id] = ui;
             continue;
         }
-        if (op.is_apply()) u.kind = "einsummable";
+        if (op.is_apply()) u.kind = (attention && attention->count(id)) ? "attention" : "einsummable";
         else if (op.is_constant()) u.kind = "constant";
         else if (op.is_move() || op.is_copy()) u.kind = "copy";
         else if (op.is_evict()) u.kind = "evict";
@@ -423,9 +437,13 @@ struct unit_cost_t {
     int    server;
 };
 
-inline unit_cost_t unit_cost_us(memgraph_t const& mg, unit_t const& u)
+inline unit_cost_t unit_cost_us(memgraph_t const& mg, unit_t const& u, attention_map_t const* attention = nullptr)
 {
     std::string const& k = u.kind;
+    if (k == "attention") {
+        cost_t c = attention_cost_us(attention->at(u.node).desc);
+        return {c.lat, c.work, SERVER_GPU};
+    }
     if (k == "einsummable") {
         cost_t c = cost_us(mg, u.node);
         return {c.lat, c.work, SERVER_GPU};
@@ -461,7 +479,8 @@ struct service_t {
 };
 
 // Ready time, finish time and place in the order of service of every unit of every rank.
-inline std::vector<std::vector<service_t>> simulate(memgraph_t const& mg, std::vector<std::vector<unit_t>> const& units_by_rank)
+inline std::vector<std::vector<service_t>> simulate(memgraph_t const& mg, std::vector<std::vector<unit_t>> const& units_by_rank,
+                                                    attention_map_t const* attention = nullptr)
 {
     using namespace detail;
     using key_t = std::pair<int, int>; // rank, index
@@ -496,7 +515,7 @@ inline std::vector<std::vector<service_t>> simulate(memgraph_t const& mg, std::v
             } else if (u.kind == "wait") {
                 for (int m : u.moves) p.push_back(pull_of.at(m));
             }
-            cost[r][i] = unit_cost_us(mg, u);
+            cost[r][i] = unit_cost_us(mg, u, attention);
         }
     }
     for (int r = 0; r != world; ++r)
@@ -570,11 +589,12 @@ inline std::vector<std::vector<service_t>> simulate(memgraph_t const& mg, std::v
 
 // The units of `rank` in the order of simulated service (the closing wait stays last), dependencies
 // renumbered; `service`, when given, receives each returned unit's simulated ready and finish time.
-inline std::vector<unit_t> order_units(memgraph_t const& mg, int world, int rank, std::vector<service_t>* service = nullptr)
+inline std::vector<unit_t> order_units(memgraph_t const& mg, int world, int rank, std::vector<service_t>* service = nullptr,
+                                       attention_map_t const* attention = nullptr)
 {
     std::vector<std::vector<unit_t>> all;
-    for (int r = 0; r != world; ++r) all.push_back(make_units(mg, r));
-    auto                       times = simulate(mg, all);
+    for (int r = 0; r != world; ++r) all.push_back(make_units(mg, r, attention));
+    auto                       times = simulate(mg, all, attention);
     std::vector<unit_t> const& units = all[rank];
     int const                  n = int(units.size());
     int const                  closing = (n && units[n - 1].kind == "wait") ? n - 1 : -1;

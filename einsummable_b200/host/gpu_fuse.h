@@ -34,6 +34,7 @@
 #endif
 
 #include <algorithm>
+#include <map>
 #include <optional>
 #include <set>
 #include <stdexcept>
@@ -283,6 +284,326 @@ inline folded_t fold_elementwise(memgraph_t const& graph, std::vector<memloc_t> 
         nodes[ia].op = memgraph_t::op_t(memgraph_t::alloc_t{loc, a_out.first, a_out.second});
     }
     // the edges the other way round
+    for (auto& node : nodes) node.outs.clear();
+    for (int id = 0; id != n; ++id)
+        for (int i : nodes[id].inns) nodes[i].outs.insert(id);
+    return out;
+}
+
+// ---- the attention chain --------------------------------------------------------------------------------
+//
+// softmax(Q K^T + mask) V is five apply nodes in the reference's graphs (src/einsummable/gwriter.cc:830-855,
+// llama/modules.cc:285-383) -- after fold_elementwise: the scores contraction, the row maximum of
+// scores + mask, the row sum of the exponentials, the normalised probabilities in f16, the contraction
+// with V.  fold_attention replaces every such chain by ONE node for the library's attention kernel
+// (es_b200_launch_attention / es_b200_program_add_attention).  A memgraph_t has no such op, so the result
+// is a memgraph_t plus a map: the chain's last node keeps its place and its einsummable but now lists the
+// memories [out, Q, K, V, mask] (five memories on a two-input einsummable: whoever executes it without
+// looking at the map fails on the input count instead of computing something else), the map gives its
+// descriptor; the other four nodes become alloc nodes.  The conditions are those of the fold above: the
+// four intermediate results have no other reader and are neither saved nor shipped, nothing between the
+// first and the last node writes memory the chain now reads later; later writers into that memory are
+// made to wait for the new node.  The same rules as fuse.py: fuse_attention.
+
+struct attention_t {
+    uint32_t batch = 0, heads = 0, rows = 0, keys = 0, head_dim = 0;
+    int32_t  skip_known = 0; // the mask is a lower-triangular fill (0 / -inf) starting at skip_from:
+    int32_t  skip_from = 0;  // the kernel computes it and leaves out the key blocks above the diagonal
+    int64_t  q_stride[3] = {0, 0, 0}, k_stride[3] = {0, 0, 0}, v_stride[3] = {0, 0, 0}, out_stride[3] = {0, 0, 0};
+    int64_t  mask_stride = 0;
+
+    // what the kernel serves: head dim a multiple of 8 up to 128, strides multiples of 8
+    bool eligible() const
+    {
+        if (head_dim % 8 || head_dim > 128 || batch > 65535 || heads > 65535) return false;
+        for (int i = 0; i != 3; ++i)
+            if (q_stride[i] % 8 || k_stride[i] % 8 || v_stride[i] % 8 || out_stride[i] % 8) return false;
+        return true;
+    }
+};
+
+struct attention_node_t {
+    attention_t desc;
+    int         loc = 0;
+    mem_t       out, q, k, v, mask;
+};
+
+struct attention_folded_t {
+    memgraph_t                      memgraph;
+    std::map<int, attention_node_t> attention; // by node id
+};
+
+namespace detail {
+
+inline std::string normal_join(std::string const& text)
+{
+    return write_with_ss(parse_with_ss<scalarop_t>(text));
+}
+
+inline std::vector<int64_t> row_major_strides(std::vector<uint64_t> const& shape)
+{
+    std::vector<int64_t> st(shape.size(), 1);
+    for (int i = int(shape.size()) - 2; i >= 0; --i) st[i] = st[i + 1] * int64_t(shape[i + 1]);
+    return st;
+}
+
+inline std::vector<int> sorted_modes(std::vector<int> v)
+{
+    std::sort(v.begin(), v.end());
+    return v;
+}
+
+struct chain_t {
+    int              idx[5]; // scores, max, sum, probabilities, output
+    attention_node_t node;
+};
+
+struct chain_matcher_t {
+    std::vector<memgraph_t::node_t> const& nodes;
+    std::vector<char> const&               alive;
+    std::vector<memloc_t> const&           saved;
+    std::map<int, attention_node_t> const& done; // the nodes that already stand for a whole chain
+    std::string const x16 = normal_join("*[hole|f16@0,hole|f16@1]");
+    std::string const x = "to_f32[+[hole|f16@0,hole|f16@1]]";
+    std::string const e = "exp[+[" + x + ",*[constant{f32|-1},hole|f32@2]]]";
+    std::string const j_max = normal_join(x);
+    std::string const j_sum = normal_join(e);
+    std::string const j_norm = normal_join("to_f16[*[" + e + ",power{-1}[hole|f32@3]]]");
+
+    // the apply nodes that read node ix's result, if they are exactly `want` many, read it as written,
+    // and nothing ships or saves it
+    std::optional<std::vector<int>> sole_readers(int ix, size_t want) const
+    {
+        auto const& a = nodes[ix].op.get_apply();
+        region_t    out = region(a.mems[0]);
+        for (memloc_t const& s : saved)
+            if (s.loc == a.loc && overlap(out, {s.offset, s.size})) return std::nullopt;
+        std::vector<int> got;
+        for (int ib = ix + 1; ib != int(nodes.size()); ++ib) {
+            if (!alive[ib] || !nodes[ib].inns.count(ix)) continue;
+            auto const& op = nodes[ib].op;
+            if (op.is_move() || op.is_copy() || op.is_evict()) return std::nullopt;
+            if (op.is_apply()) {
+                auto const& b = op.get_apply();
+                bool        reads = false;
+                for (size_t k = 1; k < b.mems.size(); ++k) reads = reads || region(b.mems[k]) == out;
+                if (b.loc != a.loc || !b.is_einsummable() || done.count(ib) || !reads) return std::nullopt;
+                got.push_back(ib);
+            }
+        }
+        if (got.size() != want) return std::nullopt;
+        return got;
+    }
+
+    std::optional<chain_t> match(int i_s) const
+    {
+        auto const&          s = nodes[i_s].op.get_apply();
+        einsummable_t const& es = s.get_einsummable();
+        if (es.join_shape.size() != 5 || es.out_rank != 4 || !plain_contraction(es) || write_with_ss(es.join) != x16)
+            return std::nullopt;
+        uint64_t const b = es.join_shape[0], h = es.join_shape[1], rows = es.join_shape[2], keys = es.join_shape[3],
+                       d = es.join_shape[4];
+        int q_slot = -1, k_slot = -1;
+        for (int slot = 0; slot != int(es.inns.size()); ++slot) {
+            auto const& modes = es.inns[slot];
+            if (sorted_modes(modes) == std::vector<int>{0, 1, 2, 4} && modes.back() == 4) q_slot = slot;
+            else if (sorted_modes(modes) == std::vector<int>{0, 1, 3, 4} && modes.back() == 4) k_slot = slot;
+        }
+        if (q_slot < 0 || k_slot < 0) return std::nullopt;
+        auto strides = [&](einsummable_t const& e, std::vector<int> const& modes, int row_mode, int64_t* out3) {
+            std::vector<uint64_t> shape;
+            for (int m : modes) shape.push_back(e.join_shape[m]);
+            auto st = row_major_strides(shape);
+            for (size_t i = 0; i != modes.size(); ++i) {
+                if (modes[i] == 0) out3[0] = st[i];
+                if (modes[i] == 1) out3[1] = st[i];
+                if (modes[i] == row_mode) out3[2] = st[i];
+            }
+        };
+        auto r_s = sole_readers(i_s, 3);
+        if (!r_s) return std::nullopt;
+        int const   i_m = (*r_s)[0], i_l = (*r_s)[1], i_p = (*r_s)[2];
+        auto const &m = nodes[i_m].op.get_apply(), &l = nodes[i_l].op.get_apply(), &pn = nodes[i_p].op.get_apply();
+        einsummable_t const &em = m.get_einsummable(), &el = l.get_einsummable(), &ep = pn.get_einsummable();
+        region_t const        s_out = region(s.mems[0]);
+        std::vector<uint64_t> shape4{b, h, rows, keys};
+        using vv = std::vector<std::vector<int>>;
+        std::vector<int> const full{0, 1, 2, 3};
+        auto                   max_c = [](einsummable_t const& e, castable_t c) { return e.castable && e.castable.value() == c; };
+        if (!(max_c(em, castable_t::max) && em.out_rank == 3 && em.join_shape == shape4 && em.inns == vv{full, {2, 3}} &&
+              write_with_ss(em.join) == j_max && m.mems.size() == 3 && region(m.mems[1]) == s_out))
+            return std::nullopt;
+        region_t const mask = region(m.mems[2]), m_out = region(m.mems[0]);
+        if (!(max_c(el, castable_t::add) && el.out_rank == 3 && el.join_shape == shape4 &&
+              el.inns == vv{full, {2, 3}, {0, 1, 2}} && write_with_ss(el.join) == j_sum && l.mems.size() == 4 &&
+              region(l.mems[1]) == s_out && region(l.mems[2]) == mask && region(l.mems[3]) == m_out))
+            return std::nullopt;
+        region_t const l_out = region(l.mems[0]);
+        if (!(ep.out_rank == 4 && ep.join_shape == shape4 && ep.inns == vv{full, {2, 3}, {0, 1, 2}, {0, 1, 2}} &&
+              write_with_ss(ep.join) == j_norm && pn.mems.size() == 5 && region(pn.mems[1]) == s_out &&
+              region(pn.mems[2]) == mask && region(pn.mems[3]) == m_out && region(pn.mems[4]) == l_out))
+            return std::nullopt;
+        auto r_m = sole_readers(i_m, 2), r_l = sole_readers(i_l, 1);
+        if (!r_m || *r_m != std::vector<int>{i_l, i_p} || !r_l || *r_l != std::vector<int>{i_p}) return std::nullopt;
+        auto r_p = sole_readers(i_p, 1);
+        if (!r_p) return std::nullopt;
+        int const            i_o = (*r_p)[0];
+        auto const&          o = nodes[i_o].op.get_apply();
+        einsummable_t const& eo = o.get_einsummable();
+        if (!(plain_contraction(eo) && write_with_ss(eo.join) == x16 && eo.out_rank == 4 &&
+              eo.join_shape == std::vector<uint64_t>{b, h, rows, d, keys}))
+            return std::nullopt;
+        region_t const p_out = region(pn.mems[0]);
+        int            v_slot = -1;
+        bool           has_p = false;
+        for (int slot = 0; slot != int(eo.inns.size()); ++slot) {
+            auto const& modes = eo.inns[slot];
+            if (modes == std::vector<int>{0, 1, 2, 4}) {
+                if (region(o.mems[1 + slot]) != p_out) return std::nullopt;
+                has_p = true;
+            } else if (sorted_modes(modes) == std::vector<int>{0, 1, 3, 4} && modes.back() == 3) {
+                v_slot = slot;
+            }
+        }
+        if (v_slot < 0 || eo.inns.size() != 2 || !has_p) return std::nullopt;
+        chain_t c;
+        c.idx[0] = i_s, c.idx[1] = i_m, c.idx[2] = i_l, c.idx[3] = i_p, c.idx[4] = i_o;
+        attention_t& a = c.node.desc;
+        a.batch = uint32_t(b), a.heads = uint32_t(h), a.rows = uint32_t(rows), a.keys = uint32_t(keys), a.head_dim = uint32_t(d);
+        strides(es, es.inns[q_slot], 2, a.q_stride);
+        strides(es, es.inns[k_slot], 3, a.k_stride);
+        strides(eo, eo.inns[v_slot], 4, a.v_stride);
+        auto ost = row_major_strides({b, h, rows, d});
+        for (int i = 0; i != 3; ++i) a.out_stride[i] = ost[i];
+        a.mask_stride = int64_t(keys);
+        c.node.loc = s.loc;
+        c.node.out = o.mems[0];
+        c.node.q = s.mems[1 + q_slot];
+        c.node.k = s.mems[1 + k_slot];
+        c.node.v = o.mems[1 + v_slot];
+        c.node.mask = m.mems[2];
+        return c;
+    }
+};
+
+// If the f16 [rows, cols] tensor in `reg` of location `loc`, as the node at `before` reads it, is a
+// lower-triangular fill -- 0 where column <= row - start, -inf elsewhere -- its start.  Looks through
+// what the compilers put between the fill and its readers: copies of row blocks (touches without a
+// castable) and moves of whole tensors.
+inline std::optional<int64_t> lowertri_start(std::vector<memgraph_t::node_t> const& nodes, std::vector<char> const& alive,
+                                             int loc, region_t reg, int before, uint64_t rows, uint64_t cols, int depth = 0)
+{
+    if (depth > 4 || reg.second != rows * cols * 2) return std::nullopt;
+    std::vector<std::pair<uint64_t, uint64_t>> covered;
+    std::optional<int64_t>                     start;
+    for (int ic = before - 1; ic >= 0; --ic) {
+        if (!alive[ic]) continue;
+        auto const& op = nodes[ic].op;
+        auto        w = written_region(op, loc);
+        if (!w || !overlap(*w, reg)) continue;
+        if (op.is_constant()) {
+            auto const& c = op.get_constant();
+            if (!covered.empty() || *w != reg || !c.fill.is_lowertri()) return std::nullopt;
+            auto const& f = c.fill.get_lowertri();
+            int64_t     bound = int64_t(1) << 30;
+            if (f.lower.dtype != dtype_t::f16 || f.nrow != rows || f.ncol != cols || f.upper.data[0] != 0 ||
+                f.upper.data[1] != 252 || f.lower.data[0] != 0 || f.lower.data[1] != 0 || f.start >= bound || f.start <= -bound)
+                return std::nullopt;
+            return f.start;
+        }
+        if (op.is_move()) {
+            auto const& m = op.get_move();
+            if (!covered.empty() || *w != reg) return std::nullopt;
+            return lowertri_start(nodes, alive, m.get_src_loc(), {std::get<1>(m.src), m.size}, ic, rows, cols, depth + 1);
+        }
+        if (op.is_touch()) {
+            auto const&    a = op.get_apply();
+            touch_t const& t = a.get_touch();
+            if (*w != reg || t.dtype != dtype_t::f16 || t.castable || t.selection.size() != 2) return std::nullopt;
+            auto const &r = t.selection[0], &c = t.selection[1];
+            if (r.d_out != rows || c.d_inn != cols || c.d_out != cols || c.offset_inn != 0 || c.offset_out != 0 || c.size != cols)
+                return std::nullopt;
+            for (auto const& [lo, hi] : covered)
+                if (r.offset_out < hi && lo < r.offset_out + r.size) return std::nullopt; // an older lifetime shows through
+            auto sub = lowertri_start(nodes, alive, loc, region(a.mems[1]), ic, r.d_inn, cols, depth + 1);
+            if (!sub) return std::nullopt;
+            int64_t here = *sub + int64_t(r.offset_out) - int64_t(r.offset_inn); // row i of the block is row i - oo + oi of the source
+            if (start && *start != here) return std::nullopt;
+            start = here;
+            covered.push_back({r.offset_out, r.offset_out + r.size});
+            uint64_t total = 0;
+            for (auto const& [lo, hi] : covered) total += hi - lo;
+            if (total == rows) return start;
+            continue;
+        }
+        return std::nullopt;
+    }
+    return std::nullopt;
+}
+
+} // namespace detail
+
+// `graph`: a memgraph after fold_elementwise (the patterns are those of the folded chain).
+inline attention_folded_t fold_attention(memgraph_t const& graph, std::vector<memloc_t> const& saved)
+{
+    using namespace detail;
+    attention_folded_t out{graph, {}};
+    auto&              nodes = out.memgraph.nodes;
+    int const          n = int(nodes.size());
+    std::vector<char>  alive(n, 1);
+    chain_matcher_t    matcher{nodes, alive, saved, out.attention};
+    for (int i_s = 0; i_s != n; ++i_s) {
+        if (!alive[i_s] || !nodes[i_s].op.is_einsummable() || out.attention.count(i_s)) continue;
+        auto got = matcher.match(i_s);
+        if (!got) continue;
+        chain_t&          c = *got;
+        attention_node_t& a = c.node;
+        if (!a.desc.eligible() || a.out.offset % 16 || a.q.offset % 16 || a.k.offset % 16 || a.v.offset % 16 || a.mask.offset % 16)
+            continue;
+        int const      i_o = c.idx[4];
+        region_t const reads[4] = {region(a.q), region(a.k), region(a.v), region(a.mask)};
+        bool           bad = false;
+        for (region_t const& r : reads) bad = bad || overlap(region(a.out), r);
+        // Q and K are now read where the last node stands instead of the first, the mask instead of
+        // where the max node stood (V is read where it always was)
+        for (int ic = i_s + 1; ic < i_o && !bad; ++ic) {
+            if (!alive[ic] || std::find(c.idx, c.idx + 5, ic) != c.idx + 5) continue;
+            auto w = written_region(nodes[ic].op, a.loc);
+            if (!w) continue;
+            bad = overlap(*w, reads[0]) || overlap(*w, reads[1]) || (ic > c.idx[1] && overlap(*w, reads[3]));
+        }
+        if (bad) continue;
+        auto tri = lowertri_start(nodes, alive, a.loc, reads[3], c.idx[1], a.desc.rows, a.desc.keys);
+        if (tri) {
+            a.desc.skip_known = 1;
+            a.desc.skip_from = int32_t(*tri);
+        }
+        std::set<int> deps;
+        for (int i : c.idx) deps.insert(nodes[i].inns.begin(), nodes[i].inns.end());
+        for (int i : c.idx) deps.erase(i);
+        memgraph_t::apply_t o = nodes[i_o].op.get_apply();
+        o.mems = {a.out, a.q, a.k, a.v, a.mask};
+        o.group = -1;
+        nodes[i_o].op = memgraph_t::op_t(o);
+        nodes[i_o].inns = deps;
+        for (int ic = i_o + 1; ic != n; ++ic) {
+            if (!alive[ic]) continue;
+            auto w = written_region(nodes[ic].op, a.loc);
+            if (!w) continue;
+            bool hits = false;
+            for (region_t const& r : reads) hits = hits || overlap(*w, r);
+            if (hits) nodes[ic].inns.insert(i_o);
+        }
+        for (int k = 0; k != 4; ++k) {
+            int         i = c.idx[k];
+            auto const& ap = nodes[i].op.get_apply();
+            mem_t       m = ap.mems[0];
+            int         loc = ap.loc;
+            alive[i] = 0;
+            nodes[i].op = memgraph_t::op_t(memgraph_t::alloc_t{loc, m.offset, m.size});
+        }
+        out.attention[i_o] = a;
+    }
     for (auto& node : nodes) node.outs.clear();
     for (int id = 0; id != n; ++id)
         for (int i : nodes[id].inns) nodes[i].outs.insert(id);

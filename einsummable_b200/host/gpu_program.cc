@@ -19,6 +19,20 @@ void scalar_bytes(scalar_t const& s, unsigned char out[8])
     std::memcpy(out, s.data, dtype_size(s.dtype));
 }
 
+es_attention_t attention_descriptor(es_fuse::attention_t const& d)
+{
+    es_attention_t a;
+    std::memset(&a, 0, sizeof(a));
+    a.batch = d.batch, a.heads = d.heads, a.rows = d.rows, a.keys = d.keys, a.head_dim = d.head_dim;
+    a.skip_known = d.skip_known, a.skip_from = d.skip_from;
+    for (int i = 0; i != 3; ++i) {
+        a.q_stride[i] = d.q_stride[i], a.k_stride[i] = d.k_stride[i];
+        a.v_stride[i] = d.v_stride[i], a.out_stride[i] = d.out_stride[i];
+    }
+    a.mask_stride = d.mask_stride;
+    return a;
+}
+
 } // namespace
 
 gpu_program_t::gpu_program_t(memgraph_t const&            memgraph,
@@ -26,7 +40,8 @@ gpu_program_t::gpu_program_t(memgraph_t const&            memgraph,
                              kernel_manager_t&            km,
                              void*                        mem,
                              map<string, scalar_t> const& scalar_vars,
-                             int                          max_lanes)
+                             int                          max_lanes,
+                             es_exchange::attention_map_t const* attention)
     : prog(nullptr), workspace(nullptr), n_ops(0)
 {
     check(es_b200_program_create(km.c_handle(), &prog), "es_b200_program_create");
@@ -61,6 +76,12 @@ gpu_program_t::gpu_program_t(memgraph_t const&            memgraph,
         if (op.is_inputmem() || op.is_inputsto() || op.is_partialize() || op.is_alloc() || op.is_del()) {
             stands_for[mid] = deps;
             continue;
+        } else if (attention && attention->count(mid)) {
+            es_fuse::attention_node_t const& a = attention->at(mid);
+            es_attention_t                   d = attention_descriptor(a.desc);
+            check(es_b200_program_add_attention(prog, &d, at(a.out.offset), at(a.q.offset), at(a.k.offset),
+                                                at(a.v.offset), at(a.mask.offset), deps.data(), int(deps.size()), &index),
+                  "es_b200_program_add_attention");
         } else if (op.is_apply()) {
             auto const& apply = op.get_apply();
             if (apply.is_einsummable()) {
@@ -181,7 +202,8 @@ gpu_exchange_program_t::gpu_exchange_program_t(memgraph_t const&            memg
                                                vector<void*> const&         peer_flags,
                                                map<string, scalar_t> const& scalar_vars,
                                                int                          max_lanes,
-                                               uint32_t                     wait_limit_ms)
+                                               uint32_t                     wait_limit_ms,
+                                               es_exchange::attention_map_t const* attention)
     : prog(nullptr), workspace(nullptr), n_ops(0)
 {
     check(es_b200_program_create(km.c_handle(), &prog), "es_b200_program_create");
@@ -201,7 +223,8 @@ gpu_exchange_program_t::gpu_exchange_program_t(memgraph_t const&            memg
     };
     // the rank's units in the order in which a simulation of all ranks serves them: the exchange ops share
     // one in-order lane, so what is expected to be ready first has to be asked for first
-    for (es_exchange::unit_t const& u : es_exchange::order_units(memgraph, memgraph.num_compute_locs, rank)) {
+    for (es_exchange::unit_t const& u :
+         es_exchange::order_units(memgraph, memgraph.num_compute_locs, rank, nullptr, attention)) {
         int         index = -1;
         int const*  deps = u.deps.data();
         int const   n_deps = int(u.deps.size());
@@ -218,6 +241,13 @@ gpu_exchange_program_t::gpu_exchange_program_t(memgraph_t const&            memg
             check(es_b200_program_add_einsummable(prog, km.kernel_id(e), at(rank, apply.mems[0].offset), inns.data(),
                                                   int(inns.size()), deps, n_deps, &index),
                   "es_b200_program_add_einsummable");
+        } else if (u.kind == "attention") {
+            es_fuse::attention_node_t const& a = attention->at(u.node);
+            es_attention_t                   d = attention_descriptor(a.desc);
+            check(es_b200_program_add_attention(prog, &d, at(rank, a.out.offset), at(rank, a.q.offset),
+                                                at(rank, a.k.offset), at(rank, a.v.offset), at(rank, a.mask.offset),
+                                                deps, n_deps, &index),
+                  "es_b200_program_add_attention");
         } else if (u.kind == "touch" || u.kind == "rtouch") {
             auto const&    apply = memgraph.nodes[u.node].op.get_apply();
             touch_t const& touch = apply.get_touch();

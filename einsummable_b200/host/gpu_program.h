@@ -20,12 +20,15 @@
 
 struct gpu_program_t {
     // mem: the global buffer of location `loc` (server.cc:38-43).  The kernel manager must outlive the program.
-    gpu_program_t(memgraph_t const&            memgraph,
-                  int                          loc,
-                  kernel_manager_t&            km,
-                  void*                        mem,
-                  map<string, scalar_t> const& scalar_vars = {},
-                  int                          max_lanes = 16);
+    // attention: for a graph from es_fuse::fold_attention (gpu_fuse.h), the nodes that stand for a whole
+    // softmax(Q K^T + mask) V chain; each becomes one es_b200_program_add_attention op.
+    gpu_program_t(memgraph_t const&                   memgraph,
+                  int                                 loc,
+                  kernel_manager_t&                   km,
+                  void*                               mem,
+                  map<string, scalar_t> const&        scalar_vars = {},
+                  int                                 max_lanes = 16,
+                  es_exchange::attention_map_t const* attention = nullptr);
     ~gpu_program_t();
 
     gpu_program_t(gpu_program_t const&) = delete;
@@ -67,7 +70,8 @@ struct gpu_exchange_program_t {
                            vector<void*> const&         peer_flags,
                            map<string, scalar_t> const& scalar_vars = {},
                            int                          max_lanes = 16,
-                           uint32_t                     wait_limit_ms = 0);
+                           uint32_t                     wait_limit_ms = 0,
+                           es_exchange::attention_map_t const* attention = nullptr);
     ~gpu_exchange_program_t();
 
     gpu_exchange_program_t(gpu_exchange_program_t const&) = delete;

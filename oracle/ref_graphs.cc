@@ -46,6 +46,8 @@ struct built_graph_t {
     vector<map<int, buffer_t>> sto;   // storage contents around ref_graph_run_storage
     map<int, string>         names; // graph id -> name (weights etc.)
     map<string, scalar_t>    vars;  // scalar variables of the updater, substituted where a node is used
+    // after ref_graph_fold_attention: the nodes that stand for a whole attention chain
+    std::map<int, es_fuse::attention_node_t> attention;
 };
 
 vector<built_graph_t*> g_graphs;
@@ -475,7 +477,7 @@ int ref_graph_exchange_units(int h, int rank, char const* path)
     G_BEGIN
     built_graph_t* b = g_graphs.at(h);
     std::ofstream  out(path);
-    out << es_exchange::units_json(es_exchange::make_units(b->memgraph, rank)) << "\n";
+    out << es_exchange::units_json(es_exchange::make_units(b->memgraph, rank, b->attention.empty() ? nullptr : &b->attention)) << "\n";
     return 0;
     G_END
 }
@@ -487,7 +489,8 @@ int ref_graph_exchange_units_ordered(int h, int rank, char const* path)
     G_BEGIN
     built_graph_t*                      b = g_graphs.at(h);
     std::vector<es_exchange::service_t> service;
-    auto units = es_exchange::order_units(b->memgraph, b->memgraph.num_compute_locs, rank, &service);
+    auto units = es_exchange::order_units(b->memgraph, b->memgraph.num_compute_locs, rank, &service,
+                                          b->attention.empty() ? nullptr : &b->attention);
     std::ofstream out(path);
     out.precision(17);
     out << "{\"units\":" << es_exchange::units_json(units) << ",\"ready_us\":[";
@@ -517,6 +520,52 @@ int ref_graph_fold_elementwise(int h, int* n_folded)
     built_graph_t*    nb = new built_graph_t(b);
     nb->memgraph = f.memgraph;
     if (n_folded) *n_folded = int(f.folded.size());
+    g_graphs.push_back(nb);
+    return int(g_graphs.size()) - 1;
+    G_END
+}
+
+// The attention chains of handle h's memgraph (which has been through ref_graph_fold_elementwise) as the
+// C++ pass finds them (es_fuse::fold_attention): a new handle whose memgraph has every chain replaced by one
+// node, and, written to `path` as JSON, that node's descriptor and memories by node id.
+int ref_graph_fold_attention(int h, char const* path)
+{
+    G_BEGIN
+    built_graph_t const&  b = *g_graphs.at(h);
+    std::vector<memloc_t> saved;
+    if (b.has_storage) {
+        for (auto const& [tid, msl] : b.save_msl)
+            if (msl.is_memloc()) saved.push_back(msl.get_memloc());
+    } else {
+        for (auto const& [tid, m] : b.save_mem) saved.push_back(memloc_t{m.offset, m.size, b.taskgraph.out_loc(tid)});
+    }
+    es_fuse::attention_folded_t f = es_fuse::fold_attention(b.memgraph, saved);
+    std::ofstream               out(path);
+    auto v3 = [&](int64_t const* v) { out << "[" << v[0] << "," << v[1] << "," << v[2] << "]"; };
+    auto mem = [&](mem_t const& m) { out << "[" << m.offset << "," << m.size << "]"; };
+    out << "{";
+    bool first = true;
+    for (auto const& [id, a] : f.attention) {
+        auto const& d = a.desc;
+        out << (first ? "" : ",") << "\"" << id << "\":{\"loc\":" << a.loc << ",\"attention\":{\"batch\":" << d.batch
+            << ",\"heads\":" << d.heads << ",\"rows\":" << d.rows << ",\"keys\":" << d.keys << ",\"head_dim\":" << d.head_dim
+            << ",\"skip_known\":" << d.skip_known << ",\"skip_from\":" << d.skip_from << ",\"q_stride\":";
+        v3(d.q_stride);
+        out << ",\"k_stride\":";
+        v3(d.k_stride);
+        out << ",\"v_stride\":";
+        v3(d.v_stride);
+        out << ",\"out_stride\":";
+        v3(d.out_stride);
+        out << ",\"mask_stride\":" << d.mask_stride << "},\"mems\":[";
+        mem(a.out), out << ",", mem(a.q), out << ",", mem(a.k), out << ",", mem(a.v), out << ",", mem(a.mask);
+        out << "]}";
+        first = false;
+    }
+    out << "}\n";
+    built_graph_t* nb = new built_graph_t(b);
+    nb->memgraph = f.memgraph;
+    nb->attention = f.attention;
     g_graphs.push_back(nb);
     return int(g_graphs.size()) - 1;
     G_END

@@ -43,6 +43,14 @@ CASES = {
                                                                                  ctypes.c_double(0.01), 1, 0, 0),
 }
 
+# full size: structure only (the reference's interpreter would take hours)
+LARGE = {
+    "LLaMA-7B layer, tensor-parallel, 8 locations": lambda L: L.ref_graph_build_llama_tp(u64(4096), u64(32), u64(256), u64(32000), 1, u64(4),
+                                                                                          u64(512), 8, 0),
+    "LLaMA-7B layer, autoplace01, 2 locations": lambda L: L.ref_graph_build_llama(u64(4096), u64(32), u64(256), u64(32000), 1, u64(4),
+                                                                                  u64(512), 2, 0),
+}
+
 
 def _json(L, h, path):
     assert L.ref_graph_write_json(h, path.encode()) >= 0, L.ref_graph_last_error().decode()
@@ -51,7 +59,7 @@ def _json(L, h, path):
 
 
 def _fold(L, case, tmp_path):
-    h = CASES[case](L)
+    h = {**CASES, **LARGE}[case](L)
     assert h >= 0, L.ref_graph_last_error().decode()
     n = ctypes.c_int(0)
     hf = L.ref_graph_fold_elementwise(h, ctypes.byref(n))
@@ -59,7 +67,7 @@ def _fold(L, case, tmp_path):
     return h, hf, n.value, _json(L, h, str(tmp_path / "mg.json")), _json(L, hf, str(tmp_path / "folded.json"))
 
 
-@pytest.mark.parametrize("case", list(CASES))
+@pytest.mark.parametrize("case", list(CASES) + list(LARGE))
 def test_cpp_fold_is_the_python_fold(case, tmp_path):
     L = _lib()
     _, _, n_folded, mg, got = _fold(L, case, tmp_path)
@@ -116,3 +124,75 @@ def test_cpp_folded_graph_through_the_reference_interpreter(case, tmp_path):
         # join point by point: the same roundings in the same order, so the same bits
         assert np.isfinite(got[k].astype(np.float64)).all(), k
         assert np.array_equal(got[k], want[k]), (case, k)
+
+
+n_chains = {}
+
+
+@pytest.mark.parametrize("case", list(CASES) + list(LARGE))
+def test_cpp_attention_fold_is_the_python_one(case, tmp_path):
+    """es_fuse::fold_attention on the C++-folded graph against fuse_attention on the Python-folded one: the
+    same chains, the same descriptor (strides, and the lower-triangular mask recognised through the row-block
+    copies and moves in front of it), the same five memories, the same dependencies on every node."""
+    L = _lib()
+    if not hasattr(L, "ref_graph_fold_attention"):
+        pytest.skip("oracle/_ref/libes_ref.so predates the attention fold")
+    _, hf, _, mg, _ = _fold(L, case, tmp_path)
+    apath = str(tmp_path / "attention.json")
+    ha = L.ref_graph_fold_attention(hf, apath.encode())
+    assert ha >= 0, L.ref_graph_last_error().decode()
+    with open(apath) as f:
+        found = json.load(f)
+    got = _json(L, ha, str(tmp_path / "attn_graph.json"))
+    want, chains = F.fuse_attention(F.fuse_elementwise_chains(mg)[0])
+    assert chains == len(found)
+    n_chains[case] = chains
+    for g, w in zip(got["nodes"], want["nodes"]):
+        assert sorted(g["inns"]) == sorted(w["inns"]), (case, g["id"])
+        if "attention" in w:
+            a = found[str(w["id"])]
+            assert a["attention"] == w["attention"], (case, w["id"], a["attention"], w["attention"])
+            assert a["mems"] == w["mems"] and g["mems"] == w["mems"] and a["loc"] == w["loc"], (case, w["id"])
+        elif w.get("folded"):
+            assert g["kind"] == "alloc", (case, g["id"])
+        else:
+            assert g["kind"] == w["kind"], (case, g["id"])
+    if "training" not in case:
+        assert all(a["attention"]["skip_known"] == 1 for a in found.values())
+
+
+def test_cpp_attention_fold_found_chains():
+    if not n_chains:
+        pytest.skip("the cases above did not run")
+    assert sum(n_chains.values()) >= 3, n_chains
+
+
+@pytest.mark.parametrize("case", ["tiny llama, tensor-parallel, 4 locations", "tiny training graph, 2 locations"] + list(LARGE))
+def test_cpp_plan_of_the_folded_graph_is_the_python_plan(case, tmp_path):
+    """Fold, attention fold, units and simulated order of service, all in C++, against the same chain in
+    Python: what the C++ host launches on every rank, and in which order, is what the Python runner launches."""
+    from einsummable_b200 import memgraph as M
+    L = _lib()
+    if not hasattr(L, "ref_graph_fold_attention"):
+        pytest.skip("oracle/_ref/libes_ref.so predates the attention fold")
+    _, hf, _, mg, _ = _fold(L, case, tmp_path)
+    ha = L.ref_graph_fold_attention(hf, str(tmp_path / "attention.json").encode())
+    assert ha >= 0, L.ref_graph_last_error().decode()
+    want_mg = F.fuse_attention(F.fuse_elementwise_chains(mg)[0])[0]
+    world = mg["num_locs"]
+    kinds = set()
+    for rank in range(world):
+        upath = str(tmp_path / ("ordered%d.json" % rank))
+        assert L.ref_graph_exchange_units_ordered(ha, rank, upath.encode()) >= 0, L.ref_graph_last_error().decode()
+        with open(upath) as f:
+            got = json.load(f)
+        want = M.order_units_by_simulation(want_mg, world, rank)
+        assert len(got["units"]) == len(want)
+        for i, (g, w) in enumerate(zip(got["units"], want)):
+            assert g["kind"] == w["kind"], (case, rank, i, g, w)
+            assert g["node"] == w.get("node", -1) or w["kind"] in ("signal", "await", "pull", "wait"), (case, rank, i, g, w)
+            assert g["moves"] == list(w.get("moves", [])), (case, rank, i, g, w)
+            assert g["deps"] == list(w["deps"]), (case, rank, i, g, w)
+            assert got["ready_us"][i] == w["sim_start_us"] and got["finish_us"][i] == w["sim_finish_us"], (case, rank, i)
+            kinds.add(w["kind"])
+    assert "training" in case or "attention" in kinds
