@@ -47,10 +47,12 @@ using attention_map_t = std::map<int, es_fuse::attention_node_t>;
 
 struct unit_t {
     std::string      kind;       // einsummable attention touch rtouch constant copy evict load signal await pull wait
+                                 // and, with group_sum: rsum ack
     int              node = -1;  // memgraph node (compute units)
     std::vector<int> moves;      // memgraph move nodes (exchange units; rtouch: the move it consumes)
     std::vector<int> deps;       // indices of earlier units of this rank
     bool             first = true; // touch / rtouch: the group's first member runs as a copy
+    std::vector<int> nodes;      // rsum: the touches it stands for (node = the first of them)
 };
 
 // incoming moves of one run share an await (and a pull) only when their sources are expected to be
@@ -186,7 +188,12 @@ inline std::vector<double> node_levels(memgraph_t const& mg, attention_map_t con
     return level;
 }
 
-inline std::vector<unit_t> make_units(memgraph_t const& mg, int rank, attention_map_t const* attention = nullptr)
+// group_sum: the remote adds of a partial-sum group -- whole dense blocks that arrive from several peers and
+// are added into the same tensor one after the other -- become ONE unit `rsum` (an elementwise kernel
+// out = out + r1 + ... + rk over the peers' memory) followed by an `ack` unit that acknowledges the k moves,
+// instead of k dependent remote touches.
+inline std::vector<unit_t> make_units(memgraph_t const& mg, int rank, attention_map_t const* attention = nullptr,
+                                      bool group_sum = false)
 {
     using namespace detail;
     int const                  n = int(mg.nodes.size());
@@ -229,6 +236,33 @@ inline std::vector<unit_t> make_units(memgraph_t const& mg, int rank, attention_
             if (n_cross != 1) continue;
             remote_touch[m] = us[0];
             touch_move[us[0]] = m;
+        }
+    }
+    // group_sum: fused_tail[touch] = (group, the touches summed together); never the group's first member
+    // (that one is the copy); the others commute, so the remote ones may be added where the last of them stands
+    std::map<int, std::pair<int, std::vector<int>>> fused_tail;
+    std::map<int, std::set<int>>                    pending_tail;
+    if (group_sum) {
+        std::map<int, std::vector<int>> members_of;
+        for (int id = 0; id != n; ++id) {
+            auto const& op = mg.nodes[id].op;
+            if (op.is_touch() && op.get_apply().group >= 0 && op.get_apply().loc == rank)
+                members_of[op.get_apply().group].push_back(id);
+        }
+        auto dense_add = [&](int tid) {
+            touch_t const& t = mg.nodes[tid].op.get_apply().get_touch();
+            if (!touch_move.count(tid) || !t.castable || t.castable.value() != castable_t::add) return false;
+            if (t.dtype != dtype_t::f16 && t.dtype != dtype_t::f32) return false;
+            for (auto const& d : t.selection)
+                if (d.d_inn != d.d_out || d.d_inn != d.size || d.offset_inn != 0 || d.offset_out != 0) return false;
+            return true;
+        };
+        for (auto const& [group, ms] : members_of) {
+            std::vector<int> tail;
+            for (size_t i = 1; i < ms.size(); ++i)
+                if (dense_add(ms[i])) tail.push_back(ms[i]);
+            if (tail.size() >= 2 && tail.size() <= 7)
+                for (int tid : tail) fused_tail[tid] = {group, tail};
         }
     }
     std::vector<unit_t> units;
@@ -376,6 +410,28 @@ inline std::vector<unit_t> make_units(memgraph_t const& mg, int rank, attention_
                     deps.erase(std::unique(deps.begin(), deps.end()), deps.end());
                 }
             }
+            auto ft = fused_tail.find(id);
+            if (ft != fused_tail.end()) {
+                auto const& [key, tail] = ft->second;
+                std::set<int>& acc = pending_tail[key];
+                acc.insert(deps.begin(), deps.end());
+                if (id != tail.back()) continue; // emitted with the last member of the tail
+                unit_t r;
+                r.kind = "rsum";
+                r.nodes = tail;
+                r.node = tail[0];
+                for (int t : tail) r.moves.push_back(touch_move.at(t));
+                r.deps.assign(acc.begin(), acc.end());
+                int const ri = emit(r);
+                for (int t : tail) unit_of[t] = ri;
+                unit_t a;
+                a.kind = "ack";
+                a.moves = r.moves;
+                a.deps = {ri};
+                emit(a);
+                group_last[key] = ri;
+                continue;
+            }
             auto tm = touch_move.find(id);
             if (tm != touch_move.end()) {
                 u.kind = "rtouch";
@@ -453,7 +509,12 @@ inline unit_cost_t unit_cost_us(memgraph_t const& mg, unit_t const& u, attention
         return {2.5, bytes / 4.5e6, SERVER_GPU};
     }
     if (k == "rtouch") return {6.0, double(mg.nodes[u.node].op.get_apply().mems[1].size) / 0.65e6, SERVER_LINK};
-    if (k == "await" || k == "signal") return {3.0, 0.0, SERVER_NONE};
+    if (k == "rsum") {
+        uint64_t size = 0;
+        for (int t : u.nodes) size += mg.nodes[t].op.get_apply().mems[1].size;
+        return {6.0, double(size) / 0.65e6, SERVER_LINK};
+    }
+    if (k == "await" || k == "signal" || k == "ack") return {3.0, 0.0, SERVER_NONE};
     if (k == "constant") return {2.5, 0.5, SERVER_GPU};
     if (k == "copy") {
         auto const& op = mg.nodes[u.node].op;
@@ -491,7 +552,7 @@ inline std::vector<std::vector<service_t>> simulate(memgraph_t const& mg, std::v
             unit_t const& u = units_by_rank[r][i];
             if (u.kind == "signal") {
                 for (int m : u.moves) sig_of[m] = {r, i};
-            } else if (u.kind == "pull" || u.kind == "rtouch") {
+            } else if (u.kind == "pull" || u.kind == "rtouch" || u.kind == "ack") {
                 for (int m : u.moves) pull_of[m] = {r, i};
             }
         }
@@ -590,10 +651,10 @@ inline std::vector<std::vector<service_t>> simulate(memgraph_t const& mg, std::v
 // The units of `rank` in the order of simulated service (the closing wait stays last), dependencies
 // renumbered; `service`, when given, receives each returned unit's simulated ready and finish time.
 inline std::vector<unit_t> order_units(memgraph_t const& mg, int world, int rank, std::vector<service_t>* service = nullptr,
-                                       attention_map_t const* attention = nullptr)
+                                       attention_map_t const* attention = nullptr, bool group_sum = false)
 {
     std::vector<std::vector<unit_t>> all;
-    for (int r = 0; r != world; ++r) all.push_back(make_units(mg, r, attention));
+    for (int r = 0; r != world; ++r) all.push_back(make_units(mg, r, attention, group_sum));
     auto                       times = simulate(mg, all, attention);
     std::vector<unit_t> const& units = all[rank];
     int const                  n = int(units.size());
@@ -637,6 +698,8 @@ inline std::string units_json(std::vector<unit_t> const& units)
         vec(u.moves);
         out << ",\"deps\":";
         vec(u.deps);
+        out << ",\"nodes\":";
+        vec(u.nodes);
         out << "}";
     }
     out << "]";

@@ -203,7 +203,8 @@ gpu_exchange_program_t::gpu_exchange_program_t(memgraph_t const&            memg
                                                map<string, scalar_t> const& scalar_vars,
                                                int                          max_lanes,
                                                uint32_t                     wait_limit_ms,
-                                               es_exchange::attention_map_t const* attention)
+                                               es_exchange::attention_map_t const* attention,
+                                               bool                         group_sum)
     : prog(nullptr), workspace(nullptr), n_ops(0)
 {
     check(es_b200_program_create(km.c_handle(), &prog), "es_b200_program_create");
@@ -224,7 +225,7 @@ gpu_exchange_program_t::gpu_exchange_program_t(memgraph_t const&            memg
     // the rank's units in the order in which a simulation of all ranks serves them: the exchange ops share
     // one in-order lane, so what is expected to be ready first has to be asked for first
     for (es_exchange::unit_t const& u :
-         es_exchange::order_units(memgraph, memgraph.num_compute_locs, rank, nullptr, attention)) {
+         es_exchange::order_units(memgraph, memgraph.num_compute_locs, rank, nullptr, attention, group_sum)) {
         int         index = -1;
         int const*  deps = u.deps.data();
         int const   n_deps = int(u.deps.size());
@@ -300,6 +301,39 @@ gpu_exchange_program_t::gpu_exchange_program_t(memgraph_t const&            memg
                                                &index),
                       "es_b200_program_add_copy");
             }
+        } else if (u.kind == "rsum") {
+            // out = out + r1 + ... + rk, the r's read where they are, in the peers' memory: one generated
+            // elementwise kernel instead of k remote touches that wait for one another
+            auto const&    first = memgraph.nodes[u.nodes[0]].op.get_apply();
+            touch_t const& touch = first.get_touch();
+            string const   dt = write_with_ss(touch.dtype);
+            uint64_t const nelem = first.mems[0].size / dtype_size(touch.dtype);
+            string         join = "hole|" + dt + "@0";
+            for (size_t i = 1; i <= u.nodes.size(); ++i) {
+                join = "+[" + join + ",hole|" + dt + "@" + std::to_string(i) + "]";
+            }
+            einsummable_t e({nelem}, vector<vector<int>>(u.nodes.size() + 1, vector<int>{0}), 1,
+                            parse_with_ss<scalarop_t>(join));
+            if (!km.build(e)) {
+                throw std::runtime_error("gpu_exchange_program_t: could not build " + write_with_ss(e));
+            }
+            void*               out = at(rank, first.mems[0].offset);
+            vector<void const*> inns{out};
+            for (int m : u.moves) {
+                auto const& mv = memgraph.nodes[m].op.get_move();
+                inns.push_back(at(mv.get_src_loc(), std::get<1>(mv.src)));
+            }
+            check(es_b200_program_add_einsummable(prog, km.kernel_id(e), out, inns.data(), int(inns.size()), deps,
+                                                  n_deps, &index),
+                  "es_b200_program_add_einsummable");
+        } else if (u.kind == "ack") {
+            // the done flags of the moves an rsum consumed, in the sources' arrays
+            vector<void*> flags;
+            for (int m : u.moves) {
+                flags.push_back(flag(memgraph.nodes[m].op.get_move().get_src_loc(), 1, m));
+            }
+            check(es_b200_program_add_signal(prog, flags.data(), int(flags.size()), deps, n_deps, &index),
+                  "es_b200_program_add_signal");
         } else if (u.kind == "signal" || u.kind == "await" || u.kind == "wait") {
             // signal: the ready flags in the destinations' arrays; await: this rank's ready flags;
             // wait: this rank's done flags

@@ -61,7 +61,8 @@ private:
 // words that every rank places at the same offset: word k is the ready flag of cross-location move k (it lives in
 // the destination's array), word n_moves + k its done flag (in the source's array), k counting the memgraph's
 // cross-location moves in node order.  All ranks build their programs from the same memgraph and launch them
-// the same number of times.
+// the same number of times.  attention: as for gpu_program_t.  group_sum: the remote adds of a partial-sum group as one
+// kernel over the peers' memory (es_exchange::make_units).
 struct gpu_exchange_program_t {
     gpu_exchange_program_t(memgraph_t const&            memgraph,
                            int                          rank,
@@ -71,7 +72,8 @@ struct gpu_exchange_program_t {
                            map<string, scalar_t> const& scalar_vars = {},
                            int                          max_lanes = 16,
                            uint32_t                     wait_limit_ms = 0,
-                           es_exchange::attention_map_t const* attention = nullptr);
+                           es_exchange::attention_map_t const* attention = nullptr,
+                           bool                         group_sum = false);
     ~gpu_exchange_program_t();
 
     gpu_exchange_program_t(gpu_exchange_program_t const&) = delete;

@@ -502,6 +502,21 @@ int ref_graph_exchange_units_ordered(int h, int rank, char const* path)
     G_END
 }
 
+// The units of one rank, in the order of simulated service, with the remote adds of every partial-sum group
+// summed by one unit (make_units' group_sum): compared with the Python planner's group_sum=True.
+int ref_graph_exchange_units_group_sum(int h, int rank, char const* path)
+{
+    G_BEGIN
+    built_graph_t*                      b = g_graphs.at(h);
+    std::vector<es_exchange::service_t> service;
+    auto units = es_exchange::order_units(b->memgraph, b->memgraph.num_compute_locs, rank, &service,
+                                          b->attention.empty() ? nullptr : &b->attention, true);
+    std::ofstream out(path);
+    out << "{\"units\":" << es_exchange::units_json(units) << "}\n";
+    return 0;
+    G_END
+}
+
 // A new handle whose memgraph is the C++ fold of handle h's (einsummable_b200/host/gpu_fuse.h): the
 // folded graph is again a memgraph_t, so ref_graph_write_json / ref_graph_run / ref_graph_exchange_units
 // take it like any other.  Returns the handle; *n_folded receives the number of nodes folded away.

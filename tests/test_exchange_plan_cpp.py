@@ -99,3 +99,34 @@ def test_cpp_and_python_orders_of_simulated_service_agree(case, tmp_path):
         moved += sum(1 for w, p in zip(want, plain) if (w["kind"], w.get("node"), tuple(w.get("moves", ()))) !=
                      (p["kind"], p.get("node"), tuple(p.get("moves", ()))))
     assert moved > 0 or "c1" in case       # the simulated order differs from memgraph order somewhere
+
+
+@pytest.mark.parametrize("case", ["tiny llama, tensor-parallel, 4 locations", "LLaMA-7B layer, tensor-parallel, 8 locations"])
+def test_cpp_and_python_planners_agree_on_summed_remote_adds(case, tmp_path):
+    """make_units' group_sum against schedule_units(group_sum=True): the remote adds of a partial-sum group as
+    one `rsum` unit and one `ack` unit, in the same place, over the same touches and moves."""
+    L = _lib()
+    if not hasattr(L, "ref_graph_exchange_units_group_sum"):
+        pytest.skip("oracle/_ref/libes_ref.so predates the summed remote adds")
+    h = CASES[case](L)
+    assert h >= 0, L.ref_graph_last_error().decode()
+    path = str(tmp_path / "mg.json")
+    assert L.ref_graph_write_json(h, path.encode()) >= 0
+    with open(path) as f:
+        mg = json.load(f)
+    world = mg["num_locs"]
+    n_rsum = 0
+    for rank in range(world):
+        upath = str(tmp_path / ("gs%d.json" % rank))
+        assert L.ref_graph_exchange_units_group_sum(h, rank, upath.encode()) >= 0, L.ref_graph_last_error().decode()
+        with open(upath) as f:
+            got = json.load(f)["units"]
+        want = M.order_units_by_simulation(mg, world, rank, group_sum=True)
+        assert len(got) == len(want)
+        for i, (g, w) in enumerate(zip(got, want)):
+            assert g["kind"] == w["kind"], (case, rank, i, g, w)
+            assert g["moves"] == list(w.get("moves", [])), (case, rank, i, g, w)
+            assert g["deps"] == list(w["deps"]), (case, rank, i, g, w)
+            assert g["nodes"] == list(w.get("nodes", [])), (case, rank, i, g, w)
+            n_rsum += w["kind"] == "rsum"
+    assert n_rsum > 0
