@@ -48,6 +48,8 @@ struct built_graph_t {
     map<string, scalar_t>    vars;  // scalar variables of the updater, substituted where a node is used
     // after ref_graph_fold_attention: the nodes that stand for a whole attention chain
     std::map<int, es_fuse::attention_node_t> attention;
+    // hand-made graphs (ref_graph_build_fold_case): regions to treat as saved results
+    std::vector<memloc_t> extra_saved;
 };
 
 vector<built_graph_t*> g_graphs;
@@ -517,6 +519,61 @@ int ref_graph_exchange_units_group_sum(int h, int rank, char const* path)
     G_END
 }
 
+// Hand-made one-location memgraphs around one elementwise producer A (exp, f32, 64 elements, reads region 0,
+// writes region 1; regions are 256 bytes apart) and its reader B (x + y over regions 1 and 4, into region 2), for
+// the conditions under which the fold must refuse:
+//   0 nothing in the way (A folds into B)          1 a fill between A and B writes the memory A reads
+//   2 B reads A's bytes under another shape         3 A's result is a saved result
+//   4 a copy node reads A's result                  5 two readers (A folds into both)
+//   6 B writes into the memory A reads              7 as 0, and a later fill into the memory A reads, which
+//                                                     depended on A alone, must afterwards depend on B
+int ref_graph_build_fold_case(int which)
+{
+    G_BEGIN
+    uint64_t const n = 64, sz = n * 4;
+    auto           mem = [&](int region) { return mem_t{uint64_t(region) * sz, sz}; };
+    memgraph_t     mg(1, 1, vector<int>{0});
+    auto           input = [&](int region) { return mg.insert(memgraph_t::op_t(memgraph_t::inputmem_t{0, region * sz, sz}), {}); };
+    auto           apply = [&](einsummable_t const& e, vector<int> regions, set<int> deps) {
+        vector<mem_t> mems;
+        for (int r : regions) mems.push_back(mem(r));
+        return mg.insert(memgraph_t::op_t(memgraph_t::apply_t{0, mems, e, -1}), deps);
+    };
+    auto fill = [&](int region, set<int> deps) {
+        fill_t f(fill_t::constant_t{scalar_t(float(1.5)), {n}});
+        return mg.insert(memgraph_t::op_t(memgraph_t::constant_t{0, region * sz, f}), deps);
+    };
+    einsummable_t e_exp({n}, {{0}}, 1, scalarop_t::make_exp(dtype_t::f32));
+    einsummable_t e_exp2({8, 8}, {{0, 1}}, 2, scalarop_t::make_exp(dtype_t::f32));
+    einsummable_t e_add({n}, {{0}, {0}}, 1, scalarop_t::make_add(dtype_t::f32));
+    einsummable_t e_mul({n}, {{0}, {0}}, 1, scalarop_t::make_mul(dtype_t::f32));
+    built_graph_t* b = new built_graph_t();
+    int            x = input(0), y = input(4);
+    int            a = apply(which == 2 ? e_exp2 : e_exp, {1, 0}, {x});
+    if (which == 1) {
+        int f = fill(0, {a});
+        apply(e_add, {2, 1, 4}, {a, y, f});
+    } else if (which == 4) {
+        apply(e_add, {2, 1, 4}, {a, y});
+        mg.insert(memgraph_t::op_t(memgraph_t::copy_t{0, sz, 1 * sz, 3 * sz}), {a});
+    } else if (which == 5) {
+        apply(e_add, {2, 1, 4}, {a, y});
+        apply(e_mul, {3, 4, 1}, {a, y});
+    } else if (which == 6) {
+        apply(e_add, {0, 1, 4}, {a, y});
+    } else if (which == 7) {
+        apply(e_add, {2, 1, 4}, {a, y});
+        fill(0, {a});
+    } else {
+        apply(e_add, {2, 1, 4}, {a, y});
+    }
+    if (which == 3) b->extra_saved.push_back(memloc_t{1 * sz, sz, 0});
+    b->memgraph = mg;
+    g_graphs.push_back(b);
+    return int(g_graphs.size()) - 1;
+    G_END
+}
+
 // A new handle whose memgraph is the C++ fold of handle h's (einsummable_b200/host/gpu_fuse.h): the
 // folded graph is again a memgraph_t, so ref_graph_write_json / ref_graph_run / ref_graph_exchange_units
 // take it like any other.  Returns the handle; *n_folded receives the number of nodes folded away.
@@ -531,6 +588,7 @@ int ref_graph_fold_elementwise(int h, int* n_folded)
     } else {
         for (auto const& [tid, m] : b.save_mem) saved.push_back(memloc_t{m.offset, m.size, b.taskgraph.out_loc(tid)});
     }
+    saved.insert(saved.end(), b.extra_saved.begin(), b.extra_saved.end());
     es_fuse::folded_t f = es_fuse::fold_elementwise(b.memgraph, saved);
     built_graph_t*    nb = new built_graph_t(b);
     nb->memgraph = f.memgraph;
@@ -554,6 +612,7 @@ int ref_graph_fold_attention(int h, char const* path)
     } else {
         for (auto const& [tid, m] : b.save_mem) saved.push_back(memloc_t{m.offset, m.size, b.taskgraph.out_loc(tid)});
     }
+    saved.insert(saved.end(), b.extra_saved.begin(), b.extra_saved.end());
     es_fuse::attention_folded_t f = es_fuse::fold_attention(b.memgraph, saved);
     std::ofstream               out(path);
     auto v3 = [&](int64_t const* v) { out << "[" << v[0] << "," << v[1] << "," << v[2] << "]"; };

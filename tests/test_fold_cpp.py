@@ -196,3 +196,50 @@ def test_cpp_plan_of_the_folded_graph_is_the_python_plan(case, tmp_path):
             assert got["ready_us"][i] == w["sim_start_us"] and got["finish_us"][i] == w["sim_finish_us"], (case, rank, i)
             kinds.add(w["kind"])
     assert "training" in case or "attention" in kinds
+
+
+# which case, nodes folded away, what it shows
+HAZARDS = [
+    (0, 1, "nothing in the way"),
+    (1, 0, "a fill between A and B writes the memory A reads"),
+    (2, 0, "B reads A's bytes under another shape"),
+    (3, 0, "A's result is a saved result"),
+    (4, 0, "a copy node reads A's result"),
+    (5, 1, "two readers: A folds into both"),
+    (6, 0, "B writes into the memory A reads"),
+    (7, 1, "a later writer into the memory A read must wait for B"),
+]
+
+
+@pytest.mark.parametrize("which,folded,what", HAZARDS)
+def test_fold_conditions_on_hand_made_graphs(which, folded, what, tmp_path):
+    """One producer, its reader(s) and whatever stands in the way, built node by node with memgraph_t::insert:
+    the C++ pass and the Python pass fold, or refuse, alike."""
+    L = _lib()
+    if not hasattr(L, "ref_graph_build_fold_case"):
+        pytest.skip("oracle/_ref/libes_ref.so predates the hand-made fold cases")
+    h = L.ref_graph_build_fold_case(which)
+    assert h >= 0, L.ref_graph_last_error().decode()
+    n = ctypes.c_int(-1)
+    hf = L.ref_graph_fold_elementwise(h, ctypes.byref(n))
+    assert hf >= 0, L.ref_graph_last_error().decode()
+    mg = _json(L, h, str(tmp_path / "mg.json"))
+    got = _json(L, hf, str(tmp_path / "folded.json"))
+    if which == 3:      # the region of A's result as a saved block
+        mg["outputs"] = [{"blocks": [{"loc": 0, "offset": 256, "size": 256}]}]
+    want, want_folded = F.fuse_elementwise_chains(mg)
+    assert n.value == folded and want_folded == folded, (what, n.value, want_folded)
+    for g, w in zip(got["nodes"], want["nodes"]):
+        assert sorted(g["inns"]) == sorted(w["inns"]), (what, g["id"])
+        if w.get("folded"):
+            assert g["kind"] == "alloc"
+        elif g["kind"] == "apply":
+            assert g["mems"] == w["mems"], (what, g["id"])
+            assert g["einsummable"]["inns"] == w["einsummable"]["inns"], (what, g["id"])
+    if which == 5:
+        composed = [g for g in got["nodes"] if g["kind"] == "apply" and len(g["mems"]) == 3 and [0, 256] in g["mems"][1:]]
+        assert len(composed) == 2
+    if which == 7:
+        fill = [g for g in got["nodes"] if g["kind"] == "constant"][0]
+        reader = [g for g in got["nodes"] if g["kind"] == "apply"][0]
+        assert reader["id"] in fill["inns"], (fill, reader)
