@@ -185,6 +185,24 @@ memgraph_t const& ref_graph_memgraph(int h)
     return g_graphs.at(h)->memgraph;
 }
 
+// the regions that hold the saved results of a built graph (what the fold passes must leave in place)
+std::vector<memloc_t> saved_regions(built_graph_t const& b)
+{
+    std::vector<memloc_t> saved;
+    if (b.has_storage) {
+        for (auto const& [tid, msl] : b.save_msl)
+            if (msl.is_memloc()) saved.push_back(msl.get_memloc());
+    } else {
+        for (auto const& [tid, m] : b.save_mem) saved.push_back(memloc_t{m.offset, m.size, b.taskgraph.out_loc(tid)});
+    }
+    saved.insert(saved.end(), b.extra_saved.begin(), b.extra_saved.end());
+    return saved;
+}
+std::vector<memloc_t> ref_graph_saved(int h)
+{
+    return saved_regions(*g_graphs.at(h));
+}
+
 extern "C" {
 
 char const* ref_graph_last_error()
@@ -581,14 +599,7 @@ int ref_graph_fold_elementwise(int h, int* n_folded)
 {
     G_BEGIN
     built_graph_t const&  b = *g_graphs.at(h);
-    std::vector<memloc_t> saved;
-    if (b.has_storage) {
-        for (auto const& [tid, msl] : b.save_msl)
-            if (msl.is_memloc()) saved.push_back(msl.get_memloc());
-    } else {
-        for (auto const& [tid, m] : b.save_mem) saved.push_back(memloc_t{m.offset, m.size, b.taskgraph.out_loc(tid)});
-    }
-    saved.insert(saved.end(), b.extra_saved.begin(), b.extra_saved.end());
+    std::vector<memloc_t> saved = saved_regions(b);
     es_fuse::folded_t f = es_fuse::fold_elementwise(b.memgraph, saved);
     built_graph_t*    nb = new built_graph_t(b);
     nb->memgraph = f.memgraph;
@@ -605,14 +616,7 @@ int ref_graph_fold_attention(int h, char const* path)
 {
     G_BEGIN
     built_graph_t const&  b = *g_graphs.at(h);
-    std::vector<memloc_t> saved;
-    if (b.has_storage) {
-        for (auto const& [tid, msl] : b.save_msl)
-            if (msl.is_memloc()) saved.push_back(msl.get_memloc());
-    } else {
-        for (auto const& [tid, m] : b.save_mem) saved.push_back(memloc_t{m.offset, m.size, b.taskgraph.out_loc(tid)});
-    }
-    saved.insert(saved.end(), b.extra_saved.begin(), b.extra_saved.end());
+    std::vector<memloc_t> saved = saved_regions(b);
     es_fuse::attention_folded_t f = es_fuse::fold_attention(b.memgraph, saved);
     std::ofstream               out(path);
     auto v3 = [&](int64_t const* v) { out << "[" << v[0] << "," << v[1] << "," << v[2] << "]"; };

@@ -29,7 +29,7 @@ CASES = [
 ]
 
 
-def run_engine(spec, tmp_path, inputs=None, iters=2):
+def run_engine(spec, tmp_path, inputs=None, iters=2, fold=False):
     if not os.path.exists(BIN):
         pytest.skip("oracle/_ref/engine_parity is not built (needs the reference tree at build time)")
     # first call: only to learn the layout the reference's compilers chose (memgraph.json)
@@ -40,7 +40,8 @@ def run_engine(spec, tmp_path, inputs=None, iters=2):
             mg = json.load(f)
         bufs = O.memgraph_place_inputs(mg, inputs)
         bufs[0][:int(mg["mem_sizes"][0])].tofile(tmp_path / "in.bin")
-    res = subprocess.run([BIN, spec, str(tmp_path), str(iters)], capture_output=True, text=True, timeout=900)
+    res = subprocess.run([BIN, spec, str(tmp_path), str(iters)] + (["fold"] if fold else []),
+                         capture_output=True, text=True, timeout=900)
     assert res.returncode == 0, res.stderr[-2000:]
     with open(tmp_path / "memgraph.json") as f:
         mg = json.load(f)
@@ -48,6 +49,8 @@ def run_engine(spec, tmp_path, inputs=None, iters=2):
     out = np.fromfile(tmp_path / "out.bin", dtype=np.uint8)
     if os.path.exists(tmp_path / "out_program.bin"):
         info["out_program"] = np.fromfile(tmp_path / "out_program.bin", dtype=np.uint8)
+    if os.path.exists(tmp_path / "out_folded.bin"):
+        info["out_folded"] = np.fromfile(tmp_path / "out_folded.bin", dtype=np.uint8)
     return mg, info, out
 
 
@@ -97,3 +100,42 @@ def test_reference_engine_llama7b_layer_times(tmp_path):
     assert min(loops) < 50.0
     # host wall clock incl. the synchronise: the program must beat the callback-driven loop clearly
     assert min(info["program_replay_ms"]) < 0.5 * min(loops)
+
+
+def test_cpp_host_folds_and_runs_the_tiny_layer(tmp_path):
+    """C++ host code alone: the memgraph_t folded by einsummable_b200/host/gpu_fuse.h (elementwise nodes into
+    their readers, the attention chain into one node) and run by gpu_program_t -- the saved tensors against the
+    reference interpreter's, at the tolerance of the graph as compiled."""
+    name, spec = CASES[1]
+    pre = name + "/in/"
+    inputs = {k[len(pre):]: ARR[k] for k in ARR.files if k.startswith(pre)}
+    mg, info, _ = run_engine(spec, tmp_path, inputs, fold=True)
+    assert info["nodes_folded"] > 20 and info["attention_chains"] == 1
+    assert 0 < info["folded_ops"] < info["program_ops"]
+    got = O.memgraph_collect_outputs(mg, [np.concatenate([info.pop("out_folded"), np.zeros(256, np.uint8)])])
+    info.pop("out_program", None)
+    pre = name + "/out/"
+    checked = 0
+    for k in ARR.files:
+        if k.startswith(pre):
+            ref = ARR[k]
+            scale = np.abs(ref.astype(np.float64)).max()
+            err = np.abs(got[k[len(pre):]].astype(np.float64) - ref.astype(np.float64)).max()
+            assert err <= (2e-2 if ref.dtype == np.float16 else 1e-5) * scale, ("folded", k, err, scale)
+            checked += 1
+    assert checked >= 1
+    print(name, info)
+
+
+def test_cpp_host_folds_and_runs_the_llama7b_layer(tmp_path):
+    """The same at full size (the buffer filled with small random f16 values): the folded graph's saved scores
+    against the unfolded graph's from the same inputs, and the time of its CUDA-graph replay from C++."""
+    mg, info, _ = run_engine("llama:4096:32:256:32000:1:4:512:0", tmp_path, None, iters=5, fold=True)
+    info.pop("out_program", None)
+    info.pop("out_folded", None)
+    print("LLaMA-7B layer from C++ host code: as compiled %d ops, replay %s ms; folded %d ops (%d nodes folded, %d attention "
+          "chain), replay %s ms" % (info["program_ops"], info["program_replay_ms"], info["folded_ops"], info["nodes_folded"],
+                                    info["attention_chains"], info["folded_replay_ms"]))
+    assert info["attention_chains"] == 1 and info["saved_finite"] and info["saved_max_abs"] > 0
+    assert info["folded_vs_program_max_abs_diff"] <= 1e-2 * info["saved_max_abs"]
+    assert min(info["folded_replay_ms"]) < min(info["program_replay_ms"])
