@@ -18,7 +18,8 @@
 //   C++ code alone), eagerly and as a CUDA-graph replay, and writes <dir>/out_program.bin.  With `fold`
 //   the memgraph then goes through the C++ fusion passes (einsummable_b200/host/gpu_fuse.h: elementwise
 //   nodes folded into their readers, every attention chain one node) and that graph through gpu_program_t:
-//   <dir>/out_folded.bin.  Prints one JSON line with the times.
+//   <dir>/out_folded.bin; and the folded graph through gpu_exchange_program_t, the program type for one
+//   process per GPU (<dir>/out_exchange.bin).  Prints one JSON line with the times.
 #include "src/engine/exec_graph.h"
 #include "src/engine/exec_state.h"
 #include "src/engine/managers.h"
@@ -194,7 +195,9 @@ int main(int argc, char** argv)
         }
         // the folded graph (C++ passes) through the program executor
         vector<double> folded_eager, folded_replay;
-        int            folded_ops = 0, n_folded = 0, n_chains = 0;
+        int            folded_ops = 0, n_folded = 0, n_chains = 0, exchange_ops = 0;
+        double         exchange_max_diff = -1;
+        vector<float>  saved_folded_values;
         if (with_fold && iters > 0) {
             fill_buffer(mem, mem_size, dir, with_fold);
             vector<memloc_t>            saved = ref_graph_saved(h);
@@ -220,6 +223,7 @@ int main(int argc, char** argv)
             }
             {
                 vector<float> saved_folded = read_saved();
+                saved_folded_values = saved_folded;
                 saved_max_diff = 0;
                 for (size_t i = 0; i != saved_folded.size(); ++i) {
                     saved_finite = saved_finite && std::isfinite(saved_folded[i]) && std::isfinite(saved_program[i]);
@@ -235,6 +239,40 @@ int main(int argc, char** argv)
                 folded_replay.push_back(now_ms() - t1);
             }
             handle_cuda_error(cudaStreamDestroy(stream));
+            // the same folded graph through gpu_exchange_program_t (the program type for one process per GPU:
+            // units and order of service from gpu_exchange_plan.h; with one location it has no exchange ops)
+            fill_buffer(mem, mem_size, dir, with_fold);
+            void* flags = nullptr;
+            handle_cuda_error(cudaMalloc(&flags, 256));
+            handle_cuda_error(cudaMemset(flags, 0, 256));
+            {
+                gpu_exchange_program_t xprogram(chains.memgraph, 0, kernel_managers[0], {mem}, {flags}, {}, 16, 0,
+                                                &chains.attention);
+                exchange_ops = xprogram.num_ops();
+                cudaStream_t xstream;
+                handle_cuda_error(cudaStreamCreate(&xstream));
+                xprogram.launch(xstream);
+                handle_cuda_error(cudaStreamSynchronize(xstream));
+                vector<float> a = read_saved();
+                {
+                    vector<char> host(mem_size);
+                    handle_cuda_error(cudaMemcpy(host.data(), mem, mem_size, cudaMemcpyDeviceToHost));
+                    std::ofstream out(dir + "/out_exchange.bin", std::ios::binary);
+                    out.write(host.data(), mem_size);
+                }
+                xprogram.instantiate();
+                xprogram.replay(xstream);
+                handle_cuda_error(cudaStreamSynchronize(xstream));
+                vector<float> b = read_saved();
+                vector<float> f = saved_folded_values;
+                exchange_max_diff = 0;
+                for (size_t i = 0; i != a.size(); ++i) {
+                    exchange_max_diff = std::max(exchange_max_diff, double(std::fabs(a[i] - f[i])));
+                    exchange_max_diff = std::max(exchange_max_diff, double(std::fabs(b[i] - f[i])));
+                }
+                handle_cuda_error(cudaStreamDestroy(xstream));
+            }
+            handle_cuda_error(cudaFree(flags));
         }
         auto list = [](vector<double> const& v) {
             std::stringstream ss;
@@ -251,7 +289,8 @@ int main(int argc, char** argv)
                   << ", \"folded_ops\": " << folded_ops << ", \"folded_eager_ms\": " << list(folded_eager)
                   << ", \"folded_replay_ms\": " << list(folded_replay) << ", \"saved_finite\": " << (saved_finite ? "true" : "false")
                   << ", \"saved_max_abs\": " << saved_max_abs << ", \"folded_vs_program_max_abs_diff\": " << saved_max_diff
-                  << "}" << std::endl;
+                  << ", \"exchange_program_ops\": " << exchange_ops
+                  << ", \"exchange_program_vs_folded_max_abs_diff\": " << exchange_max_diff << "}" << std::endl;
         return 0;
     } catch (std::exception const& e) {
         std::cerr << "engine_parity: " << e.what() << std::endl;

@@ -112,6 +112,10 @@ def test_cpp_host_folds_and_runs_the_tiny_layer(tmp_path):
     mg, info, _ = run_engine(spec, tmp_path, inputs, fold=True)
     assert info["nodes_folded"] > 20 and info["attention_chains"] == 1
     assert 0 < info["folded_ops"] < info["program_ops"]
+    # the same folded graph through gpu_exchange_program_t (units and order of service from gpu_exchange_plan.h;
+    # one location: no exchange ops): the same kernels on the same data, so the same bits
+    assert info["exchange_program_ops"] == info["folded_ops"]
+    assert info["exchange_program_vs_folded_max_abs_diff"] == 0
     got = O.memgraph_collect_outputs(mg, [np.concatenate([info.pop("out_folded"), np.zeros(256, np.uint8)])])
     info.pop("out_program", None)
     pre = name + "/out/"
@@ -139,3 +143,5 @@ def test_cpp_host_folds_and_runs_the_llama7b_layer(tmp_path):
     assert info["attention_chains"] == 1 and info["saved_finite"] and info["saved_max_abs"] > 0
     assert info["folded_vs_program_max_abs_diff"] <= 1e-2 * info["saved_max_abs"]
     assert min(info["folded_replay_ms"]) < min(info["program_replay_ms"])
+    assert info["exchange_program_ops"] == info["folded_ops"]
+    assert 0 <= info["exchange_program_vs_folded_max_abs_diff"] <= 1e-3 * info["saved_max_abs"]
