@@ -42,7 +42,7 @@
 namespace es_exchange {
 
 // the nodes of a graph that stand for a whole attention chain (es_fuse::fold_attention), by node id;
-// every function below takes it as an optional last argument
+// every function below takes it as an optional argument
 using attention_map_t = std::map<int, es_fuse::attention_node_t>;
 
 struct unit_t {
