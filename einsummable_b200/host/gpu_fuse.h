@@ -20,7 +20,7 @@
 //     dtype A wrote it in (a taskgraph node may view the same bytes under another shape or dtype,
 //     src/einsummable/taskgraph.cc:765-793: such readers are left alone),
 //   * nothing between A and its last reader in node order writes memory A reads, and no reader does,
-//   * the folded node has at most 8 inputs (ES_B200_MAX_INNS).
+//   * the folded node has at most 8 inputs (ES_MAX_INNS of es_b200.h).
 //
 // The same rules, in the same order, as einsummable_b200/fuse.py (fuse_elementwise_chains), which works on
 // the memgraph as data; the two are compared node by node in the tests.
