@@ -243,3 +243,15 @@ def test_fold_conditions_on_hand_made_graphs(which, folded, what, tmp_path):
         fill = [g for g in got["nodes"] if g["kind"] == "constant"][0]
         reader = [g for g in got["nodes"] if g["kind"] == "apply"][0]
         assert reader["id"] in fill["inns"], (fill, reader)
+
+
+def test_engine_parity_binary_loads_without_a_gpu():
+    """The binary the GPU tests run (the reference's engine, gpu_program_t, gpu_exchange_program_t and the C++
+    passes linked with the library) resolves all its symbols here: without arguments it prints its usage
+    before any CUDA call."""
+    import subprocess
+    path = os.path.join(ROOT, "oracle", "_ref", "engine_parity")
+    if not os.path.exists(path):
+        pytest.skip("the reference has not been compiled here (oracle/_ref)")
+    res = subprocess.run([path], capture_output=True, text=True, timeout=60)
+    assert res.returncode == 1 and "usage: engine_parity" in res.stderr and "[fold]" in res.stderr, res.stderr[-500:]
