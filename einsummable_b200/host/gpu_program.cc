@@ -19,6 +19,19 @@ void scalar_bytes(scalar_t const& s, unsigned char out[8])
     std::memcpy(out, s.data, dtype_size(s.dtype));
 }
 
+void* host_block(storage_blocks_t const* storage, stoloc_t const& at, char const* who)
+{
+    if (!storage) {
+        throw std::runtime_error(string(who) + ": the memgraph has evict / load nodes but no storage blocks were given");
+    }
+    auto iter = storage->find({at.loc, at.id});
+    if (iter == storage->end()) {
+        throw std::runtime_error(string(who) + ": no host block for storage id " + std::to_string(at.id) +
+                                 " of storage location " + std::to_string(at.loc));
+    }
+    return iter->second;
+}
+
 es_attention_t attention_descriptor(es_fuse::attention_t const& d)
 {
     es_attention_t a;
@@ -41,7 +54,8 @@ gpu_program_t::gpu_program_t(memgraph_t const&            memgraph,
                              void*                        mem,
                              map<string, scalar_t> const& scalar_vars,
                              int                          max_lanes,
-                             es_exchange::attention_map_t const* attention)
+                             es_exchange::attention_map_t const* attention,
+                             storage_blocks_t const*      storage)
     : prog(nullptr), workspace(nullptr), n_ops(0)
 {
     check(es_b200_program_create(km.c_handle(), &prog), "es_b200_program_create");
@@ -152,8 +166,18 @@ gpu_program_t::gpu_program_t(memgraph_t const&            memgraph,
             check(es_b200_program_add_copy(prog, at(c.src_offset), at(c.dst_offset), c.size, deps.data(),
                                            int(deps.size()), &index),
                   "es_b200_program_add_copy");
+        } else if (op.is_evict()) {
+            auto const& e = op.get_evict();
+            check(es_b200_program_add_evict(prog, at(e.src.offset), host_block(storage, e.dst, "gpu_program_t"), e.src.size,
+                                            deps.data(), int(deps.size()), &index),
+                  "es_b200_program_add_evict");
+        } else if (op.is_load()) {
+            auto const& l = op.get_load();
+            check(es_b200_program_add_load(prog, host_block(storage, l.src, "gpu_program_t"), at(l.dst.offset), l.dst.size,
+                                           deps.data(), int(deps.size()), &index),
+                  "es_b200_program_add_load");
         } else {
-            throw std::runtime_error("gpu_program_t: evict / load nodes need a storage (es_b200_program_add_evict / _add_load)");
+            throw std::runtime_error("gpu_program_t: unknown memgraph node kind");
         }
         op_of[mid] = index;
         n_ops++;
@@ -204,7 +228,8 @@ gpu_exchange_program_t::gpu_exchange_program_t(memgraph_t const&            memg
                                                int                          max_lanes,
                                                uint32_t                     wait_limit_ms,
                                                es_exchange::attention_map_t const* attention,
-                                               bool                         group_sum)
+                                               bool                         group_sum,
+                                               storage_blocks_t const*      storage)
     : prog(nullptr), workspace(nullptr), n_ops(0)
 {
     check(es_b200_program_create(km.c_handle(), &prog), "es_b200_program_create");
@@ -363,9 +388,18 @@ gpu_exchange_program_t::gpu_exchange_program_t(memgraph_t const&            memg
             }
             check(es_b200_program_add_pull(prog, items.data(), int(items.size()), deps, n_deps, &index),
                   "es_b200_program_add_pull");
+        } else if (u.kind == "evict") {
+            auto const& e = memgraph.nodes[u.node].op.get_evict();
+            check(es_b200_program_add_evict(prog, at(rank, e.src.offset), host_block(storage, e.dst, "gpu_exchange_program_t"),
+                                            e.src.size, deps, n_deps, &index),
+                  "es_b200_program_add_evict");
+        } else if (u.kind == "load") {
+            auto const& l = memgraph.nodes[u.node].op.get_load();
+            check(es_b200_program_add_load(prog, host_block(storage, l.src, "gpu_exchange_program_t"), at(rank, l.dst.offset),
+                                           l.dst.size, deps, n_deps, &index),
+                  "es_b200_program_add_load");
         } else {
-            throw std::runtime_error("gpu_exchange_program_t: evict / load nodes need a storage "
-                                     "(es_b200_program_add_evict / _add_load)");
+            throw std::runtime_error("gpu_exchange_program_t: unknown unit kind " + u.kind);
         }
         n_ops++;
     }

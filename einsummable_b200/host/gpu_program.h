@@ -18,6 +18,13 @@
 #include "gpu_exchange_plan.h"
 #include "gpu_kernel_manager.h"
 
+// Where the tensors of a memgraph with storage live on the host: (storage location, storage id) -> a pinned
+// host block of the tensor's size (e.g. from es_b200_storage_reference).  Ids are unique within a run
+// (src/einsummable/memgraph.h:311-316), so with the blocks fixed in advance evict_t / load_t
+// (src/engine/gpu/exec_graph.cc:469-577) are plain copies in a static schedule; an inputsto node's block holds
+// its tensor before the run, a saved tensor that ended up in storage is in its block afterwards.
+using storage_blocks_t = map<tuple<int, int>, void*>;
+
 struct gpu_program_t {
     // mem: the global buffer of location `loc` (server.cc:38-43).  The kernel manager must outlive the program.
     // attention: for a graph from es_fuse::fold_attention (gpu_fuse.h), the nodes that stand for a whole
@@ -28,7 +35,8 @@ struct gpu_program_t {
                   void*                               mem,
                   map<string, scalar_t> const&        scalar_vars = {},
                   int                                 max_lanes = 16,
-                  es_exchange::attention_map_t const* attention = nullptr);
+                  es_exchange::attention_map_t const* attention = nullptr,
+                  storage_blocks_t const*             storage = nullptr);
     ~gpu_program_t();
 
     gpu_program_t(gpu_program_t const&) = delete;
@@ -73,7 +81,8 @@ struct gpu_exchange_program_t {
                            int                          max_lanes = 16,
                            uint32_t                     wait_limit_ms = 0,
                            es_exchange::attention_map_t const* attention = nullptr,
-                           bool                         group_sum = false);
+                           bool                         group_sum = false,
+                           storage_blocks_t const*      storage = nullptr);
     ~gpu_exchange_program_t();
 
     gpu_exchange_program_t(gpu_exchange_program_t const&) = delete;

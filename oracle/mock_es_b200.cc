@@ -197,13 +197,19 @@ int es_b200_program_add_pull(es_b200_program_t*, const es_pull_item_t* items, in
     g_ops << "]";
     return end(op_index);
 }
-int es_b200_program_add_evict(es_b200_program_t*, const void*, void*, uint64_t, const int*, int, int*)
+int es_b200_program_add_evict(es_b200_program_t*, const void* dev_src, void* host_dst, uint64_t bytes, const int* deps,
+                              int n_deps, int* op_index)
 {
-    return ES_NOT_SUPPORTED;
+    begin("evict", deps, n_deps);
+    g_ops << ",\"dev\":" << u64(dev_src) << ",\"host\":" << u64(host_dst) << ",\"bytes\":" << bytes;
+    return end(op_index);
 }
-int es_b200_program_add_load(es_b200_program_t*, const void*, void*, uint64_t, const int*, int, int*)
+int es_b200_program_add_load(es_b200_program_t*, const void* host_src, void* dev_dst, uint64_t bytes, const int* deps,
+                             int n_deps, int* op_index)
 {
-    return ES_NOT_SUPPORTED;
+    begin("load", deps, n_deps);
+    g_ops << ",\"dev\":" << u64(dev_dst) << ",\"host\":" << u64(host_src) << ",\"bytes\":" << bytes;
+    return end(op_index);
 }
 int es_b200_program_set_wait_limit(es_b200_program_t*, uint32_t)
 {

@@ -27,6 +27,7 @@ def _lib():
 
 CASES = {
     "c1 64^3 on 2 locations": lambda L: L.ref_graph_build_c1(u64(64), 2, 2, 1),
+    "c1 64^3 on 2 locations with 12 KB each (evict / load)": lambda L: L.ref_graph_build_c1_evict(u64(64), 4, 2, 1, u64(12288)),
     "tiny llama, autoplace01, 2 locations": lambda L: L.ref_graph_build_llama(u64(64), u64(2), u64(32), u64(128), 1, u64(2), u64(16), 2, 0),
     "tiny llama, autoplace01, 4 locations": lambda L: L.ref_graph_build_llama(u64(64), u64(2), u64(32), u64(128), 1, u64(2), u64(16), 4, 0),
     "tiny llama, tensor-parallel, 4 locations": lambda L: L.ref_graph_build_llama_tp(u64(64), u64(4), u64(32), u64(128), 1, u64(2), u64(16), 4, 0),

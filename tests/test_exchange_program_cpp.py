@@ -29,6 +29,8 @@ CASES = [
     ("llama_tp:4096:32:256:32000:1:4:512:0:8", 0),
     ("llama_tp:4096:32:256:32000:1:4:512:0:8", 1),
     ("llama:4096:32:256:32000:1:4:512:0:2", 0),
+    ("c1_evict:64:4:1:12288:2", 0),          # config 1 under a memory limit: evict / load to host storage
+    ("c1_evict:64:4:1:20480:1", 0),
 ]
 
 
@@ -114,6 +116,10 @@ def test_cpp_exchange_program_ops_are_the_python_runners(spec, group_sum, tmp_pa
                 s, d = (n["src_loc"], n["dst_loc"]) if n["kind"] == "move" else (n["loc"], n["loc"])
                 assert (g["kind"], g["src"], g["dst"], g["bytes"]) == (
                     "copy", ptr(s, n["src_offset"]), ptr(d, n["dst_offset"]), n["size"]), where
+            elif k in ("evict", "load"):
+                n = nodes[u["node"]]
+                assert (g["kind"], g["dev"], g["host"], g["bytes"]) == (
+                    k, ptr(n["loc"], n["offset"]), (1 << 50) + 4096 * n["storage_id"], n["size"]), where
             elif k == "rsum":
                 n = nodes[u["nodes"][0]]
                 out = ptr(n["loc"], n["mems"][0][0])
@@ -133,6 +139,9 @@ def test_cpp_exchange_program_ops_are_the_python_runners(spec, group_sum, tmp_pa
                 assert g["kind"] == "wait" and g["flags"] == [flag(nodes[m]["src_loc"], 1, m) for m in u["moves"]], where
             else:
                 raise AssertionError(where)
-    assert {"signal", "await", "wait", "einsummable"} <= kinds, kinds
+    if spec.startswith("c1_evict"):
+        assert {"evict", "load"} <= kinds, kinds
+    if world > 1:
+        assert {"signal", "await", "wait", "einsummable"} <= kinds, kinds
     if group_sum:
         assert {"rsum", "ack"} <= kinds, kinds
