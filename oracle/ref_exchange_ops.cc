@@ -11,7 +11,8 @@
 //   Builds the memgraph in-process with the reference's compilers, writes <dir>/memgraph.json, folds it with the
 //   C++ passes (einsummable_b200/host/gpu_fuse.h), builds one gpu_exchange_program_t per rank over made-up base
 //   addresses -- location r's buffer at (r + 1) << 44, its flag words at ((r + 1) << 44) + (1 << 40) -- and
-//   writes the ops each program was given to <dir>/ops<rank>.json.  The host block of storage id k of a graph
+//   writes the ops each program was given to <dir>/ops<rank>.json (with one location also gpu_program_t's, the
+//   program type for one device: <dir>/ops_program0.json).  The host block of storage id k of a graph
 //   with storage is the made-up address (1 << 50) + 4096 * k.
 #include "src/engine/gpu/gpu_kernel_manager.h"
 #include "src/engine/gpu/gpu_program.h"
@@ -81,6 +82,14 @@ int main(int argc, char** argv)
             gpu_exchange_program_t program(chains.memgraph, rank, km, peer_mem, peer_flags, {}, 16, 0, &chains.attention,
                                            group_sum, &storage);
             std::ofstream out(dir + "/ops" + std::to_string(rank) + ".json");
+            out << "{\"n_ops\":" << program.num_ops() << ",\"ops\":[\n" << mock_take_ops() << "\n]}\n";
+        }
+        if (world == 1) {
+            // one location: also gpu_program_t, the program type for one device (memgraph order)
+            kernel_manager_t km(0);
+            mock_take_ops();
+            gpu_program_t program(chains.memgraph, 0, km, peer_mem[0], {}, 16, &chains.attention, &storage);
+            std::ofstream out(dir + "/ops_program0.json");
             out << "{\"n_ops\":" << program.num_ops() << ",\"ops\":[\n" << mock_take_ops() << "\n]}\n";
         }
         std::cout << "{\"world\": " << world << ", \"nodes_folded\": " << folded.folded.size()
